@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache hot path: KV append + split-K GQA decode attention.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One step = one decode token: for every layer, append the token's K/V to the cache, then
+attend over the whole context.  The default workload is the FP8 Qwen3-8B-like case
+(36 layers, 32 q / 8 kv / 128, batch 1, context 8192, 16 splits).  Prints ONE JSON line.
+
+value     device-timed, inputs resident in HBM, microseconds per token per layer
+e2e       the same through vfkv_decode_token_host with pinned HOST buffers (copies inside the
+          timed region)
+roofline  the attention split kernel: algorithmic KV bytes per launch / its mean launch time,
+          against the measured HBM copy bandwidth
+cpu_baseline  the CPU oracle (a C port of the reference's CPU attention and store code, the
+          reference itself is Rust and cannot be built here) on a bounded sample
+
+Under torchrun every rank runs the same workload on its own sequence(s) and GPU (sharding by
+sequence, no collective on the data path); times are the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: n_layers, Hq, Hkv, D, dtype, batch, context, n_splits, window pattern, softcap
+    "qwen3_8b_fp8_ctx8192_b1": dict(n_layers=36, hq=32, hkv=8, d=128, dtype="F8", batch=1, ctx=8192,
+                                    n_splits=16, softcap=0.0, windows=None),
+    "llama3_8b_f16_ctx2048_b1": dict(n_layers=32, hq=32, hkv=8, d=128, dtype="F16", batch=1, ctx=2048,
+                                     n_splits=0, softcap=0.0, windows=None),
+    "batch64_fp8_ctx8192": dict(n_layers=1, hq=32, hkv=8, d=128, dtype="F8", batch=64, ctx=8192,
+                                n_splits=0, softcap=0.0, windows=None),
+    "batch64_fp8_ragged_512_16384": dict(n_layers=1, hq=32, hkv=8, d=128, dtype="F8", batch=64, ctx=16384,
+                                         n_splits=0, softcap=0.0, windows=None, ragged=(512, 16384)),
+    "gemma_f16_ctx32768_b8": dict(n_layers=6, hq=16, hkv=8, d=256, dtype="F16", batch=8, ctx=32768,
+                                  n_splits=0, softcap=50.0, windows=[1024, 1024, 1024, 1024, 1024, 0]),
+    "long_fp8_ctx131072_b1": dict(n_layers=1, hq=64, hkv=8, d=128, dtype="F8", batch=1, ctx=131072,
+                                  n_splits=0, softcap=0.0, windows=None),
+}
+DEFAULT_WORKLOAD = "qwen3_8b_fp8_ctx8192_b1"
+METRIC = "kv_append_decode_attn_us_per_token_layer"
+UNIT = "us/token/layer"
+ES = {"F32": 4, "F16": 2, "F8": 1}
+DT = {"F32": 0, "F16": 1, "F8": 2}
+
+
+def algorithmic_bytes(w, lens, layer):
+    """Bytes one layer-step must move: KV rows read + Q + new K/V (f32) in; appended rows + O out."""
+    e = ES[w["dtype"]]
+    win = (w["windows"] or [0] * w["n_layers"])[layer]
+    total = 0
+    for L in lens:
+        eff = min(int(L), win) if win else int(L)
+        total += 2 * eff * w["hkv"] * w["d"] * e + w["hq"] * w["d"] * 4 + 2 * w["hkv"] * w["d"] * 4
+        total += 2 * w["hkv"] * w["d"] * e + w["hq"] * w["d"] * 4
+    return total
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read only)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz, self._halt = index, [], set(), None, threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4)}
+        while not self._halt.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._halt.wait(0.02)
+
+    def finish(self):
+        self._halt.set()
+        self.join(timeout=1.0)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ----------------------------------------------------------------------------------------------
+def run_reference(args, w, rank, world):
+    """The reference arm: the CPU code of the path (C port of the reference's CPU attention,
+    tests/correctness.rs:2567-2617, and store, fp8_ext.rs:126-211) on all host threads, on a
+    bounded sample of the same workload."""
+    if rank != 0:
+        return
+    import oracle
+    dt = DT[w["dtype"]]
+    rng = np.random.default_rng(1234)
+    lens = make_lens(w, rng)
+    # bounded sample: at most `layers` distinct layer slabs, cycled; each step = one layer-step
+    b = min(w["batch"], 8)
+    lens = lens[:b]
+    slab = int(max(lens))
+    st = oracle.NP_DTYPE[dt]
+    n_slabs = 2
+    ks, vs = [], []
+    for _ in range(n_slabs):
+        kf = rng.standard_normal((b, slab, w["hkv"], w["d"]), dtype=np.float32)
+        ks.append(oracle.store(kf, dt).reshape(kf.shape).astype(st, copy=False))
+        vs.append(oracle.store(kf[::-1].copy(), dt).reshape(kf.shape).astype(st, copy=False))
+    q = rng.standard_normal((b, w["hq"], w["d"]), dtype=np.float32)
+    kn = rng.standard_normal((b, w["hkv"], w["d"]), dtype=np.float32)
+    vn = rng.standard_normal((b, w["hkv"], w["d"]), dtype=np.float32)
+    win = (w["windows"] or [0] * w["n_layers"])
+
+    def layer_step(i):
+        wl = win[i % len(win)]
+        starts = np.array([max(0, int(L) - wl) if wl else 0 for L in lens], np.uint32)
+        oracle.decode_step(q, kn, vn, ks[i % n_slabs], vs[i % n_slabs], dt, b, slab, w["hq"], w["hkv"], w["d"],
+                           np.asarray(lens, np.uint32), starts, None, w["softcap"])
+
+    layer_step(0)
+    t0 = time.perf_counter(); layer_step(1); one = time.perf_counter() - t0
+    # keep the whole run within a couple of minutes: ~1 s of CPU work per step
+    per_step = max(1, min(w["n_layers"], int(1.0 / max(one, 1e-6))))
+    for i in range(args.warmup):
+        layer_step(i)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        for i in range(per_step):
+            layer_step(s * per_step + i)
+    dt_s = time.perf_counter() - t0
+    us = dt_s * 1e6 / (args.steps * per_step * b)
+    cores = oracle.num_threads()
+    sample = (f"{args.steps} steps x {per_step} layer-steps of {b} sequence(s) at the workload's shapes "
+              f"({w['dtype']} cache, context {slab}), {cores} OpenMP threads")
+    line = {"metric": METRIC, "value": us, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt_s * 1e3 / args.steps,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": args.workload, **{k: v for k, v in w.items() if k != "windows"}},
+            "cpu_baseline": {"value": us, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def make_lens(w, rng):
+    if "ragged" in w:
+        lo, hi = w["ragged"]
+        return [int(x) for x in rng.integers(lo, hi + 1, w["batch"])]
+    return [w["ctx"]] * w["batch"]
+
+
+def cpu_baseline_sample(w, budget_s=12.0):
+    """Oracle timing on the host cores for the JSON line's cpu_baseline object."""
+    import oracle
+    dt = DT[w["dtype"]]
+    rng = np.random.default_rng(99)
+    b = min(w["batch"], 4)
+    lens = make_lens(w, rng)[:b]
+    slab = int(max(lens))
+    st = oracle.NP_DTYPE[dt]
+    kf = rng.standard_normal((b, slab, w["hkv"], w["d"]), dtype=np.float32)
+    k = oracle.store(kf, dt).reshape(kf.shape).astype(st, copy=False)
+    v = oracle.store(kf[:, ::-1].copy(), dt).reshape(kf.shape).astype(st, copy=False)
+    q = rng.standard_normal((b, w["hq"], w["d"]), dtype=np.float32)
+    kn = rng.standard_normal((b, w["hkv"], w["d"]), dtype=np.float32)
+    win = (w["windows"] or [0])
+    n, t0 = 0, time.perf_counter()
+    oracle.decode_step(q, kn, kn, k, v, dt, b, slab, w["hq"], w["hkv"], w["d"], np.asarray(lens, np.uint32))
+    t0 = time.perf_counter()
+    while True:
+        wl = win[n % len(win)]
+        starts = np.array([max(0, int(L) - wl) if wl else 0 for L in lens], np.uint32)
+        oracle.decode_step(q, kn, kn, k, v, dt, b, slab, w["hq"], w["hkv"], w["d"], np.asarray(lens, np.uint32),
+                           starts, None, w["softcap"])
+        n += 1
+        el = time.perf_counter() - t0
+        if el > budget_s or n >= 400:
+            break
+    cores = oracle.num_threads()
+    return {"value": el * 1e6 / (n * b), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n} layer-steps of {b} sequence(s), {w['dtype']} cache, context {slab}, "
+                      f"{cores} OpenMP threads, {el:.1f} s"}
+
+
+# ----------------------------------------------------------------------------------------------
+class Job:
+    """Cache + inputs of one rank, resident on its GPU."""
+
+    def __init__(self, w, device, seed):
+        import torch
+        import vulkanforge_b200 as vf
+        self.vf, self.torch, self.w = vf, torch, w
+        torch.cuda.set_device(device)
+        self.ctx = vf.Context(device)
+        rng = np.random.default_rng(seed)
+        self.lens = make_lens(w, rng)
+        B, L = w["batch"], w["ctx"]
+        self.cache = vf.KvCache(self.ctx, vf.KvCacheConfig(w["n_layers"], w["hkv"], w["d"], L, n_slots=B),
+                                vf.KvDtype[w["dtype"]])
+        sliding = [i for i, x in enumerate(w["windows"] or []) if x]
+        window = max(w["windows"]) if w["windows"] else 0
+        self.fwd = vf.CudaForward(self.ctx, self.cache, n_heads=w["hq"], max_batch=B, n_splits=w["n_splits"],
+                                  softcap=w["softcap"], sliding_window=window, sliding_layers=sliding)
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        fp8 = w["dtype"] == "F8"
+        chunk = 4096
+        row = w["hkv"] * w["d"]
+        # pre-fill every slab through the product's own prefill append (N(0,1); 1 % x20 outliers for FP8)
+        for layer in range(w["n_layers"]):
+            for s in range(B):
+                n = self.lens[s] - 1
+                for p in range(0, n, chunk):
+                    m = min(chunk, n - p)
+                    kv = torch.randn(2, m, row, device="cuda", generator=g)
+                    if fp8:
+                        mask = torch.rand(2, m, row, device="cuda", generator=g) < 0.01
+                        kv = torch.where(mask, kv * 20.0, kv)
+                    self.fwd.b_step_kv_write(layer, kv[0], kv[1], m, p, s)
+        nl = w["n_layers"]
+        self.q = torch.randn(nl, B, w["hq"], w["d"], device="cuda", generator=g)
+        self.k = torch.randn(nl, B, w["hkv"], w["d"], device="cuda", generator=g)
+        self.v = torch.randn(nl, B, w["hkv"], w["d"], device="cuda", generator=g)
+        self.out = torch.zeros(nl, B, w["hq"], w["d"], device="cuda")
+        self.pos = torch.tensor([x - 1 for x in self.lens], dtype=torch.int32, device="cuda")
+        self.max_len = max(self.lens)
+        # pinned host copies for the end-to-end leg
+        self.h_q, self.h_k, self.h_v = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
+        self.h_out = torch.zeros_like(self.out, device="cpu").pin_memory()
+        self.h_pos = np.array([x - 1 for x in self.lens], np.uint32)
+        torch.cuda.synchronize()
+        self.ctx.poll()
+
+    def step(self):
+        f = self.fwd
+        for layer in range(self.w["n_layers"]):
+            f.decode_step(layer, self.q[layer], self.k[layer], self.v[layer], self.out[layer], None, self.pos,
+                          self.w["batch"], self.max_len)
+
+    def step_host(self):
+        self.fwd.decode_token_host(self.h_q, self.h_k, self.h_v, self.h_out, self.h_pos, self.w["batch"])
+
+    def h2d_bytes(self):
+        return self.h_q.numel() * 4 + self.h_k.numel() * 4 + self.h_v.numel() * 4 + self.h_pos.nbytes
+
+    def d2h_bytes(self):
+        return self.h_out.numel() * 4
+
+    def profile(self, steps):
+        """Mean launch time of each kernel family over `steps` more steps (events around every launch)."""
+        import ctypes as C
+        L = self.ctx._lib
+        L.vfkv_profile_enable(self.ctx.handle, 1)
+        for _ in range(steps):
+            self.step()
+        self.torch.cuda.synchronize()
+        res = {}
+        for label, name in ((0, "kv_store"), (2, "fa_split"), (3, "fa_reduce")):
+            n, tot, mn = C.c_uint64(), C.c_double(), C.c_double()
+            L.vfkv_profile_collect(self.ctx.handle, label, C.byref(n), C.byref(tot), C.byref(mn), 0)
+            if n.value:
+                res[name] = {"launches": n.value, "mean_us": tot.value * 1e3 / n.value, "min_us": mn.value * 1e3}
+        L.vfkv_profile_enable(self.ctx.handle, 0)
+        return res
+
+
+def run_ours(args, w, rank, world, local_rank):
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    job = Job(w, local_rank, seed=1000 + rank)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        job.step()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    launches0 = job.ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        job.step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = job.ctx.launch_count() - launches0
+    clocks = sampler.finish()
+    job.ctx.poll()
+
+    # end-to-end leg: host buffers in, host buffers out, every step
+    for _ in range(max(3, args.warmup)):
+        job.step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        job.step_host()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+        tot = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(tot)
+        launches = int(tot[0])
+
+    if rank == 0:
+        tokens = w["batch"] * world                       # tokens decoded per step, all ranks
+        denom = args.steps * tokens * w["n_layers"]
+        value = ms * 1e3 / denom
+        prof = job.profile(min(args.steps, 20))
+        peak, peak_kind = peaks()
+        split = prof.get("fa_split")
+        roofline = None
+        if split:
+            per_launch = float(np.mean([algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"])]))
+            achieved = per_launch / (split["mean_us"] * 1e-6) / 1e9
+            roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                        "frac": achieved / peak, "traffic": None, "kernel": "fa_split",
+                        "algorithmic_bytes_per_launch": per_launch, "mean_launch_us": split["mean_us"],
+                        "peak_source": f"{peak_kind} copy bandwidth", "frac_of_8000_nominal": achieved / 8000.0}
+        step_bytes = sum(algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"]))
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32 (fp8/f16 storage)", "data": "synthetic",
+                "config": {"workload": args.workload, "n_layers": w["n_layers"], "n_q_heads": w["hq"],
+                           "n_kv_heads": w["hkv"], "head_dim": w["d"], "kv_dtype": w["dtype"], "batch_per_gpu": w["batch"],
+                           "context": w["ctx"], "n_splits": w["n_splits"], "softcap": w["softcap"],
+                           "l2": "each step streams the whole cache (larger than the 126 MB L2) before a layer repeats"
+                                 if step_bytes > 200e6 else "working set below L2: hot-L2 numbers",
+                           "parallelism": f"sequence-sharded x{world}, no collective"},
+                "tokens_per_s": tokens * args.steps / (ms * 1e-3),
+                "achieved_gbs_whole_step": step_bytes * world * args.steps / (ms * 1e-3) / 1e9,
+                "roofline": roofline, "kernels": prof, "clocks": clocks, "gpu_launches": launches,
+                "e2e": {"value": e2e_ms * 1e3 / denom, "unit": UNIT, "h2d_bytes_per_step": job.h2d_bytes(),
+                        "d2h_bytes_per_step": job.d2h_bytes()}}
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline_sample(w)
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+    run_ours(args, w, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

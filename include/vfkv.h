@@ -1,0 +1,328 @@
+/*
+ * vfkv.h -- C ABI of libvfkv.so: VulkanForge's KV-cache hot path on NVIDIA B200
+ * (sm_100a).  KV append (FP8 E4M3 / F16 / F32), the FP8->F16 cache read and
+ * split-K GQA decode attention with its log-sum-exp merge.
+ *
+ * Each entry point cites the VulkanForge interface it stands in for, by the
+ * file's path inside that project.  A reference-side binding (Rust `extern "C"`
+ * block plus a `src/backend/cuda` module) is shown in INTEGRATION.md.
+ *
+ * Conventions
+ *   - Every function returns a vfkv_status (0 = OK) and never aborts; the text
+ *     of the last failure on a context is available from vfkv_last_error().
+ *   - All device work is enqueued on the caller's stream (a cudaStream_t passed
+ *     as void*; NULL = the default stream).  Stream order replaces the pipeline
+ *     barriers the reference records between these dispatches
+ *     (src/backend/vulkan/forward/executor/attention.rs:554,583-596;
+ *     src/backend/vulkan/forward/runs.rs:1541).
+ *   - Pointers named d_* are device pointers, h_* host pointers.
+ *   - The library does not advance sequence lengths inside append: the caller
+ *     commits them after the step, as the reference does
+ *     (src/backend/vulkan/forward/decode.rs:812, forward/prefill.rs:277).
+ *   - A context and the objects made from it may be used from one thread at a
+ *     time.
+ */
+#ifndef VFKV_H
+#define VFKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VFKV_ABI_VERSION 1
+
+typedef enum {
+    VFKV_OK = 0,
+    VFKV_ERR_INVALID = 1,      /* bad argument (null, out of range, misaligned)          */
+    VFKV_ERR_OVERFLOW = 2,     /* a size computation overflowed 64 bits                  */
+    VFKV_ERR_OOM = 3,          /* device allocation failed                               */
+    VFKV_ERR_CUDA = 4,         /* a CUDA runtime / driver call failed                    */
+    VFKV_ERR_UNSUPPORTED = 5,  /* shape or dtype outside what the kernels cover          */
+    VFKV_ERR_TIMEOUT = 6,      /* a bounded device-side wait gave up (see vfkv_ctx_poll) */
+    VFKV_ERR_PRECISION = 7     /* refused by vfkv_guard_kv_precision                     */
+} vfkv_status;
+
+/* src/backend/vulkan/kv_cache.rs:42-74 (KvDtype; element_size 4 / 2 / 1) */
+typedef enum { VFKV_F32 = 0, VFKV_F16 = 1, VFKV_F8 = 2 } vfkv_dtype;
+
+/* FP8 scaling.  NONE is the reference's behaviour: kv_store_fp8.comp casts each
+ * value directly and the readers dequantise without a scale
+ * (vk_shaders/kv_store_fp8.comp:42-50, vk_shaders/flash_attn_split.comp:34-43).
+ * PER_TOKEN_HEAD is an extension with no counterpart in the reference's KV
+ * path: one f32 scale per (position, kv-head), computed with the recipe of the
+ * reference's FP8 GEMM activation quantiser
+ * (vk_shaders/mul_coopmat_fp8_native_bn32.comp:149-152,214). */
+typedef enum { VFKV_SCALE_NONE = 0, VFKV_SCALE_PER_TOKEN_HEAD = 1 } vfkv_scale_mode;
+
+typedef struct vfkv_ctx vfkv_ctx;
+typedef struct vfkv_cache vfkv_cache;
+typedef struct vfkv_workspace vfkv_workspace;
+
+/* src/backend/vulkan/kv_cache.rs:153-176 (KvCacheConfig) plus the two build-side
+ * fields n_slots and scale_mode. */
+typedef struct {
+    uint32_t n_layers;
+    uint32_t n_kv_heads;
+    uint32_t head_dim;
+    uint32_t max_seq_len;
+    uint32_t dtype;                        /* vfkv_dtype */
+    const uint32_t *per_layer_head_dim;    /* NULL, or n_layers entries */
+    const uint32_t *per_layer_n_kv_heads;  /* NULL, or n_layers entries */
+    uint32_t n_slots;                      /* independent sequences; 0 or 1 = the reference's single slab */
+    uint32_t scale_mode;                   /* vfkv_scale_mode; must be NONE unless dtype is F8 */
+} vfkv_cache_config;
+
+/* ---------------------------------------------------------------------- */
+/* context                                                                  */
+/* ---------------------------------------------------------------------- */
+/* Stands in for the VulkanDevice + PipelineRegistry pair every run_* helper
+ * receives (src/backend/vulkan/forward/runs.rs:722-729). */
+int32_t vfkv_ctx_create(int32_t device_ordinal, vfkv_ctx **out);
+int32_t vfkv_ctx_destroy(vfkv_ctx *ctx);
+const char *vfkv_last_error(const vfkv_ctx *ctx);   /* never NULL */
+const char *vfkv_status_string(int32_t status);
+uint32_t vfkv_abi_version(void);
+/* Reads the device-side status word that bounded waits write into; clears it.
+ * Returns VFKV_OK or VFKV_ERR_TIMEOUT.  Synchronises the given stream. */
+int32_t vfkv_ctx_poll(vfkv_ctx *ctx, void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* cache: allocation, layout, bookkeeping                                   */
+/* ---------------------------------------------------------------------- */
+/* KvCache::new (src/backend/vulkan/kv_cache.rs:224-338): two device buffers,
+ * position-major [layer][slot][pos][kv_head][dim]; with one slot this is the
+ * reference's [layer][pos][kv_head][dim].  Sizes use checked arithmetic
+ * (:273-291) and overflow returns VFKV_ERR_OVERFLOW.  Unlike the reference the
+ * dtype is an explicit field, not an environment variable (:85-101); see
+ * vfkv_dtype_from_env. */
+int32_t vfkv_cache_create(vfkv_ctx *ctx, const vfkv_cache_config *cfg, vfkv_cache **out);
+/* KvCache::destroy (:496-499) */
+int32_t vfkv_cache_destroy(vfkv_cache *cache);
+/* KvCache::zero_fill (:357-376) and zero_layer (:384-407); asynchronous on `stream` */
+int32_t vfkv_cache_zero_fill(vfkv_cache *cache, void *stream);
+int32_t vfkv_cache_zero_layer(vfkv_cache *cache, uint32_t layer, void *stream);
+
+/* KvCache::current_seq_len and reset() (:208,492-494), one counter per slot.
+ * reset zeroes only the counter; cache bytes persist, as in the reference. */
+int32_t vfkv_cache_reset(vfkv_cache *cache, uint32_t slot);
+int32_t vfkv_cache_seq_len(const vfkv_cache *cache, uint32_t slot, uint32_t *out);
+int32_t vfkv_cache_set_seq_len(vfkv_cache *cache, uint32_t slot, uint32_t seq_len);
+
+/* Layout accessors (:412-490).  The *_bytes values are offsets into the K
+ * buffer (identical for V).  With n_slots > 1, layer_offset_bytes is the start
+ * of slot 0 of that layer and slot_offset_bytes the start of any slot. */
+uint32_t vfkv_cache_head_dim_for(const vfkv_cache *cache, uint32_t layer);
+uint32_t vfkv_cache_kv_heads_for(const vfkv_cache *cache, uint32_t layer);
+uint64_t vfkv_cache_row_bytes(const vfkv_cache *cache, uint32_t layer);
+uint64_t vfkv_cache_layer_size_bytes(const vfkv_cache *cache, uint32_t layer);
+uint64_t vfkv_cache_layer_offset_bytes(const vfkv_cache *cache, uint32_t layer);
+uint64_t vfkv_cache_layer_offset_elems(const vfkv_cache *cache, uint32_t layer);
+uint64_t vfkv_cache_pos_offset_bytes(const vfkv_cache *cache, uint32_t layer, uint32_t pos);
+uint64_t vfkv_cache_slot_offset_bytes(const vfkv_cache *cache, uint32_t layer, uint32_t slot);
+uint64_t vfkv_cache_bytes_per_buffer(const vfkv_cache *cache);
+uint32_t vfkv_cache_dtype(const vfkv_cache *cache);
+int32_t  vfkv_cache_is_fp8(const vfkv_cache *cache);
+int32_t  vfkv_cache_is_fp16(const vfkv_cache *cache);
+/* public k_buffer / v_buffer fields (:205-206): raw device base pointers */
+void *vfkv_cache_k_ptr(const vfkv_cache *cache);
+void *vfkv_cache_v_ptr(const vfkv_cache *cache);
+/* extension: [layer][slot][pos][kv_head] f32 scale planes, NULL when scale_mode is NONE */
+float *vfkv_cache_k_scale_ptr(const vfkv_cache *cache);
+float *vfkv_cache_v_scale_ptr(const vfkv_cache *cache);
+
+/* free functions of kv_cache.rs */
+/* kv_bytes_per_token (:186-202) */
+uint64_t vfkv_kv_bytes_per_token(uint32_t n_layers, uint32_t n_kv_heads, uint32_t head_dim,
+                                 const uint32_t *per_layer_head_dim,
+                                 const uint32_t *per_layer_n_kv_heads, uint64_t elem_size);
+/* KvDtype::element_size (:60-66) */
+uint64_t vfkv_dtype_element_size(uint32_t dtype);
+/* kv_dtype_from_env (:85-101): VULKANFORGE_KV_FP8=1|true -> F8, else
+ * VULKANFORGE_FP16_KV=0 -> F32, else F16 */
+uint32_t vfkv_dtype_from_env(void);
+/* guard_kv_precision (:118-151); `force` is VULKANFORGE_ALLOW_BROKEN_KV */
+int32_t vfkv_guard_kv_precision(int32_t is_gemma4_moe, uint32_t dtype, int32_t force);
+/* gemma4_kv_start (src/backend/vulkan/forward/arch/gemma4.rs:59-73) for a sliding layer */
+uint32_t vfkv_sliding_kv_start(uint32_t position, uint32_t sliding_window);
+
+/* ---------------------------------------------------------------------- */
+/* raw ops: the reference's dispatch level (buffers + push constants)        */
+/* ---------------------------------------------------------------------- */
+/* Forward::run_kv_store_fp8 (src/backend/vulkan/forward/runs.rs:2437-2478) +
+ * vk_shaders/kv_store_fp8.comp: n_elements f32 -> E4M3 bytes at
+ * d_dst + dst_byte_offset; offset 4-byte aligned (runs.rs:2448-2452); a ragged
+ * tail is padded to a multiple of four with the code of 0.0. */
+int32_t vfkv_kv_store_fp8(vfkv_ctx *ctx, const float *d_src, void *d_dst, uint32_t n_elements,
+                          uint64_t dst_byte_offset, void *stream);
+/* Forward::run_kv_copy_fp16 (runs.rs:2389-2430) + vk_shaders/kv_copy_fp16.comp */
+int32_t vfkv_kv_copy_fp16(vfkv_ctx *ctx, const float *d_src, void *d_dst, uint32_t n_elements,
+                          uint64_t dst_byte_offset, void *stream);
+/* vk_shaders/kv_fp8_to_f16.comp, dispatched from run_flash_attn_cm_gemma_rs
+ * (runs.rs:1103-1137): identity-indexed E4M3 -> binary16. */
+int32_t vfkv_kv_fp8_to_f16(vfkv_ctx *ctx, const void *d_src, void *d_dst, uint64_t n_elements,
+                           void *stream);
+
+/* Forward::run_flash_attn_split_reduce (runs.rs:1463-1571) +
+ * vk_shaders/flash_attn_split.comp + flash_attn_reduce.comp on raw buffers:
+ * d_k / d_v point at one layer's slab [pos][kv_head][dim] of `dtype`
+ * (the layer_offset_bytes binding of runs.rs:1475,1501-1502), d_q is
+ * [n_heads][head_dim] f32, d_out likewise.  The push-constant fields of
+ * FlashAttnSplitPushConstants (src/backend/vulkan/pipeline.rs:555-569) appear
+ * as arguments; max_seq is the slab's row count.  n_splits replaces the
+ * reference's fixed ceil(seq_len/64) partial count (0 = choose).  softcap is an
+ * extension (0 = off = reference). */
+int32_t vfkv_flash_attn_split_reduce(vfkv_ctx *ctx, vfkv_workspace *ws, const float *d_q,
+                                     const void *d_k, const void *d_v, float *d_out,
+                                     uint32_t dtype, uint32_t n_heads, uint32_t n_kv_heads,
+                                     uint32_t head_dim, uint32_t seq_len, uint32_t max_seq,
+                                     float scale, uint32_t kv_start, float softcap,
+                                     uint32_t n_splits, void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* workspace: the split-K partials                                          */
+/* ---------------------------------------------------------------------- */
+/* fa_scratch_out / fa_scratch_max / fa_scratch_sum (src/backend/vulkan/forward/setup.rs:203-230),
+ * one set per in-flight step.  Sized for max_seqs sequences x n_q_heads x
+ * max_splits partials of head_dim floats. */
+int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_heads,
+                              uint32_t head_dim, uint32_t max_splits, vfkv_workspace **out);
+int32_t vfkv_workspace_destroy(vfkv_workspace *ws);
+uint64_t vfkv_workspace_bytes(const vfkv_workspace *ws);
+
+/* ---------------------------------------------------------------------- */
+/* cache-level ops: what the forward pass calls                             */
+/* ---------------------------------------------------------------------- */
+/* step_kv_write / b_step_kv_write (executor/attention.rs:546-596,2134-2190):
+ * store n_tokens consecutive tokens of one sequence, f32
+ * [n_tokens][kv_heads_for(layer)][head_dim_for(layer)], at positions
+ * base_pos .. base_pos+n_tokens-1 of `slot`.  Both K and V in one launch.
+ * Writing below the committed length overwrites (prefix reuse,
+ * src/server/state.rs:199-229). */
+int32_t vfkv_append(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v,
+                    uint32_t n_tokens, uint32_t slot, uint32_t base_pos, void *stream);
+/* One token for each of n_seqs sequences: d_k/d_v are [n_seqs][kv_heads][head_dim],
+ * d_slot_ids (NULL = 0..n_seqs-1) and d_positions are device arrays. */
+int32_t vfkv_append_batch(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v,
+                          const uint32_t *d_slot_ids, const uint32_t *d_positions,
+                          uint32_t n_seqs, void *stream);
+
+/* run_flash_attn_cm_gemma_rs' convert pre-pass (runs.rs:1103-1137): positions
+ * [0, n_positions) of one layer of one slot, K and V, into caller buffers of
+ * n_positions*kv_heads*head_dim halfs each (the k_f16_scratch / v_f16_scratch
+ * of setup.rs:366-373). */
+int32_t vfkv_fp8_to_f16(vfkv_cache *cache, uint32_t slot, uint32_t layer, uint32_t n_positions,
+                        void *d_k_out, void *d_v_out, void *stream);
+
+/* step_attention -> run_scalar_attn (runs.rs:722-821): decode attention of one
+ * query token over positions [kv_start, seq_len) of kv_layer's slab
+ * (kv_layer != layer only for Gemma-4 KV sharing, gemma4.rs:27-49).
+ * d_q, d_out: [n_q_heads][head_dim_for(layer)] f32.  scale is explicit because
+ * the reference's rule is per model (runs.rs:1483-1489).  Every seq_len >= 1
+ * takes the same kernels, including the <= 64-token case the reference routes
+ * to flash_attn.comp (runs.rs:766-821). */
+int32_t vfkv_attend(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer, uint32_t kv_layer,
+                    const float *d_q, float *d_out, uint32_t n_q_heads, uint32_t slot,
+                    uint32_t seq_len, uint32_t kv_start, float scale, float softcap,
+                    uint32_t n_splits, void *stream);
+/* n_seqs independent sequences: d_q, d_out [n_seqs][n_q_heads][head_dim];
+ * d_slot_ids (NULL = 0..n_seqs-1), d_seq_lens, d_kv_starts (NULL = 0) on device.
+ * max_seq_len_hint bounds the largest seq_len (0 = the cache's max_seq_len) and
+ * only steers the split count. */
+int32_t vfkv_attend_batch(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer,
+                          uint32_t kv_layer, const float *d_q, float *d_out, uint32_t n_q_heads,
+                          const uint32_t *d_slot_ids, const uint32_t *d_seq_lens,
+                          const uint32_t *d_kv_starts, uint32_t n_seqs,
+                          uint32_t max_seq_len_hint, float scale, float softcap,
+                          uint32_t n_splits, void *stream);
+
+/* KvWrite followed by Attention, the order of the layer plan
+ * (src/backend/vulkan/forward/layer_plan.rs:472-483), for one token per
+ * sequence: append at d_positions[i], attend over
+ * [kv_start_i, d_positions[i]+1).  window 0 = full history, else the sliding
+ * rule of gemma4.rs:59-73. */
+int32_t vfkv_decode_step(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer,
+                         const float *d_q, const float *d_k, const float *d_v, float *d_out,
+                         uint32_t n_q_heads, const uint32_t *d_slot_ids,
+                         const uint32_t *d_positions, uint32_t n_seqs,
+                         uint32_t max_seq_len_hint, uint32_t window, float scale,
+                         float softcap, uint32_t n_splits, void *stream);
+
+/* Same step for every layer of one token with HOST buffers: copies
+ * h_q [n_layers][n_seqs][n_q_heads][D], h_k, h_v [n_layers][n_seqs][kv_heads][D]
+ * to the device, runs the layers in order, copies h_out
+ * [n_layers][n_seqs][n_q_heads][D] back and waits.  Uniform-shape caches only.
+ * h_positions / h_slot_ids (NULL = identity) are host arrays of n_seqs.
+ * windows: NULL, or n_layers entries (0 = global layer).  This is the
+ * forward_token boundary (src/backend/vulkan/forward/decode.rs:567-626) reduced
+ * to the hot path. */
+int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const float *h_q,
+                               const float *h_k, const float *h_v, float *h_out,
+                               uint32_t n_q_heads, const uint32_t *h_slot_ids,
+                               const uint32_t *h_positions, uint32_t n_seqs,
+                               const uint32_t *windows, float scale, float softcap,
+                               uint32_t n_splits, void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* sequence-dimension sharding (no counterpart in the reference, which is    */
+/* single-GPU): local partials and the merge of flash_attn_reduce.comp:51-80 */
+/* ---------------------------------------------------------------------- */
+/* Attention over positions [pos_begin, pos_end) only, unnormalised:
+ * d_m, d_l [n_seqs][n_q_heads], d_o [n_seqs][n_q_heads][head_dim] with
+ * o = sum exp(s - m) v.  An empty range gives m = -1e30, l = 0, o = 0. */
+int32_t vfkv_attend_partial(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer,
+                            uint32_t kv_layer, const float *d_q, uint32_t n_q_heads,
+                            uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale,
+                            float softcap, uint32_t n_splits, float *d_m, float *d_l,
+                            float *d_o, void *stream);
+/* d_m, d_l: [n_parts][n_rows]; d_o: [n_parts][n_rows][head_dim];
+ * d_out: [n_rows][head_dim]; n_rows = sequences x q-heads. */
+int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, const float *d_o,
+                            uint32_t n_parts, uint32_t n_rows, uint32_t head_dim, float *d_out,
+                            void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* device-memory helpers for hosts without a CUDA binding of their own       */
+/* ---------------------------------------------------------------------- */
+int32_t vfkv_malloc(vfkv_ctx *ctx, uint64_t bytes, void **d_out);
+int32_t vfkv_free(vfkv_ctx *ctx, void *d_ptr);
+int32_t vfkv_malloc_host(vfkv_ctx *ctx, uint64_t bytes, void **h_out);   /* pinned */
+int32_t vfkv_free_host(vfkv_ctx *ctx, void *h_ptr);
+int32_t vfkv_memcpy_h2d(vfkv_ctx *ctx, void *d_dst, const void *h_src, uint64_t bytes, void *stream);
+int32_t vfkv_memcpy_d2h(vfkv_ctx *ctx, void *h_dst, const void *d_src, uint64_t bytes, void *stream);
+int32_t vfkv_memset(vfkv_ctx *ctx, void *d_dst, int32_t byte, uint64_t bytes, void *stream);
+int32_t vfkv_stream_synchronize(vfkv_ctx *ctx, void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* profiling hooks: the ShaderProfiler labels (src/backend/vulkan/profiler.rs:28-187) */
+/* ---------------------------------------------------------------------- */
+/* Selects the attention implementation for subsequent calls on this context:
+ * 0 = automatic, 1 = CUDA-core kernel only, 2 = tensor-core kernel only
+ * (VFKV_ERR_UNSUPPORTED from attend when the shape is outside it). */
+int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
+/* Kernels this context has launched since creation (for launch accounting). */
+uint64_t vfkv_ctx_launch_count(const vfkv_ctx *ctx);
+
+/* Per-kernel GPU timing with the reference's profiler labels
+ * (executor/attention.rs:560-573, runs.rs:1527,1561,1127; enabled there by
+ * VF_GPU_TIMER).  While enabled every kernel launch is bracketed by a pair of
+ * CUDA events on its stream.  Labels: */
+typedef enum {
+    VFKV_PROF_KV_STORE = 0,      /* kv_store_fp8_k/_v, kv_copy_fp16_k/_v (one launch covers K and V) */
+    VFKV_PROF_FP8_TO_F16 = 1,    /* fa_cm_rs_cvt */
+    VFKV_PROF_FA_SPLIT = 2,      /* fa_split */
+    VFKV_PROF_FA_REDUCE = 3,     /* fa_reduce */
+    VFKV_PROF_LABELS = 4
+} vfkv_prof_label;
+int32_t vfkv_profile_enable(vfkv_ctx *ctx, int32_t on);
+/* Waits for the recorded events, returns count / total / minimum milliseconds of
+ * one label and, when `reset` is non-zero, forgets all records of every label. */
+int32_t vfkv_profile_collect(vfkv_ctx *ctx, uint32_t label, uint64_t *count, double *total_ms,
+                             double *min_ms, int32_t reset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VFKV_H */

@@ -1,0 +1,355 @@
+"""Split-K GQA decode attention on the GPU, through the C ABI, against the CPU oracle
+(the restatement of the reference's cpu_attention_reference, tests/correctness.rs:2567-2617).
+
+Tolerances: F32 / F16 cache: max-abs error below 1e-3 (the reference's own threshold for
+split+reduce, tests/correctness.rs:2875-2894; the build's gate is 2e-3).  FP8 cache: error
+relative to the output's max below 3e-2 against the oracle reading the same E4M3 bytes."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+import vulkanforge_b200 as vf
+from util import (GOLDEN_CASES, correctness_rs_inputs, dev_write_bytes, encode_cache, golden_inputs,
+                  kv_values, rel_err, to_dev)
+
+pytestmark = pytest.mark.gpu
+
+ABS_TOL = 1e-3
+FP8_REL_TOL = 3e-2
+
+
+def check(got, want, dtype):
+    assert np.isfinite(got).all()
+    if int(dtype) == oracle.F8:
+        assert rel_err(got, want) < FP8_REL_TOL, rel_err(got, want)
+    else:
+        err = float(np.max(np.abs(got - want)))
+        assert err < ABS_TOL, err
+
+
+class Rig:
+    """A cache with caller-chosen contents (written as raw bytes so attention is tested
+    independently of append) plus the forward-side wrapper."""
+
+    def __init__(self, ctx, dtype, hq, hkv, d, max_seq, n_layers=1, n_slots=1, scale_mode=0, **fw):
+        self.ctx, self.dtype, self.hq, self.hkv, self.d = ctx, vf.KvDtype(dtype), hq, hkv, d
+        self.cache = vf.KvCache(ctx, vf.KvCacheConfig(n_layers, hkv, d, max_seq, n_slots=n_slots,
+                                                      scale_mode=scale_mode), self.dtype)
+        self.fwd = vf.CudaForward(ctx, self.cache, n_heads=hq, max_batch=max(n_slots, 1), **fw)
+
+    def put(self, layer, slot, k_cache, v_cache, pos0=0):
+        off = self.cache.slot_offset_bytes(layer, slot) + pos0 * self.cache.row_bytes(layer)
+        dev_write_bytes(self.cache.k_buffer + off, k_cache.view(np.uint8).ravel())
+        dev_write_bytes(self.cache.v_buffer + off, v_cache.view(np.uint8).ravel())
+
+    def attend(self, q, layer, seq_len, kv_start=0, n_splits=0, slot=0, kv_layer=None):
+        import torch
+        out = torch.full((self.hq, self.d), float("nan"), device="cuda")
+        self.fwd.run_flash_attn_split_reduce(to_dev(q), out, layer, seq_len - 1, n_splits,
+                                             layer if kv_layer is None else kv_layer, kv_start, slot)
+        torch.cuda.synchronize()
+        return out.cpu().numpy()
+
+    def close(self):
+        self.fwd.workspace.destroy()
+        self.cache.destroy()
+
+
+@pytest.fixture(params=[1, 0], ids=["cuda-core", "auto"])
+def impl(request, ctx):
+    ctx.set_attn_impl(request.param)
+    yield request.param
+    ctx.set_attn_impl(0)
+
+
+@pytest.mark.parametrize("seq_len", [64, 200, 2048])
+@pytest.mark.parametrize("n_splits", [0, 1, 4, 32])
+def test_reference_split_attn_cases(ctx, impl, seq_len, n_splits):
+    """tests/correctness.rs:2791-2894: 32 q / 8 kv / 128, F32 cache, deterministic inputs, < 1e-3."""
+    hq, hkv, d = 32, 8, 128
+    q, k, v = correctness_rs_inputs(hq, hkv, d, seq_len)
+    rig = Rig(ctx, vf.KvDtype.F32, hq, hkv, d, 2048)
+    try:
+        rig.put(0, 0, k, v)
+        got = rig.attend(q, 0, seq_len, n_splits=n_splits)
+        check(got, oracle.attention_ref(q, k, v, oracle.F32, hq, hkv, d, seq_len), oracle.F32)
+    finally:
+        rig.close()
+
+
+def test_raw_pointer_entry_matches(ctx, impl):
+    """vfkv_flash_attn_split_reduce on caller buffers (the Fixture::dispatch level of the reference)."""
+    import torch
+    hq, hkv, d, L = 32, 8, 128, 200
+    q, k, v = correctness_rs_inputs(hq, hkv, d, L)
+    ws = vf.Workspace(ctx, 1, hq, d, 16)
+    try:
+        out = torch.zeros(hq, d, device="cuda")
+        ctx.check(ctx._lib.vfkv_flash_attn_split_reduce(
+            ctx.handle, ws.handle, to_dev(q).data_ptr(), to_dev(k).data_ptr(), to_dev(v).data_ptr(),
+            out.data_ptr(), oracle.F32, hq, hkv, d, L, L, 1.0 / np.sqrt(d), 0, 0.0, 4, None))
+        torch.cuda.synchronize()
+        check(out.cpu().numpy(), oracle.attention_ref(q, k, v, oracle.F32, hq, hkv, d, L), oracle.F32)
+    finally:
+        ws.destroy()
+
+
+@pytest.mark.parametrize("dtype", [vf.KvDtype.F32, vf.KvDtype.F16, vf.KvDtype.F8])
+def test_seq1_output_equals_v_and_layer_offset(ctx, impl, dtype):
+    """tests/correctness.rs:899-1035: seq_len 1 => out == V; slab bound at a non-zero layer
+    offset while layer 0 holds garbage."""
+    hq, hkv, d, max_seq = 32, 8, 128, 2048
+    rig = Rig(ctx, dtype, hq, hkv, d, max_seq, n_layers=2)
+    try:
+        garbage = np.full((max_seq, hkv, d), 999.0, np.float32)
+        rig.put(0, 0, encode_cache(garbage, int(dtype)), encode_cache(garbage, int(dtype)))
+        rig.put(1, 0, encode_cache(np.full((max_seq, hkv, d), 0.1, np.float32), int(dtype)),
+                encode_cache(np.full((max_seq, hkv, d), 1.0, np.float32), int(dtype)))
+        q = np.full((hq, d), 0.1, np.float32)
+        for L in (1, 2, 65):
+            got = rig.attend(q, 1, L)
+            assert np.max(np.abs(got - 1.0)) < 1e-5
+    finally:
+        rig.close()
+
+
+def test_golden_fixture_cases(ctx, impl):
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "attention_small.npz"))
+    for i, (name, hq, hkv, d, L, start, dt, cap) in enumerate(GOLDEN_CASES):
+        q, kc, vc = golden_inputs(i)
+        rig = Rig(ctx, dt, hq, hkv, d, L + 3, softcap=cap)
+        try:
+            rig.put(0, 0, kc, vc)
+            for n_splits in (0, 3):
+                got = rig.attend(q, 0, L, kv_start=start, n_splits=n_splits)
+                check(got, gold[name + "/out"], dt)
+        finally:
+            rig.close()
+
+
+SHAPES = [  # hq, hkv, d
+    (32, 8, 128), (64, 8, 128), (16, 8, 256), (8, 8, 64), (8, 1, 128), (40, 8, 128), (16, 2, 512), (4, 2, 64)]
+
+
+@pytest.mark.parametrize("dtype", [vf.KvDtype.F32, vf.KvDtype.F16, vf.KvDtype.F8])
+@pytest.mark.parametrize("hq,hkv,d", SHAPES)
+def test_shapes_lengths_and_starts(ctx, impl, dtype, hq, hkv, d):
+    rng = np.random.default_rng(hq * 1000 + d + int(dtype))
+    max_seq = 1200
+    fp8 = dtype == vf.KvDtype.F8
+    k = kv_values(rng, (max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0)
+    v = kv_values(rng, (max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0)
+    kc, vc = encode_cache(k, int(dtype)), encode_cache(v, int(dtype))
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    rig = Rig(ctx, dtype, hq, hkv, d, max_seq)
+    try:
+        rig.put(0, 0, kc, vc)
+        for L, start, n_splits in [(1, 0, 0), (31, 0, 1), (64, 0, 2), (65, 0, 0), (129, 128, 0), (640, 0, 5),
+                                   (1200, 0, 0), (1200, 1200 - 1024, 0), (1111, 17, 7), (1000, 999, 3),
+                                   (257, 3, 64)]:
+            got = rig.attend(q, 0, L, kv_start=start, n_splits=n_splits)
+            want = oracle.attention_ref(q, kc, vc, int(dtype), hq, hkv, d, L, start)
+            check(got, want, dtype)
+    finally:
+        rig.close()
+
+
+def test_stale_nan_rows_beyond_seq_len_do_not_leak(ctx, impl):
+    """Rows at and beyond seq_len (and below kv_start) may hold anything, including NaN codes."""
+    for dtype in (vf.KvDtype.F8, vf.KvDtype.F16, vf.KvDtype.F32):
+        hq, hkv, d, max_seq, L, start = 32, 8, 128, 512, 300, 40
+        rng = np.random.default_rng(3)
+        k = rng.standard_normal((max_seq, hkv, d), dtype=np.float32)
+        v = rng.standard_normal((max_seq, hkv, d), dtype=np.float32)
+        kc, vc = encode_cache(k, int(dtype)), encode_cache(v, int(dtype))
+        nan_code = {vf.KvDtype.F8: 0x7F, vf.KvDtype.F16: 0x7E00, vf.KvDtype.F32: 0x7FC00000}[dtype]
+        for arr in (kc, vc):
+            a = arr.view({1: np.uint8, 2: np.uint16, 4: np.uint32}[arr.itemsize])
+            a[L:] = nan_code
+            a[:start] = nan_code
+        q = rng.standard_normal((hq, d), dtype=np.float32)
+        rig = Rig(ctx, dtype, hq, hkv, d, max_seq)
+        try:
+            rig.put(0, 0, kc, vc)
+            for n_splits in (0, 1, 6):
+                got = rig.attend(q, 0, L, kv_start=start, n_splits=n_splits)
+                check(got, oracle.attention_ref(q, kc, vc, int(dtype), hq, hkv, d, L, start), dtype)
+        finally:
+            rig.close()
+
+
+@pytest.mark.parametrize("dtype", [vf.KvDtype.F16, vf.KvDtype.F8])
+def test_batch_variable_lengths_slots_and_windows(ctx, impl, dtype):
+    """Independent sequences in their own slots, ragged lengths, permuted slot ids, per-sequence
+    window starts; then the fused decode step (append + attend) for the same batch."""
+    import torch
+    hq, hkv, d, max_seq, n_slots = 32, 8, 128, 700, 6
+    rng = np.random.default_rng(21)
+    lens = np.array([1, 64, 65, 700, 333, 512], np.uint32)
+    starts = np.array([0, 0, 1, 700 - 256, 0, 500], np.uint32)
+    slots = np.array([4, 0, 5, 1, 3, 2], np.uint32)
+    fp8 = dtype == vf.KvDtype.F8
+    k = kv_values(rng, (n_slots, max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0)
+    v = kv_values(rng, (n_slots, max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0)
+    kc, vc = encode_cache(k, int(dtype)), encode_cache(v, int(dtype))
+    q = rng.standard_normal((n_slots, hq, d), dtype=np.float32)
+    rig = Rig(ctx, dtype, hq, hkv, d, max_seq, n_layers=2, n_slots=n_slots)
+    try:
+        for s in range(n_slots):
+            rig.put(1, s, kc[s], vc[s])
+        out = torch.zeros(n_slots, hq, d, device="cuda")
+        for hint in (0, 700):
+            rig.fwd.step_attention_batch(1, to_dev(q), out, to_dev(slots), to_dev(lens), to_dev(starts),
+                                         n_slots, max_seq_len_hint=hint)
+            torch.cuda.synchronize()
+            got = out.cpu().numpy()
+            for i in range(n_slots):
+                s = int(slots[i])
+                want = oracle.attention_ref(q[i], kc[s], vc[s], int(dtype), hq, hkv, d, int(lens[i]), int(starts[i]))
+                check(got[i], want, dtype)
+        # fused step: new token at position lens-1 (overwrites that row), global attention
+        kn = kv_values(rng, (n_slots, hkv, d), outlier_frac=0.0)
+        vn = kv_values(rng, (n_slots, hkv, d), outlier_frac=0.0)
+        pos = (lens - 1).astype(np.uint32)
+        rig.fwd.decode_step(1, to_dev(q), to_dev(kn), to_dev(vn), out, to_dev(slots), to_dev(pos), n_slots)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        for i in range(n_slots):
+            s = int(slots[i])
+            kk, vv = kc[s].copy(), vc[s].copy()
+            kk[pos[i]] = encode_cache(kn[i], int(dtype))
+            vv[pos[i]] = encode_cache(vn[i], int(dtype))
+            check(got[i], oracle.attention_ref(q[i], kk, vv, int(dtype), hq, hkv, d, int(lens[i])), dtype)
+    finally:
+        rig.close()
+
+
+def test_gemma_style_window_softcap_and_kv_share(ctx, impl):
+    """16 q / 8 kv / 256, F16: sliding layers use kv_start = pos+1-window (gemma4.rs:59-73), a
+    subscriber layer reads its publisher's slab (gemma4.rs:27-49), scores are soft-capped
+    (extension) and scale is 1.0 (runs.rs:1483-1489)."""
+    hq, hkv, d, max_seq, window = 16, 8, 256, 1500, 1024
+    rng = np.random.default_rng(31)
+    k = rng.standard_normal((max_seq, hkv, d), dtype=np.float32) * 0.3
+    v = rng.standard_normal((max_seq, hkv, d), dtype=np.float32)
+    kc, vc = encode_cache(k, oracle.F16), encode_cache(v, oracle.F16)
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    rig = Rig(ctx, vf.KvDtype.F16, hq, hkv, d, max_seq, n_layers=3, sliding_window=window,
+              sliding_layers=[0, 2], kv_read_layer={2: 0}, attn_scale=1.0, softcap=50.0)
+    try:
+        import torch
+        rig.put(0, 0, kc, vc)
+        rig.put(1, 0, kc, vc)
+        for layer, pos in [(0, 1499), (1, 1499), (2, 1499), (0, 500), (2, 1024)]:
+            out = torch.zeros(hq, d, device="cuda")
+            rig.fwd.step_attention(layer, to_dev(q), out, pos)
+            torch.cuda.synchronize()
+            start = vf.sliding_kv_start(pos, window) if layer in (0, 2) else 0
+            want = oracle.attention_ref(q, kc, vc, oracle.F16, hq, hkv, d, pos + 1, start, 1.0, 50.0)
+            check(out.cpu().numpy(), want, oracle.F16)
+    finally:
+        rig.close()
+
+
+def test_fp8_per_token_head_scales(ctx, impl):
+    """Extension: absmax-scaled E4M3 rows written by append, read back by attention."""
+    import torch
+    hq, hkv, d, max_seq, L = 32, 8, 128, 400, 389
+    rng = np.random.default_rng(41)
+    k = kv_values(rng, (L, hkv, d)) * 30
+    v = kv_values(rng, (L, hkv, d)) * 0.02
+    q = rng.standard_normal((hq, d), dtype=np.float32) * 0.05
+    rig = Rig(ctx, vf.KvDtype.F8, hq, hkv, d, max_seq, scale_mode=1)
+    try:
+        rig.fwd.b_step_kv_write(0, to_dev(k), to_dev(v), L, 0)
+        kc = np.zeros((L, hkv, d), np.uint8); vc = np.zeros_like(kc)
+        ks = np.zeros((L, hkv), np.float32); vs = np.zeros_like(ks)
+        for t in range(L):
+            c, s = oracle.kv_store_fp8_scaled(k[t], hkv, d); kc[t] = c.reshape(hkv, d); ks[t] = s
+            c, s = oracle.kv_store_fp8_scaled(v[t], hkv, d); vc[t] = c.reshape(hkv, d); vs[t] = s
+        for n_splits in (0, 1, 5):
+            got = rig.attend(q, 0, L, n_splits=n_splits)
+            want = oracle.attention_ref(q, kc, vc, oracle.F8, hq, hkv, d, L, 0, None, 0.0, ks, vs)
+            check(got, want, oracle.F8)
+    finally:
+        rig.close()
+
+
+@pytest.mark.parametrize("dtype", [vf.KvDtype.F16, vf.KvDtype.F8])
+def test_partials_over_position_ranges_merge_to_full(ctx, impl, dtype):
+    """Sequence-dimension sharding: (m, l, o) over disjoint position ranges, merged with the
+    reduce shader's update (flash_attn_reduce.comp:51-80), equals attention over the whole range."""
+    import torch
+    hq, hkv, d, L = 64, 8, 128, 3000
+    rng = np.random.default_rng(51)
+    k = rng.standard_normal((L, hkv, d), dtype=np.float32)
+    v = rng.standard_normal((L, hkv, d), dtype=np.float32)
+    kc, vc = encode_cache(k, int(dtype)), encode_cache(v, int(dtype))
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    rig = Rig(ctx, dtype, hq, hkv, d, L)
+    try:
+        rig.put(0, 0, kc, vc)
+        bounds = [0, 700, 700, 1536, 2999, 3000]     # includes an empty range
+        G = len(bounds) - 1
+        m = torch.zeros(G, hq, device="cuda"); l = torch.zeros(G, hq, device="cuda")
+        o = torch.zeros(G, hq, d, device="cuda")
+        dq = to_dev(q)
+        for g in range(G):
+            rig.fwd.attend_partial(0, dq, bounds[g], bounds[g + 1], m[g], l[g], o[g])
+        out = torch.zeros(hq, d, device="cuda")
+        rig.fwd.merge_partials(m, l, o, G, hq, d, out)
+        torch.cuda.synchronize()
+        assert float(l[1].abs().max()) == 0.0 and float(m[1].max()) <= -1e29
+        check(out.cpu().numpy(), oracle.attention_ref(q, kc, vc, int(dtype), hq, hkv, d, L), dtype)
+    finally:
+        rig.close()
+
+
+def test_decode_token_host_all_layers(ctx, impl):
+    """forward_token boundary with host buffers: every layer appends then attends."""
+    hq, hkv, d, max_seq, n_layers, n_seqs = 32, 8, 128, 300, 3, 2
+    rng = np.random.default_rng(61)
+    pos = np.array([299, 130], np.uint32)
+    rig = Rig(ctx, vf.KvDtype.F8, hq, hkv, d, max_seq, n_layers=n_layers, n_slots=n_seqs)
+    try:
+        kc = encode_cache(kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d)), oracle.F8)
+        vc = encode_cache(kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d)), oracle.F8)
+        for l in range(n_layers):
+            for s in range(n_seqs):
+                rig.put(l, s, kc[l, s], vc[l, s])
+        q = rng.standard_normal((n_layers, n_seqs, hq, d), dtype=np.float32)
+        kn = kv_values(rng, (n_layers, n_seqs, hkv, d))
+        vn = kv_values(rng, (n_layers, n_seqs, hkv, d))
+        out = np.zeros((n_layers, n_seqs, hq, d), np.float32)
+        rig.fwd.decode_token_host(q, kn, vn, out, pos, n_seqs)
+        for l in range(n_layers):
+            want = oracle.decode_step(q[l], kn[l], vn[l], kc[l], vc[l], oracle.F8, n_seqs, max_seq, hq, hkv, d, pos + 1)
+            check(out[l], want, oracle.F8)
+    finally:
+        rig.close()
+
+
+def test_attend_argument_errors(ctx):
+    import torch
+    rig = Rig(ctx, vf.KvDtype.F16, 32, 8, 128, 64)
+    try:
+        L = ctx._lib
+        x = torch.zeros(32 * 128, device="cuda")
+        E = vf.kv_cache.ERR_INVALID
+        h, w = rig.cache.handle, rig.fwd.workspace.handle
+        assert L.vfkv_attend(h, w, 0, 0, x.data_ptr(), x.data_ptr(), 32, 0, 65, 0, 1.0, 0.0, 0, None) == E
+        assert L.vfkv_attend(h, w, 0, 0, x.data_ptr(), x.data_ptr(), 32, 0, 10, 11, 1.0, 0.0, 0, None) == E
+        assert L.vfkv_attend(h, w, 1, 0, x.data_ptr(), x.data_ptr(), 32, 0, 10, 0, 1.0, 0.0, 0, None) == E
+        assert L.vfkv_attend(h, w, 0, 0, x.data_ptr(), x.data_ptr(), 30, 0, 10, 0, 1.0, 0.0, 0, None) == E
+        assert L.vfkv_attend(h, w, 0, 0, x.data_ptr(), x.data_ptr(), 32, 1, 10, 0, 1.0, 0.0, 0, None) == E
+        assert L.vfkv_attend(h, None, 0, 0, x.data_ptr(), x.data_ptr(), 32, 0, 10, 0, 1.0, 0.0, 4, None) == E
+        assert L.vfkv_attend(h, w, 0, 0, None, x.data_ptr(), 32, 0, 10, 0, 1.0, 0.0, 0, None) == E
+        # an empty visible range is defined as zeros
+        out = torch.full((32, 128), 7.0, device="cuda")
+        assert L.vfkv_attend(h, w, 0, 0, x.data_ptr(), out.data_ptr(), 32, 0, 10, 10, 1.0, 0.0, 0, None) == 0
+        torch.cuda.synchronize()
+        assert float(out.abs().max()) == 0.0
+    finally:
+        rig.close()

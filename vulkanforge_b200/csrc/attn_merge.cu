@@ -1,0 +1,113 @@
+// Log-sum-exp merge of split-K partials and the attention dispatcher.
+//
+// Replaces vk_shaders/flash_attn_reduce.comp and the host half of
+// Forward::run_flash_attn_split_reduce (src/backend/vulkan/forward/runs.rs:1463-1571).
+#include "attn_params.cuh"
+
+namespace vfkv {
+
+// flash_attn_reduce.comp:51-80: partials visited in ascending order with the
+// running (max, sum, acc) update; the final multiply by 1/sum is skipped when
+// the caller wants the unnormalised triple (sequence-dimension sharding).
+// Index of partial i of row r: i*part_stride + r*row_stride.
+__global__ void __launch_bounds__(128)
+merge_kernel(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po,
+             uint32_t n_parts, uint64_t part_stride, uint64_t row_stride, uint32_t head_dim,
+             float *__restrict__ out, float *__restrict__ out_m, float *__restrict__ out_l,
+             float *__restrict__ out_o)
+{
+    const uint64_t row = blockIdx.x;
+    constexpr int kMaxDims = 4;                      // 128 threads x 4 = head_dim 512
+    float acc[kMaxDims] = {0.f, 0.f, 0.f, 0.f};
+    float gmax = kMaskedScore, gsum = 0.f;
+    for (uint32_t i = 0; i < n_parts; ++i) {
+        const uint64_t pi = uint64_t(i) * part_stride + row * row_stride;
+        const float tm = pm[pi], ts = pl[pi];
+        const float nm = fmaxf(gmax, tm);
+        const float ko = __expf(gmax - nm), kn = __expf(tm - nm);
+#pragma unroll
+        for (int j = 0; j < kMaxDims; ++j) {
+            uint32_t d = threadIdx.x + j * 128;
+            float t = d < head_dim ? po[pi * head_dim + d] : 0.f;
+            acc[j] = acc[j] * ko + t * kn;
+        }
+        gsum = gsum * ko + ts * kn;
+        gmax = nm;
+    }
+    const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;   // an empty range yields zeros, not NaN
+#pragma unroll
+    for (int j = 0; j < kMaxDims; ++j) {
+        uint32_t d = threadIdx.x + j * 128;
+        if (d < head_dim) {
+            if (out) out[row * head_dim + d] = acc[j] * inv;
+            if (out_o) out_o[row * head_dim + d] = acc[j];
+        }
+    }
+    if (out_o && threadIdx.x == 0) { out_m[row] = gmax; out_l[row] = gsum; }
+}
+
+int32_t launch_merge_ws(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
+                        cudaStream_t st)
+{
+    const uint32_t rows = a.seq.n_seqs * a.n_q_heads;
+    ProfScope ps(ctx, VFKV_PROF_FA_REDUCE, st);
+    merge_kernel<<<rows, 128, 0, st>>>(ws->part_m, ws->part_l, ws->part_o, n_splits, 1, n_splits,
+                                      a.kv.head_dim, a.out, a.out_m, a.out_l, a.out_o);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "merge launch");
+}
+
+int32_t launch_merge_partials(vfkv_ctx *ctx, const float *m, const float *l, const float *o,
+                              uint32_t n_parts, uint32_t n_rows, uint32_t head_dim, float *out,
+                              cudaStream_t st)
+{
+    if (n_rows == 0) return VFKV_OK;
+    ProfScope ps(ctx, VFKV_PROF_FA_REDUCE, st);
+    merge_kernel<<<n_rows, 128, 0, st>>>(m, l, o, n_parts, n_rows, 1, head_dim, out, nullptr, nullptr,
+                                        nullptr);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "merge_partials launch");
+}
+
+// Split count when the caller passes 0.  The reference always cuts at 64
+// positions (runs.rs:766-769); here the count only has to fill the GPU: aim
+// for about two CTAs per SM, never cut below 256 positions per split.
+uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
+{
+    uint32_t max_len = a.seq.max_len_hint ? a.seq.max_len_hint : a.kv.max_seq;
+    if (!a.seq.seq_lens && !a.seq.positions) max_len = a.seq.seq_len_scalar - a.seq.kv_start_scalar;
+    if (a.seq.window && max_len > a.seq.window) max_len = a.seq.window;
+    uint64_t base = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
+    uint64_t want = (uint64_t(ctx->sm_count) * 2 + base - 1) / (base ? base : 1);
+    uint32_t min_chunk = tile < 256 ? 256 : tile;
+    uint64_t cap = (uint64_t(max_len) + min_chunk - 1) / min_chunk;
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    return uint32_t(want);
+}
+
+int32_t launch_attention(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, cudaStream_t st)
+{
+    if (a.seq.n_seqs == 0) return VFKV_OK;
+    if (a.kv.n_kv_heads == 0 || a.n_q_heads == 0 || a.n_q_heads % a.kv.n_kv_heads != 0)
+        return set_error(ctx, VFKV_ERR_INVALID, "n_q_heads must be a non-zero multiple of n_kv_heads");
+    const bool mma_ok = attn_mma_supported(a);
+    if (ctx->attn_impl == 2 && !mma_ok)
+        return set_error(ctx, VFKV_ERR_UNSUPPORTED, "shape outside the tensor-core attention kernel");
+    const bool use_mma = mma_ok && ctx->attn_impl != 1;
+
+    uint32_t n_splits = a.n_splits ? a.n_splits : choose_splits(ctx, a, use_mma ? 128 : 32);
+    if (n_splits > 1) {
+        if (!ws) return set_error(ctx, VFKV_ERR_INVALID, "a workspace is required when n_splits > 1");
+        if (n_splits > ws->max_splits) n_splits = ws->max_splits;
+        if (a.seq.n_seqs > ws->max_seqs || a.n_q_heads > ws->n_q_heads || a.kv.head_dim > ws->head_dim)
+            return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
+    }
+    int32_t rc = use_mma ? launch_attn_mma(ctx, ws, a, n_splits, st)
+                         : launch_attn_generic(ctx, ws, a, n_splits, st);
+    if (rc != VFKV_OK) return rc;
+    if (n_splits > 1) rc = launch_merge_ws(ctx, ws, a, n_splits, st);
+    return rc;
+}
+
+}  // namespace vfkv

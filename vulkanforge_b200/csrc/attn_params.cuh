@@ -1,0 +1,100 @@
+// Kernel parameter block shared by the attention kernels and the per-sequence
+// argument decoding (slot, visible length, sliding-window lower bound).
+#pragma once
+
+#include "common.cuh"
+
+namespace vfkv {
+
+struct AttnParams {
+    const uint8_t *k, *v;
+    const float *k_scales, *v_scales;
+    uint64_t slot_stride_bytes, slot_stride_scales;
+    const float *q;
+    float *part_o, *part_m, *part_l;       // workspace partials [seq][q_head][split]
+    float *out, *out_m, *out_l, *out_o;    // final outputs when one split covers a sequence
+    const uint32_t *slot_ids, *seq_lens, *kv_starts, *positions;
+    uint32_t slot0, seq_len_scalar, kv_start_scalar, window;
+    uint32_t n_q_heads, n_kv_heads, head_dim, group, max_seq, n_slots, n_splits, n_seqs;
+    float scale, softcap;
+    uint32_t *status;
+};
+
+inline AttnParams make_params(const vfkv_ctx *ctx, const vfkv_workspace *ws, const AttnArgs &a,
+                              uint32_t n_splits)
+{
+    AttnParams p{};
+    p.k = static_cast<const uint8_t *>(a.kv.k);
+    p.v = static_cast<const uint8_t *>(a.kv.v);
+    p.k_scales = a.kv.k_scales;
+    p.v_scales = a.kv.v_scales;
+    p.slot_stride_bytes = a.kv.slot_stride_bytes;
+    p.slot_stride_scales = a.kv.slot_stride_scales;
+    p.q = a.q;
+    p.part_o = ws ? ws->part_o : nullptr;
+    p.part_m = ws ? ws->part_m : nullptr;
+    p.part_l = ws ? ws->part_l : nullptr;
+    p.out = a.out; p.out_m = a.out_m; p.out_l = a.out_l; p.out_o = a.out_o;
+    p.slot_ids = a.seq.slot_ids; p.seq_lens = a.seq.seq_lens; p.kv_starts = a.seq.kv_starts;
+    p.positions = a.seq.positions;
+    p.slot0 = a.seq.slot0; p.seq_len_scalar = a.seq.seq_len_scalar;
+    p.kv_start_scalar = a.seq.kv_start_scalar; p.window = a.seq.window;
+    p.n_q_heads = a.n_q_heads; p.n_kv_heads = a.kv.n_kv_heads; p.head_dim = a.kv.head_dim;
+    p.group = a.n_q_heads / a.kv.n_kv_heads;
+    p.max_seq = a.kv.max_seq; p.n_slots = a.kv.n_slots; p.n_splits = n_splits;
+    p.n_seqs = a.seq.n_seqs;
+    p.scale = a.scale; p.softcap = a.softcap;
+    p.status = ctx->d_status;
+    return p;
+}
+
+#ifdef __CUDACC__
+// Visible range [start, len) of sequence s and its slot.  Out-of-range
+// arguments from device arrays are clamped and reported through the status
+// word instead of being dereferenced.
+__device__ __forceinline__ void seq_range(const AttnParams &p, uint32_t s, uint32_t *slot,
+                                          uint32_t *start, uint32_t *len)
+{
+    uint32_t sl = p.slot_ids ? p.slot_ids[s] : p.slot0 + s;
+    uint32_t n, st;
+    if (p.positions) {
+        n = p.positions[s] + 1u;
+        st = p.window ? (n > p.window ? n - p.window : 0u)
+                      : (p.kv_starts ? p.kv_starts[s] : p.kv_start_scalar);
+    } else {
+        n = p.seq_lens ? p.seq_lens[s] : p.seq_len_scalar;
+        st = p.kv_starts ? p.kv_starts[s] : p.kv_start_scalar;
+    }
+    if (sl >= p.n_slots || n > p.max_seq) {
+        if (threadIdx.x == 0) atomicOr(p.status, 4u);
+        if (sl >= p.n_slots) { sl = 0; n = 0; }
+        if (n > p.max_seq) n = p.max_seq;
+    }
+    if (st > n) st = n;
+    *slot = sl; *start = st; *len = n;
+}
+
+// Positions [*begin, *end) of split `split`; chunks are multiples of `align`.
+__device__ __forceinline__ void split_range(uint32_t start, uint32_t len, uint32_t n_splits,
+                                            uint32_t split, uint32_t align, uint32_t *begin,
+                                            uint32_t *end)
+{
+    uint32_t eff = len - start;
+    uint32_t chunk = (eff + n_splits - 1) / n_splits;
+    chunk = (chunk + align - 1) / align * align;
+    uint64_t b = uint64_t(start) + uint64_t(split) * chunk;
+    uint64_t e = b + chunk;
+    if (b > len) b = len;
+    if (e > len) e = len;
+    *begin = uint32_t(b); *end = uint32_t(e);
+}
+
+__device__ __forceinline__ float apply_softcap(float s, float cap)
+{
+    // extension: cap * tanh(s / cap), the formula the reference applies to final
+    // logits (src/backend/vulkan/forward/arch/gemma4.rs:85-94)
+    return cap > 0.f ? cap * tanhf(s / cap) : s;
+}
+#endif
+
+}  // namespace vfkv

@@ -1,0 +1,150 @@
+// Shared internal declarations of libvfkv: context, workspace, kernel
+// parameter blocks and the host-side launchers of each kernel family.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/vfkv.h"
+#include "kv_cache.hpp"
+
+struct vfkv_ctx {
+    int device = 0;
+    int sm_count = 0;
+    std::string last_error;
+    uint32_t *d_status = nullptr;      // device word written by bounded waits that give up
+    uint32_t attn_impl = 0;            // 0 auto, 1 CUDA-core only, 2 tensor-core only
+    uint64_t launches = 0;
+    void *encode_tiled = nullptr;      // cuTensorMapEncodeTiled, resolved at run time
+    // per-kernel GPU timing, the analogue of the reference's ShaderProfiler
+    // (src/backend/vulkan/profiler.rs:28-187); off unless vfkv_profile_enable(ctx, 1)
+    bool profiling = false;
+    struct ProfRec { uint32_t label; cudaEvent_t e0, e1; };
+    std::vector<ProfRec> prof;
+};
+
+struct vfkv_cache {
+    vfkv_ctx *ctx = nullptr;
+    vfkv::KvCache kv;
+};
+
+struct vfkv_workspace {
+    vfkv_ctx *ctx = nullptr;
+    uint32_t max_seqs = 0, n_q_heads = 0, head_dim = 0, max_splits = 0;
+    float *part_o = nullptr;    // [seq][q_head][split][head_dim]
+    float *part_m = nullptr;    // [seq][q_head][split]
+    float *part_l = nullptr;    // [seq][q_head][split]
+    uint32_t *d_u32 = nullptr;  // staging for scalar-call slot/len/start and host-step arrays
+    uint64_t bytes = 0;
+    // staging for vfkv_decode_token_host, grown on first use
+    float *stage_in = nullptr;
+    float *stage_out = nullptr;
+    uint64_t stage_in_bytes = 0, stage_out_bytes = 0;
+};
+
+namespace vfkv {
+
+int32_t set_error(vfkv_ctx *ctx, int32_t status, const std::string &msg);
+int32_t check_cuda(vfkv_ctx *ctx, cudaError_t e, const char *what);
+
+// One layer's slab(s) as seen by the attention kernels.
+struct KvView {
+    const void *k = nullptr;       // start of slot 0 of the layer
+    const void *v = nullptr;
+    const float *k_scales = nullptr;   // [slot][pos][kv_head] or null
+    const float *v_scales = nullptr;
+    uint64_t slot_stride_bytes = 0;    // bytes between consecutive slots (K or V)
+    uint64_t slot_stride_scales = 0;   // floats between consecutive slots in the scale planes
+    uint32_t max_seq = 0;              // rows per slot
+    uint32_t n_slots = 1;
+    uint32_t dtype = 0;
+    uint32_t n_kv_heads = 0;
+    uint32_t head_dim = 0;
+};
+
+// Per-sequence arguments: either device arrays (batch calls) or scalars.
+struct SeqArgs {
+    const uint32_t *slot_ids = nullptr;   // null -> slot = seq index + slot0
+    const uint32_t *seq_lens = nullptr;   // null -> seq_len_scalar
+    const uint32_t *kv_starts = nullptr;  // null -> kv_start_scalar, or derived from window
+    const uint32_t *positions = nullptr;  // when set: seq_len = positions[i] + 1
+    uint32_t slot0 = 0;
+    uint32_t seq_len_scalar = 0;
+    uint32_t kv_start_scalar = 0;
+    uint32_t window = 0;                  // with positions: kv_start = max(0, pos+1-window)
+    uint32_t n_seqs = 1;
+    uint32_t max_len_hint = 0;
+};
+
+struct AttnArgs {
+    KvView kv;
+    SeqArgs seq;
+    const float *q = nullptr;     // [seq][q_head][head_dim]
+    float *out = nullptr;         // [seq][q_head][head_dim]  (normalised)  or null
+    float *out_m = nullptr;       // partial outputs for sharded use, or null
+    float *out_l = nullptr;
+    float *out_o = nullptr;
+    uint32_t n_q_heads = 0;
+    float scale = 1.f;
+    float softcap = 0.f;
+    uint32_t n_splits = 0;        // 0 = choose
+};
+
+// Brackets one kernel launch with a pair of events on its stream while profiling is on.
+struct ProfScope {
+    vfkv_ctx *ctx; cudaStream_t st; cudaEvent_t e1 = nullptr;
+    ProfScope(vfkv_ctx *c, uint32_t label, cudaStream_t s) : ctx(c), st(s)
+    {
+        if (!ctx->profiling) return;
+        vfkv_ctx::ProfRec r{label, nullptr, nullptr};
+        if (cudaEventCreate(&r.e0) != cudaSuccess || cudaEventCreate(&r.e1) != cudaSuccess) return;
+        cudaEventRecord(r.e0, st);
+        e1 = r.e1;
+        ctx->prof.push_back(r);
+    }
+    ~ProfScope() { if (e1) cudaEventRecord(e1, st); }
+};
+
+// Launchers (each returns a vfkv_status).
+int32_t launch_store(vfkv_ctx *ctx, uint32_t dtype, const float *src, void *dst, uint64_t n,
+                     cudaStream_t st);
+int32_t launch_fp8_to_f16(vfkv_ctx *ctx, const void *src, void *dst, uint64_t n, cudaStream_t st);
+
+struct AppendArgs {
+    const float *k = nullptr, *v = nullptr;   // [n_rows][row_elems]
+    void *k_dst = nullptr, *v_dst = nullptr;  // layer base (slot 0)
+    float *k_scales = nullptr, *v_scales = nullptr;
+    uint64_t slot_stride_bytes = 0, slot_stride_scales = 0;
+    uint32_t row_elems = 0, head_dim = 0, n_kv_heads = 0, dtype = 0, max_seq = 0, n_slots = 1;
+    // rows: either n_tokens consecutive positions of one slot, or one token per sequence
+    uint32_t n_rows = 0;
+    uint32_t slot = 0, base_pos = 0;           // consecutive mode
+    const uint32_t *slot_ids = nullptr;        // batch mode (positions != null)
+    const uint32_t *positions = nullptr;
+};
+int32_t launch_append(vfkv_ctx *ctx, const AppendArgs &a, cudaStream_t st);
+
+int32_t launch_attention(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, cudaStream_t st);
+int32_t launch_merge_partials(vfkv_ctx *ctx, const float *m, const float *l, const float *o,
+                              uint32_t n_parts, uint32_t n_rows, uint32_t head_dim, float *out,
+                              cudaStream_t st);
+
+// attention implementations
+uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile);
+int32_t launch_attn_generic(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
+                            cudaStream_t st);
+bool attn_mma_supported(const AttnArgs &a);
+int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
+                        cudaStream_t st);
+// merges ws partials [seq][head][split] into a.out (normalised) or a.out_{m,l,o}
+int32_t launch_merge_ws(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
+                        cudaStream_t st);
+
+// Sentinel of vk_shaders/flash_attn_split.comp:104 for masked scores.
+constexpr float kMaskedScore = -1e30f;
+
+}  // namespace vfkv

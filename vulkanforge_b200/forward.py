@@ -1,0 +1,143 @@
+"""The forward pass's view of the hot path: ``run_*`` dispatch helpers and the
+``step_*`` executor steps of VulkanForge, bound to the CUDA library.
+
+Mirrors, name for name:
+  src/backend/vulkan/forward/runs.rs      run_kv_store_fp8, run_kv_copy_fp16,
+                                          run_scalar_attn, run_flash_attn_split_reduce
+  src/backend/vulkan/forward/executor/attention.rs   step_kv_write, step_attention,
+                                          b_step_kv_write
+
+Arguments that are Vulkan plumbing in the reference (device, registry, command
+buffer, descriptor sets) collapse into the context and a CUDA stream.  Buffers
+are device addresses: ints, or anything with ``data_ptr()``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from .kv_cache import Context, KvCache, Workspace, ptr, sliding_kv_start
+
+
+class CudaForward:
+    def __init__(self, ctx: Context, kv_cache: KvCache, n_heads: int, workspace: Optional[Workspace] = None,
+                 *, sliding_window: int = 0, sliding_layers=None, kv_read_layer=None,
+                 attn_scale: Optional[float] = None, softcap: float = 0.0, n_splits: int = 0,
+                 max_batch: int = 1, max_splits: int = 64, stream=None):
+        self.ctx = ctx
+        self.kv_cache = kv_cache
+        self.n_heads = n_heads
+        self.stream = stream
+        self.sliding_window = sliding_window
+        self.sliding_layers = set(sliding_layers or ())
+        self.kv_read_layer = dict(kv_read_layer or {})
+        # forward/setup.rs:786 -- 1/sqrt(head_dim) unless the model overrides it (runs.rs:1483-1489)
+        self.attn_scale = attn_scale if attn_scale is not None else 1.0 / float(kv_cache.config.head_dim) ** 0.5
+        self.softcap = softcap
+        self.n_splits = n_splits
+        hd = max([kv_cache.config.head_dim] + list(kv_cache.config.per_layer_head_dim or []))
+        self.workspace = workspace or Workspace(ctx, max_batch, n_heads, hd, max_splits)
+        self._L = ctx._lib
+
+    # ---- raw dispatch helpers ------------------------------------------------
+    def run_kv_store_fp8(self, src, dst, n_elements: int, dst_byte_offset: int, label: str = "kv_store_fp8"):
+        """runs.rs:2437-2478"""
+        self.ctx.check(self._L.vfkv_kv_store_fp8(self.ctx.handle, ptr(src), ptr(dst), n_elements,
+                                                 dst_byte_offset, self.stream))
+
+    def run_kv_copy_fp16(self, src, dst, n_elements: int, dst_byte_offset: int, label: str = "kv_copy_fp16"):
+        """runs.rs:2389-2430"""
+        self.ctx.check(self._L.vfkv_kv_copy_fp16(self.ctx.handle, ptr(src), ptr(dst), n_elements,
+                                                 dst_byte_offset, self.stream))
+
+    def run_kv_fp8_to_f16(self, src, dst, n_elements: int):
+        """the convert pre-pass inside run_flash_attn_cm_gemma_rs, runs.rs:1103-1137"""
+        self.ctx.check(self._L.vfkv_kv_fp8_to_f16(self.ctx.handle, ptr(src), ptr(dst), n_elements, self.stream))
+
+    # ---- routing helpers (forward/arch/gemma4.rs) ------------------------------
+    def gemma4_kv_read_layer(self, layer: int) -> int:
+        """gemma4.rs:27-49: publisher layer for a KV subscriber, else the layer itself."""
+        return self.kv_read_layer.get(layer, layer)
+
+    def gemma4_kv_start(self, layer: int, position: int) -> int:
+        """gemma4.rs:59-73"""
+        if layer in self.sliding_layers and self.sliding_window:
+            return sliding_kv_start(position, self.sliding_window)
+        return 0
+
+    # ---- attention -------------------------------------------------------------
+    def run_flash_attn_split_reduce(self, q, out, layer: int, position: int, n_tiles: int, kv_layer: int,
+                                    kv_start: int, slot: int = 0):
+        """runs.rs:1463-1571.  ``n_tiles`` is the split count (0 = choose)."""
+        self.ctx.check(self._L.vfkv_attend(self.kv_cache.handle, self.workspace.handle, layer, kv_layer,
+                                           ptr(q), ptr(out), self.n_heads, slot, position + 1, kv_start,
+                                           self.attn_scale, self.softcap, n_tiles, self.stream))
+
+    def run_scalar_attn(self, q, out, layer: int, position: int, slot: int = 0):
+        """runs.rs:722-821: kv_layer / kv_start routing, then attention at every length."""
+        kv_layer = self.gemma4_kv_read_layer(layer)
+        kv_start = self.gemma4_kv_start(layer, position)
+        self.run_flash_attn_split_reduce(q, out, layer, position, self.n_splits, kv_layer, kv_start, slot)
+
+    # ---- executor steps ----------------------------------------------------------
+    def step_kv_write(self, layer: int, k_src, v_src, position: int, slot: int = 0):
+        """executor/attention.rs:546-596 (one token)."""
+        self.ctx.check(self._L.vfkv_append(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src), 1, slot,
+                                           position, self.stream))
+
+    def b_step_kv_write(self, layer: int, k_src, v_src, seq_len: int, base_pos: int, slot: int = 0):
+        """executor/attention.rs:2134-2190 (a prefill chunk of seq_len tokens)."""
+        self.ctx.check(self._L.vfkv_append(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src), seq_len, slot,
+                                           base_pos, self.stream))
+
+    def step_attention(self, layer: int, q, attn_out, position: int, slot: int = 0):
+        """executor/attention.rs:599-626"""
+        self.run_scalar_attn(q, attn_out, layer, position, slot)
+
+    # ---- batched forms (independent sequences; no counterpart in the single-stream reference) ----
+    def step_kv_write_batch(self, layer: int, k_src, v_src, slot_ids, positions, n_seqs: int):
+        self.ctx.check(self._L.vfkv_append_batch(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src),
+                                                 ptr(slot_ids), ptr(positions), n_seqs, self.stream))
+
+    def step_attention_batch(self, layer: int, q, attn_out, slot_ids, seq_lens, kv_starts, n_seqs: int,
+                             max_seq_len_hint: int = 0, kv_layer: Optional[int] = None):
+        kv_layer = self.gemma4_kv_read_layer(layer) if kv_layer is None else kv_layer
+        self.ctx.check(self._L.vfkv_attend_batch(self.kv_cache.handle, self.workspace.handle, layer, kv_layer,
+                                                 ptr(q), ptr(attn_out), self.n_heads, ptr(slot_ids),
+                                                 ptr(seq_lens), ptr(kv_starts), n_seqs, max_seq_len_hint,
+                                                 self.attn_scale, self.softcap, self.n_splits, self.stream))
+
+    def decode_step(self, layer: int, q, k_src, v_src, attn_out, slot_ids, positions, n_seqs: int,
+                    max_seq_len_hint: int = 0):
+        """KvWrite then Attention for one token per sequence (layer_plan.rs:472-483)."""
+        window = self.sliding_window if layer in self.sliding_layers else 0
+        self.ctx.check(self._L.vfkv_decode_step(self.kv_cache.handle, self.workspace.handle, layer, ptr(q),
+                                                ptr(k_src), ptr(v_src), ptr(attn_out), self.n_heads,
+                                                ptr(slot_ids), ptr(positions), n_seqs, max_seq_len_hint,
+                                                window, self.attn_scale, self.softcap, self.n_splits,
+                                                self.stream))
+
+    def decode_token_host(self, h_q, h_k, h_v, h_out, h_positions, n_seqs: int, h_slot_ids=None):
+        """forward_token's boundary (forward/decode.rs:567-626) for this path: host buffers in and out."""
+        import ctypes as C
+        n_layers = self.kv_cache.config.n_layers
+        win = None
+        if self.sliding_layers and self.sliding_window:
+            win = (C.c_uint32 * n_layers)(*[self.sliding_window if l in self.sliding_layers else 0
+                                            for l in range(n_layers)])
+        self.ctx.check(self._L.vfkv_decode_token_host(
+            self.kv_cache.handle, self.workspace.handle, ptr(h_q), ptr(h_k), ptr(h_v), ptr(h_out), self.n_heads,
+            ptr(h_slot_ids), ptr(h_positions), n_seqs, C.cast(win, C.c_void_p) if win is not None else None,
+            self.attn_scale, self.softcap, self.n_splits, self.stream))
+
+    # ---- sequence-dimension sharding ---------------------------------------------
+    def attend_partial(self, layer: int, q, pos_begin: int, pos_end: int, m, l, o, slot: int = 0,
+                       kv_layer: Optional[int] = None):
+        kv_layer = self.gemma4_kv_read_layer(layer) if kv_layer is None else kv_layer
+        self.ctx.check(self._L.vfkv_attend_partial(self.kv_cache.handle, self.workspace.handle, layer, kv_layer,
+                                                   ptr(q), self.n_heads, slot, pos_begin, pos_end,
+                                                   self.attn_scale, self.softcap, self.n_splits, ptr(m), ptr(l),
+                                                   ptr(o), self.stream))
+
+    def merge_partials(self, m, l, o, n_parts: int, n_rows: int, head_dim: int, out):
+        self.ctx.check(self._L.vfkv_merge_partials(self.ctx.handle, ptr(m), ptr(l), ptr(o), n_parts, n_rows,
+                                                   head_dim, ptr(out), self.stream))
