@@ -87,8 +87,9 @@ def test_raw_pointer_entry_matches(ctx, impl):
     ws = vf.Workspace(ctx, 1, hq, d, 16)
     try:
         out = torch.zeros(hq, d, device="cuda")
+        dq, dk, dv = to_dev(q), to_dev(k), to_dev(v)     # keep the tensors alive across the call
         ctx.check(ctx._lib.vfkv_flash_attn_split_reduce(
-            ctx.handle, ws.handle, to_dev(q).data_ptr(), to_dev(k).data_ptr(), to_dev(v).data_ptr(),
+            ctx.handle, ws.handle, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             out.data_ptr(), oracle.F32, hq, hkv, d, L, L, 1.0 / np.sqrt(d), 0, 0.0, 4, None))
         torch.cuda.synchronize()
         check(out.cpu().numpy(), oracle.attention_ref(q, k, v, oracle.F32, hq, hkv, d, L), oracle.F32)
