@@ -181,6 +181,37 @@ int32_t vfkv_flash_attn_split_reduce(vfkv_ctx *ctx, vfkv_workspace *ws, const fl
                                      float scale, uint32_t kv_start, float softcap,
                                      uint32_t n_splits, void *stream);
 
+/* The same attention on raw buffers for hosts that may not allocate device
+ * memory while they run (an engine whose VRAM is one arena sized at start-up, a
+ * latency-critical thread that cannot afford cudaMalloc's implicit device
+ * synchronisation, a process whose memory budget belongs to someone else).  It
+ * has no counterpart in the reference; it exists so such a host can use the
+ * path without a vfkv_ctx or vfkv_workspace, both of which allocate.
+ *   - The split-K scratch lives in a fixed device array inside the library
+ *     (vfkv_noalloc_scratch_bytes(), about 2 MiB, held by every GPU that loads
+ *     the library until the process exits).  The call is refused with
+ *     VFKV_ERR_UNSUPPORTED when n_heads * n_splits * (head_dim + 2) exceeds
+ *     524288 floats.  n_splits = 0 means 1.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called, here or in
+ *     the kernels it launches.  It always runs the CUDA-core kernels.
+ *   - It works on the calling thread's current device.  The first call on each
+ *     device looks up the array's device address (a one-time set-up under a
+ *     lock); make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous
+ *     call's contents; the only word that must start at zero is cleared on the
+ *     stream at the start of every call.  Two calls whose GPU work can overlap
+ *     (different streams, or different threads) race on it: serialise them.
+ *   - Errors: the return code, and vfkv_noalloc_last_error() for the text
+ *     (per calling thread). */
+int32_t vfkv_flash_attn_split_reduce_noalloc(const float *d_q, const void *d_k, const void *d_v,
+                                             float *d_out, uint32_t dtype, uint32_t n_heads,
+                                             uint32_t n_kv_heads, uint32_t head_dim,
+                                             uint32_t seq_len, uint32_t max_seq, float scale,
+                                             uint32_t kv_start, float softcap, uint32_t n_splits,
+                                             void *stream);
+const char *vfkv_noalloc_last_error(void);
+uint64_t vfkv_noalloc_scratch_bytes(void);
+
 /* ---------------------------------------------------------------------- */
 /* workspace: the split-K partials                                          */
 /* ---------------------------------------------------------------------- */

@@ -62,6 +62,10 @@ SIGNATURES = {
     "vfkv_kv_fp8_to_f16": (i32, [vp, vp, vp, u64, vp]),
     "vfkv_flash_attn_split_reduce": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32,
                                            u32, f32, u32, vp]),
+    "vfkv_flash_attn_split_reduce_noalloc": (i32, [vp, vp, vp, vp, u32, u32, u32, u32, u32, u32, f32, u32, f32,
+                                                   u32, vp]),
+    "vfkv_noalloc_last_error": (C.c_char_p, []),
+    "vfkv_noalloc_scratch_bytes": (u64, []),
     "vfkv_workspace_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
     "vfkv_workspace_destroy": (i32, [vp]),
     "vfkv_workspace_bytes": (u64, [vp]),
