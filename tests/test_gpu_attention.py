@@ -131,7 +131,8 @@ def test_golden_fixture_cases(ctx, impl):
 
 
 SHAPES = [  # hq, hkv, d
-    (32, 8, 128), (64, 8, 128), (16, 8, 256), (8, 8, 64), (8, 1, 128), (40, 8, 128), (16, 2, 512), (4, 2, 64)]
+    (32, 8, 128), (64, 8, 128), (16, 8, 256), (8, 8, 64), (8, 1, 128), (40, 8, 128), (16, 2, 512), (4, 2, 64),
+    (32, 2, 128), (24, 2, 256), (12, 1, 64)]
 
 
 @pytest.mark.parametrize("dtype", [vf.KvDtype.F32, vf.KvDtype.F16, vf.KvDtype.F8])

@@ -44,7 +44,7 @@ struct DeviceGuard {
 inline cudaStream_t as_stream(void *s) { return static_cast<cudaStream_t>(s); }
 
 // Views of one layer for the kernels.
-KvView make_view(const vfkv_cache *c, uint32_t kv_layer)
+KvView make_view(vfkv_cache *c, uint32_t kv_layer)
 {
     const KvCache &kv = c->kv;
     KvView v;
@@ -61,6 +61,18 @@ KvView make_view(const vfkv_cache *c, uint32_t kv_layer)
         v.k_scales = kv.k_scales + kv.scale_offset(kv_layer, 0, 0);
         v.v_scales = kv.v_scales + kv.scale_offset(kv_layer, 0, 0);
         v.slot_stride_scales = uint64_t(kv.config.max_seq_len) * v.n_kv_heads;
+    }
+    // TMA descriptors are encoded once per layer and reused by every attention call
+    if (c->tm_state.empty()) {
+        c->tm_state.assign(kv.config.n_layers, 0);
+        c->tm_k.resize(kv.config.n_layers);
+        c->tm_v.resize(kv.config.n_layers);
+    }
+    if (c->tm_state[kv_layer] == 0)
+        c->tm_state[kv_layer] = encode_layer_maps(c->ctx, v, c->tm_k[kv_layer].b, c->tm_v[kv_layer].b) ? 1 : 2;
+    if (c->tm_state[kv_layer] == 1) {
+        v.tm_k = c->tm_k[kv_layer].b;
+        v.tm_v = c->tm_v[kv_layer].b;
     }
     return v;
 }
@@ -414,13 +426,16 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->part_m), parts * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->part_l), parts * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->d_u32), u32_bytes);
+    ws->n_counters = rows;
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->counters), rows * 4);
+    if (e == cudaSuccess) e = cudaMemset(ws->counters, 0, rows * 4);
     if (e != cudaSuccess) {
-        cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32);
+        cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->counters);
         cudaGetLastError();
         delete ws;
         return check_cuda(ctx, e, "vfkv_workspace_create: cudaMalloc");
     }
-    ws->bytes = ofl + parts * 8 + u32_bytes;
+    ws->bytes = ofl + parts * 8 + u32_bytes + rows * 4;
     *out = ws;
     return VFKV_OK;
 }
@@ -429,7 +444,7 @@ int32_t vfkv_workspace_destroy(vfkv_workspace *ws)
 {
     if (!ws) return VFKV_OK;
     DeviceGuard g(ws->ctx->device);
-    cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32);
+    cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->counters);
     cudaFree(ws->stage_in); cudaFree(ws->stage_out);
     delete ws;
     return VFKV_OK;

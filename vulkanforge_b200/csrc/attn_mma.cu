@@ -1,13 +1,698 @@
-// Tensor-core split-K decode attention (placeholder until the kernel lands).
+// Split-K GQA decode attention for FP8 (E4M3) and F16 caches: TMA-fed, tensor-core
+// products, fused log-sum-exp merge.
+//
+// Replaces vk_shaders/flash_attn_split.comp + flash_attn_reduce.comp (and
+// flash_attn.comp for short sequences) for the shapes it covers; the CUDA-core
+// kernel in attn_generic.cu covers the rest.  Same math as the shaders
+// (score = scale * q.k, masked lanes excluded, p = exp(score - max), running
+// (max, sum, acc) merge of partials), different organisation:
+//
+//   CTA  = (split, kv-head, sequence); the q-heads that share the kv-head are
+//          the M rows of the tensor-core tile, so K and V stream through once
+//          per kv-head (the shader streams them once per q-head).
+//   warp = owns a private ring of TMA stages.  Lane 0 issues
+//          cp.async.bulk.tensor.2d boxes of [TP positions x 128 bytes]
+//          (128-byte swizzle) for K and V and the warp waits on its own
+//          mbarrier; there is no CTA-wide synchronisation while streaming.
+//   FP8  : mma.sync.m16n8k32.e4m3 straight on the cache bytes -- the
+//          dequantisation is the tensor core's exact E4M3 product.  Q is split
+//          into two E4M3 terms (rows 0-7 and 8-15 of the M tile) and so is P,
+//          which keeps operand rounding near 2^-10.  V is transposed for the
+//          P.V product in registers (prmt).
+//   F16  : mma.sync.m16n8k16.f16 with ldmatrix / ldmatrix.trans; with up to 8 q-heads per
+//          kv-head Q and P are likewise split into two half-precision terms.
+//   tail : warp partials merge in shared memory; the last CTA of a
+//          (sequence, kv-head) to finish merges the split partials with the
+//          reduce shader's update (flash_attn_reduce.comp:51-80), so there is no
+//          second launch.
+//
+// Every mbarrier wait is bounded: on expiry the kernel raises bit 0 of the
+// context's status word and returns without touching the output.
+#include <cuda.h>
+
 #include "attn_params.cuh"
+#include "fp8_codec.cuh"
 
 namespace vfkv {
 
-bool attn_mma_supported(const AttnArgs &) { return false; }
+namespace {
 
-int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *, const AttnArgs &, uint32_t, cudaStream_t)
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kPScale = 256.0f;     // FP8 P operand is 256*p: keeps small p out of E4M3's subnormals
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
-    return set_error(ctx, VFKV_ERR_UNSUPPORTED, "tensor-core attention is not built");
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits at most about one second; false means the data never arrived.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u && global_timer_ns() - t0 > 1000000000ull) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y,
+                                            uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2,
+                                                  uint32_t &r3)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
+{
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Two values -> (hi, lo) E4M3 pairs with hi + lo ~= value, residual taken in half precision.
+__device__ __forceinline__ void split_e4m3x2(float x0, float x1, uint32_t &hi, uint32_t &lo)
+{
+    __half2 h = __floats2half2_rn(x0, x1);
+    uint32_t hb = *reinterpret_cast<uint32_t *>(&h);
+    uint16_t h8;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(h8) : "r"(hb));
+    uint32_t back;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(back) : "h"(h8));
+    __half2 r = __hsub2(h, *reinterpret_cast<__half2 *>(&back));
+    uint32_t rb = *reinterpret_cast<uint32_t *>(&r);
+    uint16_t l8;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(l8) : "r"(rb));
+    hi = h8;
+    lo = l8;
+}
+
+// Two values -> (hi, lo) half2 pairs with hi + lo == value to about 2^-22.
+__device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t &hi, uint32_t &lo)
+{
+    __half2 h = __floats2half2_rn(x0, x1);
+    float2 hf = __half22float2(h);
+    hi = *reinterpret_cast<uint32_t *>(&h);
+    lo = f32x2_to_f16x2(x0 - hf.x, x1 - hf.y);
+}
+
+struct MmaParams {
+    AttnParams a;
+    uint32_t *counters;     // one ticket per (sequence, kv-head); zero between launches
+};
+
+// Shape-dependent constants.
+template <int DT, int D> struct Shape {
+    static constexpr int ES = DT == VFKV_F8 ? 1 : 2;
+    static constexpr int TP = DT == VFKV_F8 ? 32 : 16;        // positions per tile
+    static constexpr int NB = TP / 8;                         // 8-position blocks per tile
+    static constexpr int NC = D * ES / 128;                   // 128-byte column chunks per head slice
+    static constexpr int KSTEPS = D * ES / 32;                // 32 bytes of the head slice per QK step
+    static constexpr int NDB = D / 8;                         // 8-dim blocks of the output
+    static constexpr int TILE_BYTES = TP * 128 * NC;          // K (or V) tile
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int RING_BYTES = kWarps * kStages * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// Byte address of 16-byte unit `unit` of row `row` in chunk `chunk` of a tile (128-byte swizzle:
+// the unit index is XORed with the row's low three bits; tiles are 1024-byte aligned).
+template <int TP>
+__device__ __forceinline__ uint32_t tile_addr(uint32_t tile, uint32_t chunk, uint32_t row, uint32_t unit)
+{
+    return tile + chunk * (TP * 128) + row * 128 + ((unit ^ (row & 7u)) << 4);
+}
+
+template <int DT, int D, bool ROWS2>
+__global__ void __launch_bounds__(kWarps * 32)
+attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const MmaParams mp)
+{
+    using S = Shape<DT, D>;
+    constexpr int TP = S::TP, NB = S::NB, NC = S::NC, KSTEPS = S::KSTEPS, NDB = S::NDB;
+    constexpr bool FP8 = DT == VFKV_F8;
+    constexpr int RS = (!FP8 && ROWS2) ? 2 : 1;          // logical score rows per thread
+    // With at most 8 q-heads per kv-head the M tile has room for a second term: rows 0-7 carry the
+    // high part of Q (and of P), rows 8-15 the low part, and their products are summed in f32.
+    constexpr bool SPLIT = FP8 || !ROWS2;
+    const AttnParams &p = mp.a;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    const uint32_t bars = ring + S::RING_BYTES;           // kWarps*kStages mbarriers, 8 bytes each
+    __shared__ uint32_t s_flag;
+
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t gid = lane >> 2, tig = lane & 3;
+    const uint32_t g = p.group;
+
+    uint32_t slot, start, len, begin, end;
+    seq_range(p, s, &slot, &start, &len);
+    split_range(start, len, p.n_splits, split, 32, &begin, &end);
+    const uint32_t n_tiles = (end - begin + TP - 1) / TP;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kWarps * kStages; ++i) mbar_init(bars + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_flag = 0;
+    }
+    __syncthreads();
+
+    // ---- this warp's pipeline -------------------------------------------------------------
+    const uint32_t my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
+    const uint32_t stage0 = ring + warp * kStages * S::STAGE_BYTES;
+    const uint32_t bar0 = bars + 8 * warp * kStages;
+    const int32_t x0 = int32_t(kvh * D * S::ES);
+    const int64_t row0 = int64_t(slot) * p.max_seq;
+    auto issue = [&](uint32_t n) {     // lane 0 only: fetch this warp's n-th tile into stage n % kStages
+        const uint32_t st = n % kStages;
+        const uint32_t t0 = begin + (warp + n * kWarps) * TP;
+        const uint32_t bar = bar0 + 8 * st;
+        const uint32_t kt = stage0 + st * S::STAGE_BYTES, vt = kt + S::TILE_BYTES;
+        mbar_expect_tx(bar, S::STAGE_BYTES);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            tma_load_2d(kt + c * TP * 128, &tm_k, x0 + c * 128, int32_t(row0 + t0), bar);
+            tma_load_2d(vt + c * TP * 128, &tm_v, x0 + c * 128, int32_t(row0 + t0), bar);
+        }
+    };
+    if (lane == 0) {
+        const uint32_t pre = my_tiles < uint32_t(kStages) ? my_tiles : uint32_t(kStages);
+        for (uint32_t n = 0; n < pre; ++n) issue(n);
+    }
+
+    // ---- Q fragments (A operand), scaled per head by a power of two into [128, 256) --------
+    // FP8: rows 0-7 of the M tile hold the high E4M3 term of heads 0-7, rows 8-15 the low term.
+    // F16: rows are heads 0-15.
+    uint32_t qa[KSTEPS][4];
+    float mult[RS];                      // score multiplier per logical row: scale / q_scale
+    {
+        float qv[RS][KSTEPS][4];         // FP8: [ks][0..3]=d 32ks+4tig.., plus [ks+...] second half below
+        float qv2[RS][KSTEPS][4];
+        // element layout this thread needs: FP8  d = 32ks + 4tig + i  and  32ks + 16 + 4tig + i   (i < 4)
+        //                                   F16  d = 16ks + 2tig + i  and  16ks + 8 + 2tig + i    (i < 2)
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            const uint32_t hrow = gid + 8 * r;
+            const bool hv = hrow < g;
+            const float *qp = p.q + (uint64_t(s) * p.n_q_heads + kvh * g + (hv ? hrow : 0)) * D;
+            float amax = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                if constexpr (FP8) {
+                    float4 a = hv ? *reinterpret_cast<const float4 *>(qp + 32 * ks + 4 * tig) : make_float4(0, 0, 0, 0);
+                    float4 b = hv ? *reinterpret_cast<const float4 *>(qp + 32 * ks + 16 + 4 * tig) : make_float4(0, 0, 0, 0);
+                    qv[r][ks][0] = a.x; qv[r][ks][1] = a.y; qv[r][ks][2] = a.z; qv[r][ks][3] = a.w;
+                    qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = b.z; qv2[r][ks][3] = b.w;
+                } else {
+                    float2 a = hv ? *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * tig) : make_float2(0, 0);
+                    float2 b = hv ? *reinterpret_cast<const float2 *>(qp + 16 * ks + 8 + 2 * tig) : make_float2(0, 0);
+                    qv[r][ks][0] = a.x; qv[r][ks][1] = a.y; qv[r][ks][2] = 0.f; qv[r][ks][3] = 0.f;
+                    qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = 0.f; qv2[r][ks][3] = 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(qv[r][ks][i]), fabsf(qv2[r][ks][i])));
+            }
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            // q_scale = 2^(7 - floor(log2 amax)); exact in both directions
+            int e = int((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+            e = amax > 0.f ? max(-100, min(100, e)) : 7;
+            const float qs = __uint_as_float(uint32_t(7 - e + 127) << 23);
+            const float inv_qs = __uint_as_float(uint32_t(e - 7 + 127) << 23);
+            mult[r] = p.scale * inv_qs;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                if constexpr (FP8) {
+                    uint32_t h01, l01, h23, l23;
+                    split_e4m3x2(qv[r][ks][0] * qs, qv[r][ks][1] * qs, h01, l01);
+                    split_e4m3x2(qv[r][ks][2] * qs, qv[r][ks][3] * qs, h23, l23);
+                    qa[ks][0] = h01 | (h23 << 16);
+                    qa[ks][1] = l01 | (l23 << 16);
+                    split_e4m3x2(qv2[r][ks][0] * qs, qv2[r][ks][1] * qs, h01, l01);
+                    split_e4m3x2(qv2[r][ks][2] * qs, qv2[r][ks][3] * qs, h23, l23);
+                    qa[ks][2] = h01 | (h23 << 16);
+                    qa[ks][3] = l01 | (l23 << 16);
+                } else if constexpr (SPLIT) {
+                    split_f16x2(qv[r][ks][0] * qs, qv[r][ks][1] * qs, qa[ks][0], qa[ks][1]);
+                    split_f16x2(qv2[r][ks][0] * qs, qv2[r][ks][1] * qs, qa[ks][2], qa[ks][3]);
+                } else {
+                    qa[ks][0 + r] = f32x2_to_f16x2(qv[r][ks][0] * qs, qv[r][ks][1] * qs);
+                    qa[ks][2 + r] = f32x2_to_f16x2(qv2[r][ks][0] * qs, qv2[r][ks][1] * qs);
+                }
+            }
+        }
+    }
+
+    // ---- stream the tiles -------------------------------------------------------------------
+    float m[RS], l[RS];
+#pragma unroll
+    for (int r = 0; r < RS; ++r) { m[r] = kMaskedScore; l[r] = 0.f; }
+    float acc[NDB][4];
+#pragma unroll
+    for (int nb = 0; nb < NDB; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f; }
+    bool timed_out = false;
+
+    for (uint32_t n = 0; n < my_tiles; ++n) {
+        const uint32_t st = n % kStages;
+        const uint32_t t0 = begin + (warp + n * kWarps) * TP;
+        const uint32_t kt = stage0 + st * S::STAGE_BYTES, vt = kt + S::TILE_BYTES;
+        if (!mbar_wait_bounded(bar0 + 8 * st, (n / kStages) & 1u)) { timed_out = true; break; }
+        const uint32_t n_valid = min(uint32_t(TP), end - t0);
+
+        // rows at and beyond `end` may hold anything (stale tokens, another slot): zero them in V so
+        // that 0 * garbage cannot become NaN; their scores are masked below.
+        if (n_valid < uint32_t(TP)) {
+            const uint32_t units = (TP - n_valid) * NC * 8;
+            for (uint32_t i = lane; i < units; i += 32) {
+                const uint32_t r = n_valid + i / (NC * 8), c = (i / 8) % NC, u = i % 8;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vt + c * TP * 128 + r * 128 + u * 16), "r"(0u) : "memory");
+            }
+            __syncwarp();
+        }
+
+        // ---- S = Q K^T : M = q rows, N = 8 positions per block, K = 32 bytes of the head slice ----
+        float sc[NB][4];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const uint32_t chunk = ks / 4, u0 = 2 * (ks % 4);
+#pragma unroll
+            for (int jp = 0; jp < NB / 2; ++jp) {
+                const uint32_t mi = lane >> 3, rr = lane & 7;
+                const uint32_t row = 8 * (2 * jp + (mi >> 1)) + rr;
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4(tile_addr<TP>(kt, chunk, row, u0 + (mi & 1)), r0, r1, r2, r3);
+                if constexpr (FP8) {
+                    mma_e4m3(sc[2 * jp], qa[ks], r0, r1);
+                    mma_e4m3(sc[2 * jp + 1], qa[ks], r2, r3);
+                } else {
+                    mma_f16(sc[2 * jp], qa[ks], r0, r1);
+                    mma_f16(sc[2 * jp + 1], qa[ks], r2, r3);
+                }
+            }
+        }
+
+        // ---- softmax bookkeeping in the log2 domain -------------------------------------------
+        // this thread's scores: logical row r, block j, element i  <->  position t0 + 8j + 2tig + i
+        float x[RS][NB][2];
+        float tmax[RS];
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            tmax[r] = kMaskedScore;
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    float v = SPLIT ? (sc[j][i] + sc[j][i + 2]) : sc[j][2 * r + i];
+                    v *= mult[r];
+                    if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
+                    v *= kLog2e;
+                    const bool valid = uint32_t(8 * j + 2 * tig + i) < n_valid;
+                    v = valid ? v : kMaskedScore;
+                    x[r][j][i] = v;
+                    tmax[r] = fmaxf(tmax[r], v);
+                }
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
+            tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
+        }
+        float corr[RS];
+        bool changed = false;
+#pragma unroll
+        for (int r = 0; r < RS; ++r) {
+            const float mn = fmaxf(m[r], tmax[r]);
+            corr[r] = fast_exp2(m[r] - mn);
+            changed |= mn != m[r];
+            m[r] = mn;
+            l[r] *= corr[r];
+        }
+        if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll
+            for (int nb = 0; nb < NDB; ++nb) {
+                acc[nb][0] *= corr[0]; acc[nb][1] *= corr[0];
+                acc[nb][2] *= corr[SPLIT ? 0 : 1]; acc[nb][3] *= corr[SPLIT ? 0 : 1];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RS; ++r)
+#pragma unroll
+            for (int j = 0; j < NB; ++j)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const bool valid = uint32_t(8 * j + 2 * tig + i) < n_valid;
+                    const float pv = valid ? fast_exp2(x[r][j][i] - m[r]) : 0.f;
+                    x[r][j][i] = pv;
+                    l[r] += pv;
+                }
+
+        // ---- O += P V ----------------------------------------------------------------------------
+        if constexpr (FP8) {
+            // A rows 0-7: high term of 256*p, rows 8-15: low term.  K slot 4*tig+i of the first half is
+            // position {2tig, 2tig+1, 8+2tig, 9+2tig}[i], of the second half the same + 16.
+            uint32_t pa[4];
+            {
+                uint32_t h0, l0, h1, l1;
+                split_e4m3x2(x[0][0][0] * kPScale, x[0][0][1] * kPScale, h0, l0);
+                split_e4m3x2(x[0][1][0] * kPScale, x[0][1][1] * kPScale, h1, l1);
+                pa[0] = h0 | (h1 << 16); pa[1] = l0 | (l1 << 16);
+                split_e4m3x2(x[0][2][0] * kPScale, x[0][2][1] * kPScale, h0, l0);
+                split_e4m3x2(x[0][3][0] * kPScale, x[0][3][1] * kPScale, h1, l1);
+                pa[2] = h0 | (h1 << 16); pa[3] = l0 | (l1 << 16);
+            }
+#pragma unroll
+            for (int q = 0; q < D / 32; ++q) {
+                // the four dims 32q + 4*gid + {0..3} of eight positions, transposed so that one register
+                // holds four positions of one dim
+                const uint32_t chunk = q / 4, unit = 2 * (q % 4) + (gid >> 2), wofs = (gid & 3) * 4;
+                uint32_t w[8];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t rbase = 16 * h + 2 * tig;
+                    w[4 * h + 0] = lds32(tile_addr<TP>(vt, chunk, rbase, unit) + wofs);
+                    w[4 * h + 1] = lds32(tile_addr<TP>(vt, chunk, rbase + 1, unit) + wofs);
+                    w[4 * h + 2] = lds32(tile_addr<TP>(vt, chunk, rbase + 8, unit) + wofs);
+                    w[4 * h + 3] = lds32(tile_addr<TP>(vt, chunk, rbase + 9, unit) + wofs);
+                }
+                uint32_t b[2][4];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t lo01 = prmt(w[4 * h], w[4 * h + 1], 0x5140), hi01 = prmt(w[4 * h], w[4 * h + 1], 0x7362);
+                    const uint32_t lo23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x5140), hi23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x7362);
+                    b[h][0] = prmt(lo01, lo23, 0x5410);
+                    b[h][1] = prmt(lo01, lo23, 0x7632);
+                    b[h][2] = prmt(hi01, hi23, 0x5410);
+                    b[h][3] = prmt(hi01, hi23, 0x7632);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mma_e4m3(acc[4 * q + i], pa, b[0][i], b[1][i]);
+            }
+        } else {
+            uint32_t pa[4];
+            if constexpr (SPLIT) {
+                split_f16x2(x[0][0][0], x[0][0][1], pa[0], pa[1]);
+                split_f16x2(x[0][1][0], x[0][1][1], pa[2], pa[3]);
+            } else {
+                pa[0] = f32x2_to_f16x2(x[0][0][0], x[0][0][1]);
+                pa[2] = f32x2_to_f16x2(x[0][1][0], x[0][1][1]);
+                pa[1] = f32x2_to_f16x2(x[RS - 1][0][0], x[RS - 1][0][1]);
+                pa[3] = f32x2_to_f16x2(x[RS - 1][1][0], x[RS - 1][1][1]);
+            }
+#pragma unroll
+            for (int nb = 0; nb < NDB; nb += 2) {
+                const uint32_t mi = lane >> 3, rr = lane & 7;
+                const uint32_t row = 8 * (mi & 1) + rr, blk = nb + (mi >> 1);
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4_trans(tile_addr<TP>(vt, blk / 8, row, blk % 8), r0, r1, r2, r3);
+                mma_f16(acc[nb], pa, r0, r1);
+                mma_f16(acc[nb + 1], pa, r2, r3);
+            }
+        }
+
+        // ---- refill this stage -----------------------------------------------------------------
+        __syncwarp();
+        if (lane == 0 && n + kStages < my_tiles) {
+            fence_proxy_async();
+            issue(n + kStages);
+        }
+    }
+
+    if (timed_out) {
+        if (lane == 0) { atomicOr(p.status, 1u); s_flag = 1; }
+    }
+    __syncthreads();          // all tiles consumed (or abandoned): the ring is free for the merge
+    if (s_flag) return;
+
+    // ---- merge the warps' partials in shared memory ---------------------------------------------
+    constexpr int NH = (FP8 || !ROWS2) ? 8 : 16;              // head rows this CTA can hold
+    float *sm_o = reinterpret_cast<float *>(ring_ptr);        // [kWarps][NH][D]
+    float *sm_m = sm_o + kWarps * NH * D;                     // [kWarps][NH]
+    float *sm_l = sm_m + kWarps * NH;                         // [kWarps][NH]
+#pragma unroll
+    for (int r = 0; r < RS; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        if (tig == 0) { sm_m[warp * NH + gid + 8 * r] = m[r]; sm_l[warp * NH + gid + 8 * r] = l[r]; }
+    }
+#pragma unroll
+    for (int nb = 0; nb < NDB; ++nb) {
+        if constexpr (FP8) {
+            // column n of block nb is dim 32*(nb/4) + 4n + nb%4 (see the V transpose above)
+            const uint32_t d0 = 32 * (nb / 4) + 4 * (2 * tig) + (nb % 4);
+            float *o = sm_o + (warp * NH + gid) * D;
+            o[d0] = (acc[nb][0] + acc[nb][2]) * (1.0f / kPScale);
+            o[d0 + 4] = (acc[nb][1] + acc[nb][3]) * (1.0f / kPScale);
+        } else {
+            const uint32_t d0 = 8 * nb + 2 * tig;
+            float *o = sm_o + (warp * NH + gid) * D;
+            if constexpr (SPLIT) {
+                o[d0] = acc[nb][0] + acc[nb][2]; o[d0 + 1] = acc[nb][1] + acc[nb][3];
+            } else {
+                o[d0] = acc[nb][0]; o[d0 + 1] = acc[nb][1];
+                o[8 * D + d0] = acc[nb][2]; o[8 * D + d0 + 1] = acc[nb][3];
+            }
+        }
+    }
+    __syncthreads();
+
+    const bool direct = p.n_splits == 1;
+    for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
+        const uint32_t j = idx / D, d = idx % D;
+        float M = kMaskedScore;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) M = fmaxf(M, sm_m[w * NH + j]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float f = fast_exp2(sm_m[w * NH + j] - M);
+            L = fmaf(sm_l[w * NH + j], f, L);
+            O = fmaf(sm_o[(w * NH + j) * D + d], f, O);
+        }
+        const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
+        const float m_nat = M * kLn2;                          // partials carry natural-log maxima
+        if (direct) {
+            if (p.out) p.out[row * D + d] = L > 0.f ? O * (1.0f / L) : 0.f;
+            if (p.out_o) {
+                p.out_o[row * D + d] = O;
+                if (d == 0) { p.out_m[row] = m_nat; p.out_l[row] = L; }
+            }
+        } else {
+            const uint64_t pi = row * p.n_splits + split;
+            p.part_o[pi * D + d] = O;
+            if (d == 0) { p.part_m[pi] = m_nat; p.part_l[pi] = L; }
+        }
+    }
+    if (direct) return;
+
+    // ---- the last CTA of this (sequence, kv-head) merges the splits ---------------------------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(&mp.counters[s * p.n_kv_heads + kvh], 1u);
+        s_flag = ticket == p.n_splits - 1 ? 2u : 0u;
+    }
+    __syncthreads();
+    if (s_flag != 2u) return;
+    __threadfence();
+    for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
+        const uint32_t j = idx / D, d = idx % D;
+        const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
+        float gmax = kMaskedScore, gsum = 0.f, a = 0.f;
+        for (uint32_t i = 0; i < p.n_splits; ++i) {            // flash_attn_reduce.comp:57-75
+            const uint64_t pi = row * p.n_splits + i;
+            const float tm = __ldcg(p.part_m + pi), ts = __ldcg(p.part_l + pi);
+            const float nm = fmaxf(gmax, tm);
+            const float ko = __expf(gmax - nm), kn = __expf(tm - nm);
+            a = a * ko + __ldcg(p.part_o + pi * D + d) * kn;
+            gsum = gsum * ko + ts * kn;
+            gmax = nm;
+        }
+        if (p.out) p.out[row * D + d] = gsum > 0.f ? a * (1.0f / gsum) : 0.f;
+        if (p.out_o) {
+            p.out_o[row * D + d] = a;
+            if (d == 0) { p.out_m[row] = gmax; p.out_l[row] = gsum; }
+        }
+    }
+    if (threadIdx.x == 0) mp.counters[s * p.n_kv_heads + kvh] = 0u;   // ready for the next launch
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// A byte-typed 2-D view of one layer's slab(s): inner = one token row, outer = slots * max_seq rows.
+bool encode_map(vfkv_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows)
+{
+    if (!ctx->encode_tiled) return false;
+    cuuint64_t dims[2] = {row_bytes, rows};
+    cuuint64_t strides[1] = {row_bytes};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled)(
+        out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+template <int DT, int D, bool ROWS2>
+int32_t launch_t(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
+{
+    using S = Shape<DT, D>;
+    auto kern = attn_split_mma_kernel<DT, D, ROWS2>;
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tensor-core attention)");
+        configured[ctx->device & 63] = true;
+    }
+    dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
+    {
+        ProfScope ps(ctx, VFKV_PROF_FA_SPLIT, st);
+        kern<<<grid, kWarps * 32, S::SMEM_BYTES, st>>>(tk, tv, mp);
+    }
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "tensor-core attention launch");
+}
+
+}  // namespace
+
+bool attn_mma_supported(const AttnArgs &a)
+{
+    if (a.kv.k_scales || a.kv.v_scales) return false;
+    if (a.kv.n_kv_heads == 0 || a.n_q_heads % a.kv.n_kv_heads != 0) return false;
+    const uint32_t g = a.n_q_heads / a.kv.n_kv_heads, D = a.kv.head_dim;
+    if (uint64_t(a.kv.n_slots) * a.kv.max_seq >= (1ull << 31)) return false;
+    if ((reinterpret_cast<uintptr_t>(a.kv.k) | reinterpret_cast<uintptr_t>(a.kv.v)) % 16 != 0) return false;
+    if (reinterpret_cast<uintptr_t>(a.q) % 16 != 0) return false;
+    if (a.kv.dtype == VFKV_F8) return g <= 8 && (D == 128 || D == 256);
+    if (a.kv.dtype == VFKV_F16) return g <= 16 && (D == 64 || D == 128 || D == 256);
+    return false;
+}
+
+int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits, cudaStream_t st)
+{
+    if (!ctx->encode_tiled) return set_error(ctx, VFKV_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable in this driver");
+    const uint32_t D = a.kv.head_dim, es = a.kv.dtype == VFKV_F8 ? 1 : 2;
+    const uint64_t row_bytes = uint64_t(a.kv.n_kv_heads) * D * es;
+    const uint64_t rows = uint64_t(a.kv.n_slots) * a.kv.max_seq;
+    if (a.kv.n_slots > 1 && a.kv.slot_stride_bytes != uint64_t(a.kv.max_seq) * row_bytes)
+        return set_error(ctx, VFKV_ERR_INVALID, "slots must be contiguous slabs");
+    const uint32_t box_rows = a.kv.dtype == VFKV_F8 ? 32 : 16;
+    CUtensorMap tk, tv;
+    if (a.kv.tm_k && a.kv.tm_v) {
+        tk = *static_cast<const CUtensorMap *>(a.kv.tm_k);
+        tv = *static_cast<const CUtensorMap *>(a.kv.tm_v);
+    } else if (!encode_map(ctx, &tk, a.kv.k, row_bytes, rows, box_rows) ||
+               !encode_map(ctx, &tv, a.kv.v, row_bytes, rows, box_rows)) {
+        return set_error(ctx, VFKV_ERR_CUDA, "cuTensorMapEncodeTiled failed");
+    }
+    MmaParams mp;
+    mp.a = make_params(ctx, ws, a, n_splits);
+    mp.counters = ws ? ws->counters : nullptr;
+    if (n_splits > 1 && !mp.counters) return set_error(ctx, VFKV_ERR_INVALID, "workspace has no ticket counters");
+    if (n_splits > 1 && uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads > ws->n_counters)
+        return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
+    const uint32_t g = a.n_q_heads / a.kv.n_kv_heads;
+    if (a.kv.dtype == VFKV_F8) {
+        if (D == 128) return launch_t<VFKV_F8, 128, false>(ctx, tk, tv, mp, st);
+        if (D == 256) return launch_t<VFKV_F8, 256, false>(ctx, tk, tv, mp, st);
+    } else {
+        const bool r2 = g > 8;
+        if (D == 64) return r2 ? launch_t<VFKV_F16, 64, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 64, false>(ctx, tk, tv, mp, st);
+        if (D == 128) return r2 ? launch_t<VFKV_F16, 128, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 128, false>(ctx, tk, tv, mp, st);
+        if (D == 256) return r2 ? launch_t<VFKV_F16, 256, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 256, false>(ctx, tk, tv, mp, st);
+    }
+    return set_error(ctx, VFKV_ERR_UNSUPPORTED, "shape outside the tensor-core attention kernel");
+}
+
+// Pre-encodes the two tensor maps of one layer of a cache (host memory; reused by every call).
+bool encode_layer_maps(vfkv_ctx *ctx, const KvView &v, void *tm_k_out, void *tm_v_out)
+{
+    if (v.dtype == VFKV_F32) return false;
+    const uint32_t es = v.dtype == VFKV_F8 ? 1 : 2;
+    const uint64_t row_bytes = uint64_t(v.n_kv_heads) * v.head_dim * es;
+    if (row_bytes < 128 || (uint64_t(v.head_dim) * es) % 128 != 0) return false;
+    const uint64_t rows = uint64_t(v.n_slots) * v.max_seq;
+    const uint32_t box_rows = v.dtype == VFKV_F8 ? 32 : 16;
+    return encode_map(ctx, static_cast<CUtensorMap *>(tm_k_out), v.k, row_bytes, rows, box_rows) &&
+           encode_map(ctx, static_cast<CUtensorMap *>(tm_v_out), v.v, row_bytes, rows, box_rows);
 }
 
 }  // namespace vfkv

@@ -30,6 +30,10 @@ struct vfkv_ctx {
 struct vfkv_cache {
     vfkv_ctx *ctx = nullptr;
     vfkv::KvCache kv;
+    // per-layer TMA descriptors of the K and V slabs, encoded on first use (128 bytes each)
+    struct alignas(64) TmapBytes { unsigned char b[128]; };
+    std::vector<TmapBytes> tm_k, tm_v;
+    std::vector<unsigned char> tm_state;   // 0 = not tried, 1 = ready, 2 = not encodable
 };
 
 struct vfkv_workspace {
@@ -39,6 +43,8 @@ struct vfkv_workspace {
     float *part_m = nullptr;    // [seq][q_head][split]
     float *part_l = nullptr;    // [seq][q_head][split]
     uint32_t *d_u32 = nullptr;  // staging for scalar-call slot/len/start and host-step arrays
+    uint32_t *counters = nullptr;   // split tickets of the fused merge, one per (sequence, kv-head); zero at rest
+    uint64_t n_counters = 0;
     uint64_t bytes = 0;
     // staging for vfkv_decode_token_host, grown on first use
     float *stage_in = nullptr;
@@ -64,6 +70,8 @@ struct KvView {
     uint32_t dtype = 0;
     uint32_t n_kv_heads = 0;
     uint32_t head_dim = 0;
+    const void *tm_k = nullptr;        // pre-encoded CUtensorMap of k / v (host memory), or null
+    const void *tm_v = nullptr;
 };
 
 // Per-sequence arguments: either device arrays (batch calls) or scalars.
@@ -138,6 +146,7 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile);
 int32_t launch_attn_generic(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
                             cudaStream_t st);
 bool attn_mma_supported(const AttnArgs &a);
+bool encode_layer_maps(vfkv_ctx *ctx, const KvView &v, void *tm_k_out, void *tm_v_out);
 int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
                         cudaStream_t st);
 // merges ws partials [seq][head][split] into a.out (normalised) or a.out_{m,l,o}
