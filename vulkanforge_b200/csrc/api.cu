@@ -594,13 +594,23 @@ int32_t vfkv_decode_step(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer, 
     vfkv_ctx *ctx = cache->ctx;
     if (!d_q || !d_k || !d_v || !d_out || !d_positions)
         return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_step: null argument");
-    rc = vfkv_append_batch(cache, layer, d_k, d_v, d_slot_ids, d_positions, n_seqs, stream);
-    if (rc) return rc;
+    if ((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) % 16 != 0)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_step: K and V inputs must be 16-byte aligned");
     AttnArgs a;
     a.kv = make_view(cache, layer);
     a.seq.n_seqs = n_seqs; a.seq.slot_ids = d_slot_ids; a.seq.positions = d_positions; a.seq.window = window;
     a.seq.max_len_hint = max_seq_len_hint;
     a.q = d_q; a.out = d_out; a.n_q_heads = n_q_heads; a.scale = scale; a.softcap = softcap; a.n_splits = n_splits;
+    // The tensor-core kernel stores the new rows itself (one launch per layer); otherwise the
+    // append runs first, as KvWrite precedes Attention in the reference's layer plan.
+    const bool fused = ctx->attn_impl != 1 && attn_mma_supported(a);
+    if (fused) {
+        a.k_new = d_k;
+        a.v_new = d_v;
+    } else {
+        rc = vfkv_append_batch(cache, layer, d_k, d_v, d_slot_ids, d_positions, n_seqs, stream);
+        if (rc) return rc;
+    }
     DeviceGuard g(ctx->device);
     return launch_attention(ctx, ws, a, as_stream(stream));
 }

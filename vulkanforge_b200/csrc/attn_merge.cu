@@ -6,8 +6,8 @@
 
 namespace vfkv {
 
-// flash_attn_reduce.comp:51-80: partials visited in ascending order with the
-// running (max, sum, acc) update; the final multiply by 1/sum is skipped when
+// flash_attn_reduce.comp:51-80: out = sum_i o_i e^(m_i - M) / sum_i l_i e^(m_i - M) with M the
+// maximum of the partial maxima; the final multiply by 1/sum is skipped when
 // the caller wants the unnormalised triple (sequence-dimension sharding).
 // Index of partial i of row r: i*part_stride + r*row_stride.
 __global__ void __launch_bounds__(128)
@@ -19,20 +19,24 @@ merge_kernel(const float *__restrict__ pm, const float *__restrict__ pl, const f
     const uint64_t row = blockIdx.x;
     constexpr int kMaxDims = 4;                      // 128 threads x 4 = head_dim 512
     float acc[kMaxDims] = {0.f, 0.f, 0.f, 0.f};
-    float gmax = kMaskedScore, gsum = 0.f;
+    // The shader walks the partials with a running (max, sum, acc); the same result, up to
+    // rounding, comes from taking the maximum first and then one weighted sum, which leaves
+    // every load independent of the others.
+    float gmax = kMaskedScore;
+#pragma unroll 8
+    for (uint32_t i = 0; i < n_parts; ++i) gmax = fmaxf(gmax, pm[uint64_t(i) * part_stride + row * row_stride]);
+    float gsum = 0.f;
+#pragma unroll 4
     for (uint32_t i = 0; i < n_parts; ++i) {
         const uint64_t pi = uint64_t(i) * part_stride + row * row_stride;
-        const float tm = pm[pi], ts = pl[pi];
-        const float nm = fmaxf(gmax, tm);
-        const float ko = __expf(gmax - nm), kn = __expf(tm - nm);
+        const float kn = __expf(pm[pi] - gmax);
+        gsum = fmaf(pl[pi], kn, gsum);
 #pragma unroll
         for (int j = 0; j < kMaxDims; ++j) {
             uint32_t d = threadIdx.x + j * 128;
             float t = d < head_dim ? po[pi * head_dim + d] : 0.f;
-            acc[j] = acc[j] * ko + t * kn;
+            acc[j] = fmaf(t, kn, acc[j]);
         }
-        gsum = gsum * ko + ts * kn;
-        gmax = nm;
     }
     const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;   // an empty range yields zeros, not NaN
 #pragma unroll
@@ -77,13 +81,24 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     uint32_t max_len = a.seq.max_len_hint ? a.seq.max_len_hint : a.kv.max_seq;
     if (!a.seq.seq_lens && !a.seq.positions) max_len = a.seq.seq_len_scalar - a.seq.kv_start_scalar;
     if (a.seq.window && max_len > a.seq.window) max_len = a.seq.window;
-    uint64_t base = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
-    uint64_t want = (uint64_t(ctx->sm_count) * 2 + base - 1) / (base ? base : 1);
-    uint32_t min_chunk = tile < 256 ? 256 : tile;
+    const uint64_t base = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
+    const uint64_t slots = uint64_t(ctx->sm_count) * 2;          // CTAs resident at once
+    const uint32_t min_chunk = tile < 256 ? 256 : tile;
     uint64_t cap = (uint64_t(max_len) + min_chunk - 1) / min_chunk;
-    if (want > cap) want = cap;
-    if (want < 1) want = 1;
-    return uint32_t(want);
+    if (cap < 1) cap = 1;
+    if (cap > 64) cap = 64;
+    // Smallest count whose grid fills whole waves of resident CTAs to 95 %; failing that, the
+    // count with the best fill.  (512 CTAs on 296 slots would idle 14 % of the GPU in the second
+    // wave; 2048 CTAs fill 98.8 %.)
+    uint64_t best = 1;
+    double best_eff = 0.0;
+    for (uint64_t ns = 1; ns <= cap; ++ns) {
+        const uint64_t ctas = base * ns, waves = (ctas + slots - 1) / slots;
+        const double eff = double(ctas) / double(waves * slots);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
+        if (eff >= 0.95) { best = ns; break; }
+    }
+    return uint32_t(best);
 }
 
 int32_t launch_attention(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, cudaStream_t st)
@@ -106,7 +121,8 @@ int32_t launch_attention(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, c
     int32_t rc = use_mma ? launch_attn_mma(ctx, ws, a, n_splits, st)
                          : launch_attn_generic(ctx, ws, a, n_splits, st);
     if (rc != VFKV_OK) return rc;
-    if (n_splits > 1) rc = launch_merge_ws(ctx, ws, a, n_splits, st);
+    // the tensor-core kernel merges its own partials (last CTA of each kv-head)
+    if (n_splits > 1 && !use_mma) rc = launch_merge_ws(ctx, ws, a, n_splits, st);
     return rc;
 }
 

@@ -37,7 +37,6 @@ namespace vfkv {
 
 namespace {
 
-constexpr int kWarps = 4;
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -171,10 +170,11 @@ __device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t &hi, ui
 struct MmaParams {
     AttnParams a;
     uint32_t *counters;     // one ticket per (sequence, kv-head); zero between launches
+    const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
 };
 
 // Shape-dependent constants.
-template <int DT, int D> struct Shape {
+template <int DT, int D, int W> struct Shape {
     static constexpr int ES = DT == VFKV_F8 ? 1 : 2;
     static constexpr int TP = DT == VFKV_F8 ? 32 : 16;        // positions per tile
     static constexpr int NB = TP / 8;                         // 8-position blocks per tile
@@ -183,7 +183,7 @@ template <int DT, int D> struct Shape {
     static constexpr int NDB = D / 8;                         // 8-dim blocks of the output
     static constexpr int TILE_BYTES = TP * 128 * NC;          // K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int RING_BYTES = kWarps * kStages * STAGE_BYTES;
+    static constexpr int RING_BYTES = W * kStages * STAGE_BYTES;
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -195,12 +195,15 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, uint32_t chunk, uin
     return tile + chunk * (TP * 128) + row * 128 + ((unit ^ (row & 7u)) << 4);
 }
 
-template <int DT, int D, bool ROWS2>
-__global__ void __launch_bounds__(kWarps * 32)
+// W = warps per CTA: 4 (two CTAs per SM) for grids of several waves, 8 for grids that leave SMs
+// idle, where a CTA's stream is short and the tiles are better spread over more warps.
+template <int DT, int D, bool ROWS2, int W>
+__global__ void __launch_bounds__(W * 32)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const MmaParams mp)
 {
-    using S = Shape<DT, D>;
+    using S = Shape<DT, D, W>;
+    constexpr int kWarps = W;
     constexpr int TP = S::TP, NB = S::NB, NC = S::NC, KSTEPS = S::KSTEPS, NDB = S::NDB;
     constexpr bool FP8 = DT == VFKV_F8;
     constexpr int RS = (!FP8 && ROWS2) ? 2 : 1;          // logical score rows per thread
@@ -253,6 +256,41 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (lane == 0) {
         const uint32_t pre = my_tiles < uint32_t(kStages) ? my_tiles : uint32_t(kStages);
         for (uint32_t n = 0; n < pre; ++n) issue(n);
+    }
+
+    // ---- fused append (KvWrite of the decode step): the CTA whose range ends at the sequence's
+    // last position quantises this kv-head's slice of the new token, stores it in the cache and
+    // patches it into the tile it has just fetched, so the row is used whether or not the TMA
+    // read saw the store.  Encoding as in append.cu (kv_store_fp8.comp / kv_copy_fp16.comp).
+    constexpr uint32_t UPT = D * S::ES / 16;             // 16-byte units per head slice
+    constexpr uint32_t NEWU = (2 * UPT + 31) / 32;       // units per lane, K then V
+    const bool has_new = mp.k_new != nullptr && end == len && begin < end;
+    const uint32_t new_tile = has_new ? (len - 1 - begin) / TP : 0;
+    const bool new_owner = has_new && (new_tile % kWarps) == warp;
+    uint4 newu[NEWU];
+    if (new_owner) {
+#pragma unroll
+        for (uint32_t i = 0; i < NEWU; ++i) {
+            const uint32_t u = lane + 32 * i;
+            newu[i] = make_uint4(0, 0, 0, 0);
+            if (u < 2 * UPT) {
+                const float *src = (u < UPT ? mp.k_new : mp.v_new) + (uint64_t(s) * p.n_kv_heads + kvh) * D +
+                                   (u % UPT) * (16 / S::ES);
+                const float4 *s4 = reinterpret_cast<const float4 *>(src);
+                if constexpr (FP8) {
+                    const float4 a = s4[0], b = s4[1], c = s4[2], d = s4[3];
+                    newu[i] = make_uint4(f32x4_to_e4m3x4(a.x, a.y, a.z, a.w), f32x4_to_e4m3x4(b.x, b.y, b.z, b.w),
+                                         f32x4_to_e4m3x4(c.x, c.y, c.z, c.w), f32x4_to_e4m3x4(d.x, d.y, d.z, d.w));
+                } else {
+                    const float4 a = s4[0], b = s4[1];
+                    newu[i] = make_uint4(f32x2_to_f16x2(a.x, a.y), f32x2_to_f16x2(a.z, a.w),
+                                         f32x2_to_f16x2(b.x, b.y), f32x2_to_f16x2(b.z, b.w));
+                }
+                uint8_t *dst = const_cast<uint8_t *>(u < UPT ? p.k : p.v) + uint64_t(slot) * p.slot_stride_bytes +
+                               uint64_t(len - 1) * p.n_kv_heads * D * S::ES + uint64_t(kvh) * D * S::ES + (u % UPT) * 16;
+                *reinterpret_cast<uint4 *>(dst) = newu[i];
+            }
+        }
     }
 
     // ---- Q fragments (A operand), scaled per head by a power of two into [128, 256) --------
@@ -341,6 +379,21 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             for (uint32_t i = lane; i < units; i += 32) {
                 const uint32_t r = n_valid + i / (NC * 8), c = (i / 8) % NC, u = i % 8;
                 asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vt + c * TP * 128 + r * 128 + u * 16), "r"(0u) : "memory");
+            }
+            __syncwarp();
+        }
+
+        if (new_owner && n == new_tile / kWarps) {       // the appended token's row of this tile
+            const uint32_t r = len - 1 - t0;
+#pragma unroll
+            for (uint32_t i = 0; i < NEWU; ++i) {
+                const uint32_t u = lane + 32 * i;
+                if (u < 2 * UPT) {
+                    const uint32_t uu = u % UPT;
+                    const uint32_t addr = tile_addr<TP>(u < UPT ? kt : vt, uu / 8, r, uu % 8);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(newu[i].x), "r"(newu[i].y),
+                                 "r"(newu[i].z), "r"(newu[i].w) : "memory");
+                }
             }
             __syncwarp();
         }
@@ -568,22 +621,29 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     __syncthreads();
     if (s_flag != 2u) return;
     __threadfence();
-    for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
-        const uint32_t j = idx / D, d = idx % D;
+    // flash_attn_reduce.comp:57-75 with the maximum taken first, so that no load waits for another
+    for (uint32_t idx = threadIdx.x; idx < g * (D / 4); idx += blockDim.x) {
+        const uint32_t j = idx / (D / 4), d = 4 * (idx % (D / 4));
         const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
-        float gmax = kMaskedScore, gsum = 0.f, a = 0.f;
-        for (uint32_t i = 0; i < p.n_splits; ++i) {            // flash_attn_reduce.comp:57-75
-            const uint64_t pi = row * p.n_splits + i;
-            const float tm = __ldcg(p.part_m + pi), ts = __ldcg(p.part_l + pi);
-            const float nm = fmaxf(gmax, tm);
-            const float ko = __expf(gmax - nm), kn = __expf(tm - nm);
-            a = a * ko + __ldcg(p.part_o + pi * D + d) * kn;
-            gsum = gsum * ko + ts * kn;
-            gmax = nm;
+        const float *pm = p.part_m + row * p.n_splits, *pl = p.part_l + row * p.n_splits;
+        float gmax = kMaskedScore;
+#pragma unroll 8
+        for (uint32_t i = 0; i < p.n_splits; ++i) gmax = fmaxf(gmax, __ldcg(pm + i));
+        float gsum = 0.f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+        for (uint32_t i = 0; i < p.n_splits; ++i) {
+            const float kn = __expf(__ldcg(pm + i) - gmax);
+            const float4 o = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (row * p.n_splits + i) * D + d));
+            gsum = fmaf(__ldcg(pl + i), kn, gsum);
+            a.x = fmaf(o.x, kn, a.x); a.y = fmaf(o.y, kn, a.y); a.z = fmaf(o.z, kn, a.z); a.w = fmaf(o.w, kn, a.w);
         }
-        if (p.out) p.out[row * D + d] = gsum > 0.f ? a * (1.0f / gsum) : 0.f;
+        if (p.out) {
+            const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;
+            *reinterpret_cast<float4 *>(p.out + row * D + d) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+        }
         if (p.out_o) {
-            p.out_o[row * D + d] = a;
+            *reinterpret_cast<float4 *>(p.out_o + row * D + d) = a;
             if (d == 0) { p.out_m[row] = gmax; p.out_l[row] = gsum; }
         }
     }
@@ -611,11 +671,11 @@ bool encode_map(vfkv_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_
     return r == CUDA_SUCCESS;
 }
 
-template <int DT, int D, bool ROWS2>
-int32_t launch_t(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
+template <int DT, int D, bool ROWS2, int W>
+int32_t launch_w(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
-    using S = Shape<DT, D>;
-    auto kern = attn_split_mma_kernel<DT, D, ROWS2>;
+    using S = Shape<DT, D, W>;
+    auto kern = attn_split_mma_kernel<DT, D, ROWS2, W>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
@@ -625,10 +685,22 @@ int32_t launch_t(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
     dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
     {
         ProfScope ps(ctx, VFKV_PROF_FA_SPLIT, st);
-        kern<<<grid, kWarps * 32, S::SMEM_BYTES, st>>>(tk, tv, mp);
+        kern<<<grid, W * 32, S::SMEM_BYTES, st>>>(tk, tv, mp);
     }
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "tensor-core attention launch");
+}
+
+template <int DT, int D, bool ROWS2>
+int32_t launch_t(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
+{
+    // eight warps only where three stages of them fit in shared memory (8 KB stages)
+    constexpr bool kWide = Shape<DT, D, 8>::SMEM_BYTES <= 200 * 1024;
+    const uint64_t ctas = uint64_t(mp.a.n_splits) * mp.a.n_kv_heads * mp.a.n_seqs;
+    if constexpr (kWide) {
+        if (ctas <= uint64_t(ctx->sm_count)) return launch_w<DT, D, ROWS2, 8>(ctx, tk, tv, mp, st);
+    }
+    return launch_w<DT, D, ROWS2, 4>(ctx, tk, tv, mp, st);
 }
 
 }  // namespace
@@ -641,6 +713,7 @@ bool attn_mma_supported(const AttnArgs &a)
     if (uint64_t(a.kv.n_slots) * a.kv.max_seq >= (1ull << 31)) return false;
     if ((reinterpret_cast<uintptr_t>(a.kv.k) | reinterpret_cast<uintptr_t>(a.kv.v)) % 16 != 0) return false;
     if (reinterpret_cast<uintptr_t>(a.q) % 16 != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.out_o)) % 16 != 0) return false;
     if (a.kv.dtype == VFKV_F8) return g <= 8 && (D == 128 || D == 256);
     if (a.kv.dtype == VFKV_F16) return g <= 16 && (D == 64 || D == 128 || D == 256);
     return false;
@@ -666,6 +739,10 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     MmaParams mp;
     mp.a = make_params(ctx, ws, a, n_splits);
     mp.counters = ws ? ws->counters : nullptr;
+    mp.k_new = a.k_new;
+    mp.v_new = a.v_new;
+    if ((reinterpret_cast<uintptr_t>(a.k_new) | reinterpret_cast<uintptr_t>(a.v_new)) % 16 != 0)
+        return set_error(ctx, VFKV_ERR_INVALID, "new K/V rows must be 16-byte aligned");
     if (n_splits > 1 && !mp.counters) return set_error(ctx, VFKV_ERR_INVALID, "workspace has no ticket counters");
     if (n_splits > 1 && uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads > ws->n_counters)
         return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");

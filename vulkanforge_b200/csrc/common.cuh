@@ -100,6 +100,10 @@ struct AttnArgs {
     float scale = 1.f;
     float softcap = 0.f;
     uint32_t n_splits = 0;        // 0 = choose
+    // decode step: the token to append at each sequence's last position, [seq][kv_head][dim] f32;
+    // only the tensor-core kernel consumes these (it writes the cache rows itself)
+    const float *k_new = nullptr;
+    const float *v_new = nullptr;
 };
 
 // Brackets one kernel launch with a pair of events on its stream while profiling is on.
