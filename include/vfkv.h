@@ -333,6 +333,16 @@ int32_t vfkv_stream_synchronize(vfkv_ctx *ctx, void *stream);
  * 0 = automatic, 1 = CUDA-core kernel only, 2 = tensor-core kernel only
  * (VFKV_ERR_UNSUPPORTED from attend when the shape is outside it). */
 int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
+/* Shape of the tensor-core attention kernel for subsequent calls: warps per CTA x TMA stages per
+ * warp; 4x2, 4x3 or 8x3, 0x0 = choose per call (4x2, or 8x3 when the grid has at most one CTA per
+ * SM).  The reference has fixed workgroup shapes; this is a measurement knob. */
+int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages);
+/* Latency analysis of the tensor-core attention kernel: while d_buffer is non-NULL, thread 0 of
+ * every CTA stores 16 x uint64 nanosecond timestamps (globaltimer) at fixed phases -- 0 entry,
+ * 1 range known, 2 barriers ready, 3 Q ready, 4 first tile landed, 5 stream done, 6 CTA joined,
+ * 7 partial written, 8 ticket taken, 9 merged (last CTA only) -- at CTA index * 16.  The buffer
+ * must hold 16 x 8 bytes per CTA of the largest grid.  NULL switches it off. */
+int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer);
 /* Kernels this context has launched since creation (for launch accounting). */
 uint64_t vfkv_ctx_launch_count(const vfkv_ctx *ctx);
 

@@ -87,6 +87,8 @@ SIGNATURES = {
     "vfkv_memset": (i32, [vp, vp, i32, u64, vp]),
     "vfkv_stream_synchronize": (i32, [vp, vp]),
     "vfkv_ctx_set_attn_impl": (i32, [vp, u32]),
+    "vfkv_ctx_set_attn_tuning": (i32, [vp, u32, u32]),
+    "vfkv_ctx_set_trace_buffer": (i32, [vp, vp]),
     "vfkv_ctx_launch_count": (u64, [vp]),
     "vfkv_profile_enable": (i32, [vp, i32]),
     "vfkv_profile_collect": (i32, [vp, u32, C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double), i32]),

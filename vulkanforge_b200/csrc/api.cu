@@ -176,6 +176,23 @@ int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl)
     return VFKV_OK;
 }
 
+int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages)
+{
+    if (!ctx) return VFKV_ERR_INVALID;
+    const bool ok = (warps == 0 && stages == 0) || (warps == 4 && (stages == 2 || stages == 3)) || (warps == 8 && stages == 3);
+    if (!ok) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_ctx_set_attn_tuning: warps x stages must be 0x0, 4x2, 4x3 or 8x3");
+    ctx->tune_warps = warps;
+    ctx->tune_stages = stages;
+    return VFKV_OK;
+}
+
+int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer)
+{
+    if (!ctx) return VFKV_ERR_INVALID;
+    ctx->d_trace = static_cast<unsigned long long *>(d_buffer);
+    return VFKV_OK;
+}
+
 uint64_t vfkv_ctx_launch_count(const vfkv_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
 int32_t vfkv_profile_enable(vfkv_ctx *ctx, int32_t on)

@@ -81,24 +81,20 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     uint32_t max_len = a.seq.max_len_hint ? a.seq.max_len_hint : a.kv.max_seq;
     if (!a.seq.seq_lens && !a.seq.positions) max_len = a.seq.seq_len_scalar - a.seq.kv_start_scalar;
     if (a.seq.window && max_len > a.seq.window) max_len = a.seq.window;
+    // One split per (sequence, kv-head) once that alone gives every SM two CTAs: the stream is
+    // HBM-bound, so a ragged last wave costs little, while every extra split costs a partial
+    // write, a ticket and a merge.  Smaller grids are cut until about two CTAs per SM exist, but
+    // never below 256 positions per split.
     const uint64_t base = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
-    const uint64_t slots = uint64_t(ctx->sm_count) * 2;          // CTAs resident at once
+    const uint64_t slots = uint64_t(ctx->sm_count) * 2;
     const uint32_t min_chunk = tile < 256 ? 256 : tile;
     uint64_t cap = (uint64_t(max_len) + min_chunk - 1) / min_chunk;
     if (cap < 1) cap = 1;
     if (cap > 64) cap = 64;
-    // Smallest count whose grid fills whole waves of resident CTAs to 95 %; failing that, the
-    // count with the best fill.  (512 CTAs on 296 slots would idle 14 % of the GPU in the second
-    // wave; 2048 CTAs fill 98.8 %.)
-    uint64_t best = 1;
-    double best_eff = 0.0;
-    for (uint64_t ns = 1; ns <= cap; ++ns) {
-        const uint64_t ctas = base * ns, waves = (ctas + slots - 1) / slots;
-        const double eff = double(ctas) / double(waves * slots);
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
-        if (eff >= 0.95) { best = ns; break; }
-    }
-    return uint32_t(best);
+    uint64_t want = base ? (slots + base - 1) / base : 1;
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    return uint32_t(want);
 }
 
 int32_t launch_attention(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, cudaStream_t st)

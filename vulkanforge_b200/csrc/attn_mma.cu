@@ -37,10 +37,10 @@ namespace vfkv {
 
 namespace {
 
-constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kPScale = 256.0f;     // FP8 P operand is 256*p: keeps small p out of E4M3's subnormals
+constexpr float kPShift = 8.0f;       // FP8 P operand is 2^8 * p: keeps small p out of E4M3's subnormals
+constexpr float kPScale = 256.0f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -94,18 +94,22 @@ __device__ __forceinline__ void fence_proxy_async()
 {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
+// The shared-memory loads take a register base plus a compile-time byte offset, so that the
+// per-lane swizzled part of an address is computed once per tile and the rest is an immediate.
+template <int IMM>
+__device__ __forceinline__ void ldmatrix_x4(uint32_t base, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
 {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4+%5];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+                 : "r"(base), "n"(IMM));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2,
+template <int IMM>
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t base, uint32_t &r0, uint32_t &r1, uint32_t &r2,
                                                   uint32_t &r3)
 {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4+%5];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+                 : "r"(base), "n"(IMM));
 }
 __device__ __forceinline__ void mma_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
@@ -129,10 +133,10 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel)
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
     return d;
 }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+template <int IMM> __device__ __forceinline__ uint32_t lds32(uint32_t base)
 {
     uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(base), "n"(IMM));
     return v;
 }
 __device__ __forceinline__ float fast_exp2(float x)
@@ -171,10 +175,18 @@ struct MmaParams {
     AttnParams a;
     uint32_t *counters;     // one ticket per (sequence, kv-head); zero between launches
     const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
+    unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0
 };
 
+// Phase timestamps for latency analysis; costs one predicated branch when tracing is off.
+#define VFKV_TRACE(i)                                                                               \
+    do {                                                                                            \
+        if (mp.trace != nullptr && threadIdx.x == 0)                                                \
+            mp.trace[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (i)] = global_timer_ns(); \
+    } while (0)
+
 // Shape-dependent constants.
-template <int DT, int D, int W> struct Shape {
+template <int DT, int D, int W, int NS> struct Shape {
     static constexpr int ES = DT == VFKV_F8 ? 1 : 2;
     static constexpr int TP = DT == VFKV_F8 ? 32 : 16;        // positions per tile
     static constexpr int NB = TP / 8;                         // 8-position blocks per tile
@@ -183,7 +195,7 @@ template <int DT, int D, int W> struct Shape {
     static constexpr int NDB = D / 8;                         // 8-dim blocks of the output
     static constexpr int TILE_BYTES = TP * 128 * NC;          // K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int RING_BYTES = W * kStages * STAGE_BYTES;
+    static constexpr int RING_BYTES = W * NS * STAGE_BYTES;
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -195,15 +207,89 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, uint32_t chunk, uin
     return tile + chunk * (TP * 128) + row * 128 + ((unit ^ (row & 7u)) << 4);
 }
 
-// W = warps per CTA: 4 (two CTAs per SM) for grids of several waves, 8 for grids that leave SMs
-// idle, where a CTA's stream is short and the tiles are better spread over more warps.
-template <int DT, int D, bool ROWS2, int W>
-__global__ void __launch_bounds__(W * 32)
+// ---- unrolled tile steps; the recursion only exists to make the shared-memory offsets immediates ----
+
+// S += Q K^T for one 32-byte step of the head slice: N blocks JP*2 and JP*2+1 (16 positions).
+template <bool FP8, int NB, int IMM, int JP = 0>
+__device__ __forceinline__ void qk_blocks(uint32_t base, const uint32_t (&a)[4], float (&sc)[NB][4])
+{
+    if constexpr (JP < NB / 2) {
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4<IMM + JP * 16 * 128>(base, r0, r1, r2, r3);
+        if constexpr (FP8) {
+            mma_e4m3(sc[2 * JP], a, r0, r1);
+            mma_e4m3(sc[2 * JP + 1], a, r2, r3);
+        } else {
+            mma_f16(sc[2 * JP], a, r0, r1);
+            mma_f16(sc[2 * JP + 1], a, r2, r3);
+        }
+        qk_blocks<FP8, NB, IMM, JP + 1>(base, a, sc);
+    }
+}
+// kb[u] = K tile base + this lane's swizzled offset for units 2u, 2u+1
+template <bool FP8, int TP, int NB, int KSTEPS, int KS = 0>
+__device__ __forceinline__ void qk_steps(const uint32_t (&kb)[4], const uint32_t (&qa)[KSTEPS][4], float (&sc)[NB][4])
+{
+    if constexpr (KS < KSTEPS) {
+        qk_blocks<FP8, NB, (KS / 4) * TP * 128>(kb[KS % 4], qa[KS], sc);
+        qk_steps<FP8, TP, NB, KSTEPS, KS + 1>(kb, qa, sc);
+    }
+}
+// FP8 O += P V for dims 32Q .. 32Q+31.  vb[2u + e] = V tile base + this lane's offset for rows of
+// parity e and unit pair u.  The eight words are dims 32Q + 4*gid + {0..3} of positions
+// {2tig, 2tig+1, 2tig+8, 2tig+9} and the same + 16; a 4x4 byte transpose (prmt) turns them into
+// B fragments that hold four positions of one dim.
+template <int TP, int D, int Q = 0>
+__device__ __forceinline__ void pv_fp8(const uint32_t (&vb)[8], const uint32_t (&pa)[4], float (&acc)[D / 8][4])
+{
+    if constexpr (Q < D / 32) {
+        constexpr int C = (Q / 4) * TP * 128, u = Q % 4;
+        const uint32_t be = vb[2 * u], bo = vb[2 * u + 1];
+        uint32_t w[8];
+        w[0] = lds32<C>(be);             w[1] = lds32<C>(bo);
+        w[2] = lds32<C + 8 * 128>(be);   w[3] = lds32<C + 8 * 128>(bo);
+        w[4] = lds32<C + 16 * 128>(be);  w[5] = lds32<C + 16 * 128>(bo);
+        w[6] = lds32<C + 24 * 128>(be);  w[7] = lds32<C + 24 * 128>(bo);
+        uint32_t b[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t lo01 = prmt(w[4 * h], w[4 * h + 1], 0x5140), hi01 = prmt(w[4 * h], w[4 * h + 1], 0x7362);
+            const uint32_t lo23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x5140), hi23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x7362);
+            b[h][0] = prmt(lo01, lo23, 0x5410);
+            b[h][1] = prmt(lo01, lo23, 0x7632);
+            b[h][2] = prmt(hi01, hi23, 0x5410);
+            b[h][3] = prmt(hi01, hi23, 0x7632);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mma_e4m3(acc[4 * Q + i], pa, b[0][i], b[1][i]);
+        pv_fp8<TP, D, Q + 1>(vb, pa, acc);
+    }
+}
+// F16 O += P V for the 8-dim blocks NBK and NBK+1 (ldmatrix.trans gives the B fragments directly).
+template <int TP, int D, int NBK = 0>
+__device__ __forceinline__ void pv_f16(const uint32_t (&vb)[4], const uint32_t (&pa)[4], float (&acc)[D / 8][4])
+{
+    if constexpr (NBK < D / 8) {
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4_trans<(NBK / 8) * TP * 128>(vb[(NBK % 8) / 2], r0, r1, r2, r3);
+        mma_f16(acc[NBK], pa, r0, r1);
+        mma_f16(acc[NBK + 1], pa, r2, r3);
+        pv_f16<TP, D, NBK + 2>(vb, pa, acc);
+    }
+}
+
+// W = warps per CTA, NS = TMA stages per warp.  Grids of several waves run 4 warps x 2 stages, which
+// lets three CTAs share an SM (12 warps hide the MMA / shuffle latencies of one another); grids that
+// leave SMs idle run 8 warps x 3 stages, spreading a CTA's short stream over more warps.
+// CAP compiles the score soft-cap in or out.
+template <int DT, int D, bool ROWS2, int W, int NS, bool CAP>
+__global__ void __launch_bounds__(W * 32, (W == 4 && NS == 2 && Shape<DT, D, W, NS>::STAGE_BYTES <= 8192) ? 3 : 1)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const MmaParams mp)
 {
-    using S = Shape<DT, D, W>;
+    using S = Shape<DT, D, W, NS>;
     constexpr int kWarps = W;
+    constexpr int kStages = NS;
     constexpr int TP = S::TP, NB = S::NB, NC = S::NC, KSTEPS = S::KSTEPS, NDB = S::NDB;
     constexpr bool FP8 = DT == VFKV_F8;
     constexpr int RS = (!FP8 && ROWS2) ? 2 : 1;          // logical score rows per thread
@@ -223,10 +309,38 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t gid = lane >> 2, tig = lane & 3;
     const uint32_t g = p.group;
 
+    // Q is fetched first: its address depends on the block index only, so these loads overlap the
+    // (dependent) read of the sequence's position and the first TMA round trip.
+    // element layout this thread needs: FP8  d = 32ks + 4tig + i  and  32ks + 16 + 4tig + i   (i < 4)
+    //                                   F16  d = 16ks + 2tig + i  and  16ks + 8 + 2tig + i    (i < 2)
+    float qv[RS][KSTEPS][4], qv2[RS][KSTEPS][4];
+#pragma unroll
+    for (int r = 0; r < RS; ++r) {
+        const uint32_t hrow = gid + 8 * r;
+        const bool hv = hrow < g;
+        const float *qp = p.q + (uint64_t(s) * p.n_q_heads + kvh * g + (hv ? hrow : 0)) * D;
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            if constexpr (FP8) {
+                float4 a = hv ? *reinterpret_cast<const float4 *>(qp + 32 * ks + 4 * tig) : make_float4(0, 0, 0, 0);
+                float4 b = hv ? *reinterpret_cast<const float4 *>(qp + 32 * ks + 16 + 4 * tig) : make_float4(0, 0, 0, 0);
+                qv[r][ks][0] = a.x; qv[r][ks][1] = a.y; qv[r][ks][2] = a.z; qv[r][ks][3] = a.w;
+                qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = b.z; qv2[r][ks][3] = b.w;
+            } else {
+                float2 a = hv ? *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * tig) : make_float2(0, 0);
+                float2 b = hv ? *reinterpret_cast<const float2 *>(qp + 16 * ks + 8 + 2 * tig) : make_float2(0, 0);
+                qv[r][ks][0] = a.x; qv[r][ks][1] = a.y; qv[r][ks][2] = 0.f; qv[r][ks][3] = 0.f;
+                qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = 0.f; qv2[r][ks][3] = 0.f;
+            }
+        }
+    }
+
+    VFKV_TRACE(0);
     uint32_t slot, start, len, begin, end;
     seq_range(p, s, &slot, &start, &len);
     split_range(start, len, p.n_splits, split, 32, &begin, &end);
     const uint32_t n_tiles = (end - begin + TP - 1) / TP;
+    VFKV_TRACE(1);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kWarps * kStages; ++i) mbar_init(bars + 8 * i, 1);
@@ -234,6 +348,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         s_flag = 0;
     }
     __syncthreads();
+    VFKV_TRACE(2);
 
     // ---- this warp's pipeline -------------------------------------------------------------
     const uint32_t my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
@@ -299,32 +414,13 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     uint32_t qa[KSTEPS][4];
     float mult[RS];                      // score multiplier per logical row: scale / q_scale
     {
-        float qv[RS][KSTEPS][4];         // FP8: [ks][0..3]=d 32ks+4tig.., plus [ks+...] second half below
-        float qv2[RS][KSTEPS][4];
-        // element layout this thread needs: FP8  d = 32ks + 4tig + i  and  32ks + 16 + 4tig + i   (i < 4)
-        //                                   F16  d = 16ks + 2tig + i  and  16ks + 8 + 2tig + i    (i < 2)
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
-            const uint32_t hrow = gid + 8 * r;
-            const bool hv = hrow < g;
-            const float *qp = p.q + (uint64_t(s) * p.n_q_heads + kvh * g + (hv ? hrow : 0)) * D;
             float amax = 0.f;
 #pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                if constexpr (FP8) {
-                    float4 a = hv ? *reinterpret_cast<const float4 *>(qp + 32 * ks + 4 * tig) : make_float4(0, 0, 0, 0);
-                    float4 b = hv ? *reinterpret_cast<const float4 *>(qp + 32 * ks + 16 + 4 * tig) : make_float4(0, 0, 0, 0);
-                    qv[r][ks][0] = a.x; qv[r][ks][1] = a.y; qv[r][ks][2] = a.z; qv[r][ks][3] = a.w;
-                    qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = b.z; qv2[r][ks][3] = b.w;
-                } else {
-                    float2 a = hv ? *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * tig) : make_float2(0, 0);
-                    float2 b = hv ? *reinterpret_cast<const float2 *>(qp + 16 * ks + 8 + 2 * tig) : make_float2(0, 0);
-                    qv[r][ks][0] = a.x; qv[r][ks][1] = a.y; qv[r][ks][2] = 0.f; qv[r][ks][3] = 0.f;
-                    qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = 0.f; qv2[r][ks][3] = 0.f;
-                }
+            for (int ks = 0; ks < KSTEPS; ++ks)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(qv[r][ks][i]), fabsf(qv2[r][ks][i])));
-            }
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             // q_scale = 2^(7 - floor(log2 amax)); exact in both directions
@@ -332,7 +428,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             e = amax > 0.f ? max(-100, min(100, e)) : 7;
             const float qs = __uint_as_float(uint32_t(7 - e + 127) << 23);
             const float inv_qs = __uint_as_float(uint32_t(e - 7 + 127) << 23);
-            mult[r] = p.scale * inv_qs;
+            mult[r] = p.scale * inv_qs * (CAP ? 1.0f : kLog2e);
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
                 if constexpr (FP8) {
@@ -364,6 +460,29 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
     for (int nb = 0; nb < NDB; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f; }
     bool timed_out = false;
+    VFKV_TRACE(3);
+
+    // Lane-constant parts of the swizzled shared-memory addresses (tile_addr with the tile base
+    // left out).  In every case the unit index is an even compile-time number plus a lane bit, so
+    // unit ^ (row & 7) = even_part ^ (lane_bit ^ row & 7) and four variants cover all units.
+    const uint32_t lm = lane >> 3, lr = lane & 7;
+    uint32_t qk_sw[4];        // K ldmatrix: row 8*(2jp + lm/2) + lr, unit 2u + (lm & 1)
+#pragma unroll
+    for (uint32_t u = 0; u < 4; ++u) qk_sw[u] = ((lm >> 1) * 8 + lr) * 128 + (((2 * u) ^ ((lm & 1) ^ lr)) << 4);
+    // FP8 V words: row 2*tig + e (+8, +16, +24), unit 2u + gid/4, word gid%4
+    // F16 V ldmatrix.trans: row 8*(lm & 1) + lr, unit 2u + lm/2
+    uint32_t v_sw[FP8 ? 8 : 4];
+    if constexpr (FP8) {
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+#pragma unroll
+            for (uint32_t e = 0; e < 2; ++e)
+                v_sw[2 * u + e] = (2 * tig + e) * 128 + ((u ^ tig) << 5) + (((gid >> 2) ^ e) << 4) + (gid & 3) * 4;
+    } else {
+#pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+            v_sw[u] = (8 * (lm & 1) + lr) * 128 + (((2 * u) ^ ((lm >> 1) ^ lr)) << 4);
+    }
 
     for (uint32_t n = 0; n < my_tiles; ++n) {
         const uint32_t st = n % kStages;
@@ -371,6 +490,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const uint32_t kt = stage0 + st * S::STAGE_BYTES, vt = kt + S::TILE_BYTES;
         if (!mbar_wait_bounded(bar0 + 8 * st, (n / kStages) & 1u)) { timed_out = true; break; }
         const uint32_t n_valid = min(uint32_t(TP), end - t0);
+        if (n == 0) VFKV_TRACE(4);
 
         // rows at and beyond `end` may hold anything (stale tokens, another slot): zero them in V so
         // that 0 * garbage cannot become NaN; their scores are masked below.
@@ -402,29 +522,16 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         float sc[NB][4];
 #pragma unroll
         for (int j = 0; j < NB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint32_t chunk = ks / 4, u0 = 2 * (ks % 4);
-#pragma unroll
-            for (int jp = 0; jp < NB / 2; ++jp) {
-                const uint32_t mi = lane >> 3, rr = lane & 7;
-                const uint32_t row = 8 * (2 * jp + (mi >> 1)) + rr;
-                uint32_t r0, r1, r2, r3;
-                ldmatrix_x4(tile_addr<TP>(kt, chunk, row, u0 + (mi & 1)), r0, r1, r2, r3);
-                if constexpr (FP8) {
-                    mma_e4m3(sc[2 * jp], qa[ks], r0, r1);
-                    mma_e4m3(sc[2 * jp + 1], qa[ks], r2, r3);
-                } else {
-                    mma_f16(sc[2 * jp], qa[ks], r0, r1);
-                    mma_f16(sc[2 * jp + 1], qa[ks], r2, r3);
-                }
-            }
+        {
+            const uint32_t kb[4] = {kt + qk_sw[0], kt + qk_sw[1], kt + qk_sw[2], kt + qk_sw[3]};
+            qk_steps<FP8, TP, NB, KSTEPS>(kb, qa, sc);
         }
 
         // ---- softmax bookkeeping in the log2 domain -------------------------------------------
         // this thread's scores: logical row r, block j, element i  <->  position t0 + 8j + 2tig + i
         float x[RS][NB][2];
         float tmax[RS];
+        const bool full = n_valid == uint32_t(TP);
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
             tmax[r] = kMaskedScore;
@@ -433,14 +540,23 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     float v = SPLIT ? (sc[j][i] + sc[j][i + 2]) : sc[j][2 * r + i];
-                    v *= mult[r];
-                    if (p.softcap > 0.f) v = p.softcap * tanhf(v / p.softcap);
-                    v *= kLog2e;
-                    const bool valid = uint32_t(8 * j + 2 * tig + i) < n_valid;
-                    v = valid ? v : kMaskedScore;
+                    if constexpr (CAP) {
+                        v *= mult[r];
+                        v = p.softcap * tanhf(v / p.softcap) * kLog2e;
+                    } else {
+                        v *= mult[r];                      // scale * log2(e) / q_scale
+                    }
                     x[r][j][i] = v;
-                    tmax[r] = fmaxf(tmax[r], v);
                 }
+            if (!full) {                                   // a split's last tile: mask the tail
+#pragma unroll
+                for (int j = 0; j < NB; ++j)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i)
+                        x[r][j][i] = uint32_t(8 * j + 2 * tig + i) < n_valid ? x[r][j][i] : kMaskedScore;
+            }
+#pragma unroll
+            for (int j = 0; j < NB; ++j) tmax[r] = fmaxf(tmax[r], fmaxf(x[r][j][0], x[r][j][1]));
             tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
             tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
         }
@@ -461,17 +577,22 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 acc[nb][2] *= corr[SPLIT ? 0 : 1]; acc[nb][3] *= corr[SPLIT ? 0 : 1];
             }
         }
+        // p = 2^(x - m); a masked score is -1e30 against a finite m (every tile has a valid position),
+        // which gives exactly 0.  For FP8 the tensor-core operand is 2^kPShift * p so that small
+        // weights stay out of E4M3's subnormals; l is summed in the same units and the epilogue
+        // divides both out.
 #pragma unroll
-        for (int r = 0; r < RS; ++r)
+        for (int r = 0; r < RS; ++r) {
+            const float mo = FP8 ? m[r] - kPShift : m[r];
 #pragma unroll
             for (int j = 0; j < NB; ++j)
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
-                    const bool valid = uint32_t(8 * j + 2 * tig + i) < n_valid;
-                    const float pv = valid ? fast_exp2(x[r][j][i] - m[r]) : 0.f;
+                    const float pv = fast_exp2(x[r][j][i] - mo);
                     x[r][j][i] = pv;
                     l[r] += pv;
                 }
+        }
 
         // ---- O += P V ----------------------------------------------------------------------------
         if constexpr (FP8) {
@@ -480,40 +601,17 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             uint32_t pa[4];
             {
                 uint32_t h0, l0, h1, l1;
-                split_e4m3x2(x[0][0][0] * kPScale, x[0][0][1] * kPScale, h0, l0);
-                split_e4m3x2(x[0][1][0] * kPScale, x[0][1][1] * kPScale, h1, l1);
+                split_e4m3x2(x[0][0][0], x[0][0][1], h0, l0);
+                split_e4m3x2(x[0][1][0], x[0][1][1], h1, l1);
                 pa[0] = h0 | (h1 << 16); pa[1] = l0 | (l1 << 16);
-                split_e4m3x2(x[0][2][0] * kPScale, x[0][2][1] * kPScale, h0, l0);
-                split_e4m3x2(x[0][3][0] * kPScale, x[0][3][1] * kPScale, h1, l1);
+                split_e4m3x2(x[0][2][0], x[0][2][1], h0, l0);
+                split_e4m3x2(x[0][3][0], x[0][3][1], h1, l1);
                 pa[2] = h0 | (h1 << 16); pa[3] = l0 | (l1 << 16);
             }
+            uint32_t vb[8];
 #pragma unroll
-            for (int q = 0; q < D / 32; ++q) {
-                // the four dims 32q + 4*gid + {0..3} of eight positions, transposed so that one register
-                // holds four positions of one dim
-                const uint32_t chunk = q / 4, unit = 2 * (q % 4) + (gid >> 2), wofs = (gid & 3) * 4;
-                uint32_t w[8];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t rbase = 16 * h + 2 * tig;
-                    w[4 * h + 0] = lds32(tile_addr<TP>(vt, chunk, rbase, unit) + wofs);
-                    w[4 * h + 1] = lds32(tile_addr<TP>(vt, chunk, rbase + 1, unit) + wofs);
-                    w[4 * h + 2] = lds32(tile_addr<TP>(vt, chunk, rbase + 8, unit) + wofs);
-                    w[4 * h + 3] = lds32(tile_addr<TP>(vt, chunk, rbase + 9, unit) + wofs);
-                }
-                uint32_t b[2][4];
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t lo01 = prmt(w[4 * h], w[4 * h + 1], 0x5140), hi01 = prmt(w[4 * h], w[4 * h + 1], 0x7362);
-                    const uint32_t lo23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x5140), hi23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x7362);
-                    b[h][0] = prmt(lo01, lo23, 0x5410);
-                    b[h][1] = prmt(lo01, lo23, 0x7632);
-                    b[h][2] = prmt(hi01, hi23, 0x5410);
-                    b[h][3] = prmt(hi01, hi23, 0x7632);
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) mma_e4m3(acc[4 * q + i], pa, b[0][i], b[1][i]);
-            }
+            for (int i = 0; i < 8; ++i) vb[i] = vt + v_sw[i];
+            pv_fp8<TP, D>(vb, pa, acc);
         } else {
             uint32_t pa[4];
             if constexpr (SPLIT) {
@@ -525,29 +623,23 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 pa[1] = f32x2_to_f16x2(x[RS - 1][0][0], x[RS - 1][0][1]);
                 pa[3] = f32x2_to_f16x2(x[RS - 1][1][0], x[RS - 1][1][1]);
             }
-#pragma unroll
-            for (int nb = 0; nb < NDB; nb += 2) {
-                const uint32_t mi = lane >> 3, rr = lane & 7;
-                const uint32_t row = 8 * (mi & 1) + rr, blk = nb + (mi >> 1);
-                uint32_t r0, r1, r2, r3;
-                ldmatrix_x4_trans(tile_addr<TP>(vt, blk / 8, row, blk % 8), r0, r1, r2, r3);
-                mma_f16(acc[nb], pa, r0, r1);
-                mma_f16(acc[nb + 1], pa, r2, r3);
-            }
+            const uint32_t vb[4] = {vt + v_sw[0], vt + v_sw[1], vt + v_sw[2], vt + v_sw[3]};
+            pv_f16<TP, D>(vb, pa, acc);
         }
 
         // ---- refill this stage -----------------------------------------------------------------
+        // The stage was only read (ldmatrix / ld.shared) since its barrier completed, except in a
+        // split's last tile, which is never refilled; __syncwarp orders those reads before the issue.
         __syncwarp();
-        if (lane == 0 && n + kStages < my_tiles) {
-            fence_proxy_async();
-            issue(n + kStages);
-        }
+        if (lane == 0 && n + kStages < my_tiles) issue(n + kStages);
     }
 
+    VFKV_TRACE(5);
     if (timed_out) {
         if (lane == 0) { atomicOr(p.status, 1u); s_flag = 1; }
     }
     __syncthreads();          // all tiles consumed (or abandoned): the ring is free for the merge
+    VFKV_TRACE(6);
     if (s_flag) return;
 
     // ---- merge the warps' partials in shared memory ---------------------------------------------
@@ -559,7 +651,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     for (int r = 0; r < RS; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-        if (tig == 0) { sm_m[warp * NH + gid + 8 * r] = m[r]; sm_l[warp * NH + gid + 8 * r] = l[r]; }
+        if (tig == 0) {
+            sm_m[warp * NH + gid + 8 * r] = m[r];
+            sm_l[warp * NH + gid + 8 * r] = FP8 ? l[r] * (1.0f / kPScale) : l[r];
+        }
     }
 #pragma unroll
     for (int nb = 0; nb < NDB; ++nb) {
@@ -609,34 +704,60 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             if (d == 0) { p.part_m[pi] = m_nat; p.part_l[pi] = L; }
         }
     }
+    VFKV_TRACE(7);
     if (direct) return;
 
     // ---- the last CTA of this (sequence, kv-head) merges the splits ---------------------------------
-    __threadfence();
+    // The barrier orders every thread's partial stores before thread 0's ticket; the ticket is an
+    // acq_rel atomic at GPU scope, so it publishes them (release) and, for the CTA that draws the
+    // last ticket, makes the other CTAs' partials visible (acquire).  One round trip, no fences.
     __syncthreads();
     if (threadIdx.x == 0) {
-        const uint32_t ticket = atomicAdd(&mp.counters[s * p.n_kv_heads + kvh], 1u);
+        uint32_t ticket;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
+                     : "=r"(ticket) : "l"(mp.counters + s * p.n_kv_heads + kvh), "r"(1u) : "memory");
         s_flag = ticket == p.n_splits - 1 ? 2u : 0u;
     }
     __syncthreads();
+    VFKV_TRACE(8);
     if (s_flag != 2u) return;
-    __threadfence();
-    // flash_attn_reduce.comp:57-75 with the maximum taken first, so that no load waits for another
+    // flash_attn_reduce.comp:57-75 with the maximum taken first.  Everything the merge of up to 16
+    // splits needs is requested in one batch, so it costs a single L2 round trip.
     for (uint32_t idx = threadIdx.x; idx < g * (D / 4); idx += blockDim.x) {
         const uint32_t j = idx / (D / 4), d = 4 * (idx % (D / 4));
         const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
         const float *pm = p.part_m + row * p.n_splits, *pl = p.part_l + row * p.n_splits;
+        const float4 *po = reinterpret_cast<const float4 *>(p.part_o + row * p.n_splits * D + d);
+        constexpr uint32_t CH = 16;
+        float4 o[CH];
+        float mm[CH], ll[CH];
+#pragma unroll
+        for (uint32_t i = 0; i < CH; ++i) {
+            const bool in = i < p.n_splits;
+            o[i] = in ? __ldcg(po + uint64_t(i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            mm[i] = in ? __ldcg(pm + i) : kMaskedScore;
+            ll[i] = in ? __ldcg(pl + i) : 0.f;
+        }
         float gmax = kMaskedScore;
+#pragma unroll
+        for (uint32_t i = 0; i < CH; ++i) gmax = fmaxf(gmax, mm[i]);
 #pragma unroll 8
-        for (uint32_t i = 0; i < p.n_splits; ++i) gmax = fmaxf(gmax, __ldcg(pm + i));
+        for (uint32_t i = CH; i < p.n_splits; ++i) gmax = fmaxf(gmax, __ldcg(pm + i));
         float gsum = 0.f;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (uint32_t i = 0; i < p.n_splits; ++i) {
+#pragma unroll
+        for (uint32_t i = 0; i < CH; ++i) {
+            const float kn = __expf(mm[i] - gmax);       // absent splits: l = 0 and o = 0
+            gsum = fmaf(ll[i], kn, gsum);
+            a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
+            a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
+        }
+#pragma unroll 4
+        for (uint32_t i = CH; i < p.n_splits; ++i) {
             const float kn = __expf(__ldcg(pm + i) - gmax);
-            const float4 o = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (row * p.n_splits + i) * D + d));
+            const float4 ov = __ldcg(po + uint64_t(i) * (D / 4));
             gsum = fmaf(__ldcg(pl + i), kn, gsum);
-            a.x = fmaf(o.x, kn, a.x); a.y = fmaf(o.y, kn, a.y); a.z = fmaf(o.z, kn, a.z); a.w = fmaf(o.w, kn, a.w);
+            a.x = fmaf(ov.x, kn, a.x); a.y = fmaf(ov.y, kn, a.y); a.z = fmaf(ov.z, kn, a.z); a.w = fmaf(ov.w, kn, a.w);
         }
         if (p.out) {
             const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;
@@ -647,6 +768,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             if (d == 0) { p.out_m[row] = gmax; p.out_l[row] = gsum; }
         }
     }
+    VFKV_TRACE(9);
     if (threadIdx.x == 0) mp.counters[s * p.n_kv_heads + kvh] = 0u;   // ready for the next launch
 }
 
@@ -671,36 +793,52 @@ bool encode_map(vfkv_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_
     return r == CUDA_SUCCESS;
 }
 
-template <int DT, int D, bool ROWS2, int W>
-int32_t launch_w(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
+template <int DT, int D, bool ROWS2, int W, int NS, bool CAP>
+int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
-    using S = Shape<DT, D, W>;
-    auto kern = attn_split_mma_kernel<DT, D, ROWS2, W>;
-    static bool configured[64] = {};
-    if (!configured[ctx->device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
-        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tensor-core attention)");
-        configured[ctx->device & 63] = true;
+    using S = Shape<DT, D, W, NS>;
+    if constexpr (S::SMEM_BYTES > 227 * 1024) {
+        return set_error(ctx, VFKV_ERR_UNSUPPORTED, "tuning does not fit in shared memory for this shape");
+    } else {
+        auto kern = attn_split_mma_kernel<DT, D, ROWS2, W, NS, CAP>;
+        static bool configured[64] = {};
+        if (!configured[ctx->device & 63]) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tensor-core attention)");
+            configured[ctx->device & 63] = true;
+        }
+        dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
+        {
+            ProfScope ps(ctx, VFKV_PROF_FA_SPLIT, st);
+            kern<<<grid, W * 32, S::SMEM_BYTES, st>>>(tk, tv, mp);
+        }
+        ctx->launches++;
+        return check_cuda(ctx, cudaGetLastError(), "tensor-core attention launch");
     }
-    dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
-    {
-        ProfScope ps(ctx, VFKV_PROF_FA_SPLIT, st);
-        kern<<<grid, W * 32, S::SMEM_BYTES, st>>>(tk, tv, mp);
-    }
-    ctx->launches++;
-    return check_cuda(ctx, cudaGetLastError(), "tensor-core attention launch");
+}
+
+template <int DT, int D, bool ROWS2, bool CAP>
+int32_t launch_c(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
+{
+    // Small grids (at most one CTA per SM): 8 warps x 3 stages where that fits in shared memory.
+    // Everything else: 4 warps x 3 stages, two CTAs per SM at 8 KB stages (measured faster than
+    // three CTAs of 4 x 2, whose 168-register cap costs more than the extra warps give).
+    constexpr bool kWide = Shape<DT, D, 8, 3>::SMEM_BYTES <= 200 * 1024;
+    const uint64_t ctas = uint64_t(mp.a.n_splits) * mp.a.n_kv_heads * mp.a.n_seqs;
+    uint32_t w = ctx->tune_warps, ns = ctx->tune_stages;
+    if (w == 0) w = (kWide && ctas <= uint64_t(ctx->sm_count)) ? 8 : 4;
+    if (ns == 0) ns = 3;
+    if (w == 8 && ns == 3) return launch_k<DT, D, ROWS2, 8, 3, CAP>(ctx, tk, tv, mp, st);
+    if (w == 4 && ns == 3) return launch_k<DT, D, ROWS2, 4, 3, CAP>(ctx, tk, tv, mp, st);
+    if (w == 4 && ns == 2) return launch_k<DT, D, ROWS2, 4, 2, CAP>(ctx, tk, tv, mp, st);
+    return set_error(ctx, VFKV_ERR_INVALID, "attention tuning must be 4x2, 4x3 or 8x3 (warps x stages)");
 }
 
 template <int DT, int D, bool ROWS2>
 int32_t launch_t(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
-    // eight warps only where three stages of them fit in shared memory (8 KB stages)
-    constexpr bool kWide = Shape<DT, D, 8>::SMEM_BYTES <= 200 * 1024;
-    const uint64_t ctas = uint64_t(mp.a.n_splits) * mp.a.n_kv_heads * mp.a.n_seqs;
-    if constexpr (kWide) {
-        if (ctas <= uint64_t(ctx->sm_count)) return launch_w<DT, D, ROWS2, 8>(ctx, tk, tv, mp, st);
-    }
-    return launch_w<DT, D, ROWS2, 4>(ctx, tk, tv, mp, st);
+    return mp.a.softcap > 0.f ? launch_c<DT, D, ROWS2, true>(ctx, tk, tv, mp, st)
+                              : launch_c<DT, D, ROWS2, false>(ctx, tk, tv, mp, st);
 }
 
 }  // namespace
@@ -739,6 +877,7 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     MmaParams mp;
     mp.a = make_params(ctx, ws, a, n_splits);
     mp.counters = ws ? ws->counters : nullptr;
+    mp.trace = ctx->d_trace;
     mp.k_new = a.k_new;
     mp.v_new = a.v_new;
     if ((reinterpret_cast<uintptr_t>(a.k_new) | reinterpret_cast<uintptr_t>(a.v_new)) % 16 != 0)
