@@ -271,12 +271,24 @@ class Job:
         self.h_pos = np.array([x - 1 for x in self.lens], np.uint32)
         torch.cuda.synchronize()
         self.ctx.poll()
+        # the timed work runs on its own stream (CUDA graphs cannot capture the default stream)
+        self.stream = torch.cuda.Stream(device=device)
+        self.fwd.stream = self.stream.cuda_stream
+        self.graph = None
+        self.launches_per_step = 0
 
     def step(self):
-        f = self.fwd
-        for layer in range(self.w["n_layers"]):
-            f.decode_step(layer, self.q[layer], self.k[layer], self.v[layer], self.out[layer], None, self.pos,
-                          self.w["batch"], self.max_len)
+        """One token: every layer's append + attention, recorded by one library call."""
+        self.fwd.decode_token(self.q, self.k, self.v, self.out, None, self.pos, self.w["batch"], self.max_len)
+
+    def capture(self):
+        """Records one step into a CUDA graph, the counterpart of the reference's pre-recorded
+        per-token command buffer (forward/decode.rs:169-259); positions stay device-side inputs."""
+        torch = self.torch
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.stream):
+            self.step()
+        self.graph = g
 
     def step_host(self):
         self.fwd.decode_token_host(self.h_q, self.h_k, self.h_v, self.h_out, self.h_pos, self.w["batch"])
@@ -292,8 +304,9 @@ class Job:
         import ctypes as C
         L = self.ctx._lib
         L.vfkv_profile_enable(self.ctx.handle, 1)
-        for _ in range(steps):
-            self.step()
+        with self.torch.cuda.stream(self.stream):
+            for _ in range(steps):
+                self.step()
         self.torch.cuda.synchronize()
         res = {}
         for label, name in ((0, "kv_store"), (2, "fa_split"), (3, "fa_reduce")):
@@ -314,28 +327,47 @@ def run_ours(args, w, rank, world, local_rank):
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     job = Job(w, local_rank, seed=1000 + rank)
+    if args.tune:
+        wt, st = (int(x) for x in args.tune.split("x"))
+        job.ctx.check(job.ctx._lib.vfkv_ctx_set_attn_tuning(job.ctx.handle, wt, st))
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    def timed(fn):
+        """W warm-up steps, then K steps between two events on the job's stream."""
+        with torch.cuda.stream(job.stream):
+            for _ in range(args.warmup):
+                fn()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            barrier()
+        return e0.elapsed_time(e1)
+
+    with torch.cuda.stream(job.stream):
+        for _ in range(args.warmup):
+            job.step()
+    barrier()
+    n0 = job.ctx.launch_count()
+    with torch.cuda.stream(job.stream):
         job.step()
+    barrier()
+    job.launches_per_step = job.ctx.launch_count() - n0       # kernels of libvfkv.so per token
+    if not args.no_graph:
+        job.capture()
     barrier()
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    launches0 = job.ctx.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        job.step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = job.ctx.launch_count() - launches0
+    ms = timed(job.graph.replay if job.graph is not None else job.step)
+    launches = job.launches_per_step * args.steps
     clocks = sampler.finish()
+    ms_stream = timed(job.step) if job.graph is not None else ms      # same steps, one launch call per kernel
     job.ctx.poll()
 
     # end-to-end leg: host buffers in, host buffers out, every step
@@ -380,7 +412,9 @@ def run_ours(args, w, rank, world, local_rank):
                            "context": w["ctx"], "n_splits": w["n_splits"], "softcap": w["softcap"],
                            "l2": "each step streams the whole cache (larger than the 126 MB L2) before a layer repeats"
                                  if step_bytes > 200e6 else "working set below L2: hot-L2 numbers",
+                           "launch": "one CUDA graph replay per token" if job.graph is not None else "stream launches",
                            "parallelism": f"sequence-sharded x{world}, no collective"},
+                "value_stream_launches": ms_stream * 1e3 / denom,
                 "tokens_per_s": tokens * args.steps / (ms * 1e-3),
                 "achieved_gbs_whole_step": step_bytes * world * args.steps / (ms * 1e-3) / 1e9,
                 "roofline": roofline, "kernels": prof, "clocks": clocks, "gpu_launches": launches,
@@ -402,9 +436,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline sample")
+    ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
+    ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
+    ap.add_argument("--tune", default=None, help="tensor-core kernel shape WxS (warps x stages), e.g. 4x3")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.n_splits is not None:
+        w["n_splits"] = args.n_splits
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -281,6 +281,19 @@ int32_t vfkv_decode_step(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer,
                          uint32_t max_seq_len_hint, uint32_t window, float scale,
                          float softcap, uint32_t n_splits, void *stream);
 
+/* The decode step for every layer of one token, device buffers: d_q, d_out
+ * [n_layers][n_seqs][n_q_heads][D]; d_k, d_v [n_layers][n_seqs][kv_heads][D].  One call records
+ * what record_decode_dispatches (src/backend/vulkan/forward/decode.rs:43-82) records for this
+ * path: per layer, KvWrite then Attention.  windows: NULL, or n_layers host entries (0 = global
+ * layer).  Uniform-shape caches only.  Nothing in it synchronises or allocates, so a caller may
+ * capture it in a CUDA graph (after one warm-up call) and replay it per token: positions and
+ * slot ids are read from device memory at run time. */
+int32_t vfkv_decode_token(vfkv_cache *cache, vfkv_workspace *ws, const float *d_q, const float *d_k,
+                          const float *d_v, float *d_out, uint32_t n_q_heads,
+                          const uint32_t *d_slot_ids, const uint32_t *d_positions, uint32_t n_seqs,
+                          uint32_t max_seq_len_hint, const uint32_t *windows, float scale,
+                          float softcap, uint32_t n_splits, void *stream);
+
 /* Same step for every layer of one token with HOST buffers: copies
  * h_q [n_layers][n_seqs][n_q_heads][D], h_k, h_v [n_layers][n_seqs][kv_heads][D]
  * to the device, runs the layers in order, copies h_out

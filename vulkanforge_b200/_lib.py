@@ -75,6 +75,7 @@ SIGNATURES = {
     "vfkv_attend": (i32, [vp, vp, u32, u32, vp, vp, u32, u32, u32, u32, f32, f32, u32, vp]),
     "vfkv_attend_batch": (i32, [vp, vp, u32, u32, vp, vp, u32, vp, vp, vp, u32, u32, f32, f32, u32, vp]),
     "vfkv_decode_step": (i32, [vp, vp, u32, vp, vp, vp, vp, u32, vp, vp, u32, u32, u32, f32, f32, u32, vp]),
+    "vfkv_decode_token": (i32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, u32, vp, f32, f32, u32, vp]),
     "vfkv_decode_token_host": (i32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, vp, f32, f32, u32, vp]),
     "vfkv_attend_partial": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp, vp, vp]),
     "vfkv_merge_partials": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, vp]),

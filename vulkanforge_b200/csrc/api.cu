@@ -632,6 +632,26 @@ int32_t vfkv_decode_step(vfkv_cache *cache, vfkv_workspace *ws, uint32_t layer, 
     return launch_attention(ctx, ws, a, as_stream(stream));
 }
 
+int32_t vfkv_decode_token(vfkv_cache *cache, vfkv_workspace *ws, const float *d_q, const float *d_k, const float *d_v,
+                          float *d_out, uint32_t n_q_heads, const uint32_t *d_slot_ids, const uint32_t *d_positions,
+                          uint32_t n_seqs, uint32_t max_seq_len_hint, const uint32_t *windows, float scale,
+                          float softcap, uint32_t n_splits, void *stream)
+{
+    if (!cache) return VFKV_ERR_INVALID;
+    vfkv_ctx *ctx = cache->ctx;
+    KvCache &kv = cache->kv;
+    if (kv.layer_byte_offsets) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_decode_token: uniform-shape caches only");
+    const uint32_t L = kv.config.n_layers, D = kv.config.head_dim, Hkv = kv.config.n_kv_heads;
+    const uint64_t q_stride = uint64_t(n_seqs) * n_q_heads * D, kv_stride = uint64_t(n_seqs) * Hkv * D;
+    for (uint32_t l = 0; l < L; ++l) {
+        int32_t rc = vfkv_decode_step(cache, ws, l, d_q + l * q_stride, d_k + l * kv_stride, d_v + l * kv_stride,
+                                      d_out + l * q_stride, n_q_heads, d_slot_ids, d_positions, n_seqs,
+                                      max_seq_len_hint, windows ? windows[l] : 0, scale, softcap, n_splits, stream);
+        if (rc) return rc;
+    }
+    return VFKV_OK;
+}
+
 int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const float *h_q, const float *h_k,
                                const float *h_v, float *h_out, uint32_t n_q_heads, const uint32_t *h_slot_ids,
                                const uint32_t *h_positions, uint32_t n_seqs, const uint32_t *windows, float scale,
@@ -680,12 +700,9 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
     if (e == cudaSuccess) e = cudaMemcpyAsync(d_pos, h_positions, n_seqs * 4, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess && h_slot_ids) e = cudaMemcpyAsync(d_slots, h_slot_ids, n_seqs * 4, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host: H2D");
-    for (uint32_t l = 0; l < L; ++l) {
-        int32_t rc = vfkv_decode_step(cache, ws, l, dq + uint64_t(l) * n_seqs * n_q_heads * D,
-                                      dk + uint64_t(l) * n_seqs * Hkv * D, dv + uint64_t(l) * n_seqs * Hkv * D,
-                                      ws->stage_out + uint64_t(l) * n_seqs * n_q_heads * D, n_q_heads,
-                                      h_slot_ids ? d_slots : nullptr, d_pos, n_seqs, max_pos + 1,
-                                      windows ? windows[l] : 0, scale, softcap, n_splits, stream);
+    {
+        int32_t rc = vfkv_decode_token(cache, ws, dq, dk, dv, ws->stage_out, n_q_heads, h_slot_ids ? d_slots : nullptr,
+                                       d_pos, n_seqs, max_pos + 1, windows, scale, softcap, n_splits, stream);
         if (rc) return rc;
     }
     e = cudaMemcpyAsync(h_out, ws->stage_out, out_bytes, cudaMemcpyDeviceToHost, st);

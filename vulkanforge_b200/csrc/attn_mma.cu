@@ -644,8 +644,9 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     // ---- merge the warps' partials in shared memory ---------------------------------------------
     constexpr int NH = (FP8 || !ROWS2) ? 8 : 16;              // head rows this CTA can hold
-    float *sm_o = reinterpret_cast<float *>(ring_ptr);        // [kWarps][NH][D]
-    float *sm_m = sm_o + kWarps * NH * D;                     // [kWarps][NH]
+    constexpr int DP = D + 1;                                 // odd row pitch: the 32 lanes hit 32 banks
+    float *sm_o = reinterpret_cast<float *>(ring_ptr);        // [kWarps][NH][DP]
+    float *sm_m = sm_o + kWarps * NH * DP;                    // [kWarps][NH]
     float *sm_l = sm_m + kWarps * NH;                         // [kWarps][NH]
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
@@ -661,17 +662,17 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         if constexpr (FP8) {
             // column n of block nb is dim 32*(nb/4) + 4n + nb%4 (see the V transpose above)
             const uint32_t d0 = 32 * (nb / 4) + 4 * (2 * tig) + (nb % 4);
-            float *o = sm_o + (warp * NH + gid) * D;
+            float *o = sm_o + (warp * NH + gid) * DP;
             o[d0] = (acc[nb][0] + acc[nb][2]) * (1.0f / kPScale);
             o[d0 + 4] = (acc[nb][1] + acc[nb][3]) * (1.0f / kPScale);
         } else {
             const uint32_t d0 = 8 * nb + 2 * tig;
-            float *o = sm_o + (warp * NH + gid) * D;
+            float *o = sm_o + (warp * NH + gid) * DP;
             if constexpr (SPLIT) {
                 o[d0] = acc[nb][0] + acc[nb][2]; o[d0 + 1] = acc[nb][1] + acc[nb][3];
             } else {
                 o[d0] = acc[nb][0]; o[d0 + 1] = acc[nb][1];
-                o[8 * D + d0] = acc[nb][2]; o[8 * D + d0 + 1] = acc[nb][3];
+                o[8 * DP + d0] = acc[nb][2]; o[8 * DP + d0 + 1] = acc[nb][3];
             }
         }
     }
@@ -688,7 +689,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         for (int w = 0; w < kWarps; ++w) {
             const float f = fast_exp2(sm_m[w * NH + j] - M);
             L = fmaf(sm_l[w * NH + j], f, L);
-            O = fmaf(sm_o[(w * NH + j) * D + d], f, O);
+            O = fmaf(sm_o[(w * NH + j) * DP + d], f, O);
         }
         const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
         const float m_nat = M * kLn2;                          // partials carry natural-log maxima

@@ -116,6 +116,27 @@ class CudaForward:
                                                 window, self.attn_scale, self.softcap, self.n_splits,
                                                 self.stream))
 
+    def _windows_array(self):
+        import ctypes as C
+        n_layers = self.kv_cache.config.n_layers
+        if self.sliding_layers and self.sliding_window:
+            return (C.c_uint32 * n_layers)(*[self.sliding_window if l in self.sliding_layers else 0
+                                             for l in range(n_layers)])
+        return None
+
+    def decode_token(self, q, k_src, v_src, attn_out, slot_ids, positions, n_seqs: int,
+                     max_seq_len_hint: int = 0):
+        """Every layer's KvWrite + Attention for one token in one call (device buffers
+        [n_layers][n_seqs][...]); what record_decode_dispatches records for this path
+        (forward/decode.rs:43-82)."""
+        import ctypes as C
+        win = self._windows_array()
+        self.ctx.check(self._L.vfkv_decode_token(
+            self.kv_cache.handle, self.workspace.handle, ptr(q), ptr(k_src), ptr(v_src), ptr(attn_out),
+            self.n_heads, ptr(slot_ids), ptr(positions), n_seqs, max_seq_len_hint,
+            C.cast(win, C.c_void_p) if win is not None else None, self.attn_scale, self.softcap,
+            self.n_splits, self.stream))
+
     def decode_token_host(self, h_q, h_k, h_v, h_out, h_positions, n_seqs: int, h_slot_ids=None):
         """forward_token's boundary (forward/decode.rs:567-626) for this path: host buffers in and out."""
         import ctypes as C
