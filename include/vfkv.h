@@ -350,6 +350,19 @@ int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
  * warp; 4x2, 4x3 or 8x3, 0x0 = choose per call (4x2, or 8x3 when the grid has at most one CTA per
  * SM).  The reference has fixed workgroup shapes; this is a measurement knob. */
 int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages);
+/* Programmatic dependent launch of the tensor-core attention kernel, the CUDA counterpart of
+ * relaxing the full pipeline barrier the reference records between dispatches
+ * (src/backend/vulkan/forward/runs.rs:1541, executor/attention.rs:583-596) to the buffers that
+ * really depend on one another.
+ *   0  off: a kernel starts when the previous work in the stream has finished (default).
+ *   1  the kernel may be scheduled while its predecessor in the stream drains; it waits for the
+ *      predecessor before it reads or writes any global memory.  Always safe.
+ *   2  as 1, but it reads the position / slot arrays and prefetches this layer's K/V rows before
+ *      that wait.  The caller promises that the kernel enqueued immediately before on the stream
+ *      writes neither those arrays nor this layer's cache rows (true for consecutive layers of a
+ *      decode step, and for a forward pass whose preceding kernel is a projection or RoPE).
+ *      Q, the token to append and all outputs are still touched only after the wait. */
+int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
 /* Latency analysis of the tensor-core attention kernel: while d_buffer is non-NULL, thread 0 of
  * every CTA stores 16 x uint64 nanosecond timestamps (globaltimer) at fixed phases -- 0 entry,
  * 1 range known, 2 barriers ready, 3 Q ready, 4 first tile landed, 5 stream done, 6 CTA joined,

@@ -355,3 +355,62 @@ def test_attend_argument_errors(ctx):
         assert float(out.abs().max()) == 0.0
     finally:
         rig.close()
+
+
+@pytest.mark.parametrize("dtype", [vf.KvDtype.F8, vf.KvDtype.F16])
+def test_decode_token_kernel_shapes_dependent_launch_and_graph_replay(ctx, dtype):
+    """vfkv_decode_token (every layer in one call) under each tensor-core kernel shape and each
+    dependent-launch mode, launched directly and replayed from a CUDA graph: same results."""
+    import torch
+    hq, hkv, d, max_seq, n_layers, n_seqs = 32, 8, 128, 900, 3, 2
+    rng = np.random.default_rng(71)
+    pos = np.array([899, 400], np.uint32)
+    fp8 = dtype == vf.KvDtype.F8
+    kc = encode_cache(kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0), int(dtype))
+    vc = encode_cache(kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0), int(dtype))
+    q = rng.standard_normal((n_layers, n_seqs, hq, d), dtype=np.float32)
+    kn = kv_values(rng, (n_layers, n_seqs, hkv, d), outlier_frac=0.0)
+    vn = kv_values(rng, (n_layers, n_seqs, hkv, d), outlier_frac=0.0)
+    want = []
+    for l in range(n_layers):
+        kk, vv = kc[l].copy(), vc[l].copy()
+        want.append(oracle.decode_step(q[l], kn[l], vn[l], kk, vv, int(dtype), n_seqs, max_seq, hq, hkv, d, pos + 1))
+    L = ctx._lib
+    stream = torch.cuda.Stream()
+    rig = Rig(ctx, dtype, hq, hkv, d, max_seq, n_layers=n_layers, n_slots=n_seqs, n_splits=5)
+    try:
+        dq, dk, dv, dpos = to_dev(q), to_dev(kn), to_dev(vn), to_dev(pos)
+        out = torch.zeros(n_layers, n_seqs, hq, d, device="cuda")
+        rig.fwd.stream = stream.cuda_stream
+        for tune in ((4, 2), (4, 3), (8, 3), (0, 0)):
+            for mode in (0, 1, 2):
+                ctx.check(L.vfkv_ctx_set_attn_tuning(ctx.handle, *tune))
+                ctx.check(L.vfkv_ctx_set_dependent_launch(ctx.handle, mode))
+                for l in range(n_layers):
+                    for s in range(n_seqs):
+                        rig.put(l, s, kc[l, s], vc[l, s])        # restore the rows the step overwrites
+                torch.cuda.synchronize()
+                with torch.cuda.stream(stream):
+                    out.zero_()
+                    rig.fwd.decode_token(dq, dk, dv, out, None, dpos, n_seqs, 900)
+                stream.synchronize()
+                got = out.cpu().numpy()
+                for l in range(n_layers):
+                    check(got[l], want[l], dtype)
+        # graph replay of the last configuration's successor: default shape, mode 2
+        ctx.check(L.vfkv_ctx_set_attn_tuning(ctx.handle, 0, 0))
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            rig.fwd.decode_token(dq, dk, dv, out, None, dpos, n_seqs, 900)
+        for _ in range(3):
+            with torch.cuda.stream(stream):
+                out.zero_()
+                g.replay()
+            stream.synchronize()
+            got = out.cpu().numpy()
+            for l in range(n_layers):
+                check(got[l], want[l], dtype)
+    finally:
+        ctx.check(L.vfkv_ctx_set_attn_tuning(ctx.handle, 0, 0))
+        ctx.check(L.vfkv_ctx_set_dependent_launch(ctx.handle, 0))
+        rig.close()

@@ -186,6 +186,13 @@ int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages)
     return VFKV_OK;
 }
 
+int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode)
+{
+    if (!ctx || mode > 2) return VFKV_ERR_INVALID;
+    ctx->pdl = mode;
+    return VFKV_OK;
+}
+
 int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer)
 {
     if (!ctx) return VFKV_ERR_INVALID;

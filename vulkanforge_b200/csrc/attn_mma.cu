@@ -176,6 +176,7 @@ struct MmaParams {
     uint32_t *counters;     // one ticket per (sequence, kv-head); zero between launches
     const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
     unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0
+    uint32_t pdl;                 // 0 plain launch, 1 dependent launch, 2 dependent launch with early K/V prefetch
 };
 
 // Phase timestamps for latency analysis; costs one predicated branch when tracing is off.
@@ -314,6 +315,15 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // element layout this thread needs: FP8  d = 32ks + 4tig + i  and  32ks + 16 + 4tig + i   (i < 4)
     //                                   F16  d = 16ks + 2tig + i  and  16ks + 8 + 2tig + i    (i < 2)
     float qv[RS][KSTEPS][4], qv2[RS][KSTEPS][4];
+    // Programmatic dependent launch: this grid lets its successor in the stream begin as soon as
+    // all of this grid's CTAs are running, and itself waits for its predecessor before it touches
+    // anything the predecessor may have produced.  mp.pdl == 2 is the caller's promise that the
+    // predecessor writes neither the position / slot arrays nor this layer's cache rows, so the
+    // K/V prefetch may start before the wait; Q, the new token and every store come after it.
+    // Both instructions do nothing in a launch without the attribute.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (mp.pdl != 2u) asm volatile("griddepcontrol.wait;" ::: "memory");
+    auto load_q = [&]() {
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
         const uint32_t hrow = gid + 8 * r;
@@ -334,6 +344,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             }
         }
     }
+    };
+    if (mp.pdl != 2u) load_q();
 
     VFKV_TRACE(0);
     uint32_t slot, start, len, begin, end;
@@ -371,6 +383,11 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (lane == 0) {
         const uint32_t pre = my_tiles < uint32_t(kStages) ? my_tiles : uint32_t(kStages);
         for (uint32_t n = 0; n < pre; ++n) issue(n);
+    }
+
+    if (mp.pdl == 2u) {       // the prefetch is in flight; now wait for the predecessor, then read Q
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        load_q();
     }
 
     // ---- fused append (KvWrite of the decode step): the CTA whose range ends at the sequence's
@@ -811,7 +828,18 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
         dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
         {
             ProfScope ps(ctx, VFKV_PROF_FA_SPLIT, st);
-            kern<<<grid, W * 32, S::SMEM_BYTES, st>>>(tk, tv, mp);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid;
+            cfg.blockDim = dim3(W * 32);
+            cfg.dynamicSmemBytes = S::SMEM_BYTES;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = mp.pdl ? 1 : 0;
+            cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tk, tv, mp);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "tensor-core attention launch");
         }
         ctx->launches++;
         return check_cuda(ctx, cudaGetLastError(), "tensor-core attention launch");
@@ -879,6 +907,7 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     mp.a = make_params(ctx, ws, a, n_splits);
     mp.counters = ws ? ws->counters : nullptr;
     mp.trace = ctx->d_trace;
+    mp.pdl = ctx->pdl;
     mp.k_new = a.k_new;
     mp.v_new = a.v_new;
     if ((reinterpret_cast<uintptr_t>(a.k_new) | reinterpret_cast<uintptr_t>(a.v_new)) % 16 != 0)
