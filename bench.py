@@ -46,7 +46,7 @@ WORKLOADS = {
     "gemma_f16_ctx32768_b8": dict(n_layers=6, hq=16, hkv=8, d=256, dtype="F16", batch=8, ctx=32768,
                                   n_splits=0, softcap=50.0, windows=[1024, 1024, 1024, 1024, 1024, 0]),
     "long_fp8_ctx131072_b1": dict(n_layers=1, hq=64, hkv=8, d=128, dtype="F8", batch=1, ctx=131072,
-                                  n_splits=0, softcap=0.0, windows=None),
+                                  n_splits=0, softcap=0.0, windows=None, shard="positions"),
 }
 DEFAULT_WORKLOAD = "qwen3_8b_fp8_ctx8192_b1"
 METRIC = "kv_append_decode_attn_us_per_token_layer"
@@ -430,6 +430,115 @@ def run_ours(args, w, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_position_sharded(args, w, rank, world, local_rank):
+    """One long sequence cut into round-robin pages over the ranks (strong scaling): per step the
+    owner of the new position appends, every rank attends over its pages, the (m, l, o) partials are
+    all-gathered over NCCL and merged on every rank."""
+    import torch
+    import torch.distributed as dist
+    import vulkanforge_b200 as vf
+    from vulkanforge_b200.shard import PositionShards, ShardedSequenceDecoder
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = vf.Context(local_rank)
+    sh = PositionShards(world, 256)
+    L, hq, hkv, d = w["ctx"], w["hq"], w["hkv"], w["d"]
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(w["n_layers"], hkv, d, sh.local_capacity(L)), vf.KvDtype[w["dtype"]])
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=w["n_splits"])
+    dec = ShardedSequenceDecoder(fwd, sh, rank)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    n_local = sh.local_len(L - 1, rank)
+    for p in range(0, n_local, 4096):                      # this rank's pages of the 131071 earlier tokens
+        m = min(4096, n_local - p)
+        kv = torch.randn(2, m, hkv * d, device="cuda", generator=g)
+        mask = torch.rand(2, m, hkv * d, device="cuda", generator=g) < 0.01
+        kv = torch.where(mask, kv * 20.0, kv)
+        fwd.b_step_kv_write(0, kv[0], kv[1], m, p, 0)
+    chunk = torch.randn(2, 512, hkv * d, device="cuda", generator=g)   # a 512-token chunked-prefill append
+    q = torch.randn(hq, d, device="cuda", generator=g)
+    kn = torch.randn(2, 1, hkv * d, device="cuda", generator=g)
+    out = torch.zeros(hq, d, device="cuda")
+
+    def step():
+        dec.append(0, kn[0], kn[1], L - 1)
+        dec.attend(0, q, out, L)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+    fwd.stream = stream.cuda_stream
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step()
+    barrier()
+    n0 = ctx.launch_count()
+    with torch.cuda.stream(stream):
+        step()
+    barrier()
+    launches = (ctx.launch_count() - n0) * args.steps
+    run, launch_kind = step, "stream launches"
+    if not args.no_graph:
+        try:                                               # the whole step, collective included, as one graph
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            run, launch_kind = graph.replay, "one CUDA graph replay per token (NCCL all-gather captured)"
+        except Exception as exc:                           # capture of the collective refused: plain launches
+            launch_kind = f"stream launches (graph capture failed: {type(exc).__name__})"
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            run()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.finish()
+    fwd.stream = None
+    # the chunked-prefill append of the same config, timed on its own
+    base = max(0, L - 1 - 512)
+    for _ in range(3):
+        dec.prefill(0, chunk[0].view(512, hkv, d), chunk[1].view(512, hkv, d), base, 512)
+    barrier()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for _ in range(args.steps):
+        dec.prefill(0, chunk[0].view(512, hkv, d), chunk[1].view(512, hkv, d), base, 512)
+    p1.record()
+    barrier()
+    prefill_ms = p0.elapsed_time(p1) / args.steps
+    t = torch.tensor([ms, prefill_ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tot = torch.tensor([launches], device="cuda", dtype=torch.int64)
+    dist.all_reduce(tot)
+    ctx.poll()
+    if rank == 0:
+        ms, prefill_ms = float(t[0]), float(t[1])
+        step_bytes = algorithmic_bytes(w, [L], 0)
+        line = {"metric": METRIC, "value": ms * 1e3 / args.steps / w["n_layers"], "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32 (fp8/f16 storage)", "data": "synthetic",
+                "config": {"workload": args.workload, "n_layers": w["n_layers"], "n_q_heads": hq, "n_kv_heads": hkv,
+                           "head_dim": d, "kv_dtype": w["dtype"], "context": L,
+                           "parallelism": f"positions sharded x{world} in 256-row pages, NCCL all-gather of (m, l, o)",
+                           "collective_bytes_per_rank": (d + 2) * hq * 4, "launch": launch_kind,
+                           "l2": "per-GPU share of the cache is %d MiB per step" % (step_bytes // world >> 20)},
+                "achieved_gbs_whole_step": step_bytes * args.steps / (ms * 1e-3) / 1e9,
+                "prefill_chunk_512_us": prefill_ms * 1e3, "clocks": clocks, "gpu_launches": int(tot[0])}
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -453,6 +562,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, w, rank, world)
+        return
+    if world > 1 and w.get("shard") == "positions":
+        run_position_sharded(args, w, rank, world, local_rank)
         return
     run_ours(args, w, rank, world, local_rank)
 

@@ -327,6 +327,11 @@ int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, c
                             uint32_t n_parts, uint32_t n_rows, uint32_t head_dim, float *d_out,
                             void *stream);
 
+/* The same merge over the buffer an all-gather of per-GPU partials produces: n_parts blocks of
+ * n_rows*(head_dim+2) floats, each block m[n_rows], l[n_rows], o[n_rows][head_dim]. */
+int32_t vfkv_merge_partials_packed(vfkv_ctx *ctx, const float *d_packed, uint32_t n_parts,
+                                   uint32_t n_rows, uint32_t head_dim, float *d_out, void *stream);
+
 /* ---------------------------------------------------------------------- */
 /* device-memory helpers for hosts without a CUDA binding of their own       */
 /* ---------------------------------------------------------------------- */

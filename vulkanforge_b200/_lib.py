@@ -79,6 +79,7 @@ SIGNATURES = {
     "vfkv_decode_token_host": (i32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, vp, f32, f32, u32, vp]),
     "vfkv_attend_partial": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp, vp, vp]),
     "vfkv_merge_partials": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, vp]),
+    "vfkv_merge_partials_packed": (i32, [vp, vp, u32, u32, u32, vp, vp]),
     "vfkv_malloc": (i32, [vp, u64, C.POINTER(vp)]),
     "vfkv_free": (i32, [vp, vp]),
     "vfkv_malloc_host": (i32, [vp, u64, C.POINTER(vp)]),

@@ -749,6 +749,16 @@ int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, c
     return launch_merge_partials(ctx, d_m, d_l, d_o, n_parts, n_rows, head_dim, d_out, as_stream(stream));
 }
 
+int32_t vfkv_merge_partials_packed(vfkv_ctx *ctx, const float *d_packed, uint32_t n_parts, uint32_t n_rows,
+                                   uint32_t head_dim, float *d_out, void *stream)
+{
+    if (!ctx) return VFKV_ERR_INVALID;
+    if (!d_packed || !d_out) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_merge_partials_packed: null argument");
+    if (head_dim == 0 || head_dim > 512) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_merge_partials_packed: head_dim must be 1..512");
+    DeviceGuard g(ctx->device);
+    return launch_merge_partials_packed(ctx, d_packed, n_parts, n_rows, head_dim, d_out, as_stream(stream));
+}
+
 /* ---- device-memory helpers -------------------------------------------------- */
 
 int32_t vfkv_malloc(vfkv_ctx *ctx, uint64_t bytes, void **d_out)

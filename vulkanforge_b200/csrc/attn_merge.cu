@@ -9,10 +9,10 @@ namespace vfkv {
 // flash_attn_reduce.comp:51-80: out = sum_i o_i e^(m_i - M) / sum_i l_i e^(m_i - M) with M the
 // maximum of the partial maxima; the final multiply by 1/sum is skipped when
 // the caller wants the unnormalised triple (sequence-dimension sharding).
-// Index of partial i of row r: i*part_stride + r*row_stride.
+// Partial i of row r: m and l at i*ml_part + r*ml_row, o at i*o_part + r*o_row (+ dim), all in floats.
 __global__ void __launch_bounds__(128)
 merge_kernel(const float *__restrict__ pm, const float *__restrict__ pl, const float *__restrict__ po,
-             uint32_t n_parts, uint64_t part_stride, uint64_t row_stride, uint32_t head_dim,
+             uint32_t n_parts, uint64_t ml_part, uint64_t ml_row, uint64_t o_part, uint64_t o_row, uint32_t head_dim,
              float *__restrict__ out, float *__restrict__ out_m, float *__restrict__ out_l,
              float *__restrict__ out_o)
 {
@@ -24,17 +24,18 @@ merge_kernel(const float *__restrict__ pm, const float *__restrict__ pl, const f
     // every load independent of the others.
     float gmax = kMaskedScore;
 #pragma unroll 8
-    for (uint32_t i = 0; i < n_parts; ++i) gmax = fmaxf(gmax, pm[uint64_t(i) * part_stride + row * row_stride]);
+    for (uint32_t i = 0; i < n_parts; ++i) gmax = fmaxf(gmax, pm[uint64_t(i) * ml_part + row * ml_row]);
     float gsum = 0.f;
 #pragma unroll 4
     for (uint32_t i = 0; i < n_parts; ++i) {
-        const uint64_t pi = uint64_t(i) * part_stride + row * row_stride;
+        const uint64_t pi = uint64_t(i) * ml_part + row * ml_row;
+        const uint64_t oi = uint64_t(i) * o_part + row * o_row;
         const float kn = __expf(pm[pi] - gmax);
         gsum = fmaf(pl[pi], kn, gsum);
 #pragma unroll
         for (int j = 0; j < kMaxDims; ++j) {
             uint32_t d = threadIdx.x + j * 128;
-            float t = d < head_dim ? po[pi * head_dim + d] : 0.f;
+            float t = d < head_dim ? po[oi + d] : 0.f;
             acc[j] = fmaf(t, kn, acc[j]);
         }
     }
@@ -55,7 +56,8 @@ int32_t launch_merge_ws(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
 {
     const uint32_t rows = a.seq.n_seqs * a.n_q_heads;
     ProfScope ps(ctx, VFKV_PROF_FA_REDUCE, st);
-    merge_kernel<<<rows, 128, 0, st>>>(ws->part_m, ws->part_l, ws->part_o, n_splits, 1, n_splits,
+    const uint64_t D = a.kv.head_dim;
+    merge_kernel<<<rows, 128, 0, st>>>(ws->part_m, ws->part_l, ws->part_o, n_splits, 1, n_splits, D, n_splits * D,
                                       a.kv.head_dim, a.out, a.out_m, a.out_l, a.out_o);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "merge launch");
@@ -67,10 +69,24 @@ int32_t launch_merge_partials(vfkv_ctx *ctx, const float *m, const float *l, con
 {
     if (n_rows == 0) return VFKV_OK;
     ProfScope ps(ctx, VFKV_PROF_FA_REDUCE, st);
-    merge_kernel<<<n_rows, 128, 0, st>>>(m, l, o, n_parts, n_rows, 1, head_dim, out, nullptr, nullptr,
-                                        nullptr);
+    merge_kernel<<<n_rows, 128, 0, st>>>(m, l, o, n_parts, n_rows, 1, uint64_t(n_rows) * head_dim, head_dim,
+                                        head_dim, out, nullptr, nullptr, nullptr);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "merge_partials launch");
+}
+
+// One block of n_rows*(head_dim+2) floats per part: m[n_rows], l[n_rows], o[n_rows][head_dim] --
+// the layout an all-gather of per-GPU partials produces.
+int32_t launch_merge_partials_packed(vfkv_ctx *ctx, const float *packed, uint32_t n_parts, uint32_t n_rows,
+                                     uint32_t head_dim, float *out, cudaStream_t st)
+{
+    if (n_rows == 0) return VFKV_OK;
+    const uint64_t block = uint64_t(n_rows) * (head_dim + 2);
+    ProfScope ps(ctx, VFKV_PROF_FA_REDUCE, st);
+    merge_kernel<<<n_rows, 128, 0, st>>>(packed, packed + n_rows, packed + 2 * uint64_t(n_rows), n_parts, block, 1,
+                                        block, head_dim, head_dim, out, nullptr, nullptr, nullptr);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "merge_partials_packed launch");
 }
 
 // Split count when the caller passes 0.  The reference always cuts at 64

@@ -148,6 +148,9 @@ int32_t launch_merge_partials(vfkv_ctx *ctx, const float *m, const float *l, con
                               uint32_t n_parts, uint32_t n_rows, uint32_t head_dim, float *out,
                               cudaStream_t st);
 
+int32_t launch_merge_partials_packed(vfkv_ctx *ctx, const float *packed, uint32_t n_parts, uint32_t n_rows,
+                                     uint32_t head_dim, float *out, cudaStream_t st);
+
 // attention implementations
 uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile);
 int32_t launch_attn_generic(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,

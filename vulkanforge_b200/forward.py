@@ -162,3 +162,8 @@ class CudaForward:
     def merge_partials(self, m, l, o, n_parts: int, n_rows: int, head_dim: int, out):
         self.ctx.check(self._L.vfkv_merge_partials(self.ctx.handle, ptr(m), ptr(l), ptr(o), n_parts, n_rows,
                                                    head_dim, ptr(out), self.stream))
+
+    def merge_partials_packed(self, packed, n_parts: int, n_rows: int, head_dim: int, out):
+        """Merge of all-gathered partials: n_parts blocks of m[n_rows], l[n_rows], o[n_rows][head_dim]."""
+        self.ctx.check(self._L.vfkv_merge_partials_packed(self.ctx.handle, ptr(packed), n_parts, n_rows,
+                                                          head_dim, ptr(out), self.stream))

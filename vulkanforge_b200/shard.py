@@ -1,0 +1,138 @@
+"""Multi-GPU partitioning of the KV-cache hot path (one process per GPU).
+
+VulkanForge itself is single-GPU and single-sequence (``docs/BENCHMARKS.md``: "VulkanForge is
+single-stream"; one ``current_seq_len`` in ``src/backend/vulkan/kv_cache.rs:208``), so nothing
+here has a counterpart in it.  The path shards in two ways:
+
+* by sequence -- every sequence lives wholly on one GPU; no communication on the data path
+  (``assign_sequences``);
+* by position -- one long sequence is cut into pages that are dealt round-robin to the GPUs
+  (``PositionShards``).  Each GPU attends over the pages it holds and produces, per q-head, the
+  softmax partial (max m, sum l, unnormalised output o).  One all-gather of those partials
+  (``Hq * (D + 2)`` floats per GPU) followed by the log-sum-exp merge of
+  ``vk_shaders/flash_attn_reduce.comp:51-80`` gives the full result on every GPU.
+
+The collective is ``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests); the merge is
+``vfkv_merge_partials_packed``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence
+
+
+def assign_sequences(lengths: Sequence[int], world_size: int) -> List[List[int]]:
+    """Longest-first greedy balancing of sequences over ranks by total context length.
+    Returns, per rank, the indices of the sequences it owns."""
+    loads = [0] * world_size
+    owned: List[List[int]] = [[] for _ in range(world_size)]
+    for i in sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i)):
+        r = min(range(world_size), key=lambda r: (loads[r], r))
+        owned[r].append(i)
+        loads[r] += int(lengths[i])
+    for o in owned:
+        o.sort()
+    return owned
+
+
+@dataclass(frozen=True)
+class PositionShards:
+    """Round-robin pages of ``page`` positions: global position p is held by rank
+    ``(p // page) % world_size`` at local position ``((p // page) // world_size) * page + p % page``.
+    Appends therefore rotate over the GPUs instead of always landing on the last one, and every
+    rank's share of a context of any length differs by at most one page."""
+    world_size: int
+    page: int = 256
+
+    def owner(self, pos: int) -> int:
+        return (pos // self.page) % self.world_size
+
+    def local_pos(self, pos: int) -> int:
+        return ((pos // self.page) // self.world_size) * self.page + pos % self.page
+
+    def local_len(self, seq_len: int, rank: int) -> int:
+        """How many of the positions [0, seq_len) rank holds (they occupy local [0, local_len))."""
+        full_pages, rest = divmod(seq_len, self.page)
+        n = (full_pages // self.world_size) * self.page
+        extra = full_pages % self.world_size
+        if rank < extra:
+            n += self.page
+        elif rank == extra:
+            n += rest
+        return n
+
+    def local_capacity(self, max_seq_len: int) -> int:
+        """Rows a rank's slab needs for contexts up to max_seq_len."""
+        pages = (max_seq_len + self.page - 1) // self.page
+        return ((pages + self.world_size - 1) // self.world_size) * self.page
+
+    def global_positions(self, seq_len: int, rank: int) -> List[int]:
+        """The global positions behind local 0 .. local_len-1, in local order."""
+        out = []
+        for page_id in range(rank, (seq_len + self.page - 1) // self.page, self.world_size):
+            lo = page_id * self.page
+            out.extend(range(lo, min(lo + self.page, seq_len)))
+        return out
+
+
+def packed_partial_floats(n_q_heads: int, head_dim: int) -> int:
+    """Floats one rank contributes: m[Hq], l[Hq], o[Hq][D]."""
+    return n_q_heads * (head_dim + 2)
+
+
+def all_gather_partials(local_packed, group=None):
+    """All-gathers every rank's packed partial (a 1-D float32 tensor) into a
+    [world_size, packed_floats] tensor on the same device."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    n = local_packed.numel()
+    out = torch.empty(world * n, dtype=local_packed.dtype, device=local_packed.device)
+    dist.all_gather_into_tensor(out, local_packed.contiguous().view(-1), group=group)
+    return out.view(world, n)
+
+
+class ShardedSequenceDecoder:
+    """Position-sharded decode attention for one long sequence on this rank's GPU.
+
+    ``fwd`` is this rank's ``CudaForward`` over a cache whose ``max_seq_len`` is at least
+    ``shards.local_capacity(global max)``; slot 0 holds this rank's pages.
+    """
+
+    def __init__(self, fwd, shards: PositionShards, rank: int, group=None):
+        import torch
+        self.fwd, self.shards, self.rank, self.group = fwd, shards, rank, group
+        hd = fwd.kv_cache.config.head_dim
+        self.n_rows, self.head_dim = fwd.n_heads, hd
+        self.packed = torch.zeros(packed_partial_floats(fwd.n_heads, hd), dtype=torch.float32, device="cuda")
+
+    def append(self, layer: int, k_src, v_src, position: int) -> bool:
+        """Stores the token of global ``position`` if this rank owns its page; returns whether it did."""
+        if self.shards.owner(position) != self.rank:
+            return False
+        self.fwd.step_kv_write(layer, k_src, v_src, self.shards.local_pos(position), 0)
+        return True
+
+    def prefill(self, layer: int, k_src, v_src, base_pos: int, n_tokens: int) -> int:
+        """Chunked-prefill append: stores the rows of [base_pos, base_pos + n_tokens) this rank owns,
+        one call per page piece.  k_src / v_src are torch tensors [n_tokens][kv_heads][D]."""
+        done, p, end = 0, base_pos, base_pos + n_tokens
+        while p < end:
+            stop = min(end, (p // self.shards.page + 1) * self.shards.page)
+            if self.shards.owner(p) == self.rank:
+                i = p - base_pos
+                self.fwd.b_step_kv_write(layer, k_src[i:i + stop - p], v_src[i:i + stop - p], stop - p,
+                                         self.shards.local_pos(p), 0)
+                done += stop - p
+            p = stop
+        return done
+
+    def attend(self, layer: int, q, out, seq_len: int):
+        """Attention of one query token over global positions [0, seq_len): local partial, one
+        all-gather, merge.  ``out`` [Hq][D] is complete on every rank."""
+        n, hd = self.n_rows, self.head_dim
+        m, l, o = self.packed[:n], self.packed[n:2 * n], self.packed[2 * n:]
+        self.fwd.attend_partial(layer, q, 0, self.shards.local_len(seq_len, self.rank), m, l, o)
+        gathered = all_gather_partials(self.packed, self.group)
+        self.fwd.merge_partials_packed(gathered, gathered.shape[0], n, hd, out)
+        return out
