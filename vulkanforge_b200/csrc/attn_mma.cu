@@ -14,13 +14,15 @@
 //          cp.async.bulk.tensor.2d boxes of [TP positions x 128 bytes]
 //          (128-byte swizzle) for K and V and the warp waits on its own
 //          mbarrier; there is no CTA-wide synchronisation while streaming.
-//   FP8  : mma.sync.m16n8k32.e4m3 straight on the cache bytes -- the
-//          dequantisation is the tensor core's exact E4M3 product.  Q is split
-//          into two E4M3 terms (rows 0-7 and 8-15 of the M tile) and so is P,
-//          which keeps operand rounding near 2^-10.  V is transposed for the
-//          P.V product in registers (prmt).
-//   F16  : mma.sync.m16n8k16.f16 with ldmatrix / ldmatrix.trans; with up to 8 q-heads per
-//          kv-head Q and P are likewise split into two half-precision terms.
+//   FP8  : the E4M3 codes go from shared memory to registers (ldmatrix for K, ld.shared + prmt
+//          pairing for V) and are widened there to half precision (cvt.rn.f16x2.e4m3x2, exact):
+//          the FP8 -> F16 cache read fused into the load.  The products run on
+//          mma.sync.m16n8k16.f16.  (mma.sync with e4m3 operands measured slower here: each one
+//          costs a dozen conversion instructions on the ALU pipe on top of two f16 MMAs.)
+//   F16  : mma.sync.m16n8k16.f16 with ldmatrix / ldmatrix.trans.
+//   both : with up to 8 q-heads per kv-head the M tile has rows to spare, so Q and P are each
+//          split into a high and a low half-precision term (rows 0-7 / 8-15) and the result
+//          carries f32-grade operand precision.
 //   tail : warp partials merge in shared memory; the last CTA of a
 //          (sequence, kv-head) to finish merges the split partials with the
 //          reduce shader's update (flash_attn_reduce.comp:51-80), so there is no
@@ -39,8 +41,6 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr float kPShift = 8.0f;       // FP8 P operand is 2^8 * p: keeps small p out of E4M3's subnormals
-constexpr float kPScale = 256.0f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -111,14 +111,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t base, uint32_t &r0, u
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"(base), "n"(IMM));
 }
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
 {
     asm volatile(
@@ -145,23 +137,6 @@ __device__ __forceinline__ float fast_exp2(float x)
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// Two values -> (hi, lo) E4M3 pairs with hi + lo ~= value, residual taken in half precision.
-__device__ __forceinline__ void split_e4m3x2(float x0, float x1, uint32_t &hi, uint32_t &lo)
-{
-    __half2 h = __floats2half2_rn(x0, x1);
-    uint32_t hb = *reinterpret_cast<uint32_t *>(&h);
-    uint16_t h8;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(h8) : "r"(hb));
-    uint32_t back;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(back) : "h"(h8));
-    __half2 r = __hsub2(h, *reinterpret_cast<__half2 *>(&back));
-    uint32_t rb = *reinterpret_cast<uint32_t *>(&r);
-    uint16_t l8;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(l8) : "r"(rb));
-    hi = h8;
-    lo = l8;
-}
-
 // Two values -> (hi, lo) half2 pairs with hi + lo == value to about 2^-22.
 __device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t &hi, uint32_t &lo)
 {
@@ -210,59 +185,78 @@ __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, uint32_t chunk, uin
 
 // ---- unrolled tile steps; the recursion only exists to make the shared-memory offsets immediates ----
 
+// Four E4M3 codes -> two half2: bytes 0,1 and bytes 2,3 (exact).
+__device__ __forceinline__ void e4m3x4_to_half2x2(uint32_t w, uint32_t &lo, uint32_t &hi)
+{
+    asm("{\n\t.reg .b16 a, b;\n\t"
+        "mov.b32 {a, b}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, a;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+        : "=r"(lo), "=r"(hi)
+        : "r"(w));
+}
+
 // S += Q K^T for one 32-byte step of the head slice: N blocks JP*2 and JP*2+1 (16 positions).
+// F16 cache: 32 bytes = 16 dims = one MMA, a = its A fragment, a2 unused.
+// FP8 cache: 32 bytes = 32 dims = two MMAs (a, a2).  ldmatrix hands each thread four consecutive
+// codes of its position; they are widened to half precision in registers (the cache read's
+// FP8 -> F16 step, kv_fp8_to_f16.comp, fused into the load) and fed as k slots {2tig, 2tig+1} and
+// {8+2tig, 9+2tig}, the order the Q fragments were built in.
 template <bool FP8, int NB, int IMM, int JP = 0>
-__device__ __forceinline__ void qk_blocks(uint32_t base, const uint32_t (&a)[4], float (&sc)[NB][4])
+__device__ __forceinline__ void qk_blocks(uint32_t base, const uint32_t (&a)[4], const uint32_t (&a2)[4],
+                                          float (&sc)[NB][4])
 {
     if constexpr (JP < NB / 2) {
         uint32_t r0, r1, r2, r3;
         ldmatrix_x4<IMM + JP * 16 * 128>(base, r0, r1, r2, r3);
         if constexpr (FP8) {
-            mma_e4m3(sc[2 * JP], a, r0, r1);
-            mma_e4m3(sc[2 * JP + 1], a, r2, r3);
+            uint32_t b0, b1;
+            e4m3x4_to_half2x2(r0, b0, b1); mma_f16(sc[2 * JP], a, b0, b1);
+            e4m3x4_to_half2x2(r1, b0, b1); mma_f16(sc[2 * JP], a2, b0, b1);
+            e4m3x4_to_half2x2(r2, b0, b1); mma_f16(sc[2 * JP + 1], a, b0, b1);
+            e4m3x4_to_half2x2(r3, b0, b1); mma_f16(sc[2 * JP + 1], a2, b0, b1);
         } else {
             mma_f16(sc[2 * JP], a, r0, r1);
             mma_f16(sc[2 * JP + 1], a, r2, r3);
         }
-        qk_blocks<FP8, NB, IMM, JP + 1>(base, a, sc);
+        qk_blocks<FP8, NB, IMM, JP + 1>(base, a, a2, sc);
     }
 }
 // kb[u] = K tile base + this lane's swizzled offset for units 2u, 2u+1
-template <bool FP8, int TP, int NB, int KSTEPS, int KS = 0>
-__device__ __forceinline__ void qk_steps(const uint32_t (&kb)[4], const uint32_t (&qa)[KSTEPS][4], float (&sc)[NB][4])
+template <bool FP8, int TP, int NB, int KSTEPS, int QSTEPS, int KS = 0>
+__device__ __forceinline__ void qk_steps(const uint32_t (&kb)[4], const uint32_t (&qa)[QSTEPS][4], float (&sc)[NB][4])
 {
     if constexpr (KS < KSTEPS) {
-        qk_blocks<FP8, NB, (KS / 4) * TP * 128>(kb[KS % 4], qa[KS], sc);
-        qk_steps<FP8, TP, NB, KSTEPS, KS + 1>(kb, qa, sc);
+        if constexpr (FP8) qk_blocks<FP8, NB, (KS / 4) * TP * 128>(kb[KS % 4], qa[2 * KS], qa[2 * KS + 1], sc);
+        else qk_blocks<FP8, NB, (KS / 4) * TP * 128>(kb[KS % 4], qa[KS], qa[KS], sc);
+        qk_steps<FP8, TP, NB, KSTEPS, QSTEPS, KS + 1>(kb, qa, sc);
     }
 }
 // FP8 O += P V for dims 32Q .. 32Q+31.  vb[2u + e] = V tile base + this lane's offset for rows of
-// parity e and unit pair u.  The eight words are dims 32Q + 4*gid + {0..3} of positions
-// {2tig, 2tig+1, 2tig+8, 2tig+9} and the same + 16; a 4x4 byte transpose (prmt) turns them into
-// B fragments that hold four positions of one dim.
+// parity e and unit pair u.  A word holds dims 32Q + 4*gid + {0..3} of one position; prmt pairs the
+// codes of two positions dim by dim, the widening cvt turns each pair into the half2 B fragment of
+// one 8-dim output block.  pa[h] is the A fragment of positions 16h .. 16h+15.
 template <int TP, int D, int Q = 0>
-__device__ __forceinline__ void pv_fp8(const uint32_t (&vb)[8], const uint32_t (&pa)[4], float (&acc)[D / 8][4])
+__device__ __forceinline__ void pv_fp8(const uint32_t (&vb)[8], const uint32_t (&pa)[2][4], float (&acc)[D / 8][4])
 {
     if constexpr (Q < D / 32) {
         constexpr int C = (Q / 4) * TP * 128, u = Q % 4;
         const uint32_t be = vb[2 * u], bo = vb[2 * u + 1];
         uint32_t w[8];
-        w[0] = lds32<C>(be);             w[1] = lds32<C>(bo);
-        w[2] = lds32<C + 8 * 128>(be);   w[3] = lds32<C + 8 * 128>(bo);
-        w[4] = lds32<C + 16 * 128>(be);  w[5] = lds32<C + 16 * 128>(bo);
-        w[6] = lds32<C + 24 * 128>(be);  w[7] = lds32<C + 24 * 128>(bo);
-        uint32_t b[2][4];
+        w[0] = lds32<C>(be);             w[1] = lds32<C>(bo);              // positions 2tig, 2tig+1
+        w[2] = lds32<C + 8 * 128>(be);   w[3] = lds32<C + 8 * 128>(bo);    // + 8
+        w[4] = lds32<C + 16 * 128>(be);  w[5] = lds32<C + 16 * 128>(bo);   // + 16
+        w[6] = lds32<C + 24 * 128>(be);  w[7] = lds32<C + 24 * 128>(bo);   // + 24
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const uint32_t lo01 = prmt(w[4 * h], w[4 * h + 1], 0x5140), hi01 = prmt(w[4 * h], w[4 * h + 1], 0x7362);
-            const uint32_t lo23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x5140), hi23 = prmt(w[4 * h + 2], w[4 * h + 3], 0x7362);
-            b[h][0] = prmt(lo01, lo23, 0x5410);
-            b[h][1] = prmt(lo01, lo23, 0x7632);
-            b[h][2] = prmt(hi01, hi23, 0x5410);
-            b[h][3] = prmt(hi01, hi23, 0x7632);
-        }
+            uint32_t b0[4], b1[4];       // per dim i: (pos, pos+1) and (pos+8, pos+9) as half2
+            e4m3x4_to_half2x2(prmt(w[4 * h], w[4 * h + 1], 0x5140), b0[0], b0[1]);
+            e4m3x4_to_half2x2(prmt(w[4 * h], w[4 * h + 1], 0x7362), b0[2], b0[3]);
+            e4m3x4_to_half2x2(prmt(w[4 * h + 2], w[4 * h + 3], 0x5140), b1[0], b1[1]);
+            e4m3x4_to_half2x2(prmt(w[4 * h + 2], w[4 * h + 3], 0x7362), b1[2], b1[3]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mma_e4m3(acc[4 * Q + i], pa, b[0][i], b[1][i]);
+            for (int i = 0; i < 4; ++i) mma_f16(acc[4 * Q + i], pa[h], b0[i], b1[i]);
+        }
         pv_fp8<TP, D, Q + 1>(vb, pa, acc);
     }
 }
@@ -428,7 +422,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // ---- Q fragments (A operand), scaled per head by a power of two into [128, 256) --------
     // FP8: rows 0-7 of the M tile hold the high E4M3 term of heads 0-7, rows 8-15 the low term.
     // F16: rows are heads 0-15.
-    uint32_t qa[KSTEPS][4];
+    constexpr int QSTEPS = D / 16;       // one A fragment per 16 dims
+    uint32_t qa[QSTEPS][4];
     float mult[RS];                      // score multiplier per logical row: scale / q_scale
     {
 #pragma unroll
@@ -449,15 +444,14 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
                 if constexpr (FP8) {
-                    uint32_t h01, l01, h23, l23;
-                    split_e4m3x2(qv[r][ks][0] * qs, qv[r][ks][1] * qs, h01, l01);
-                    split_e4m3x2(qv[r][ks][2] * qs, qv[r][ks][3] * qs, h23, l23);
-                    qa[ks][0] = h01 | (h23 << 16);
-                    qa[ks][1] = l01 | (l23 << 16);
-                    split_e4m3x2(qv2[r][ks][0] * qs, qv2[r][ks][1] * qs, h01, l01);
-                    split_e4m3x2(qv2[r][ks][2] * qs, qv2[r][ks][3] * qs, h23, l23);
-                    qa[ks][2] = h01 | (h23 << 16);
-                    qa[ks][3] = l01 | (l23 << 16);
+                    // 16-dim block 2ks holds dims 32ks + 4tig + {0..3} of this thread, block 2ks+1 the
+                    // same + 16.  Within a block the MMA's k slots {2tig, 2tig+1} are dims 4tig + {0, 1}
+                    // and slots {8+2tig, 9+2tig} are dims 4tig + {2, 3}: the order in which the bytes of
+                    // a K row arrive from ldmatrix.
+                    split_f16x2(qv[r][ks][0] * qs, qv[r][ks][1] * qs, qa[2 * ks][0], qa[2 * ks][1]);
+                    split_f16x2(qv[r][ks][2] * qs, qv[r][ks][3] * qs, qa[2 * ks][2], qa[2 * ks][3]);
+                    split_f16x2(qv2[r][ks][0] * qs, qv2[r][ks][1] * qs, qa[2 * ks + 1][0], qa[2 * ks + 1][1]);
+                    split_f16x2(qv2[r][ks][2] * qs, qv2[r][ks][3] * qs, qa[2 * ks + 1][2], qa[2 * ks + 1][3]);
                 } else if constexpr (SPLIT) {
                     split_f16x2(qv[r][ks][0] * qs, qv[r][ks][1] * qs, qa[ks][0], qa[ks][1]);
                     split_f16x2(qv2[r][ks][0] * qs, qv2[r][ks][1] * qs, qa[ks][2], qa[ks][3]);
@@ -541,7 +535,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         for (int j = 0; j < NB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
         {
             const uint32_t kb[4] = {kt + qk_sw[0], kt + qk_sw[1], kt + qk_sw[2], kt + qk_sw[3]};
-            qk_steps<FP8, TP, NB, KSTEPS>(kb, qa, sc);
+            qk_steps<FP8, TP, NB, KSTEPS, QSTEPS>(kb, qa, sc);
         }
 
         // ---- softmax bookkeeping in the log2 domain -------------------------------------------
@@ -595,12 +589,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             }
         }
         // p = 2^(x - m); a masked score is -1e30 against a finite m (every tile has a valid position),
-        // which gives exactly 0.  For FP8 the tensor-core operand is 2^kPShift * p so that small
-        // weights stay out of E4M3's subnormals; l is summed in the same units and the epilogue
-        // divides both out.
+        // which gives exactly 0.
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
-            const float mo = FP8 ? m[r] - kPShift : m[r];
+            const float mo = m[r];
 #pragma unroll
             for (int j = 0; j < NB; ++j)
 #pragma unroll
@@ -613,18 +605,13 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
         // ---- O += P V ----------------------------------------------------------------------------
         if constexpr (FP8) {
-            // A rows 0-7: high term of 256*p, rows 8-15: low term.  K slot 4*tig+i of the first half is
-            // position {2tig, 2tig+1, 8+2tig, 9+2tig}[i], of the second half the same + 16.
-            uint32_t pa[4];
-            {
-                uint32_t h0, l0, h1, l1;
-                split_e4m3x2(x[0][0][0], x[0][0][1], h0, l0);
-                split_e4m3x2(x[0][1][0], x[0][1][1], h1, l1);
-                pa[0] = h0 | (h1 << 16); pa[1] = l0 | (l1 << 16);
-                split_e4m3x2(x[0][2][0], x[0][2][1], h0, l0);
-                split_e4m3x2(x[0][3][0], x[0][3][1], h1, l1);
-                pa[2] = h0 | (h1 << 16); pa[3] = l0 | (l1 << 16);
-            }
+            // A rows 0-7: high half-precision term of p, rows 8-15: low term.  First k step: positions
+            // {2tig, 2tig+1} and {8+2tig, 9+2tig}; second k step: the same + 16.
+            uint32_t pa[2][4];
+            split_f16x2(x[0][0][0], x[0][0][1], pa[0][0], pa[0][1]);
+            split_f16x2(x[0][1][0], x[0][1][1], pa[0][2], pa[0][3]);
+            split_f16x2(x[0][2][0], x[0][2][1], pa[1][0], pa[1][1]);
+            split_f16x2(x[0][3][0], x[0][3][1], pa[1][2], pa[1][3]);
             uint32_t vb[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) vb[i] = vt + v_sw[i];
@@ -671,7 +658,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
         if (tig == 0) {
             sm_m[warp * NH + gid + 8 * r] = m[r];
-            sm_l[warp * NH + gid + 8 * r] = FP8 ? l[r] * (1.0f / kPScale) : l[r];
+            sm_l[warp * NH + gid + 8 * r] = l[r];
         }
     }
 #pragma unroll
@@ -680,8 +667,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             // column n of block nb is dim 32*(nb/4) + 4n + nb%4 (see the V transpose above)
             const uint32_t d0 = 32 * (nb / 4) + 4 * (2 * tig) + (nb % 4);
             float *o = sm_o + (warp * NH + gid) * DP;
-            o[d0] = (acc[nb][0] + acc[nb][2]) * (1.0f / kPScale);
-            o[d0 + 4] = (acc[nb][1] + acc[nb][3]) * (1.0f / kPScale);
+            o[d0] = acc[nb][0] + acc[nb][2];
+            o[d0 + 4] = acc[nb][1] + acc[nb][3];
         } else {
             const uint32_t d0 = 8 * nb + 2 * tig;
             float *o = sm_o + (warp * NH + gid) * DP;
