@@ -55,6 +55,11 @@ ES = {"F32": 4, "F16": 2, "F8": 1}
 DT = {"F32": 0, "F16": 1, "F8": 2}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
+# captures summarised under profiles/ (attn_split_mma_fp8_*.md)
+NCU_TRAFFIC_BYTES = {"qwen3_8b_fp8_ctx8192_b1": 16_843_000, "batch64_fp8_ctx8192": 1_081_500_000}
+
+
 def algorithmic_bytes(w, lens, layer):
     """Bytes one layer-step must move: KV rows read + Q + new K/V (f32) in; appended rows + O out."""
     e = ES[w["dtype"]]
@@ -216,7 +221,7 @@ def cpu_baseline_sample(w, budget_s=12.0):
                            starts, None, w["softcap"])
         n += 1
         el = time.perf_counter() - t0
-        if el > budget_s or n >= 400:
+        if el > budget_s or n >= 20000:
             break
     cores = oracle.num_threads()
     return {"value": el * 1e6 / (n * b), "unit": UNIT, "cores": cores, "kind": "port",
@@ -228,12 +233,12 @@ def cpu_baseline_sample(w, budget_s=12.0):
 class Job:
     """Cache + inputs of one rank, resident on its GPU."""
 
-    def __init__(self, w, device, seed):
+    def __init__(self, w, device, seed, ctx=None):
         import torch
         import vulkanforge_b200 as vf
         self.vf, self.torch, self.w = vf, torch, w
         torch.cuda.set_device(device)
-        self.ctx = vf.Context(device)
+        self.ctx = ctx if ctx is not None else vf.Context(device)
         rng = np.random.default_rng(seed)
         self.lens = make_lens(w, rng)
         B, L = w["batch"], w["ctx"]
@@ -290,6 +295,11 @@ class Job:
             self.step()
         self.graph = g
 
+    def close(self):
+        self.torch.cuda.synchronize()
+        self.fwd.workspace.destroy()
+        self.cache.destroy()
+
     def step_host(self):
         self.fwd.decode_token_host(self.h_q, self.h_k, self.h_v, self.h_out, self.h_pos, self.w["batch"])
 
@@ -316,6 +326,35 @@ class Job:
                 res[name] = {"launches": n.value, "mean_us": tot.value * 1e3 / n.value, "min_us": mn.value * 1e3}
         L.vfkv_profile_enable(self.ctx.handle, 0)
         return res
+
+
+def batch64_roofline(ctx, args, peak):
+    """The same kernel where it is bandwidth-bound: 64 sequences x 8192 tokens, FP8, one layer
+    (1 GiB of K/V per launch, far beyond L2).  Device events around `steps` launches."""
+    import torch
+    w = WORKLOADS["batch64_fp8_ctx8192"]
+    job = None
+    try:
+        job = Job(w, ctx.device, seed=77, ctx=ctx)
+        with torch.cuda.stream(job.stream):
+            for _ in range(3):
+                job.step()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                job.step()
+            e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        nbytes = algorithmic_bytes(w, job.lens, 0)
+        achieved = nbytes / (us * 1e-6) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES["batch64_fp8_ctx8192"], "algorithmic_bytes_per_launch": nbytes,
+                "mean_launch_us": us, "frac_of_8000_nominal": achieved / 8000.0,
+                "workload": "batch64_fp8_ctx8192: 64 sequences x 8192 tokens, 32 q / 8 kv / 128, FP8, 1 layer"}
+    finally:
+        if job is not None:
+            job.close()
 
 
 def run_ours(args, w, rank, world, local_rank):
@@ -398,11 +437,19 @@ def run_ours(args, w, rank, world, local_rank):
         split = prof.get("fa_split")
         roofline = None
         if split:
+            # The timed region launches one kernel per layer-step and nothing else (append and merge
+            # are fused into it), so its mean launch duration inside the region is region time /
+            # launches; consecutive launches overlap under dependent launch, which per-launch event
+            # pairs (kept in "kernels", measured in a separate pass) cannot show.
             per_launch = float(np.mean([algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"])]))
-            achieved = per_launch / (split["mean_us"] * 1e-6) / 1e9
+            fused = job.launches_per_step == w["n_layers"]
+            mean_us = ms * 1e3 / (args.steps * w["n_layers"]) if fused else split["mean_us"]
+            achieved = per_launch / (mean_us * 1e-6) / 1e9
             roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                        "frac": achieved / peak, "traffic": None, "kernel": "fa_split",
-                        "algorithmic_bytes_per_launch": per_launch, "mean_launch_us": split["mean_us"],
+                        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                        "kernel": "attn_split_mma_kernel (fa_split: append + attention + merge)" if fused else "fa_split",
+                        "algorithmic_bytes_per_launch": per_launch, "mean_launch_us": mean_us,
+                        "mean_launch_us_isolated_events": split["mean_us"],
                         "peak_source": f"{peak_kind} copy bandwidth", "frac_of_8000_nominal": achieved / 8000.0}
         step_bytes = sum(algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"]))
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -422,6 +469,8 @@ def run_ours(args, w, rank, world, local_rank):
                 "roofline": roofline, "kernels": prof, "clocks": clocks, "gpu_launches": launches,
                 "e2e": {"value": e2e_ms * 1e3 / denom, "unit": UNIT, "h2d_bytes_per_step": job.h2d_bytes(),
                         "d2h_bytes_per_step": job.d2h_bytes()}}
+        if world == 1 and not args.no_extra and args.workload == DEFAULT_WORKLOAD:
+            line["roofline_batch64_ctx8192"] = batch64_roofline(job.ctx, args, peak)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_sample(w)
         print(json.dumps(line), flush=True)
@@ -547,6 +596,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline sample")
+    ap.add_argument("--no-extra", action="store_true", help="skip the batch-64 roofline measurement")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
     ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
