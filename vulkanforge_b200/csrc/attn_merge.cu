@@ -108,6 +108,14 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     if (cap < 1) cap = 1;
     if (cap > 64) cap = 64;
     uint64_t want = base ? (slots + base - 1) / base : 1;
+    // A CTA keeps at most its own ring of stages in flight, which bounds one CTA's stream to a few
+    // tens of GB/s: in a ragged batch a sequence much longer than the rest would finish last on
+    // its own.  No CTA gets more than 8192 positions, 4096 once contexts beyond 8192 are possible
+    // (measured: 64 sequences of 512..16384 tokens 5.0 / 5.5 / 6.1 TB/s with 1 / 2 / 4 splits;
+    // 64 x 8192 uniform 6.3 / 6.0 / 5.9 TB/s).
+    const uint64_t per_cta = max_len > 8192 ? 4096 : 8192;
+    const uint64_t by_len = (uint64_t(max_len) + per_cta - 1) / per_cta;
+    if (want < by_len) want = by_len;
     if (want > cap) want = cap;
     if (want < 1) want = 1;
     return uint32_t(want);

@@ -734,35 +734,31 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const float *pm = p.part_m + row * p.n_splits, *pl = p.part_l + row * p.n_splits;
         const float4 *po = reinterpret_cast<const float4 *>(p.part_o + row * p.n_splits * D + d);
         constexpr uint32_t CH = 16;
-        float4 o[CH];
-        float mm[CH], ll[CH];
-#pragma unroll
-        for (uint32_t i = 0; i < CH; ++i) {
-            const bool in = i < p.n_splits;
-            o[i] = in ? __ldcg(po + uint64_t(i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            mm[i] = in ? __ldcg(pm + i) : kMaskedScore;
-            ll[i] = in ? __ldcg(pl + i) : 0.f;
-        }
-        float gmax = kMaskedScore;
-#pragma unroll
-        for (uint32_t i = 0; i < CH; ++i) gmax = fmaxf(gmax, mm[i]);
-#pragma unroll 8
-        for (uint32_t i = CH; i < p.n_splits; ++i) gmax = fmaxf(gmax, __ldcg(pm + i));
-        float gsum = 0.f;
+        float gmax = kMaskedScore, gsum = 0.f;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t c0 = 0; c0 < p.n_splits; c0 += CH) {       // one L2 round trip per 16 splits
+            float4 o[CH];
+            float mm[CH], ll[CH];
 #pragma unroll
-        for (uint32_t i = 0; i < CH; ++i) {
-            const float kn = __expf(mm[i] - gmax);       // absent splits: l = 0 and o = 0
-            gsum = fmaf(ll[i], kn, gsum);
-            a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
-            a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
-        }
-#pragma unroll 4
-        for (uint32_t i = CH; i < p.n_splits; ++i) {
-            const float kn = __expf(__ldcg(pm + i) - gmax);
-            const float4 ov = __ldcg(po + uint64_t(i) * (D / 4));
-            gsum = fmaf(__ldcg(pl + i), kn, gsum);
-            a.x = fmaf(ov.x, kn, a.x); a.y = fmaf(ov.y, kn, a.y); a.z = fmaf(ov.z, kn, a.z); a.w = fmaf(ov.w, kn, a.w);
+            for (uint32_t i = 0; i < CH; ++i) {
+                const bool in = c0 + i < p.n_splits;
+                o[i] = in ? __ldcg(po + uint64_t(c0 + i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                mm[i] = in ? __ldcg(pm + c0 + i) : kMaskedScore;
+                ll[i] = in ? __ldcg(pl + c0 + i) : 0.f;
+            }
+            float nmax = gmax;
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) nmax = fmaxf(nmax, mm[i]);
+            const float ko = __expf(gmax - nmax);                 // running update of flash_attn_reduce.comp:57-75
+            gsum *= ko; a.x *= ko; a.y *= ko; a.z *= ko; a.w *= ko;
+            gmax = nmax;
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                const float kn = __expf(mm[i] - gmax);            // absent splits: l = 0 and o = 0
+                gsum = fmaf(ll[i], kn, gsum);
+                a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
+                a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
+            }
         }
         if (p.out) {
             const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;
