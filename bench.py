@@ -489,13 +489,19 @@ def run_position_sharded(args, w, rank, world, local_rank):
     from vulkanforge_b200.shard import PositionShards, ShardedSequenceDecoder
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import datetime
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                            timeout=datetime.timedelta(seconds=90))
     ctx = vf.Context(local_rank)
     sh = PositionShards(world, 256)
     L, hq, hkv, d = w["ctx"], w["hq"], w["hkv"], w["d"]
     cache = vf.KvCache(ctx, vf.KvCacheConfig(w["n_layers"], hkv, d, sh.local_capacity(L)), vf.KvDtype[w["dtype"]])
     fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=w["n_splits"])
-    dec = ShardedSequenceDecoder(fwd, sh, rank)
+    exchange = None
+    if args.exchange == "peer":                            # partials by peer stores from the attention kernel
+        exchange = vf.PeerExchange(ctx, world, rank, hq, hkv, d)
+        exchange.connect()
+    dec = ShardedSequenceDecoder(fwd, sh, rank, exchange=exchange)
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
     n_local = sh.local_len(L - 1, rank)
     for p in range(0, n_local, 4096):                      # this rank's pages of the 131071 earlier tokens
@@ -529,7 +535,12 @@ def run_position_sharded(args, w, rank, world, local_rank):
     barrier()
     launches = (ctx.launch_count() - n0) * args.steps
     run, launch_kind = step, "stream launches"
-    if not args.no_graph:
+    if exchange is not None and not args.no_graph:         # only this library's kernels: always capturable
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        run, launch_kind = graph.replay, "one CUDA graph replay per token"
+    elif args.graph_collective:
         try:                                               # the whole step, collective included, as one graph
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
@@ -578,13 +589,18 @@ def run_position_sharded(args, w, rank, world, local_rank):
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32 (fp8/f16 storage)", "data": "synthetic",
                 "config": {"workload": args.workload, "n_layers": w["n_layers"], "n_q_heads": hq, "n_kv_heads": hkv,
                            "head_dim": d, "kv_dtype": w["dtype"], "context": L,
-                           "parallelism": f"positions sharded x{world} in 256-row pages, NCCL all-gather of (m, l, o)",
+                           "parallelism": f"positions sharded x{world} in 256-row pages, " + (
+                               "(m, l, o) stored into every GPU's buffer by the attention kernel, flag-waiting merge"
+                               if exchange is not None else "NCCL all-gather of (m, l, o)"),
+                           "exchange": args.exchange,
                            "collective_bytes_per_rank": (d + 2) * hq * 4, "launch": launch_kind,
                            "l2": "per-GPU share of the cache is %d MiB per step" % (step_bytes // world >> 20)},
                 "achieved_gbs_whole_step": step_bytes * args.steps / (ms * 1e-3) / 1e9,
                 "prefill_chunk_512_us": prefill_ms * 1e3, "clocks": clocks, "gpu_launches": int(tot[0])}
         print(json.dumps(line), flush=True)
     dist.barrier()
+    if exchange is not None:
+        exchange.destroy()
     dist.destroy_process_group()
 
 
@@ -598,6 +614,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline sample")
     ap.add_argument("--no-extra", action="store_true", help="skip the batch-64 roofline measurement")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="position-sharded mode: how the per-GPU partials travel (peer stores fused into the "
+                         "attention kernel, or an NCCL all-gather)")
+    ap.add_argument("--graph-collective", action="store_true",
+                    help="position-sharded mode: capture the step, NCCL all-gather included, in one CUDA graph "
+                         "(off by default: a 2-GPU run with it did not finish)")
     ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch mode of the attention kernel (vfkv_ctx_set_dependent_launch)")

@@ -60,6 +60,7 @@ typedef enum { VFKV_SCALE_NONE = 0, VFKV_SCALE_PER_TOKEN_HEAD = 1 } vfkv_scale_m
 typedef struct vfkv_ctx vfkv_ctx;
 typedef struct vfkv_cache vfkv_cache;
 typedef struct vfkv_workspace vfkv_workspace;
+typedef struct vfkv_exchange vfkv_exchange;
 
 /* src/backend/vulkan/kv_cache.rs:153-176 (KvCacheConfig) plus the two build-side
  * fields n_slots and scale_mode. */
@@ -331,6 +332,49 @@ int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, c
  * n_rows*(head_dim+2) floats, each block m[n_rows], l[n_rows], o[n_rows][head_dim]. */
 int32_t vfkv_merge_partials_packed(vfkv_ctx *ctx, const float *d_packed, uint32_t n_parts,
                                    uint32_t n_rows, uint32_t head_dim, float *d_out, void *stream);
+
+/* ---- peer exchange of partials (position sharding without a library collective) -----------
+ *
+ * No counterpart in the reference.  Each GPU of the group owns one exchange buffer.  The attention
+ * kernel of vfkv_attend_push stores this GPU's (m, l, o) block into the buffer of EVERY rank with
+ * plain peer stores and then publishes per-(kv-head) arrival flags (release, system scope);
+ * vfkv_exchange_merge waits for the flags of all ranks in its own buffer -- at most the time set
+ * with vfkv_exchange_set_timeout_ms (default 1000 ms); a wait that runs out sets bit 8 of the
+ * status word read by vfkv_ctx_poll and writes zeros -- and applies the flash_attn_reduce.comp:51-80
+ * merge.  Blocks and flags are double-buffered by the parity of a device-side exchange counter,
+ * so both calls can be captured in a CUDA graph and replayed.  Every rank must make the same
+ * sequence of push / merge calls, one merge per push.
+ *
+ * Set-up: create on every rank with the same shape; make each rank's buffer known to the others,
+ * either through vfkv_exchange_export / vfkv_exchange_import (CUDA IPC handles, one process per
+ * GPU) or vfkv_exchange_set_peer (pointers the caller has mapped itself, or several ranks of one
+ * process); synchronise the ranks once (the buffers are zeroed by create) before the first push.
+ * world <= 8; n_rows = q-heads, n_groups = kv-heads of the sequence; head_dim a multiple of 4. */
+int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint32_t n_rows,
+                             uint32_t n_groups, uint32_t head_dim, vfkv_exchange **out);
+void vfkv_exchange_destroy(vfkv_exchange *ex);
+uint64_t vfkv_exchange_bytes(const vfkv_exchange *ex);
+void *vfkv_exchange_local_ptr(const vfkv_exchange *ex);
+int32_t vfkv_exchange_export(vfkv_exchange *ex, uint8_t handle[64]);
+int32_t vfkv_exchange_import(vfkv_exchange *ex, uint32_t rank, const uint8_t handle[64]);
+int32_t vfkv_exchange_set_peer(vfkv_exchange *ex, uint32_t rank, void *d_peer_buffer);
+int32_t vfkv_exchange_set_timeout_ms(vfkv_exchange *ex, uint32_t ms);
+/* 1 once every rank's buffer is known. */
+uint32_t vfkv_exchange_ready(const vfkv_exchange *ex);
+/* Attention of one query token over local positions [pos_begin, pos_end) of `slot`, the partial
+ * delivered to every rank (arguments as vfkv_attend_partial). */
+int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer,
+                         uint32_t kv_layer, const float *d_q, uint32_t n_q_heads, uint32_t slot,
+                         uint32_t pos_begin, uint32_t pos_end, float scale, float softcap,
+                         uint32_t n_splits, void *stream);
+/* Waits for all ranks' blocks of the current exchange and writes d_out [n_rows][head_dim]. */
+int32_t vfkv_exchange_merge(vfkv_exchange *ex, float *d_out, void *stream);
+/* vfkv_attend_push followed by vfkv_exchange_merge. */
+int32_t vfkv_attend_exchange(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex,
+                             uint32_t layer, uint32_t kv_layer, const float *d_q,
+                             uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin,
+                             uint32_t pos_end, float scale, float softcap, uint32_t n_splits,
+                             float *d_out, void *stream);
 
 /* ---------------------------------------------------------------------- */
 /* device-memory helpers for hosts without a CUDA binding of their own       */

@@ -66,6 +66,122 @@ def test_emulated_ranks_chunked_prefill_append_and_merge(ctx, world, page, seq_l
             cache.destroy()
 
 
+def _emulated_group(ctx, world, seq_len, dtype, hq=HQ, hkv=HKV, d=D, page=256):
+    """world ranks of one process on one GPU: caches, forwards, decoders and connected exchanges."""
+    sh = PositionShards(world, page)
+    ranks = []
+    for r in range(world):
+        cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, sh.local_capacity(seq_len + 8)), dtype)
+        fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+        ex = vf.PeerExchange(ctx, world, r, hq, hkv, d)
+        ranks.append((cache, fwd, ShardedSequenceDecoder(fwd, sh, r), ex))
+    for r, (_, _, _, ex) in enumerate(ranks):
+        for o, (_, _, _, other) in enumerate(ranks):
+            if o != r:
+                ex.set_peer(o, other.local_ptr())
+        assert ex.ready()
+    return sh, ranks
+
+
+def _destroy_group(ranks):
+    for cache, fwd, _, ex in ranks:
+        ex.destroy()
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+@pytest.mark.parametrize("world,seq_len,dtype,hq,hkv,d", [
+    (2, 3000, "F8", 64, 8, 128),      # tensor-core kernel, several splits: fan-out from the merging CTA
+    (4, 900, "F8", 64, 8, 128),       # one split per rank: fan-out from the direct epilogue
+    (8, 5000, "F16", 32, 8, 128),
+    (3, 100, "F8", 64, 8, 128),       # ranks 1 and 2 hold nothing
+    (2, 700, "F32", 8, 2, 64),        # CUDA-core kernel + push kernel
+])
+def test_peer_exchange_emulated_ranks(ctx, world, seq_len, dtype, hq, hkv, d):
+    """The partial of every rank is stored by its attention kernel into all ranks' buffers; each
+    rank's merge then finds every flag set.  Several decode steps in a row exercise the parity
+    double-buffering and the device-side exchange counter.  On one GPU the producers all run
+    before the consumers, so no kernel ever waits."""
+    import torch
+    kv_dtype = vf.KvDtype[dtype]
+    odt = {"F8": oracle.F8, "F16": oracle.F16, "F32": oracle.F32}[dtype]
+    rng = np.random.default_rng(world * 100 + seq_len)
+    steps = 3
+    k = kv_values(rng, (seq_len + steps, hkv, d))
+    v = kv_values(rng, (seq_len + steps, hkv, d))
+    sh, ranks = _emulated_group(ctx, world, seq_len, kv_dtype, hq, hkv, d)
+    try:
+        dk, dv = to_dev(k), to_dev(v)
+        for _, _, dec, _ in ranks:
+            dec.prefill(0, dk[:seq_len], dv[:seq_len], 0, seq_len)
+        outs = [torch.zeros(hq, d, device="cuda") for _ in ranks]
+        for t in range(steps):
+            L = seq_len + t + 1
+            q = rng.standard_normal((hq, d), dtype=np.float32)
+            dq = to_dev(q)
+            for r, (_, fwd, dec, ex) in enumerate(ranks):
+                dec.append(0, dk[L - 1:L], dv[L - 1:L], L - 1)
+                fwd.attend_push(ex, 0, dq, 0, sh.local_len(L, r))
+            for r, (_, fwd, _, ex) in enumerate(ranks):
+                fwd.exchange_merge(ex, outs[r])
+            torch.cuda.synchronize()
+            ctx.poll()
+            kc, vc = encode_cache(k[:L], odt), encode_cache(v[:L], odt)
+            want = oracle.attention_ref(q, kc, vc, odt, hq, hkv, d, L)
+            for r in range(world):
+                got = outs[r].cpu().numpy()
+                if dtype == "F8":
+                    assert rel_err(got, want) < 3e-2
+                else:
+                    assert np.max(np.abs(got - want)) < 2e-3
+                assert np.array_equal(got, outs[0].cpu().numpy())      # every rank merges the same blocks
+    finally:
+        _destroy_group(ranks)
+
+
+def test_peer_exchange_wait_runs_out_and_context_survives(ctx):
+    """A flag that nothing sets: the merge gives up after its time limit, reports it through the
+    status word, and the next exchanges work."""
+    import torch
+    world, seq_len = 2, 600
+    rng = np.random.default_rng(5)
+    k = kv_values(rng, (seq_len, HKV, D))
+    v = kv_values(rng, (seq_len, HKV, D))
+    q = rng.standard_normal((HQ, D), dtype=np.float32)
+    sh, ranks = _emulated_group(ctx, world, seq_len, vf.KvDtype.F8)
+    try:
+        dk, dv, dq = to_dev(k), to_dev(v), to_dev(q)
+        for _, _, dec, ex in ranks:
+            dec.prefill(0, dk, dv, 0, seq_len)
+            ex.set_timeout_ms(20)
+        outs = [torch.ones(HQ, D, device="cuda") for _ in ranks]
+        (_, f0, _, e0), (_, f1, _, e1) = ranks
+        f0.attend_push(e0, 0, dq, 0, sh.local_len(seq_len, 0))
+        f0.exchange_merge(e0, outs[0])                    # rank 1 has not pushed
+        torch.cuda.synchronize()
+        with pytest.raises(vf.VfkvError) as err:
+            ctx.poll()
+        assert err.value.status == vf.kv_cache.ERR_TIMEOUT
+        assert float(outs[0].abs().max()) == 0.0          # the row is written as zeros, not garbage
+        f1.attend_push(e1, 0, dq, 0, sh.local_len(seq_len, 1))
+        f1.exchange_merge(e1, outs[1])                    # both blocks of exchange 1 are there now
+        torch.cuda.synchronize()
+        ctx.poll()
+        kc, vc = encode_cache(k, oracle.F8), encode_cache(v, oracle.F8)
+        want = oracle.attention_ref(q, kc, vc, oracle.F8, HQ, HKV, D, seq_len)
+        assert rel_err(outs[1].cpu().numpy(), want) < 3e-2
+        for r, (_, fwd, _, ex) in enumerate(ranks):       # exchange 2 on both ranks
+            fwd.attend_push(ex, 0, dq, 0, sh.local_len(seq_len, r))
+        for r, (_, fwd, _, ex) in enumerate(ranks):
+            fwd.exchange_merge(ex, outs[r])
+        torch.cuda.synchronize()
+        ctx.poll()
+        for r in range(world):
+            assert rel_err(outs[r].cpu().numpy(), want) < 3e-2
+    finally:
+        _destroy_group(ranks)
+
+
 def _nccl_rank(rank, world, port, seq_len, result_dir):
     import torch
     import torch.distributed as dist
@@ -90,7 +206,35 @@ def _nccl_rank(rank, world, port, seq_len, result_dir):
         ctx.poll()
         kc, vc = encode_cache(k, oracle.F8), encode_cache(v, oracle.F8)
         want = oracle.attention_ref(q, kc, vc, oracle.F8, HQ, HKV, D, seq_len + 1)
-        np.save(os.path.join(result_dir, f"err{rank}.npy"), np.array([rel_err(out.cpu().numpy(), want)]))
+        errs = [rel_err(out.cpu().numpy(), want)]
+        # the same attention with the partials exchanged by peer stores (IPC-mapped buffers),
+        # first as plain launches, then replayed from a CUDA graph
+        ex = vf.PeerExchange(ctx, world, rank, HQ, HKV, D)
+        ex.connect()
+        pdec = ShardedSequenceDecoder(fwd, sh, rank, exchange=ex)
+        dq = torch.from_numpy(q).cuda()
+        for _ in range(3):
+            out.zero_()
+            pdec.attend(0, dq, out, seq_len + 1)
+            torch.cuda.synchronize()
+            ctx.poll()
+            errs.append(rel_err(out.cpu().numpy(), want))
+        stream = torch.cuda.Stream()
+        fwd.stream = stream.cuda_stream
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            pdec.attend(0, dq, out, seq_len + 1)
+        for _ in range(4):
+            out.zero_()
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            ctx.poll()
+            errs.append(rel_err(out.cpu().numpy(), want))
+        fwd.stream = None
+        dist.barrier()
+        np.save(os.path.join(result_dir, f"err{rank}.npy"), np.array([max(errs)]))
+        ex.destroy()
         fwd.workspace.destroy()
         cache.destroy()
         ctx.destroy()

@@ -9,11 +9,11 @@ no CPU fallback: without ``libvfkv.so`` every entry point raises.
 from ._lib import LIB_PATH, load
 from .forward import CudaForward
 from .shard import PositionShards, ShardedSequenceDecoder, all_gather_partials, assign_sequences
-from .kv_cache import (Context, KvCache, KvCacheConfig, KvDtype, VfkvError, Workspace,
+from .kv_cache import (Context, KvCache, KvCacheConfig, KvDtype, VfkvError, Workspace, PeerExchange,
                        guard_kv_precision, kv_bytes_per_token, kv_dtype_from_env, ptr,
                        sliding_kv_start)
 
 __all__ = ["LIB_PATH", "load", "CudaForward", "PositionShards", "ShardedSequenceDecoder", "all_gather_partials",
            "assign_sequences", "Context", "KvCache", "KvCacheConfig", "KvDtype",
-           "VfkvError", "Workspace", "guard_kv_precision", "kv_bytes_per_token",
+           "VfkvError", "Workspace", "PeerExchange", "guard_kv_precision", "kv_bytes_per_token",
            "kv_dtype_from_env", "ptr", "sliding_kv_start"]

@@ -4,7 +4,7 @@
 #include <cstring>
 #include <new>
 
-#include "common.cuh"
+#include "attn_params.cuh"
 
 using namespace vfkv;
 
@@ -166,7 +166,8 @@ int32_t vfkv_ctx_poll(vfkv_ctx *ctx, void *stream)
     if (h == 0) return VFKV_OK;
     return set_error(ctx, VFKV_ERR_TIMEOUT,
                      std::string("device status word = ") + std::to_string(h) +
-                         " (1: bounded wait gave up, 2: append row out of range, 4: attend slot/length out of range)");
+                         " (1: bounded wait gave up, 2: append row out of range, 4: attend slot/length out of range, "
+                         "8: a peer's partial did not arrive in time)");
 }
 
 int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl)
@@ -737,6 +738,50 @@ int32_t vfkv_attend_partial(vfkv_cache *cache, vfkv_workspace *ws, uint32_t laye
     a.softcap = softcap; a.n_splits = n_splits;
     DeviceGuard g(ctx->device);
     return launch_attention(ctx, ws, a, as_stream(stream));
+}
+
+int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer, uint32_t kv_layer,
+                         const float *d_q, uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin, uint32_t pos_end,
+                         float scale, float softcap, uint32_t n_splits, void *stream)
+{
+    int32_t rc = attend_common(cache, layer, kv_layer, n_q_heads, "vfkv_attend_push");
+    if (rc) return rc;
+    vfkv_ctx *ctx = cache->ctx;
+    if (!d_q || !ex) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: null argument");
+    if (ex->ctx != ctx) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: exchange belongs to another context");
+    if (!vfkv_exchange_ready(ex)) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: not every rank's buffer is set");
+    if (slot >= cache->kv.config.n_slots || pos_end > cache->kv.config.max_seq_len || pos_begin > pos_end)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: slot or position range out of bounds");
+    AttnArgs a;
+    a.kv = make_view(cache, kv_layer);
+    if (ex->fan.n_rows != n_q_heads || ex->fan.n_groups != a.kv.n_kv_heads || ex->head_dim != a.kv.head_dim)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: exchange was created for another shape");
+    a.seq.n_seqs = 1; a.seq.slot0 = slot; a.seq.seq_len_scalar = pos_end; a.seq.kv_start_scalar = pos_begin;
+    a.q = d_q; a.n_q_heads = n_q_heads; a.scale = scale; a.softcap = softcap; a.n_splits = n_splits;
+    // the staged block has the layout of one exchange block
+    a.out_m = ex->staging;
+    a.out_l = ex->staging + n_q_heads;
+    a.out_o = ex->staging + fanout_o_offset(n_q_heads);
+    DeviceGuard g(ctx->device);
+    if (attn_mma_supported(a) && ctx->attn_impl != 1) {
+        a.out_m = a.out_l = a.out_o = nullptr;          // the kernel stores into the exchange buffers itself
+        a.fan = ex->fan;
+        return launch_attention(ctx, ws, a, as_stream(stream));
+    }
+    rc = launch_attention(ctx, ws, a, as_stream(stream));
+    if (rc) return rc;
+    return launch_fanout_push(ctx, ex->fan, ex->staging, ex->head_dim, as_stream(stream));
+}
+
+int32_t vfkv_attend_exchange(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer,
+                             uint32_t kv_layer, const float *d_q, uint32_t n_q_heads, uint32_t slot,
+                             uint32_t pos_begin, uint32_t pos_end, float scale, float softcap, uint32_t n_splits,
+                             float *d_out, void *stream)
+{
+    int32_t rc = vfkv_attend_push(cache, ws, ex, layer, kv_layer, d_q, n_q_heads, slot, pos_begin, pos_end, scale,
+                                  softcap, n_splits, stream);
+    if (rc) return rc;
+    return vfkv_exchange_merge(ex, d_out, stream);
 }
 
 int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, const float *d_o, uint32_t n_parts,

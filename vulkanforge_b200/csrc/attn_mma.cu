@@ -683,6 +683,9 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     __syncthreads();
 
     const bool direct = p.n_splits == 1;
+    const bool fan = p.fan.world != 0u;
+    FanoutSlot fs{};
+    if (fan) fs = fanout_slot(p.fan, D, p.fan.rank, *p.fan.epoch + 1u);
     for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
         const uint32_t j = idx / D, d = idx % D;
         float M = kMaskedScore;
@@ -703,6 +706,16 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 p.out_o[row * D + d] = O;
                 if (d == 0) { p.out_m[row] = m_nat; p.out_l[row] = L; }
             }
+            if (fan) {
+#pragma unroll
+                for (uint32_t r = 0; r < 8; ++r) {
+                    if (r < p.fan.world) {
+                        float *dst = p.fan.base[r];
+                        dst[fs.o + row * D + d] = O;
+                        if (d == 0) { dst[fs.m + row] = m_nat; dst[fs.m + p.fan.n_rows + row] = L; }
+                    }
+                }
+            }
         } else {
             const uint64_t pi = row * p.n_splits + split;
             p.part_o[pi * D + d] = O;
@@ -710,7 +723,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     }
     VFKV_TRACE(7);
-    if (direct) return;
+    if (direct) {
+        if (fan) { __syncthreads(); fanout_publish(p.fan, fs, s * p.n_kv_heads + kvh); }
+        return;
+    }
 
     // ---- the last CTA of this (sequence, kv-head) merges the splits ---------------------------------
     // The barrier orders every thread's partial stores before thread 0's ticket; the ticket is an
@@ -768,7 +784,18 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             *reinterpret_cast<float4 *>(p.out_o + row * D + d) = a;
             if (d == 0) { p.out_m[row] = gmax; p.out_l[row] = gsum; }
         }
+        if (fan) {            // the merged partial goes straight into every GPU's exchange buffer
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) {
+                if (r < p.fan.world) {
+                    float *dst = p.fan.base[r];
+                    *reinterpret_cast<float4 *>(dst + fs.o + row * D + d) = a;
+                    if (d == 0) { dst[fs.m + row] = gmax; dst[fs.m + p.fan.n_rows + row] = gsum; }
+                }
+            }
+        }
     }
+    if (fan) { __syncthreads(); fanout_publish(p.fan, fs, s * p.n_kv_heads + kvh); }
     VFKV_TRACE(9);
     if (threadIdx.x == 0) mp.counters[s * p.n_kv_heads + kvh] = 0u;   // ready for the next launch
 }

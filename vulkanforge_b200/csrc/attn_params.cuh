@@ -18,6 +18,7 @@ struct AttnParams {
     uint32_t n_q_heads, n_kv_heads, head_dim, group, max_seq, n_slots, n_splits, n_seqs;
     float scale, softcap;
     uint32_t *status;
+    PeerFanout fan;
 };
 
 inline AttnParams make_params(const vfkv_ctx *ctx, const vfkv_workspace *ws, const AttnArgs &a,
@@ -45,6 +46,7 @@ inline AttnParams make_params(const vfkv_ctx *ctx, const vfkv_workspace *ws, con
     p.n_seqs = a.seq.n_seqs;
     p.scale = a.scale; p.softcap = a.softcap;
     p.status = ctx->d_status;
+    p.fan = a.fan;
     return p;
 }
 
@@ -87,6 +89,44 @@ __device__ __forceinline__ void split_range(uint32_t start, uint32_t len, uint32
     if (b > len) b = len;
     if (e > len) e = len;
     *begin = uint32_t(b); *end = uint32_t(e);
+}
+
+// Layout of one source rank's block inside an exchange buffer, in floats: m[n_rows], l[n_rows],
+// padding to a multiple of 4, o[n_rows][head_dim]; the block itself is padded to a multiple of 4.
+__host__ __device__ __forceinline__ uint64_t fanout_o_offset(uint32_t n_rows) { return (2ull * n_rows + 3) & ~3ull; }
+__host__ __device__ __forceinline__ uint64_t fanout_block_floats(uint32_t n_rows, uint32_t head_dim)
+{
+    return (fanout_o_offset(n_rows) + uint64_t(n_rows) * head_dim + 3) & ~3ull;
+}
+// Where source rank `src`'s block of exchange number e lives inside any rank's exchange buffer.
+struct FanoutSlot {
+    uint32_t epoch;      // e
+    uint64_t m;          // float offset of m[n_rows]; l follows at + n_rows
+    uint64_t o;          // float offset of o[n_rows][head_dim] (16-byte aligned)
+    uint64_t flags;      // 4-byte offset of this rank's flag row
+};
+__device__ __forceinline__ FanoutSlot fanout_slot(const PeerFanout &f, uint32_t head_dim, uint32_t src, uint32_t epoch)
+{
+    FanoutSlot s;
+    s.epoch = epoch;
+    const uint64_t packed = fanout_block_floats(f.n_rows, head_dim);
+    const uint64_t blk = uint64_t(epoch & 1u) * f.world + src;
+    s.m = blk * packed;
+    s.o = s.m + fanout_o_offset(f.n_rows);
+    s.flags = 2ull * f.world * packed + blk * f.n_groups;
+    return s;
+}
+// Publishes flag `group` of this rank's block on every GPU.  Call after a CTA barrier that follows
+// the CTA's stores of the block: the release at system scope is cumulative over them.
+__device__ __forceinline__ void fanout_publish(const PeerFanout &f, const FanoutSlot &s, uint32_t group)
+{
+#pragma unroll
+    for (uint32_t r = 0; r < 8; ++r) {          // static indices: the pointer table stays in the parameter bank
+        if (threadIdx.x == r && r < f.world) {
+            uint32_t *flag = reinterpret_cast<uint32_t *>(f.base[r]) + s.flags + group;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flag), "r"(s.epoch) : "memory");
+        }
+    }
 }
 
 __device__ __forceinline__ float apply_softcap(float s, float cap)

@@ -91,6 +91,20 @@ struct SeqArgs {
     uint32_t max_len_hint = 0;
 };
 
+// Fan-out of the (m, l, o) partial to every GPU of a position-sharded group, written by the
+// attention kernel itself.  base[r] is rank r's exchange buffer (peer memory except base[rank]):
+//   floats  [parity 2][source rank][ m[n_rows] | l[n_rows] | o[n_rows][head_dim] ]
+//   uint32  [parity 2][source rank][group]      arrival flags, one per (sequence, kv-head)
+// A kernel of exchange number e = *epoch + 1 uses parity e & 1 and stores e into the flags.
+struct PeerFanout {
+    float *base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    const uint32_t *epoch = nullptr;   // this GPU's count of completed exchanges (device memory)
+    uint32_t world = 0;                // 0 = no fan-out
+    uint32_t rank = 0;
+    uint32_t n_rows = 0;               // sequences * q-heads
+    uint32_t n_groups = 0;             // sequences * kv-heads
+};
+
 struct AttnArgs {
     KvView kv;
     SeqArgs seq;
@@ -107,6 +121,7 @@ struct AttnArgs {
     // only the tensor-core kernel consumes these (it writes the cache rows itself)
     const float *k_new = nullptr;
     const float *v_new = nullptr;
+    PeerFanout fan;               // tensor-core kernel only
 };
 
 // Brackets one kernel launch with a pair of events on its stream while profiling is on.
@@ -151,6 +166,10 @@ int32_t launch_merge_partials(vfkv_ctx *ctx, const float *m, const float *l, con
 int32_t launch_merge_partials_packed(vfkv_ctx *ctx, const float *packed, uint32_t n_parts, uint32_t n_rows,
                                      uint32_t head_dim, float *out, cudaStream_t st);
 
+// peer exchange of partials (exchange.cu)
+int32_t launch_fanout_push(vfkv_ctx *ctx, const PeerFanout &fan, const float *staging, uint32_t head_dim,
+                           cudaStream_t st);
+
 // attention implementations
 uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile);
 int32_t launch_attn_generic(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
@@ -167,3 +186,16 @@ int32_t launch_merge_ws(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
 constexpr float kMaskedScore = -1e30f;
 
 }  // namespace vfkv
+
+// One GPU's end of a peer exchange of partials (exchange.cu).
+struct vfkv_exchange {
+    vfkv_ctx *ctx = nullptr;
+    vfkv::PeerFanout fan;          // base[], epoch pointer, world, rank, rows, groups
+    uint32_t head_dim = 0;
+    float *local = nullptr;        // this rank's buffer: blocks, then flags
+    uint64_t bytes = 0;
+    uint32_t *ctl = nullptr;       // [0] completed exchanges, [1] merge ticket (never shared)
+    float *staging = nullptr;      // one block, for attention kernels that cannot fan out themselves
+    bool imported[8] = {false, false, false, false, false, false, false, false};
+    uint64_t wait_ns = 1000000000ull;
+};

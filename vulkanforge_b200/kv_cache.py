@@ -149,6 +149,57 @@ class Workspace:
             self.handle = None
 
 
+class PeerExchange:
+    """One GPU's end of the peer exchange of (m, l, o) partials used by position sharding
+    (``vfkv_exchange_*``; no counterpart in the reference)."""
+
+    def __init__(self, ctx: Context, world: int, rank: int, n_rows: int, n_groups: int, head_dim: int):
+        self.ctx, self.world, self.rank = ctx, world, rank
+        h = C.c_void_p()
+        ctx.check(ctx._lib.vfkv_exchange_create(ctx.handle, world, rank, n_rows, n_groups, head_dim, C.byref(h)))
+        self.handle = h
+
+    def bytes(self) -> int:
+        return int(self.ctx._lib.vfkv_exchange_bytes(self.handle))
+
+    def local_ptr(self) -> int:
+        return int(self.ctx._lib.vfkv_exchange_local_ptr(self.handle) or 0)
+
+    def export_handle(self) -> bytes:
+        buf = (C.c_uint8 * 64)()
+        self.ctx.check(self.ctx._lib.vfkv_exchange_export(self.handle, buf))
+        return bytes(buf)
+
+    def import_handle(self, rank: int, handle: bytes) -> None:
+        buf = (C.c_uint8 * 64).from_buffer_copy(handle)
+        self.ctx.check(self.ctx._lib.vfkv_exchange_import(self.handle, rank, buf))
+
+    def set_peer(self, rank: int, device_ptr: int) -> None:
+        self.ctx.check(self.ctx._lib.vfkv_exchange_set_peer(self.handle, rank, C.c_void_p(device_ptr)))
+
+    def set_timeout_ms(self, ms: int) -> None:
+        self.ctx.check(self.ctx._lib.vfkv_exchange_set_timeout_ms(self.handle, ms))
+
+    def ready(self) -> bool:
+        return bool(self.ctx._lib.vfkv_exchange_ready(self.handle))
+
+    def connect(self, group=None) -> None:
+        """One process per GPU: swaps CUDA IPC handles over ``torch.distributed`` and ends with a
+        barrier, after which pushes may start."""
+        import torch.distributed as dist
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.export_handle(), group=group)
+        for r, h in enumerate(handles):
+            if r != self.rank:
+                self.import_handle(r, h)
+        dist.barrier(group=group)
+
+    def destroy(self) -> None:
+        if self.handle:
+            self.ctx._lib.vfkv_exchange_destroy(self.handle)
+            self.handle = None
+
+
 class KvCache:
     """kv_cache.rs:204-499.  ``KvCache.new`` mirrors ``KvCache::new``; the dtype is explicit
     (pass ``kv_dtype_from_env()`` for the reference's environment selection)."""

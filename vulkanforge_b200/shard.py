@@ -12,8 +12,11 @@ here has a counterpart in it.  The path shards in two ways:
   (``Hq * (D + 2)`` floats per GPU) followed by the log-sum-exp merge of
   ``vk_shaders/flash_attn_reduce.comp:51-80`` gives the full result on every GPU.
 
-The collective is ``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests); the merge is
-``vfkv_merge_partials_packed``.
+The exchange is either ``torch.distributed`` (NCCL on GPUs, gloo in the CPU tests) followed by
+``vfkv_merge_partials_packed``, or -- ``ShardedSequenceDecoder(exchange=...)`` -- peer stores issued
+by the attention kernel itself into every GPU's ``PeerExchange`` buffer and a merge kernel that
+waits, with a time limit, on arrival flags (``vfkv_attend_exchange``); the second form has no
+library call on the data path and can be replayed from a CUDA graph.
 """
 from __future__ import annotations
 
@@ -99,9 +102,10 @@ class ShardedSequenceDecoder:
     ``shards.local_capacity(global max)``; slot 0 holds this rank's pages.
     """
 
-    def __init__(self, fwd, shards: PositionShards, rank: int, group=None):
+    def __init__(self, fwd, shards: PositionShards, rank: int, group=None, exchange=None):
         import torch
         self.fwd, self.shards, self.rank, self.group = fwd, shards, rank, group
+        self.exchange = exchange      # a connected PeerExchange: partials travel by peer stores, no collective
         hd = fwd.kv_cache.config.head_dim
         self.n_rows, self.head_dim = fwd.n_heads, hd
         self.packed = torch.zeros(packed_partial_floats(fwd.n_heads, hd), dtype=torch.float32, device="cuda")
@@ -131,6 +135,9 @@ class ShardedSequenceDecoder:
         """Attention of one query token over global positions [0, seq_len): local partial, one
         all-gather, merge.  ``out`` [Hq][D] is complete on every rank."""
         n, hd = self.n_rows, self.head_dim
+        if self.exchange is not None:
+            self.fwd.attend_exchange(self.exchange, layer, q, 0, self.shards.local_len(seq_len, self.rank), out)
+            return out
         m, l, o = self.packed[:n], self.packed[n:2 * n], self.packed[2 * n:]
         self.fwd.attend_partial(layer, q, 0, self.shards.local_len(seq_len, self.rank), m, l, o)
         gathered = all_gather_partials(self.packed, self.group)
