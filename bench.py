@@ -45,7 +45,7 @@ WORKLOADS = {
                                          n_splits=0, softcap=0.0, windows=None, ragged=(512, 16384)),
     "gemma_f16_ctx32768_b8": dict(n_layers=6, hq=16, hkv=8, d=256, dtype="F16", batch=8, ctx=32768,
                                   n_splits=0, softcap=50.0, windows=[1024, 1024, 1024, 1024, 1024, 0]),
-    "long_fp8_ctx131072_b1": dict(n_layers=1, hq=64, hkv=8, d=128, dtype="F8", batch=1, ctx=131072,
+    "long_fp8_ctx131072_b1": dict(n_layers=8, hq=64, hkv=8, d=128, dtype="F8", batch=1, ctx=131072,
                                   n_splits=0, softcap=0.0, windows=None, shard="positions"),
 }
 DEFAULT_WORKLOAD = "qwen3_8b_fp8_ctx8192_b1"
@@ -499,25 +499,28 @@ def run_position_sharded(args, w, rank, world, local_rank):
     fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=w["n_splits"])
     exchange = None
     if args.exchange == "peer":                            # partials by peer stores from the attention kernel
-        exchange = vf.PeerExchange(ctx, world, rank, hq, hkv, d)
+        exchange = vf.PeerExchange(ctx, world, rank, hq, d)
         exchange.connect()
     dec = ShardedSequenceDecoder(fwd, sh, rank, exchange=exchange)
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
     n_local = sh.local_len(L - 1, rank)
+    n_layers = w["n_layers"]
+    ctx.check(ctx._lib.vfkv_ctx_set_dependent_launch(ctx.handle, 1 if args.pdl else 0))
     for p in range(0, n_local, 4096):                      # this rank's pages of the 131071 earlier tokens
         m = min(4096, n_local - p)
         kv = torch.randn(2, m, hkv * d, device="cuda", generator=g)
         mask = torch.rand(2, m, hkv * d, device="cuda", generator=g) < 0.01
         kv = torch.where(mask, kv * 20.0, kv)
-        fwd.b_step_kv_write(0, kv[0], kv[1], m, p, 0)
+        for layer in range(n_layers):
+            fwd.b_step_kv_write(layer, kv[0], kv[1], m, p, 0)
     chunk = torch.randn(2, 512, hkv * d, device="cuda", generator=g)   # a 512-token chunked-prefill append
-    q = torch.randn(hq, d, device="cuda", generator=g)
-    kn = torch.randn(2, 1, hkv * d, device="cuda", generator=g)
-    out = torch.zeros(hq, d, device="cuda")
+    q = torch.randn(n_layers, hq, d, device="cuda", generator=g)
+    kn = torch.randn(n_layers, 2, 1, hkv * d, device="cuda", generator=g)
+    out = torch.zeros(n_layers, hq, d, device="cuda")
 
     def step():
-        dec.append(0, kn[0], kn[1], L - 1)
-        dec.attend(0, q, out, L)
+        for layer in range(n_layers):
+            dec.decode(layer, q[layer], kn[layer, 0], kn[layer, 1], out[layer], L - 1)
 
     def barrier():
         dist.barrier()
@@ -583,7 +586,7 @@ def run_position_sharded(args, w, rank, world, local_rank):
     ctx.poll()
     if rank == 0:
         ms, prefill_ms = float(t[0]), float(t[1])
-        step_bytes = algorithmic_bytes(w, [L], 0)
+        step_bytes = algorithmic_bytes(w, [L], 0) * w["n_layers"]
         line = {"metric": METRIC, "value": ms * 1e3 / args.steps / w["n_layers"], "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f32 (fp8/f16 storage)", "data": "synthetic",

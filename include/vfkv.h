@@ -335,23 +335,24 @@ int32_t vfkv_merge_partials_packed(vfkv_ctx *ctx, const float *d_packed, uint32_
 
 /* ---- peer exchange of partials (position sharding without a library collective) -----------
  *
- * No counterpart in the reference.  Each GPU of the group owns one exchange buffer.  The attention
- * kernel of vfkv_attend_push stores this GPU's (m, l, o) block into the buffer of EVERY rank with
- * plain peer stores and then publishes per-(kv-head) arrival flags (release, system scope);
- * vfkv_exchange_merge waits for the flags of all ranks in its own buffer -- at most the time set
- * with vfkv_exchange_set_timeout_ms (default 1000 ms); a wait that runs out sets bit 8 of the
- * status word read by vfkv_ctx_poll and writes zeros -- and applies the flash_attn_reduce.comp:51-80
- * merge.  Blocks and flags are double-buffered by the parity of a device-side exchange counter,
- * so both calls can be captured in a CUDA graph and replayed.  Every rank must make the same
- * sequence of push / merge calls, one merge per push.
+ * No counterpart in the reference.  Each GPU of the group owns one exchange buffer of 8-byte words
+ * {f32 value, u32 tag}.  The attention kernel of vfkv_attend_push stores this GPU's (m, l, o)
+ * block into the buffer of EVERY rank with plain peer stores, each word tagged with the number of
+ * the exchange (one 8-byte store per word, so a reader that finds the tag has the value: no
+ * flags, no fences).  vfkv_exchange_merge polls the words of all ranks in its own buffer -- at
+ * most the time set with vfkv_exchange_set_timeout_ms (default 1000 ms); a wait that runs out
+ * sets bit 8 of the status word read by vfkv_ctx_poll and writes zeros -- and applies the
+ * flash_attn_reduce.comp:51-80 merge.  Blocks are double-buffered by the parity of a device-side
+ * exchange counter, so both calls can be captured in a CUDA graph and replayed.  Every rank must
+ * make the same sequence of push / merge calls, one merge per push.
  *
  * Set-up: create on every rank with the same shape; make each rank's buffer known to the others,
  * either through vfkv_exchange_export / vfkv_exchange_import (CUDA IPC handles, one process per
  * GPU) or vfkv_exchange_set_peer (pointers the caller has mapped itself, or several ranks of one
  * process); synchronise the ranks once (the buffers are zeroed by create) before the first push.
- * world <= 8; n_rows = q-heads, n_groups = kv-heads of the sequence; head_dim a multiple of 4. */
+ * world <= 8; n_rows = q-heads of the sequence; head_dim a multiple of 4. */
 int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint32_t n_rows,
-                             uint32_t n_groups, uint32_t head_dim, vfkv_exchange **out);
+                             uint32_t head_dim, vfkv_exchange **out);
 void vfkv_exchange_destroy(vfkv_exchange *ex);
 uint64_t vfkv_exchange_bytes(const vfkv_exchange *ex);
 void *vfkv_exchange_local_ptr(const vfkv_exchange *ex);
@@ -362,9 +363,13 @@ int32_t vfkv_exchange_set_timeout_ms(vfkv_exchange *ex, uint32_t ms);
 /* 1 once every rank's buffer is known. */
 uint32_t vfkv_exchange_ready(const vfkv_exchange *ex);
 /* Attention of one query token over local positions [pos_begin, pos_end) of `slot`, the partial
- * delivered to every rank (arguments as vfkv_attend_partial). */
+ * delivered to every rank (arguments as vfkv_attend_partial).  d_k_new / d_v_new: null, or -- on
+ * the rank that owns the new token -- its K and V rows [kv_heads][head_dim] f32, stored at local
+ * position pos_end - 1 before the attention reads it (KvWrite + Attention of one layer in one
+ * launch where the tensor-core kernel covers the shape). */
 int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer,
-                         uint32_t kv_layer, const float *d_q, uint32_t n_q_heads, uint32_t slot,
+                         uint32_t kv_layer, const float *d_q, const float *d_k_new,
+                         const float *d_v_new, uint32_t n_q_heads, uint32_t slot,
                          uint32_t pos_begin, uint32_t pos_end, float scale, float softcap,
                          uint32_t n_splits, void *stream);
 /* Waits for all ranks' blocks of the current exchange and writes d_out [n_rows][head_dim]. */
@@ -372,9 +377,9 @@ int32_t vfkv_exchange_merge(vfkv_exchange *ex, float *d_out, void *stream);
 /* vfkv_attend_push followed by vfkv_exchange_merge. */
 int32_t vfkv_attend_exchange(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex,
                              uint32_t layer, uint32_t kv_layer, const float *d_q,
-                             uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin,
-                             uint32_t pos_end, float scale, float softcap, uint32_t n_splits,
-                             float *d_out, void *stream);
+                             const float *d_k_new, const float *d_v_new, uint32_t n_q_heads,
+                             uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale,
+                             float softcap, uint32_t n_splits, float *d_out, void *stream);
 
 /* ---------------------------------------------------------------------- */
 /* device-memory helpers for hosts without a CUDA binding of their own       */

@@ -73,7 +73,7 @@ def _emulated_group(ctx, world, seq_len, dtype, hq=HQ, hkv=HKV, d=D, page=256):
     for r in range(world):
         cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, sh.local_capacity(seq_len + 8)), dtype)
         fwd = vf.CudaForward(ctx, cache, n_heads=hq)
-        ex = vf.PeerExchange(ctx, world, r, hq, hkv, d)
+        ex = vf.PeerExchange(ctx, world, r, hq, d)
         ranks.append((cache, fwd, ShardedSequenceDecoder(fwd, sh, r), ex))
     for r, (_, _, _, ex) in enumerate(ranks):
         for o, (_, _, _, other) in enumerate(ranks):
@@ -106,7 +106,7 @@ def test_peer_exchange_emulated_ranks(ctx, world, seq_len, dtype, hq, hkv, d):
     kv_dtype = vf.KvDtype[dtype]
     odt = {"F8": oracle.F8, "F16": oracle.F16, "F32": oracle.F32}[dtype]
     rng = np.random.default_rng(world * 100 + seq_len)
-    steps = 3
+    steps = 4
     k = kv_values(rng, (seq_len + steps, hkv, d))
     v = kv_values(rng, (seq_len + steps, hkv, d))
     sh, ranks = _emulated_group(ctx, world, seq_len, kv_dtype, hq, hkv, d)
@@ -120,8 +120,13 @@ def test_peer_exchange_emulated_ranks(ctx, world, seq_len, dtype, hq, hkv, d):
             q = rng.standard_normal((hq, d), dtype=np.float32)
             dq = to_dev(q)
             for r, (_, fwd, dec, ex) in enumerate(ranks):
-                dec.append(0, dk[L - 1:L], dv[L - 1:L], L - 1)
-                fwd.attend_push(ex, 0, dq, 0, sh.local_len(L, r))
+                if t % 2 == 0:        # KvWrite as its own launch, then the attention
+                    dec.append(0, dk[L - 1:L], dv[L - 1:L], L - 1)
+                    fwd.attend_push(ex, 0, dq, 0, sh.local_len(L, r))
+                else:                 # the owner's attention kernel stores the new row itself
+                    mine = sh.owner(L - 1) == r
+                    fwd.attend_push(ex, 0, dq, 0, sh.local_len(L, r), k_new=dk[L - 1] if mine else None,
+                                    v_new=dv[L - 1] if mine else None)
             for r, (_, fwd, _, ex) in enumerate(ranks):
                 fwd.exchange_merge(ex, outs[r])
             torch.cuda.synchronize()
@@ -209,7 +214,7 @@ def _nccl_rank(rank, world, port, seq_len, result_dir):
         errs = [rel_err(out.cpu().numpy(), want)]
         # the same attention with the partials exchanged by peer stores (IPC-mapped buffers),
         # first as plain launches, then replayed from a CUDA graph
-        ex = vf.PeerExchange(ctx, world, rank, HQ, HKV, D)
+        ex = vf.PeerExchange(ctx, world, rank, HQ, D)
         ex.connect()
         pdec = ShardedSequenceDecoder(fwd, sh, rank, exchange=ex)
         dq = torch.from_numpy(q).cuda()

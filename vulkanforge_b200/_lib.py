@@ -80,7 +80,7 @@ SIGNATURES = {
     "vfkv_attend_partial": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp, vp, vp]),
     "vfkv_merge_partials": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, vp]),
     "vfkv_merge_partials_packed": (i32, [vp, vp, u32, u32, u32, vp, vp]),
-    "vfkv_exchange_create": (i32, [vp, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+    "vfkv_exchange_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
     "vfkv_exchange_destroy": (None, [vp]),
     "vfkv_exchange_bytes": (u64, [vp]),
     "vfkv_exchange_local_ptr": (vp, [vp]),
@@ -89,9 +89,9 @@ SIGNATURES = {
     "vfkv_exchange_set_peer": (i32, [vp, u32, vp]),
     "vfkv_exchange_set_timeout_ms": (i32, [vp, u32]),
     "vfkv_exchange_ready": (u32, [vp]),
-    "vfkv_attend_push": (i32, [vp, vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp]),
+    "vfkv_attend_push": (i32, [vp, vp, vp, u32, u32, vp, vp, vp, u32, u32, u32, u32, f32, f32, u32, vp]),
     "vfkv_exchange_merge": (i32, [vp, vp, vp]),
-    "vfkv_attend_exchange": (i32, [vp, vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp]),
+    "vfkv_attend_exchange": (i32, [vp, vp, vp, u32, u32, vp, vp, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp]),
     "vfkv_malloc": (i32, [vp, u64, C.POINTER(vp)]),
     "vfkv_free": (i32, [vp, vp]),
     "vfkv_malloc_host": (i32, [vp, u64, C.POINTER(vp)]),

@@ -741,8 +741,9 @@ int32_t vfkv_attend_partial(vfkv_cache *cache, vfkv_workspace *ws, uint32_t laye
 }
 
 int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer, uint32_t kv_layer,
-                         const float *d_q, uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin, uint32_t pos_end,
-                         float scale, float softcap, uint32_t n_splits, void *stream)
+                         const float *d_q, const float *d_k_new, const float *d_v_new, uint32_t n_q_heads,
+                         uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale, float softcap,
+                         uint32_t n_splits, void *stream)
 {
     int32_t rc = attend_common(cache, layer, kv_layer, n_q_heads, "vfkv_attend_push");
     if (rc) return rc;
@@ -752,34 +753,46 @@ int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *e
     if (!vfkv_exchange_ready(ex)) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: not every rank's buffer is set");
     if (slot >= cache->kv.config.n_slots || pos_end > cache->kv.config.max_seq_len || pos_begin > pos_end)
         return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: slot or position range out of bounds");
+    const bool has_new = d_k_new || d_v_new;
+    if (has_new && (!d_k_new || !d_v_new || pos_end == 0 || pos_begin == pos_end || kv_layer != layer))
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: a new token needs both K and V, a non-empty range and kv_layer == layer");
+    if ((reinterpret_cast<uintptr_t>(d_k_new) | reinterpret_cast<uintptr_t>(d_v_new)) % 16 != 0)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: K and V inputs must be 16-byte aligned");
     AttnArgs a;
     a.kv = make_view(cache, kv_layer);
-    if (ex->fan.n_rows != n_q_heads || ex->fan.n_groups != a.kv.n_kv_heads || ex->head_dim != a.kv.head_dim)
+    if (ex->fan.n_rows != n_q_heads || ex->head_dim != a.kv.head_dim)
         return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: exchange was created for another shape");
     a.seq.n_seqs = 1; a.seq.slot0 = slot; a.seq.seq_len_scalar = pos_end; a.seq.kv_start_scalar = pos_begin;
     a.q = d_q; a.n_q_heads = n_q_heads; a.scale = scale; a.softcap = softcap; a.n_splits = n_splits;
-    // the staged block has the layout of one exchange block
+    // the staged block has the layout of one exchange block, in plain floats
     a.out_m = ex->staging;
     a.out_l = ex->staging + n_q_heads;
-    a.out_o = ex->staging + fanout_o_offset(n_q_heads);
-    DeviceGuard g(ctx->device);
+    a.out_o = ex->staging + 2ull * n_q_heads;
     if (attn_mma_supported(a) && ctx->attn_impl != 1) {
-        a.out_m = a.out_l = a.out_o = nullptr;          // the kernel stores into the exchange buffers itself
-        a.fan = ex->fan;
+        a.out_m = a.out_l = a.out_o = nullptr;          // the kernel stores into the exchange buffers itself,
+        a.fan = ex->fan;                                // and writes the new token's cache row as well
+        a.k_new = d_k_new;
+        a.v_new = d_v_new;
+        DeviceGuard g(ctx->device);
         return launch_attention(ctx, ws, a, as_stream(stream));
     }
+    if (has_new) {
+        rc = vfkv_append(cache, layer, d_k_new, d_v_new, 1, slot, pos_end - 1, stream);
+        if (rc) return rc;
+    }
+    DeviceGuard g(ctx->device);
     rc = launch_attention(ctx, ws, a, as_stream(stream));
     if (rc) return rc;
     return launch_fanout_push(ctx, ex->fan, ex->staging, ex->head_dim, as_stream(stream));
 }
 
 int32_t vfkv_attend_exchange(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer,
-                             uint32_t kv_layer, const float *d_q, uint32_t n_q_heads, uint32_t slot,
-                             uint32_t pos_begin, uint32_t pos_end, float scale, float softcap, uint32_t n_splits,
-                             float *d_out, void *stream)
+                             uint32_t kv_layer, const float *d_q, const float *d_k_new, const float *d_v_new,
+                             uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale,
+                             float softcap, uint32_t n_splits, float *d_out, void *stream)
 {
-    int32_t rc = vfkv_attend_push(cache, ws, ex, layer, kv_layer, d_q, n_q_heads, slot, pos_begin, pos_end, scale,
-                                  softcap, n_splits, stream);
+    int32_t rc = vfkv_attend_push(cache, ws, ex, layer, kv_layer, d_q, d_k_new, d_v_new, n_q_heads, slot, pos_begin,
+                                  pos_end, scale, softcap, n_splits, stream);
     if (rc) return rc;
     return vfkv_exchange_merge(ex, d_out, stream);
 }

@@ -108,6 +108,10 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     if (cap < 1) cap = 1;
     if (cap > 64) cap = 64;
     uint64_t want = base ? (slots + base - 1) / base : 1;
+    // The CTA that merges reads every split's partial: beyond 16 splits that tail costs more than
+    // the extra CTAs save (one sequence of 16384 positions, 64 q-heads: 15.9 us with 16 splits,
+    // 19.5 us with 37), unless the length rule below asks for more.
+    if (want > 16) want = 16;
     // A CTA keeps at most its own ring of stages in flight, which bounds one CTA's stream to a few
     // tens of GB/s: in a ragged batch a sequence much longer than the rest would finish last on
     // its own.  No CTA gets more than 8192 positions, 4096 once contexts beyond 8192 are possible

@@ -297,7 +297,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
     const uint32_t bars = ring + S::RING_BYTES;           // kWarps*kStages mbarriers, 8 bytes each
-    __shared__ uint32_t s_flag;
+    __shared__ uint32_t s_flag, s_epoch;
 
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -339,7 +339,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     }
     };
-    if (mp.pdl != 2u) load_q();
+    // exchange number of a position-sharded call (written by the merge kernel of the previous
+    // exchange): fetched right after the wait so that the epilogue finds it in shared memory
+    auto load_epoch = [&]() { if (threadIdx.x == 32 && p.fan.world != 0u) s_epoch = *p.fan.epoch; };
+    if (mp.pdl != 2u) { load_q(); load_epoch(); }
 
     VFKV_TRACE(0);
     uint32_t slot, start, len, begin, end;
@@ -353,6 +356,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_flag = 0;
     }
+
     __syncthreads();
     VFKV_TRACE(2);
 
@@ -382,6 +386,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (mp.pdl == 2u) {       // the prefetch is in flight; now wait for the predecessor, then read Q
         asm volatile("griddepcontrol.wait;" ::: "memory");
         load_q();
+        load_epoch();
     }
 
     // ---- fused append (KvWrite of the decode step): the CTA whose range ends at the sequence's
@@ -685,7 +690,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const bool direct = p.n_splits == 1;
     const bool fan = p.fan.world != 0u;
     FanoutSlot fs{};
-    if (fan) fs = fanout_slot(p.fan, D, p.fan.rank, *p.fan.epoch + 1u);
+    if (fan) fs = fanout_slot(p.fan, D, p.fan.rank, s_epoch + 1u);
     for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
         const uint32_t j = idx / D, d = idx % D;
         float M = kMaskedScore;
@@ -710,9 +715,12 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
                 for (uint32_t r = 0; r < 8; ++r) {
                     if (r < p.fan.world) {
-                        float *dst = p.fan.base[r];
-                        dst[fs.o + row * D + d] = O;
-                        if (d == 0) { dst[fs.m + row] = m_nat; dst[fs.m + p.fan.n_rows + row] = L; }
+                        uint64_t *dst = p.fan.base[r];
+                        fanout_store(dst + fs.o + row * D + d, O, fs.epoch);
+                        if (d == 0) {
+                            fanout_store(dst + fs.m + row, m_nat, fs.epoch);
+                            fanout_store(dst + fs.m + p.fan.n_rows + row, L, fs.epoch);
+                        }
                     }
                 }
             }
@@ -723,10 +731,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     }
     VFKV_TRACE(7);
-    if (direct) {
-        if (fan) { __syncthreads(); fanout_publish(p.fan, fs, s * p.n_kv_heads + kvh); }
-        return;
-    }
+    if (direct) return;
 
     // ---- the last CTA of this (sequence, kv-head) merges the splits ---------------------------------
     // The barrier orders every thread's partial stores before thread 0's ticket; the ticket is an
@@ -788,14 +793,16 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
             for (uint32_t r = 0; r < 8; ++r) {
                 if (r < p.fan.world) {
-                    float *dst = p.fan.base[r];
-                    *reinterpret_cast<float4 *>(dst + fs.o + row * D + d) = a;
-                    if (d == 0) { dst[fs.m + row] = gmax; dst[fs.m + p.fan.n_rows + row] = gsum; }
+                    uint64_t *dst = p.fan.base[r];
+                    fanout_store4(dst + fs.o + row * D + d, a, fs.epoch);
+                    if (d == 0) {
+                        fanout_store(dst + fs.m + row, gmax, fs.epoch);
+                        fanout_store(dst + fs.m + p.fan.n_rows + row, gsum, fs.epoch);
+                    }
                 }
             }
         }
     }
-    if (fan) { __syncthreads(); fanout_publish(p.fan, fs, s * p.n_kv_heads + kvh); }
     VFKV_TRACE(9);
     if (threadIdx.x == 0) mp.counters[s * p.n_kv_heads + kvh] = 0u;   // ready for the next launch
 }

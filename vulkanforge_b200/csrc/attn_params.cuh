@@ -91,42 +91,38 @@ __device__ __forceinline__ void split_range(uint32_t start, uint32_t len, uint32
     *begin = uint32_t(b); *end = uint32_t(e);
 }
 
-// Layout of one source rank's block inside an exchange buffer, in floats: m[n_rows], l[n_rows],
-// padding to a multiple of 4, o[n_rows][head_dim]; the block itself is padded to a multiple of 4.
-__host__ __device__ __forceinline__ uint64_t fanout_o_offset(uint32_t n_rows) { return (2ull * n_rows + 3) & ~3ull; }
-__host__ __device__ __forceinline__ uint64_t fanout_block_floats(uint32_t n_rows, uint32_t head_dim)
+// Words in one source rank's block of an exchange buffer: m[n_rows], l[n_rows], o[n_rows][head_dim].
+__host__ __device__ __forceinline__ uint64_t fanout_block_words(uint32_t n_rows, uint32_t head_dim)
 {
-    return (fanout_o_offset(n_rows) + uint64_t(n_rows) * head_dim + 3) & ~3ull;
+    return uint64_t(n_rows) * (head_dim + 2);
 }
-// Where source rank `src`'s block of exchange number e lives inside any rank's exchange buffer.
+// Word offsets of source rank `src`'s block of exchange number `epoch` inside any rank's buffer.
 struct FanoutSlot {
-    uint32_t epoch;      // e
-    uint64_t m;          // float offset of m[n_rows]; l follows at + n_rows
-    uint64_t o;          // float offset of o[n_rows][head_dim] (16-byte aligned)
-    uint64_t flags;      // 4-byte offset of this rank's flag row
+    uint32_t epoch;
+    uint64_t m;          // m[n_rows]; l follows at + n_rows
+    uint64_t o;          // o[n_rows][head_dim]; even, so pairs of words are 16-byte aligned
 };
 __device__ __forceinline__ FanoutSlot fanout_slot(const PeerFanout &f, uint32_t head_dim, uint32_t src, uint32_t epoch)
 {
     FanoutSlot s;
     s.epoch = epoch;
-    const uint64_t packed = fanout_block_floats(f.n_rows, head_dim);
-    const uint64_t blk = uint64_t(epoch & 1u) * f.world + src;
-    s.m = blk * packed;
-    s.o = s.m + fanout_o_offset(f.n_rows);
-    s.flags = 2ull * f.world * packed + blk * f.n_groups;
+    s.m = (uint64_t(epoch & 1u) * f.world + src) * fanout_block_words(f.n_rows, head_dim);
+    s.o = s.m + 2ull * f.n_rows;
     return s;
 }
-// Publishes flag `group` of this rank's block on every GPU.  Call after a CTA barrier that follows
-// the CTA's stores of the block: the release at system scope is cumulative over them.
-__device__ __forceinline__ void fanout_publish(const PeerFanout &f, const FanoutSlot &s, uint32_t group)
+__device__ __forceinline__ uint64_t fanout_word(float v, uint32_t tag)
 {
-#pragma unroll
-    for (uint32_t r = 0; r < 8; ++r) {          // static indices: the pointer table stays in the parameter bank
-        if (threadIdx.x == r && r < f.world) {
-            uint32_t *flag = reinterpret_cast<uint32_t *>(f.base[r]) + s.flags + group;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(flag), "r"(s.epoch) : "memory");
-        }
-    }
+    return uint64_t(__float_as_uint(v)) | (uint64_t(tag) << 32);
+}
+__device__ __forceinline__ void fanout_store(uint64_t *dst, float v, uint32_t tag)
+{
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(dst), "l"(fanout_word(v, tag)) : "memory");
+}
+// four consecutive values (dst 16-byte aligned) as two 16-byte stores
+__device__ __forceinline__ void fanout_store4(uint64_t *dst, float4 v, uint32_t tag)
+{
+    asm volatile("st.global.v2.u64 [%0], {%1, %2};" :: "l"(dst), "l"(fanout_word(v.x, tag)), "l"(fanout_word(v.y, tag)) : "memory");
+    asm volatile("st.global.v2.u64 [%0], {%1, %2};" :: "l"(dst + 2), "l"(fanout_word(v.z, tag)), "l"(fanout_word(v.w, tag)) : "memory");
 }
 
 __device__ __forceinline__ float apply_softcap(float s, float cap)

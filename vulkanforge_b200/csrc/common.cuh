@@ -92,17 +92,17 @@ struct SeqArgs {
 };
 
 // Fan-out of the (m, l, o) partial to every GPU of a position-sharded group, written by the
-// attention kernel itself.  base[r] is rank r's exchange buffer (peer memory except base[rank]):
-//   floats  [parity 2][source rank][ m[n_rows] | l[n_rows] | o[n_rows][head_dim] ]
-//   uint32  [parity 2][source rank][group]      arrival flags, one per (sequence, kv-head)
-// A kernel of exchange number e = *epoch + 1 uses parity e & 1 and stores e into the flags.
+// attention kernel itself.  base[r] is rank r's exchange buffer (peer memory except base[rank]),
+// an array of 8-byte words {f32 value, u32 tag}:
+//   [parity 2][source rank][ m[n_rows] | l[n_rows] | o[n_rows][head_dim] ]
+// A kernel of exchange number e = *epoch + 1 uses parity e & 1 and tags every word with e.  A word
+// is written by one 8-byte store, so a reader that sees the tag has the value: no flag, no fence.
 struct PeerFanout {
-    float *base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    uint64_t *base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     const uint32_t *epoch = nullptr;   // this GPU's count of completed exchanges (device memory)
     uint32_t world = 0;                // 0 = no fan-out
     uint32_t rank = 0;
     uint32_t n_rows = 0;               // sequences * q-heads
-    uint32_t n_groups = 0;             // sequences * kv-heads
 };
 
 struct AttnArgs {
@@ -192,7 +192,7 @@ struct vfkv_exchange {
     vfkv_ctx *ctx = nullptr;
     vfkv::PeerFanout fan;          // base[], epoch pointer, world, rank, rows, groups
     uint32_t head_dim = 0;
-    float *local = nullptr;        // this rank's buffer: blocks, then flags
+    uint64_t *local = nullptr;     // this rank's buffer of tagged words
     uint64_t bytes = 0;
     uint32_t *ctl = nullptr;       // [0] completed exchanges, [1] merge ticket (never shared)
     float *staging = nullptr;      // one block, for attention kernels that cannot fan out themselves

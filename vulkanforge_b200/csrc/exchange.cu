@@ -2,12 +2,13 @@
 //
 // No counterpart in the reference (it is single-GPU).  The math of the merge is
 // vk_shaders/flash_attn_reduce.comp:51-80 over one part per GPU.  Every GPU owns one exchange
-// buffer; the attention kernel of rank r stores its (m, l, o) block into the buffer of every rank
-// (plain peer stores) and then sets that block's arrival flags with a release at system scope.
-// The merge kernel of each rank waits, with a time limit, for the flags of all source ranks in its
-// own buffer and reduces the blocks.  Blocks and flags are double-buffered by the parity of the
-// exchange number: a rank cannot be more than one exchange ahead of the slowest rank, because its
-// own merge needs that rank's flags first.
+// buffer of 8-byte words {f32 value, u32 tag}.  The attention kernel of rank r stores its (m, l, o)
+// block into the buffer of every rank with plain peer stores, every word tagged with the number of
+// the exchange; a word is written by a single 8-byte store, so a reader that finds the tag has
+// the value, and neither a flag nor a fence is needed.  The merge kernel of each rank polls, with
+// a time limit, the words of all source ranks in its own buffer and reduces them.  Blocks are
+// double-buffered by the parity of the exchange number: a rank cannot be more than one exchange
+// ahead of the slowest rank, because its own merge needs that rank's words first.
 #include "attn_params.cuh"
 
 #include <cstring>
@@ -22,77 +23,106 @@ __device__ __forceinline__ uint64_t global_ns()
     return t;
 }
 
-// Copies one staged block into every rank's buffer and publishes its flags (the path of attention
-// kernels without the fused fan-out).  One CTA per group so the flag follows that group's rows.
+// Copies one staged block (plain floats: m[n_rows], l[n_rows], o[n_rows][head_dim]) into every
+// rank's buffer as tagged words: the path of attention kernels without the fused fan-out.
 __global__ void __launch_bounds__(256)
 fanout_push_kernel(PeerFanout fan, const float *__restrict__ staging, uint32_t head_dim)
 {
-    const uint32_t group = blockIdx.x;
-    const uint32_t g = fan.n_rows / fan.n_groups;
     const FanoutSlot fs = fanout_slot(fan, head_dim, fan.rank, *fan.epoch + 1u);
-    const uint64_t o_off = fanout_o_offset(fan.n_rows);
-    for (uint32_t idx = threadIdx.x; idx < g * head_dim; idx += blockDim.x) {
-        const uint32_t row = group * g + idx / head_dim, d = idx % head_dim;
-        const float o = staging[o_off + uint64_t(row) * head_dim + d];
-        const float m = staging[row], l = staging[fan.n_rows + row];
+    const uint64_t n = fanout_block_words(fan.n_rows, head_dim);
+    for (uint64_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
+        const float v = staging[i];
 #pragma unroll
-        for (uint32_t r = 0; r < 8; ++r) {
-            if (r < fan.world) {
-                float *dst = fan.base[r];
-                dst[fs.o + uint64_t(row) * head_dim + d] = o;
-                if (d == 0) { dst[fs.m + row] = m; dst[fs.m + fan.n_rows + row] = l; }
-            }
-        }
+        for (uint32_t r = 0; r < 8; ++r)
+            if (r < fan.world) fanout_store(fan.base[r] + fs.m + i, v, fs.epoch);
     }
-    __syncthreads();
-    fanout_publish(fan, fs, group);
 }
 
-// One CTA per output row.  Thread r < world waits for source rank r's flag of this row's group;
-// a wait that runs out sets bit 8 of the status word and the row is written as zeros.
+__device__ __forceinline__ uint64_t load_word(const uint64_t *p)
+{
+    uint64_t w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+
+// Re-reads *p until it carries tag e or the time limit passes; returns false on a time-out.
+__device__ __forceinline__ bool await_word(const uint64_t *p, uint64_t &w, uint32_t e, uint64_t t0, uint64_t wait_ns)
+{
+    while (uint32_t(w >> 32) != e) {
+        if (global_ns() - t0 > wait_ns) return false;
+        __nanosleep(32);
+        w = load_word(p);
+    }
+    return true;
+}
+
+// One CTA per output row, thread t owning dims t, t+128, ...  All words a thread needs are
+// requested at once; only those whose tag is not there yet are polled.  A wait that runs out sets
+// bit 8 of the status word and the row is written as zeros.
 __global__ void __launch_bounds__(128)
-exchange_merge_kernel(PeerFanout fan, const float *__restrict__ local, uint32_t *__restrict__ ctl,
+exchange_merge_kernel(PeerFanout fan, const uint64_t *__restrict__ local, uint32_t *__restrict__ ctl,
                       uint32_t head_dim, uint64_t wait_ns, float *__restrict__ out, uint32_t *__restrict__ status)
 {
+    constexpr int kMaxDims = 4, kMaxWorld = 8;
+    __shared__ float s_m[kMaxWorld], s_l[kMaxWorld];
     __shared__ uint32_t s_bad;
+    // Dependent launch: lets the next kernel of the stream start its prologue, and waits for the
+    // attention kernel before it (and through it for the previous merge, which wrote ctl[0]).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t row = blockIdx.x;
-    const uint32_t g = fan.n_rows / fan.n_groups;
     const uint32_t e = ctl[0] + 1u;
+    const uint64_t t0 = global_ns();
     if (threadIdx.x == 0) s_bad = 0u;
     __syncthreads();
-    if (threadIdx.x < fan.world) {
-        const FanoutSlot fs = fanout_slot(fan, head_dim, threadIdx.x, e);
-        const uint32_t *flag = reinterpret_cast<const uint32_t *>(local) + fs.flags + row / g;
-        const uint64_t t0 = global_ns();
-        for (;;) {
-            uint32_t v;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-            if (int32_t(v - e) >= 0) break;
-            if (global_ns() - t0 > wait_ns) { atomicOr(&s_bad, 1u); break; }
-            __nanosleep(64);
+
+    uint64_t w[kMaxWorld][kMaxDims];
+#pragma unroll
+    for (uint32_t r = 0; r < kMaxWorld; ++r) {
+        const FanoutSlot fs = fanout_slot(fan, head_dim, r, e);
+#pragma unroll
+        for (int j = 0; j < kMaxDims; ++j) {
+            const uint32_t d = threadIdx.x + j * 128;
+            w[r][j] = (r < fan.world && d < head_dim) ? load_word(local + fs.o + uint64_t(row) * head_dim + d) : 0ull;
         }
     }
+    bool ok = true;
+    if (threadIdx.x < 2 * fan.world) {                       // m and l of every source rank
+        const uint32_t r = threadIdx.x >> 1, which = threadIdx.x & 1;
+        const FanoutSlot fs = fanout_slot(fan, head_dim, r, e);
+        const uint64_t *p = local + fs.m + uint64_t(which) * fan.n_rows + row;
+        uint64_t v = load_word(p);
+        ok = await_word(p, v, e, t0, wait_ns);
+        (which ? s_l : s_m)[r] = __uint_as_float(uint32_t(v));
+    }
+#pragma unroll
+    for (uint32_t r = 0; r < kMaxWorld; ++r) {
+        const FanoutSlot fs = fanout_slot(fan, head_dim, r, e);
+#pragma unroll
+        for (int j = 0; j < kMaxDims; ++j) {
+            const uint32_t d = threadIdx.x + j * 128;
+            if (r < fan.world && d < head_dim)
+                ok = await_word(local + fs.o + uint64_t(row) * head_dim + d, w[r][j], e, t0, wait_ns) && ok;
+        }
+    }
+    if (!ok) atomicOr(&s_bad, 1u);
     __syncthreads();
     const bool bad = s_bad != 0u;
     if (bad && threadIdx.x == 0) atomicOr(status, 8u);
 
-    constexpr int kMaxDims = 4;
     float acc[kMaxDims] = {0.f, 0.f, 0.f, 0.f};
     float gmax = kMaskedScore, gsum = 0.f;
     if (!bad) {
-        for (uint32_t r = 0; r < fan.world; ++r) {
-            const FanoutSlot fs = fanout_slot(fan, head_dim, r, e);
-            gmax = fmaxf(gmax, __ldcg(local + fs.m + row));
-        }
-        for (uint32_t r = 0; r < fan.world; ++r) {
-            const FanoutSlot fs = fanout_slot(fan, head_dim, r, e);
-            const float kn = __expf(__ldcg(local + fs.m + row) - gmax);
-            gsum = fmaf(__ldcg(local + fs.m + fan.n_rows + row), kn, gsum);
 #pragma unroll
-            for (int j = 0; j < kMaxDims; ++j) {
-                const uint32_t d = threadIdx.x + j * 128;
-                const float t = d < head_dim ? __ldcg(local + fs.o + uint64_t(row) * head_dim + d) : 0.f;
-                acc[j] = fmaf(t, kn, acc[j]);
+        for (uint32_t r = 0; r < kMaxWorld; ++r)
+            if (r < fan.world) gmax = fmaxf(gmax, s_m[r]);
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxWorld; ++r) {
+            if (r < fan.world) {
+                const float kn = __expf(s_m[r] - gmax);
+                gsum = fmaf(s_l[r], kn, gsum);
+#pragma unroll
+                for (int j = 0; j < kMaxDims; ++j) acc[j] = fmaf(__uint_as_float(uint32_t(w[r][j])), kn, acc[j]);
             }
         }
     }
@@ -113,7 +143,8 @@ exchange_merge_kernel(PeerFanout fan, const float *__restrict__ local, uint32_t 
 int32_t launch_fanout_push(vfkv_ctx *ctx, const PeerFanout &fan, const float *staging, uint32_t head_dim,
                            cudaStream_t st)
 {
-    fanout_push_kernel<<<fan.n_groups, 256, 0, st>>>(fan, staging, head_dim);
+    const uint64_t n = fanout_block_words(fan.n_rows, head_dim);
+    fanout_push_kernel<<<uint32_t((n + 255) / 256), 256, 0, st>>>(fan, staging, head_dim);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "fanout_push launch");
 }
@@ -132,22 +163,22 @@ struct Guard {
 
 extern "C" {
 
-int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint32_t n_rows, uint32_t n_groups,
-                             uint32_t head_dim, vfkv_exchange **out)
+int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint32_t n_rows, uint32_t head_dim,
+                             vfkv_exchange **out)
 {
     if (!ctx || !out) return VFKV_ERR_INVALID;
     *out = nullptr;
     if (world == 0 || world > 8 || rank >= world)
         return set_error(ctx, VFKV_ERR_INVALID, "vfkv_exchange_create: world must be 1..8 and rank below it");
-    if (n_rows == 0 || n_groups == 0 || n_rows % n_groups != 0 || head_dim == 0 || head_dim > 512 || head_dim % 4 != 0)
-        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_exchange_create: rows must be a multiple of groups, head_dim a multiple of 4 up to 512");
+    if (n_rows == 0 || head_dim == 0 || head_dim > 512 || head_dim % 4 != 0)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_exchange_create: head_dim must be a multiple of 4 up to 512");
     Guard g(ctx->device);
     vfkv_exchange *ex = new (std::nothrow) vfkv_exchange();
     if (!ex) return set_error(ctx, VFKV_ERR_OOM, "vfkv_exchange_create: host allocation failed");
     ex->ctx = ctx;
     ex->head_dim = head_dim;
-    const uint64_t block = fanout_block_floats(n_rows, head_dim);
-    ex->bytes = (2ull * world * block + 2ull * world * n_groups) * 4;
+    const uint64_t block = fanout_block_words(n_rows, head_dim);
+    ex->bytes = 2ull * world * block * 8;
     cudaError_t e = cudaMalloc(&ex->local, ex->bytes);
     if (e == cudaSuccess) e = cudaMalloc(&ex->ctl, 16);
     if (e == cudaSuccess) e = cudaMalloc(&ex->staging, block * 4);
@@ -161,7 +192,7 @@ int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint3
         return set_error(ctx, e == cudaErrorMemoryAllocation ? VFKV_ERR_OOM : VFKV_ERR_CUDA,
                          std::string("vfkv_exchange_create: ") + cudaGetErrorString(e));
     }
-    ex->fan.world = world; ex->fan.rank = rank; ex->fan.n_rows = n_rows; ex->fan.n_groups = n_groups;
+    ex->fan.world = world; ex->fan.rank = rank; ex->fan.n_rows = n_rows;
     ex->fan.epoch = ex->ctl;
     ex->fan.base[rank] = ex->local;
     *out = ex;
@@ -207,7 +238,7 @@ int32_t vfkv_exchange_import(vfkv_exchange *ex, uint32_t rank, const uint8_t han
     void *p = nullptr;
     cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
     if (e != cudaSuccess) return check_cuda(ex->ctx, e, "vfkv_exchange_import");
-    ex->fan.base[rank] = static_cast<float *>(p);
+    ex->fan.base[rank] = static_cast<uint64_t *>(p);
     ex->imported[rank] = true;
     return VFKV_OK;
 }
@@ -219,7 +250,7 @@ int32_t vfkv_exchange_set_peer(vfkv_exchange *ex, uint32_t rank, void *d_peer_bu
         return set_error(ex->ctx, VFKV_ERR_INVALID, "vfkv_exchange_set_peer: rank must be another member of the group");
     if (reinterpret_cast<uintptr_t>(d_peer_buffer) % 16 != 0)
         return set_error(ex->ctx, VFKV_ERR_INVALID, "vfkv_exchange_set_peer: buffer must be 16-byte aligned");
-    ex->fan.base[rank] = static_cast<float *>(d_peer_buffer);
+    ex->fan.base[rank] = static_cast<uint64_t *>(d_peer_buffer);
     ex->imported[rank] = false;
     return VFKV_OK;
 }
@@ -245,8 +276,18 @@ int32_t vfkv_exchange_merge(vfkv_exchange *ex, float *d_out, void *stream)
     vfkv_ctx *ctx = ex->ctx;
     Guard g(ctx->device);
     ProfScope ps(ctx, VFKV_PROF_FA_REDUCE, static_cast<cudaStream_t>(stream));
-    exchange_merge_kernel<<<ex->fan.n_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        ex->fan, ex->local, ex->ctl, ex->head_dim, ex->wait_ns, d_out, ctx->d_status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ex->fan.n_rows);
+    cfg.blockDim = dim3(128);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, exchange_merge_kernel, ex->fan, static_cast<const uint64_t *>(ex->local),
+                                        ex->ctl, ex->head_dim, ex->wait_ns, d_out, ctx->d_status);
+    if (le != cudaSuccess) return check_cuda(ctx, le, "exchange_merge launch");
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "exchange_merge launch");
 }

@@ -160,24 +160,26 @@ class CudaForward:
                                                    ptr(o), self.stream))
 
     def attend_push(self, exchange, layer: int, q, pos_begin: int, pos_end: int, slot: int = 0,
-                    kv_layer: Optional[int] = None):
-        """Local partial over [pos_begin, pos_end), stored by the kernel into every rank's exchange buffer."""
+                    kv_layer: Optional[int] = None, k_new=None, v_new=None):
+        """Local partial over [pos_begin, pos_end), stored by the kernel into every rank's exchange
+        buffer.  k_new / v_new: the new token's rows when this rank owns local position pos_end - 1."""
         kv_layer = self.gemma4_kv_read_layer(layer) if kv_layer is None else kv_layer
         self.ctx.check(self._L.vfkv_attend_push(self.kv_cache.handle, self.workspace.handle, exchange.handle, layer,
-                                                kv_layer, ptr(q), self.n_heads, slot, pos_begin, pos_end,
-                                                self.attn_scale, self.softcap, self.n_splits, self.stream))
+                                                kv_layer, ptr(q), ptr(k_new), ptr(v_new), self.n_heads, slot,
+                                                pos_begin, pos_end, self.attn_scale, self.softcap, self.n_splits,
+                                                self.stream))
 
     def exchange_merge(self, exchange, out):
         """Waits (bounded) for every rank's partial of the current exchange and merges them into out."""
         self.ctx.check(self._L.vfkv_exchange_merge(exchange.handle, ptr(out), self.stream))
 
     def attend_exchange(self, exchange, layer: int, q, pos_begin: int, pos_end: int, out, slot: int = 0,
-                        kv_layer: Optional[int] = None):
+                        kv_layer: Optional[int] = None, k_new=None, v_new=None):
         kv_layer = self.gemma4_kv_read_layer(layer) if kv_layer is None else kv_layer
         self.ctx.check(self._L.vfkv_attend_exchange(self.kv_cache.handle, self.workspace.handle, exchange.handle,
-                                                    layer, kv_layer, ptr(q), self.n_heads, slot, pos_begin, pos_end,
-                                                    self.attn_scale, self.softcap, self.n_splits, ptr(out),
-                                                    self.stream))
+                                                    layer, kv_layer, ptr(q), ptr(k_new), ptr(v_new), self.n_heads,
+                                                    slot, pos_begin, pos_end, self.attn_scale, self.softcap,
+                                                    self.n_splits, ptr(out), self.stream))
 
     def merge_partials(self, m, l, o, n_parts: int, n_rows: int, head_dim: int, out):
         self.ctx.check(self._L.vfkv_merge_partials(self.ctx.handle, ptr(m), ptr(l), ptr(o), n_parts, n_rows,

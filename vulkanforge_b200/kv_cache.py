@@ -153,10 +153,10 @@ class PeerExchange:
     """One GPU's end of the peer exchange of (m, l, o) partials used by position sharding
     (``vfkv_exchange_*``; no counterpart in the reference)."""
 
-    def __init__(self, ctx: Context, world: int, rank: int, n_rows: int, n_groups: int, head_dim: int):
+    def __init__(self, ctx: Context, world: int, rank: int, n_rows: int, head_dim: int):
         self.ctx, self.world, self.rank = ctx, world, rank
         h = C.c_void_p()
-        ctx.check(ctx._lib.vfkv_exchange_create(ctx.handle, world, rank, n_rows, n_groups, head_dim, C.byref(h)))
+        ctx.check(ctx._lib.vfkv_exchange_create(ctx.handle, world, rank, n_rows, head_dim, C.byref(h)))
         self.handle = h
 
     def bytes(self) -> int:

@@ -131,6 +131,18 @@ class ShardedSequenceDecoder:
             p = stop
         return done
 
+    def decode(self, layer: int, q, k_src, v_src, out, position: int):
+        """One decode step of global ``position``: append (owner rank only) and attention over
+        [0, position], merged over the ranks.  With a peer exchange the owner's attention kernel
+        stores the new row itself."""
+        if self.exchange is None:
+            self.append(layer, k_src, v_src, position)
+            return self.attend(layer, q, out, position + 1)
+        mine = self.shards.owner(position) == self.rank
+        self.fwd.attend_exchange(self.exchange, layer, q, 0, self.shards.local_len(position + 1, self.rank), out,
+                                 k_new=k_src if mine else None, v_new=v_src if mine else None)
+        return out
+
     def attend(self, layer: int, q, out, seq_len: int):
         """Attention of one query token over global positions [0, seq_len): local partial, one
         all-gather, merge.  ``out`` [Hq][D] is complete on every rank."""
