@@ -245,3 +245,30 @@ def decode_step(q, k_new, v_new, k_slabs, v_slabs, dtype, n_seqs, slab_positions
 
 def num_threads() -> int:
     return int(lib().vfo_num_threads())
+
+
+def batch_attention_ref(q, k, v, dtype, n_heads, n_kv_heads, head_dim, m, q_start, n_kv, kv_start=0,
+                        window=0, scale=None, softcap=0.0) -> np.ndarray:
+    """Causal attention of m queries over the cache rows: cpu_batch_attn_reference
+    (tests/correctness.rs:3016-3071) with the kv_start mask of flash_attn_batch.comp:141-147.
+    Query i attends over [lo_i, min(q_start + i + 1, n_kv)); lo_i = kv_start, or with
+    window != 0 (the build's per-query extension) max(kv_start, causal_len_i - window).
+    A query with an empty range yields zeros.  q: [m][n_heads][head_dim]."""
+    q = _c(q, np.float32).reshape(m, n_heads, head_dim)
+    out = np.zeros((m, n_heads, head_dim), np.float32)
+    for i in range(m):
+        causal = min(q_start + i + 1, n_kv)
+        lo = kv_start
+        if window and causal > window:
+            lo = max(lo, causal - window)
+        lo = min(lo, causal)
+        if causal > lo:
+            out[i] = attention_ref(q[i], k, v, dtype, n_heads, n_kv_heads, head_dim, causal, lo, scale, softcap)
+    return out
+
+
+def rope_neox_rows(x, n_heads: int, head_dim: int, n_dims: int, positions, freq_base: float) -> np.ndarray:
+    """rope_neox applied row by row: x [rows][n_heads][head_dim], positions [rows]."""
+    x = _c(x, np.float32).reshape(len(positions), n_heads, head_dim)
+    return np.stack([rope_neox(x[r], n_heads, head_dim, n_dims, int(positions[r]), freq_base).reshape(n_heads, head_dim)
+                     for r in range(len(positions))])

@@ -1,4 +1,4 @@
-"""The C-ABI library loads without a GPU and exports every symbol include/vfkv.h declares;
+"""The C-ABI library loads without a GPU and exports every symbol include/*.h declares;
 host-only entry points behave like their reference counterparts."""
 import ctypes as C
 import os
@@ -9,13 +9,18 @@ import pytest
 import vulkanforge_b200 as vf
 from vulkanforge_b200 import _lib
 
-HEADER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "vfkv.h")
+INCLUDE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
 
 
 def declared_functions():
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(vfkv_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in sorted(os.listdir(INCLUDE)):
+        if not header.endswith(".h"):
+            continue
+        text = open(os.path.join(INCLUDE, header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(vfkv_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_every_declared_symbol_is_exported_and_bound():
@@ -23,7 +28,7 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert len(names) >= 50
     lib = C.CDLL(vf.LIB_PATH)
     for n in names:
-        assert hasattr(lib, n), f"{n} declared in vfkv.h but not exported"
+        assert hasattr(lib, n), f"{n} declared in include/ but not exported"
     assert set(names) == set(_lib.SIGNATURES), set(names) ^ set(_lib.SIGNATURES)
     assert vf.load().vfkv_abi_version() == 1
 

@@ -1,0 +1,273 @@
+"""The callers either side of the hot path on the GPU: decode attention routing
+(run_scalar_attn / flash_attn), chunked-prefill causal attention over the cache, RoPE fused with
+the append, and the prefix-reuse bookkeeping.  Everything is compared with the CPU oracle."""
+import numpy as np
+import pytest
+
+import oracle
+import vulkanforge_b200 as vf
+from util import dev_view_bytes, encode_cache, kv_values, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+ODT = {"F32": oracle.F32, "F16": oracle.F16, "F8": oracle.F8}
+
+
+def _fill(fwd, k, v, layer=0, slot=0):
+    fwd.b_step_kv_write(layer, to_dev(k), to_dev(v), k.shape[0], 0, slot)
+
+
+def _check(got, want, dtype, abs_tol=2e-3):
+    if dtype == "F8":
+        assert rel_err(got, want) < 3e-2
+    else:
+        assert float(np.max(np.abs(got - want))) < abs_tol
+
+
+# ---- decode routing (runs.rs:722-821; tests/correctness.rs:2708-2784 for the short cases) -----------
+@pytest.mark.parametrize("dtype", ["F32", "F16", "F8"])
+@pytest.mark.parametrize("seq_len", [1, 2, 63, 64, 65, 200])
+def test_scalar_attn_routes_short_and_long(ctx, dtype, seq_len):
+    import torch
+    hq, hkv, d = 32, 8, 128
+    rng = np.random.default_rng(seq_len)
+    k, v = kv_values(rng, (seq_len, hkv, d)), kv_values(rng, (seq_len, hkv, d))
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, 256), vf.KvDtype[dtype])
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        _fill(fwd, k, v)
+        out = torch.zeros(hq, d, device="cuda")
+        n0 = ctx.launch_count()
+        fwd.run_scalar_attn(to_dev(q), out, 0, seq_len - 1)
+        torch.cuda.synchronize()
+        kc, vc = encode_cache(k, ODT[dtype]), encode_cache(v, ODT[dtype])
+        want = oracle.attention_ref(q, kc, vc, ODT[dtype], hq, hkv, d, seq_len)
+        _check(out.cpu().numpy(), want, dtype, 1e-3)
+        if seq_len <= 64:
+            assert ctx.launch_count() - n0 == 1          # the single-pass route: one launch, no reduce
+        if seq_len == 1:                                 # seq 1 => out == V (tests/correctness.rs:1003-1035)
+            vdec = oracle.attention_ref(np.ones((hq, d), np.float32), kc, vc, ODT[dtype], hq, hkv, d, 1)
+            assert np.allclose(out.cpu().numpy(), vdec, atol=1e-6)
+        # the distinct flash_attn entry gives the same answer at any length and needs no workspace
+        out2 = torch.zeros(hq, d, device="cuda")
+        fwd.run_flash_attn(to_dev(q), out2, 0, seq_len - 1, 0, 0)
+        torch.cuda.synchronize()
+        _check(out2.cpu().numpy(), want, dtype, 1e-3)
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+# ---- prefill attention ---------------------------------------------------------------------------
+def _reference_batch_inputs(m, q_start, hq, hkv, d):
+    """The deterministic inputs of run_batch_attn (tests/correctness.rs:3093-3112), evaluated in
+    f32 as there: sines / cosines of index combinations, so that a wrong stride or group size shows."""
+    n_kv = q_start + m
+    f = np.float32
+    qi, h, dd = (a.astype(f) for a in np.meshgrid(np.arange(m), np.arange(hq), np.arange(d), indexing="ij"))
+    q = np.sin(qi * f(0.017) + h * f(0.011) + dd * f(0.003)).astype(f)
+    t, kh, dd = (a.astype(f) for a in np.meshgrid(np.arange(n_kv), np.arange(hkv), np.arange(d), indexing="ij"))
+    k = np.cos((t + f(1.0)) * f(0.01) + dd * f(0.001) + kh * f(0.7)).astype(f)
+    v = np.sin(t * f(0.013) + kh * f(0.5) + dd * f(0.0007)).astype(f)
+    return q, k, v
+
+
+@pytest.mark.parametrize("dtype", ["F32", "F16", "F8"])
+@pytest.mark.parametrize("m,q_start,tol", [(1, 0, 1e-4), (4, 0, 1e-3), (16, 0, 1e-3), (64, 0, 1e-3), (200, 0, 1e-3),
+                                           (4, 60, 1e-3)])
+def test_batch_attn_reference_cases(ctx, dtype, m, q_start, tol):
+    """test_batch_attn_m1/m4/m16/m64/m200_vs_cpu and _q_start_offset (tests/correctness.rs:3159-3200)
+    at the reference's shape 32 / 8 / 128 and thresholds."""
+    import torch
+    hq, hkv, d = 32, 8, 128
+    q, k, v = _reference_batch_inputs(m, q_start, hq, hkv, d)
+    n_kv = q_start + m
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, 512), vf.KvDtype[dtype])
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        _fill(fwd, k, v)
+        out = torch.zeros(m, hq, d, device="cuda")
+        fwd.run_flash_attn_batch(0, to_dev(q), out, m, q_start, n_kv, 0, 0)
+        torch.cuda.synchronize()
+        kc, vc = encode_cache(k, ODT[dtype]), encode_cache(v, ODT[dtype])
+        want = oracle.batch_attention_ref(q, kc, vc, ODT[dtype], hq, hkv, d, m, q_start, n_kv)
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        if dtype == "F8":
+            assert rel_err(got, want) < 3e-2
+        else:
+            assert float(np.max(np.abs(got - want))) < (tol if dtype == "F32" else max(tol, 1e-3))
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+@pytest.mark.parametrize("dtype,hq,hkv,d,m,q_start,kv_start,window,softcap,n_kv_cut", [
+    ("F8", 32, 8, 128, 512, 1536, 0, 0, 0.0, 0),        # a 512-token chunk late in a 2048 context
+    ("F8", 64, 8, 128, 100, 300, 0, 0, 0.0, 0),         # g = 8, ragged last row block
+    ("F8", 32, 8, 128, 96, 200, 130, 0, 0.0, 0),        # chunk-wide kv_start (the reference's window form)
+    ("F8", 32, 8, 128, 96, 200, 0, 64, 0.0, 0),         # exact per-query window
+    ("F16", 32, 8, 128, 130, 70, 0, 0, 0.0, 0),
+    ("F16", 16, 8, 256, 48, 500, 0, 128, 50.0, 0),      # Gemma-like: D 256, soft-cap, window
+    ("F16", 8, 8, 64, 70, 0, 0, 0, 0.0, 0),             # g = 1, D 64
+    ("F8", 32, 8, 256, 40, 90, 0, 0, 0.0, 0),
+    ("F8", 32, 8, 128, 64, 100, 0, 0, 0.0, 20),         # n_kv below q_start + m clamps the causal length
+    ("F8", 24, 8, 128, 50, 10, 0, 0, 0.0, 0),           # g = 3 does not tile 64 rows: CUDA-core kernel
+    ("F32", 32, 8, 128, 33, 40, 7, 0, 30.0, 0),
+    ("F8", 32, 8, 128, 80, 0, 50, 0, 0.0, 0),           # early queries have an empty range -> zeros
+])
+def test_prefill_attention_shapes(ctx, dtype, hq, hkv, d, m, q_start, kv_start, window, softcap, n_kv_cut):
+    import torch
+    n_kv = q_start + m - n_kv_cut
+    rng = np.random.default_rng(m * 7 + q_start)
+    # N(0,1); the x20 outliers belong to the FP8 configurations only
+    frac = 0.01 if dtype == "F8" else 0.0
+    k, v = kv_values(rng, (q_start + m, hkv, d), frac), kv_values(rng, (q_start + m, hkv, d), frac)
+    q = rng.standard_normal((m, hq, d), dtype=np.float32)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(2, hkv, d, q_start + m + 3, n_slots=2), vf.KvDtype[dtype])
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, softcap=softcap)
+    try:
+        _fill(fwd, k, v, layer=1, slot=1)                  # non-zero layer and slot offsets
+        out = torch.zeros(m, hq, d, device="cuda")
+        fwd.run_flash_attn_batch(1, to_dev(q), out, m, q_start, n_kv, 1, kv_start, slot=1, window=window)
+        torch.cuda.synchronize()
+        kc, vc = encode_cache(k, ODT[dtype]), encode_cache(v, ODT[dtype])
+        want = oracle.batch_attention_ref(q, kc, vc, ODT[dtype], hq, hkv, d, m, q_start, n_kv, kv_start, window,
+                                          softcap=softcap)
+        got = out.cpu().numpy()
+        assert np.isfinite(got).all()
+        _check(got, want, dtype)
+        # the CUDA-core kernel agrees as well (independent implementation)
+        ctx.set_attn_impl(1)
+        out2 = torch.zeros(m, hq, d, device="cuda")
+        fwd.run_flash_attn_batch(1, to_dev(q), out2, m, q_start, n_kv, 1, kv_start, slot=1, window=window)
+        torch.cuda.synchronize()
+        _check(out2.cpu().numpy(), want, dtype)
+    finally:
+        ctx.set_attn_impl(0)
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+def test_prefill_then_decode_agree(ctx):
+    """The last query of a prefill chunk and a decode step at the same position see the same
+    cache: their outputs agree (the force_per_token_prefill bisect of executor/attention.rs:2207-2213)."""
+    import torch
+    hq, hkv, d, m, q_start = 32, 8, 128, 64, 448
+    rng = np.random.default_rng(3)
+    k, v = kv_values(rng, (q_start + m, hkv, d)), kv_values(rng, (q_start + m, hkv, d))
+    q = rng.standard_normal((m, hq, d), dtype=np.float32)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, 512), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        _fill(fwd, k, v)
+        dq = to_dev(q)
+        out = torch.zeros(m, hq, d, device="cuda")
+        fwd.b_step_attention(0, dq, out, m, q_start)
+        dec = torch.zeros(hq, d, device="cuda")
+        for i in (0, 17, m - 1):
+            fwd.step_attention(0, dq[i], dec, q_start + i)
+            torch.cuda.synchronize()
+            assert rel_err(out[i].cpu().numpy(), dec.cpu().numpy()) < 2e-2
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+# ---- RoPE + append ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,hkv,d,n_dims,n_tokens,base_pos", [
+    ("F8", 8, 128, 128, 512, 1000), ("F16", 8, 128, 128, 33, 0), ("F32", 2, 64, 64, 5, 7),
+    ("F8", 8, 128, 64, 20, 300),        # partial rotary: dims 64..127 pass through
+    ("F16", 4, 256, 256, 9, 8000),
+    ("F8", 2, 64, 24, 6, 11),           # half of 12 does not tile 16-byte pieces: rotate, then append
+])
+def test_rope_append_matches_oracle(ctx, dtype, hkv, d, n_dims, n_tokens, base_pos):
+    import torch
+    rng = np.random.default_rng(n_tokens)
+    k, v = kv_values(rng, (n_tokens, hkv, d)), kv_values(rng, (n_tokens, hkv, d))
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, base_pos + n_tokens + 4), vf.KvDtype[dtype])
+    fwd = vf.CudaForward(ctx, cache, n_heads=hkv)
+    try:
+        k_rot = torch.zeros(n_tokens, hkv, d, device="cuda")
+        fwd.rope_kv_write(0, to_dev(k), to_dev(v), n_tokens, base_pos, k_rot=k_rot, n_dims=n_dims, freq_base=500000.0)
+        torch.cuda.synchronize()
+        got_rot = k_rot.cpu().numpy()
+        want_rot = oracle.rope_neox_rows(k, hkv, d, n_dims, range(base_pos, base_pos + n_tokens), 500000.0)
+        # same angles bit for bit; sin / cos differ from the host's by an ulp or two
+        assert float(np.max(np.abs(got_rot - want_rot))) < 2e-5 * max(1.0, float(np.abs(k).max()))
+        if n_dims < d:
+            assert np.array_equal(got_rot[..., n_dims:], k[..., n_dims:])
+        # the cache holds exactly the encoding of the rotated rows the kernel reports, and of V
+        es = {"F32": 4, "F16": 2, "F8": 1}[dtype]
+        row = hkv * d * es
+        kb = dev_view_bytes(cache.k_buffer + base_pos * row, n_tokens * row)
+        vb = dev_view_bytes(cache.v_buffer + base_pos * row, n_tokens * row)
+        assert np.array_equal(kb, oracle.store(got_rot, ODT[dtype]).view(np.uint8).ravel())
+        assert np.array_equal(vb, oracle.store(v, ODT[dtype]).view(np.uint8).ravel())
+        # without the f32 copy the bytes are the same
+        if (n_dims // 2) % 16 == 0:
+            cache.zero_fill()
+            fwd.rope_kv_write(0, to_dev(k), to_dev(v), n_tokens, base_pos, n_dims=n_dims, freq_base=500000.0)
+            torch.cuda.synchronize()
+            assert np.array_equal(dev_view_bytes(cache.k_buffer + base_pos * row, n_tokens * row), kb)
+        else:
+            with pytest.raises(vf.VfkvError):
+                fwd.rope_kv_write(0, to_dev(k), to_dev(v), n_tokens, base_pos, n_dims=n_dims, freq_base=500000.0)
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+def test_rope_append_batch_and_q_rotation(ctx):
+    import torch
+    hq, hkv, d, n = 32, 8, 128, 5
+    rng = np.random.default_rng(8)
+    k, v = kv_values(rng, (n, hkv, d)), kv_values(rng, (n, hkv, d))
+    q = rng.standard_normal((n, hq, d), dtype=np.float32)
+    positions = np.array([0, 100, 7, 4095, 33], np.uint32)
+    slots = np.array([4, 0, 2, 1, 3], np.uint32)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, 4096, n_slots=5), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        k_rot = torch.zeros(n, hkv, d, device="cuda")
+        fwd.rope_kv_write_batch(0, to_dev(k), to_dev(v), to_dev(slots), to_dev(positions), n, k_rot=k_rot,
+                                freq_base=500000.0)
+        dq = to_dev(q)
+        fwd.run_rope_neox(dq, dq, n, hq, d, positions=to_dev(positions), freq_base=500000.0)   # in place
+        torch.cuda.synchronize()
+        want_k = oracle.rope_neox_rows(k, hkv, d, d, positions, 500000.0)
+        want_q = oracle.rope_neox_rows(q, hq, d, d, positions, 500000.0)
+        assert float(np.max(np.abs(k_rot.cpu().numpy() - want_k))) < 5e-4
+        assert float(np.max(np.abs(dq.cpu().numpy() - want_q))) < 5e-5
+        row = hkv * d
+        for i in range(n):
+            kb = dev_view_bytes(cache.k_buffer + cache.slot_offset_bytes(0, int(slots[i])) + int(positions[i]) * row, row)
+            assert np.array_equal(kb, oracle.store(k_rot[i].cpu().numpy(), oracle.F8).view(np.uint8).ravel())
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+# ---- prefix reuse (src/server/state.rs:199-229,284-287; tests/kv_reuse_ident.rs) --------------------
+def test_kv_reuse_prepare_and_invalidate(ctx):
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, 2, 64, 64, n_slots=2), vf.KvDtype.F8)
+    try:
+        cache.set_seq_len(0, 5)
+        assert cache.reuse_prepare([1, 2, 3, 4, 5], [1, 2, 3, 9]) == 3 and cache.seq_len(0) == 3
+        # identical prompt: one token is always left to prefill
+        assert cache.reuse_prepare([1, 2, 3, 4, 5], [1, 2, 3, 4, 5]) == 4 and cache.seq_len(0) == 4
+        # the new prompt is a prefix of the cached sequence
+        assert cache.reuse_prepare([1, 2, 3, 4, 5], [1, 2]) == 1 and cache.seq_len(0) == 1
+        # nothing in common, or reuse switched off: reset
+        cache.set_seq_len(0, 5)
+        assert cache.reuse_prepare([1, 2, 3], [7, 8]) == 0 and cache.seq_len(0) == 0
+        cache.set_seq_len(0, 5)
+        assert cache.reuse_prepare([1, 2, 3], [1, 2, 3, 4], reuse=False) == 0 and cache.seq_len(0) == 0
+        # slots are independent
+        cache.set_seq_len(1, 9)
+        assert cache.reuse_prepare([5, 6, 7], [5, 6, 1], slot=1) == 2 and cache.seq_len(1) == 2 and cache.seq_len(0) == 0
+        cache.invalidate(1)
+        assert cache.seq_len(1) == 0
+    finally:
+        cache.destroy()

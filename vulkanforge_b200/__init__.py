@@ -11,9 +11,10 @@ from .forward import CudaForward
 from .shard import PositionShards, ShardedSequenceDecoder, all_gather_partials, assign_sequences
 from .kv_cache import (Context, KvCache, KvCacheConfig, KvDtype, VfkvError, Workspace, PeerExchange,
                        guard_kv_precision, kv_bytes_per_token, kv_dtype_from_env, ptr,
-                       sliding_kv_start)
+                       sliding_kv_start, longest_common_prefix, compute_auto_ctx, gemma4_kv_read_layer)
 
 __all__ = ["LIB_PATH", "load", "CudaForward", "PositionShards", "ShardedSequenceDecoder", "all_gather_partials",
            "assign_sequences", "Context", "KvCache", "KvCacheConfig", "KvDtype",
            "VfkvError", "Workspace", "PeerExchange", "guard_kv_precision", "kv_bytes_per_token",
-           "kv_dtype_from_env", "ptr", "sliding_kv_start"]
+           "kv_dtype_from_env", "ptr", "sliding_kv_start", "longest_common_prefix", "compute_auto_ctx",
+           "gemma4_kv_read_layer"]

@@ -21,7 +21,12 @@ class CacheConfig(C.Structure):
                 ("n_slots", u32), ("scale_mode", u32)]
 
 
-# name -> (restype, argtypes); kept in the order of include/vfkv.h
+class RopeParams(C.Structure):
+    """vfkv_rope_params (include/vfkv_next.h)."""
+    _fields_ = [("n_dims", u32), ("freq_base", f32), ("freq_scale", f32)]
+
+
+# name -> (restype, argtypes); kept in the order of include/vfkv.h, then include/vfkv_next.h
 SIGNATURES = {
     "vfkv_ctx_create": (i32, [i32, C.POINTER(vp)]),
     "vfkv_ctx_destroy": (i32, [vp]),
@@ -93,6 +98,19 @@ SIGNATURES = {
     "vfkv_exchange_merge": (i32, [vp, vp, vp]),
     "vfkv_attend_exchange": (i32, [vp, vp, vp, u32, u32, vp, vp, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp]),
     "vfkv_malloc": (i32, [vp, u64, C.POINTER(vp)]),
+    # ---- include/vfkv_next.h ----
+    "vfkv_flash_attn": (i32, [vp, u32, u32, vp, vp, u32, u32, u32, u32, f32, f32, vp]),
+    "vfkv_scalar_attn": (i32, [vp, vp, u32, u32, vp, vp, u32, u32, u32, u32, f32, f32, vp]),
+    "vfkv_scalar_attn_uses_split": (u32, [u32]),
+    "vfkv_attend_prefill": (i32, [vp, u32, u32, vp, vp, u32, u32, u32, u32, u32, u32, u32, f32, f32, vp]),
+    "vfkv_rope_append": (i32, [vp, u32, vp, vp, u32, u32, u32, C.POINTER(RopeParams), vp, vp]),
+    "vfkv_rope_append_batch": (i32, [vp, u32, vp, vp, vp, vp, u32, C.POINTER(RopeParams), vp, vp]),
+    "vfkv_rope_neox": (i32, [vp, vp, vp, u32, u32, u32, vp, u32, C.POINTER(RopeParams), vp]),
+    "vfkv_longest_common_prefix": (u64, [pu32, u64, pu32, u64]),
+    "vfkv_kv_reuse_prepare": (i32, [vp, u32, pu32, u64, pu32, u64, i32, pu32]),
+    "vfkv_kv_invalidate": (i32, [vp, u32]),
+    "vfkv_compute_auto_ctx": (i32, [u64, u64, u64, u64, u32, u32, u32, pu32, pu32, C.POINTER(u64)]),
+    "vfkv_gemma4_kv_read_layer": (u32, [pu32, u32, u32]),
     "vfkv_free": (i32, [vp, vp]),
     "vfkv_malloc_host": (i32, [vp, u64, C.POINTER(vp)]),
     "vfkv_free_host": (i32, [vp, vp]),

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libvfkv.so")
-SOURCES = ["api.cu", "append.cu", "attn_generic.cu", "attn_mma.cu", "attn_merge.cu", "exchange.cu", "noalloc.cu", "kv_cache.cpp"]
+SOURCES = ["api.cu", "append.cu", "attn_generic.cu", "attn_mma.cu", "attn_merge.cu", "exchange.cu", "attn_prefill.cu", "rope_append.cu", "routes.cpp", "noalloc.cu", "kv_cache.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -31,6 +31,7 @@ def _stale() -> bool:
     t = os.path.getmtime(OUT)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
     deps.append(os.path.join(HERE, "..", "include", "vfkv.h"))
+    deps.append(os.path.join(HERE, "..", "include", "vfkv_next.h"))
     deps.append(os.path.abspath(__file__))
     return any(os.path.getmtime(d) > t for d in deps)
 

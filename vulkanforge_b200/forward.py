@@ -72,11 +72,73 @@ class CudaForward:
                                            ptr(q), ptr(out), self.n_heads, slot, position + 1, kv_start,
                                            self.attn_scale, self.softcap, n_tiles, self.stream))
 
+    def run_flash_attn(self, q, out, layer: int, position: int, kv_layer: int, kv_start: int, slot: int = 0):
+        """The single-workgroup shader of runs.rs:776-821 (flash_attn.comp): one pass, no scratch."""
+        self.ctx.check(self._L.vfkv_flash_attn(self.kv_cache.handle, layer, kv_layer, ptr(q), ptr(out), self.n_heads,
+                                               slot, position + 1, kv_start, self.attn_scale, self.softcap,
+                                               self.stream))
+
     def run_scalar_attn(self, q, out, layer: int, position: int, slot: int = 0):
-        """runs.rs:722-821: kv_layer / kv_start routing, then attention at every length."""
+        """runs.rs:722-821: kv_layer / kv_start routing; two or more 64-position tiles go to the
+        split + reduce path, shorter sequences to ``run_flash_attn``.  A split count given to the
+        constructor overrides the library's choice on the split path."""
         kv_layer = self.gemma4_kv_read_layer(layer)
         kv_start = self.gemma4_kv_start(layer, position)
-        self.run_flash_attn_split_reduce(q, out, layer, position, self.n_splits, kv_layer, kv_start, slot)
+        if self.n_splits and self._L.vfkv_scalar_attn_uses_split(position):
+            self.run_flash_attn_split_reduce(q, out, layer, position, self.n_splits, kv_layer, kv_start, slot)
+            return
+        self.ctx.check(self._L.vfkv_scalar_attn(self.kv_cache.handle, self.workspace.handle, layer, kv_layer, ptr(q),
+                                                ptr(out), self.n_heads, slot, position, kv_start, self.attn_scale,
+                                                self.softcap, self.stream))
+
+    # ---- prefill chunk ------------------------------------------------------------
+    def run_flash_attn_batch(self, layer: int, q, out, m: int, q_start: int, n_kv: int, kv_layer: int,
+                             kv_start: int, slot: int = 0, window: int = 0):
+        """runs.rs:933-1010 (flash_attn_batch.comp): m queries, query i at position q_start + i over
+        [kv_start, min(q_start + i + 1, n_kv)).  ``window`` (extension): exact per-query window."""
+        self.ctx.check(self._L.vfkv_attend_prefill(self.kv_cache.handle, layer, kv_layer, ptr(q), ptr(out),
+                                                   self.n_heads, slot, m, q_start, n_kv, kv_start, window,
+                                                   self.attn_scale, self.softcap, self.stream))
+
+    def b_step_attention(self, layer: int, q, out, seq_len: int, base_pos: int, slot: int = 0,
+                         exact_window: bool = False):
+        """executor/attention.rs:2192-2393: kv_start is the LAST query's window bound for the whole
+        chunk (:2215-2219), as the reference documents; ``exact_window`` masks per query instead."""
+        kv_layer = self.gemma4_kv_read_layer(layer)
+        window = self.sliding_window if layer in self.sliding_layers else 0
+        kv_start = max(0, base_pos + seq_len - window) if window and not exact_window else 0
+        self.run_flash_attn_batch(layer, q, out, seq_len, base_pos, base_pos + seq_len, kv_layer, kv_start, slot,
+                                  window if exact_window else 0)
+
+    # ---- RoPE (input preparation; fused with the append) -------------------------------
+    def _rope(self, n_dims: Optional[int], freq_base: float, freq_scale: float):
+        from ._lib import RopeParams
+        return RopeParams(n_dims or self.kv_cache.config.head_dim, freq_base, freq_scale)
+
+    def run_rope_neox(self, x, out, n_rows: int, n_heads: int, head_dim: int, base_pos: int = 0, positions=None,
+                      n_dims: Optional[int] = None, freq_base: float = 10000.0, freq_scale: float = 1.0):
+        """runs.rs:647-720 (rope_funcs.glsl:73-107) for [rows][heads][head_dim] f32, e.g. Q."""
+        import ctypes as C
+        rp = self._rope(n_dims or head_dim, freq_base, freq_scale)
+        self.ctx.check(self._L.vfkv_rope_neox(self.ctx.handle, ptr(x), ptr(out), n_rows, n_heads, head_dim,
+                                              ptr(positions), base_pos, C.byref(rp), self.stream))
+
+    def rope_kv_write(self, layer: int, k_src, v_src, n_tokens: int, base_pos: int, slot: int = 0, k_rot=None,
+                      n_dims: Optional[int] = None, freq_base: float = 10000.0, freq_scale: float = 1.0):
+        """K rotated at base_pos.. and stored, V stored, in one launch (rope dispatch + KvWrite of
+        executor/attention.rs:435-530,546-596)."""
+        import ctypes as C
+        rp = self._rope(n_dims, freq_base, freq_scale)
+        self.ctx.check(self._L.vfkv_rope_append(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src), n_tokens, slot,
+                                                base_pos, C.byref(rp), ptr(k_rot), self.stream))
+
+    def rope_kv_write_batch(self, layer: int, k_src, v_src, slot_ids, positions, n_seqs: int, k_rot=None,
+                            n_dims: Optional[int] = None, freq_base: float = 10000.0, freq_scale: float = 1.0):
+        import ctypes as C
+        rp = self._rope(n_dims, freq_base, freq_scale)
+        self.ctx.check(self._L.vfkv_rope_append_batch(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src),
+                                                      ptr(slot_ids), ptr(positions), n_seqs, C.byref(rp), ptr(k_rot),
+                                                      self.stream))
 
     # ---- executor steps ----------------------------------------------------------
     def step_kv_write(self, layer: int, k_src, v_src, position: int, slot: int = 0):

@@ -149,6 +149,40 @@ class Workspace:
             self.handle = None
 
 
+def longest_common_prefix(a, b) -> int:
+    """src/server/state.rs:49-51 over two token-id sequences."""
+    import numpy as np
+    a = np.ascontiguousarray(a, dtype=np.uint32)
+    b = np.ascontiguousarray(b, dtype=np.uint32)
+    pa = a.ctypes.data_as(C.POINTER(C.c_uint32))
+    pb = b.ctypes.data_as(C.POINTER(C.c_uint32))
+    return int(_lib.load().vfkv_longest_common_prefix(pa, a.size, pb, b.size))
+
+
+AUTO_CTX_BOUNDS = ("VRAM", "model max context", "hardware limit", "sane cap")   # CtxBound::label, auto_ctx.rs:72-80
+
+
+def compute_auto_ctx(free_bytes: int, weight_bytes: int, reserve_bytes: int, kv_bytes_per_token_: int,
+                     model_max_ctx: int, hw_cap: int, sane_cap: int = 32768):
+    """src/server/auto_ctx.rs:107-141 -> (ctx, bound label, bytes available for KV)."""
+    ctx, bound, avail = C.c_uint32(), C.c_uint32(), C.c_uint64()
+    rc = _lib.load().vfkv_compute_auto_ctx(free_bytes, weight_bytes, reserve_bytes, kv_bytes_per_token_, model_max_ctx,
+                                      hw_cap, sane_cap, C.byref(ctx), C.byref(bound), C.byref(avail))
+    if rc:
+        raise VfkvError(rc, "vfkv_compute_auto_ctx")
+    return ctx.value, AUTO_CTX_BOUNDS[bound.value], avail.value
+
+
+KV_OWN, KV_PUBLISH_SLIDING, KV_PUBLISH_FULL, KV_SUBSCRIBE_SLIDING, KV_SUBSCRIBE_FULL = range(5)
+
+
+def gemma4_kv_read_layer(kv_source, layer: int) -> int:
+    """src/backend/vulkan/forward/arch/gemma4.rs:27-49 over a list of Gemma4KvSource codes."""
+    import numpy as np
+    src = np.ascontiguousarray(kv_source, dtype=np.uint32)
+    return int(_lib.load().vfkv_gemma4_kv_read_layer(src.ctypes.data_as(C.POINTER(C.c_uint32)), src.size, layer))
+
+
 class PeerExchange:
     """One GPU's end of the peer exchange of (m, l, o) partials used by position sharding
     (``vfkv_exchange_*``; no counterpart in the reference)."""
@@ -297,6 +331,22 @@ class KvCache:
 
     def reset(self, slot: int = 0) -> None:
         self.ctx.check(self.ctx._lib.vfkv_cache_reset(self.handle, slot))
+
+    def reuse_prepare(self, cached_tokens, full_tokens, reuse: bool = True, slot: int = 0) -> int:
+        """The KV-prepare step of ServerSession::generate_reuse (src/server/state.rs:199-229):
+        returns the start position k; rows [0, k) are kept and the counter is set to k."""
+        import numpy as np
+        a = np.ascontiguousarray(cached_tokens, dtype=np.uint32)
+        b = np.ascontiguousarray(full_tokens, dtype=np.uint32)
+        k = C.c_uint32()
+        p32 = C.POINTER(C.c_uint32)
+        self.ctx.check(self.ctx._lib.vfkv_kv_reuse_prepare(self.handle, slot, a.ctypes.data_as(p32), a.size,
+                                                           b.ctypes.data_as(p32), b.size, int(reuse), C.byref(k)))
+        return k.value
+
+    def invalidate(self, slot: int = 0) -> None:
+        """kv_invalidate (state.rs:284-287)."""
+        self.ctx.check(self.ctx._lib.vfkv_kv_invalidate(self.handle, slot))
 
     def zero_fill(self, stream=None) -> None:
         self.ctx.check(self.ctx._lib.vfkv_cache_zero_fill(self.handle, stream))
