@@ -770,7 +770,7 @@ int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *e
     a.out_o = ex->staging + 2ull * n_q_heads;
     if (attn_mma_supported(a) && ctx->attn_impl != 1) {
         a.out_m = a.out_l = a.out_o = nullptr;          // the kernel stores into the exchange buffers itself,
-        a.fan = ex->fan;                                // and writes the new token's cache row as well
+        a.fan = ex->d_fan;                              // and writes the new token's cache row as well
         a.k_new = d_k_new;
         a.v_new = d_v_new;
         DeviceGuard g(ctx->device);

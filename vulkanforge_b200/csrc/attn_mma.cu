@@ -298,6 +298,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
     const uint32_t bars = ring + S::RING_BYTES;           // kWarps*kStages mbarriers, 8 bytes each
     __shared__ uint32_t s_flag, s_epoch;
+    __shared__ PeerFanout s_fan;          // the group's fan-out table (position-sharded calls only)
 
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -341,7 +342,9 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     };
     // exchange number of a position-sharded call (written by the merge kernel of the previous
     // exchange): fetched right after the wait so that the epilogue finds it in shared memory
-    auto load_epoch = [&]() { if (threadIdx.x == 32 && p.fan.world != 0u) s_epoch = *p.fan.epoch; };
+    auto load_epoch = [&]() {
+        if (threadIdx.x == 32 && p.fan != nullptr) { s_fan = *p.fan; s_epoch = *s_fan.epoch; }
+    };
     if (mp.pdl != 2u) { load_q(); load_epoch(); }
 
     VFKV_TRACE(0);
@@ -688,9 +691,9 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     __syncthreads();
 
     const bool direct = p.n_splits == 1;
-    const bool fan = p.fan.world != 0u;
+    const bool fan = p.fan != nullptr;
     FanoutSlot fs{};
-    if (fan) fs = fanout_slot(p.fan, D, p.fan.rank, s_epoch + 1u);
+    if (fan) fs = fanout_slot(s_fan, D, s_fan.rank, s_epoch + 1u);
     for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
         const uint32_t j = idx / D, d = idx % D;
         float M = kMaskedScore;
@@ -714,12 +717,12 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             if (fan) {
 #pragma unroll
                 for (uint32_t r = 0; r < 8; ++r) {
-                    if (r < p.fan.world) {
-                        uint64_t *dst = p.fan.base[r];
+                    if (r < s_fan.world) {
+                        uint64_t *dst = s_fan.base[r];
                         fanout_store(dst + fs.o + row * D + d, O, fs.epoch);
                         if (d == 0) {
                             fanout_store(dst + fs.m + row, m_nat, fs.epoch);
-                            fanout_store(dst + fs.m + p.fan.n_rows + row, L, fs.epoch);
+                            fanout_store(dst + fs.m + s_fan.n_rows + row, L, fs.epoch);
                         }
                     }
                 }
@@ -757,7 +760,27 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         constexpr uint32_t CH = 16;
         float gmax = kMaskedScore, gsum = 0.f;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t c0 = 0; c0 < p.n_splits; c0 += CH) {       // one L2 round trip per 16 splits
+        {   // the first 16 splits: everything is requested in one batch, a single L2 round trip
+            float4 o[CH];
+            float mm[CH], ll[CH];
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                const bool in = i < p.n_splits;
+                o[i] = in ? __ldcg(po + uint64_t(i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                mm[i] = in ? __ldcg(pm + i) : kMaskedScore;
+                ll[i] = in ? __ldcg(pl + i) : 0.f;
+            }
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) gmax = fmaxf(gmax, mm[i]);
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                const float kn = __expf(mm[i] - gmax);            // absent splits: l = 0 and o = 0
+                gsum = fmaf(ll[i], kn, gsum);
+                a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
+                a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
+            }
+        }
+        for (uint32_t c0 = CH; c0 < p.n_splits; c0 += CH) {       // further splits: one round trip per 16
             float4 o[CH];
             float mm[CH], ll[CH];
 #pragma unroll
@@ -775,7 +798,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             gmax = nmax;
 #pragma unroll
             for (uint32_t i = 0; i < CH; ++i) {
-                const float kn = __expf(mm[i] - gmax);            // absent splits: l = 0 and o = 0
+                const float kn = __expf(mm[i] - gmax);
                 gsum = fmaf(ll[i], kn, gsum);
                 a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
                 a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
@@ -792,12 +815,12 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         if (fan) {            // the merged partial goes straight into every GPU's exchange buffer
 #pragma unroll
             for (uint32_t r = 0; r < 8; ++r) {
-                if (r < p.fan.world) {
-                    uint64_t *dst = p.fan.base[r];
+                if (r < s_fan.world) {
+                    uint64_t *dst = s_fan.base[r];
                     fanout_store4(dst + fs.o + row * D + d, a, fs.epoch);
                     if (d == 0) {
                         fanout_store(dst + fs.m + row, gmax, fs.epoch);
-                        fanout_store(dst + fs.m + p.fan.n_rows + row, gsum, fs.epoch);
+                        fanout_store(dst + fs.m + s_fan.n_rows + row, gsum, fs.epoch);
                     }
                 }
             }

@@ -18,7 +18,7 @@ struct AttnParams {
     uint32_t n_q_heads, n_kv_heads, head_dim, group, max_seq, n_slots, n_splits, n_seqs;
     float scale, softcap;
     uint32_t *status;
-    PeerFanout fan;
+    const PeerFanout *fan;             // device memory, or null
 };
 
 inline AttnParams make_params(const vfkv_ctx *ctx, const vfkv_workspace *ws, const AttnArgs &a,

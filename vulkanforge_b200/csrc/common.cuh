@@ -121,7 +121,7 @@ struct AttnArgs {
     // only the tensor-core kernel consumes these (it writes the cache rows itself)
     const float *k_new = nullptr;
     const float *v_new = nullptr;
-    PeerFanout fan;               // tensor-core kernel only
+    const PeerFanout *fan = nullptr;   // device copy of the group's fan-out table, or null (tensor-core kernel only)
 };
 
 // Brackets one kernel launch with a pair of events on its stream while profiling is on.
@@ -195,6 +195,7 @@ struct vfkv_exchange {
     uint64_t *local = nullptr;     // this rank's buffer of tagged words
     uint64_t bytes = 0;
     uint32_t *ctl = nullptr;       // [0] completed exchanges, [1] merge ticket (never shared)
+    vfkv::PeerFanout *d_fan = nullptr;   // device copy of `fan`, read by the attention kernel
     float *staging = nullptr;      // one block, for attention kernels that cannot fan out themselves
     bool imported[8] = {false, false, false, false, false, false, false, false};
     uint64_t wait_ns = 1000000000ull;

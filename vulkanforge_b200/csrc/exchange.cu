@@ -195,6 +195,13 @@ int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint3
     ex->fan.world = world; ex->fan.rank = rank; ex->fan.n_rows = n_rows;
     ex->fan.epoch = ex->ctl;
     ex->fan.base[rank] = ex->local;
+    if (cudaMalloc(&ex->d_fan, sizeof(PeerFanout)) != cudaSuccess ||
+        cudaMemcpy(ex->d_fan, &ex->fan, sizeof(PeerFanout), cudaMemcpyHostToDevice) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(ex->local); cudaFree(ex->ctl); cudaFree(ex->staging); cudaFree(ex->d_fan);
+        delete ex;
+        return set_error(ctx, VFKV_ERR_OOM, "vfkv_exchange_create: device allocation failed");
+    }
     *out = ex;
     return VFKV_OK;
 }
@@ -205,7 +212,7 @@ void vfkv_exchange_destroy(vfkv_exchange *ex)
     Guard g(ex->ctx->device);
     for (uint32_t r = 0; r < 8; ++r)
         if (ex->imported[r] && ex->fan.base[r]) cudaIpcCloseMemHandle(ex->fan.base[r]);
-    cudaFree(ex->local); cudaFree(ex->ctl); cudaFree(ex->staging);
+    cudaFree(ex->local); cudaFree(ex->ctl); cudaFree(ex->staging); cudaFree(ex->d_fan);
     cudaGetLastError();
     delete ex;
 }
@@ -240,7 +247,8 @@ int32_t vfkv_exchange_import(vfkv_exchange *ex, uint32_t rank, const uint8_t han
     if (e != cudaSuccess) return check_cuda(ex->ctx, e, "vfkv_exchange_import");
     ex->fan.base[rank] = static_cast<uint64_t *>(p);
     ex->imported[rank] = true;
-    return VFKV_OK;
+    return check_cuda(ex->ctx, cudaMemcpy(ex->d_fan, &ex->fan, sizeof(PeerFanout), cudaMemcpyHostToDevice),
+                      "vfkv_exchange_import");
 }
 
 int32_t vfkv_exchange_set_peer(vfkv_exchange *ex, uint32_t rank, void *d_peer_buffer)
@@ -252,7 +260,9 @@ int32_t vfkv_exchange_set_peer(vfkv_exchange *ex, uint32_t rank, void *d_peer_bu
         return set_error(ex->ctx, VFKV_ERR_INVALID, "vfkv_exchange_set_peer: buffer must be 16-byte aligned");
     ex->fan.base[rank] = static_cast<uint64_t *>(d_peer_buffer);
     ex->imported[rank] = false;
-    return VFKV_OK;
+    Guard g(ex->ctx->device);
+    return check_cuda(ex->ctx, cudaMemcpy(ex->d_fan, &ex->fan, sizeof(PeerFanout), cudaMemcpyHostToDevice),
+                      "vfkv_exchange_set_peer");
 }
 
 int32_t vfkv_exchange_set_timeout_ms(vfkv_exchange *ex, uint32_t ms)
