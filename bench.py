@@ -367,6 +367,7 @@ def run_ours(args, w, rank, world, local_rank):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     job = Job(w, local_rank, seed=1000 + rank)
     job.ctx.check(job.ctx._lib.vfkv_ctx_set_dependent_launch(job.ctx.handle, args.pdl))
+    job.ctx.set_cluster_merge(bool(args.cluster))
     if args.tune:
         wt, st = (int(x) for x in args.tune.split("x"))
         job.ctx.check(job.ctx._lib.vfkv_ctx_set_attn_tuning(job.ctx.handle, wt, st))
@@ -461,7 +462,7 @@ def run_ours(args, w, rank, world, local_rank):
                            "l2": "each step streams the whole cache (larger than the 126 MB L2) before a layer repeats"
                                  if step_bytes > 200e6 else "working set below L2: hot-L2 numbers",
                            "launch": "one CUDA graph replay per token" if job.graph is not None else "stream launches",
-                           "dependent_launch_mode": args.pdl,
+                           "dependent_launch_mode": args.pdl, "cluster_merge": args.cluster,
                            "parallelism": f"sequence-sharded x{world}, no collective"},
                 "value_stream_launches": ms_stream * 1e3 / denom,
                 "tokens_per_s": tokens * args.steps / (ms * 1e-3),
@@ -626,6 +627,8 @@ def main():
     ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch mode of the attention kernel (vfkv_ctx_set_dependent_launch)")
+    ap.add_argument("--cluster", type=int, default=0, choices=[0, 1],
+                    help="merge the splits inside a thread-block cluster (vfkv_ctx_set_cluster_merge)")
     ap.add_argument("--tune", default=None, help="tensor-core kernel shape WxS (warps x stages), e.g. 4x3")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -422,6 +422,11 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * 1 range known, 2 barriers ready, 3 Q ready, 4 first tile landed, 5 stream done, 6 CTA joined,
  * 7 partial written, 8 ticket taken, 9 merged (last CTA only) -- at CTA index * 16.  The buffer
  * must hold 16 x 8 bytes per CTA of the largest grid.  NULL switches it off. */
+/* Split merge inside a thread-block cluster (tensor-core kernel, 2..16 splits): the CTAs of one
+ * (sequence, kv-head) exchange their partials through distributed shared memory instead of
+ * global scratch and a ticket.  Taken only when every cluster of the grid can be resident at
+ * once; otherwise the call falls back to the scratch + ticket form.  0 = off (default), 1 = on. */
+int32_t vfkv_ctx_set_cluster_merge(vfkv_ctx *ctx, uint32_t on);
 int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer);
 /* Kernels this context has launched since creation (for launch accounting). */
 uint64_t vfkv_ctx_launch_count(const vfkv_ctx *ctx);

@@ -121,6 +121,7 @@ SIGNATURES = {
     "vfkv_ctx_set_attn_impl": (i32, [vp, u32]),
     "vfkv_ctx_set_attn_tuning": (i32, [vp, u32, u32]),
     "vfkv_ctx_set_dependent_launch": (i32, [vp, u32]),
+    "vfkv_ctx_set_cluster_merge": (i32, [vp, u32]),
     "vfkv_ctx_set_trace_buffer": (i32, [vp, vp]),
     "vfkv_ctx_launch_count": (u64, [vp]),
     "vfkv_profile_enable": (i32, [vp, i32]),

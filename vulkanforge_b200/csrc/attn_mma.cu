@@ -152,6 +152,7 @@ struct MmaParams {
     const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
     unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0
     uint32_t pdl;                 // 0 plain launch, 1 dependent launch, 2 dependent launch with early K/V prefetch
+    uint32_t cluster;             // 1: the splits of a (sequence, kv-head) are one thread-block cluster
 };
 
 // Phase timestamps for latency analysis; costs one predicated branch when tracing is off.
@@ -652,7 +653,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     }
     __syncthreads();          // all tiles consumed (or abandoned): the ring is free for the merge
     VFKV_TRACE(6);
-    if (s_flag) return;
+    const bool gave_up = s_flag != 0u;
+    if (gave_up && mp.cluster == 0u) return;      // in a cluster every CTA has to reach the cluster barriers
 
     // ---- merge the warps' partials in shared memory ---------------------------------------------
     constexpr int NH = (FP8 || !ROWS2) ? 8 : 16;              // head rows this CTA can hold
@@ -694,6 +696,94 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const bool fan = p.fan != nullptr;
     FanoutSlot fs{};
     if (fan) fs = fanout_slot(s_fan, D, s_fan.rank, s_epoch + 1u);
+
+    // ---- cluster form of the split merge -----------------------------------------------------------
+    // The CTAs of one (sequence, kv-head) are a thread-block cluster: each leaves its partial in its
+    // own shared memory, and after one cluster barrier CTA r merges the r-th slice of the g x D
+    // outputs across all CTAs through distributed shared memory (flash_attn_reduce.comp:51-80).
+    // No partial goes to global memory, no ticket is drawn.  The closing barrier keeps every CTA's
+    // shared memory alive until its peers have read it.
+    if (mp.cluster != 0u) {
+        float *cx_o = sm_l + kWarps * NH;                      // [g][D]
+        float *cx_m = cx_o + NH * D;                           // [g]
+        float *cx_l = cx_m + NH;                               // [g]
+        for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
+            const uint32_t j = idx / D, d = idx % D;
+            float M = kMaskedScore;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) M = fmaxf(M, sm_m[w * NH + j]);
+            float L = 0.f, O = 0.f;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                const float f = fast_exp2(sm_m[w * NH + j] - M);
+                L = fmaf(sm_l[w * NH + j], f, L);
+                O = fmaf(sm_o[(w * NH + j) * DP + d], f, O);
+            }
+            if (gave_up) { M = kMaskedScore; L = 0.f; O = 0.f; }
+            cx_o[idx] = O;
+            if (d == 0) { cx_m[j] = M * kLn2; cx_l[j] = L; }
+        }
+        VFKV_TRACE(7);
+        __syncthreads();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        VFKV_TRACE(8);
+        const uint32_t n = p.n_splits;
+        const uint32_t per = (g * D + n - 1) / n;
+        const uint32_t e_end = min((split + 1) * per, g * D);
+        for (uint32_t e = split * per + threadIdx.x; e < e_end; e += blockDim.x) {
+            const uint32_t j = e / D, d = e % D;
+            const uint32_t a_o = smem_u32(cx_o + e), a_m = smem_u32(cx_m + j), a_l = smem_u32(cx_l + j);
+            constexpr uint32_t CH = 16;
+            float oo[CH], mm[CH], ll[CH];
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                oo[i] = 0.f; mm[i] = kMaskedScore; ll[i] = 0.f;
+                if (i < n) {
+                    uint32_t ro, rm, rl;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ro) : "r"(a_o), "r"(i));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rm) : "r"(a_m), "r"(i));
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rl) : "r"(a_l), "r"(i));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(oo[i]) : "r"(ro) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(mm[i]) : "r"(rm) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ll[i]) : "r"(rl) : "memory");
+                }
+            }
+            float gmax = kMaskedScore, gsum = 0.f, a = 0.f;
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) gmax = fmaxf(gmax, mm[i]);
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                const float kn = __expf(mm[i] - gmax);
+                gsum = fmaf(ll[i], kn, gsum);
+                a = fmaf(oo[i], kn, a);
+            }
+            const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
+            if (p.out) p.out[row * D + d] = gsum > 0.f ? a * (1.0f / gsum) : 0.f;
+            if (p.out_o) {
+                p.out_o[row * D + d] = a;
+                if (d == 0) { p.out_m[row] = gmax; p.out_l[row] = gsum; }
+            }
+            if (fan) {
+#pragma unroll
+                for (uint32_t r = 0; r < 8; ++r) {
+                    if (r < s_fan.world) {
+                        uint64_t *dst = s_fan.base[r];
+                        fanout_store(dst + fs.o + row * D + d, a, fs.epoch);
+                        if (d == 0) {
+                            fanout_store(dst + fs.m + row, gmax, fs.epoch);
+                            fanout_store(dst + fs.m + s_fan.n_rows + row, gsum, fs.epoch);
+                        }
+                    }
+                }
+            }
+        }
+        VFKV_TRACE(9);
+        __syncthreads();                                       // reconverge before the aligned barrier
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        return;
+    }
     for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
         const uint32_t j = idx / D, d = idx % D;
         float M = kMaskedScore;
@@ -873,12 +963,42 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
             cfg.blockDim = dim3(W * 32);
             cfg.dynamicSmemBytes = S::SMEM_BYTES;
             cfg.stream = st;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cudaLaunchAttribute attr[2];
+            unsigned n_attr = 0;
+            if (mp.pdl) {
+                attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+                ++n_attr;
+            }
             cfg.attrs = attr;
-            cfg.numAttrs = mp.pdl ? 1 : 0;
-            cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tk, tv, mp);
+            cfg.numAttrs = n_attr;
+            // Cluster form of the split merge: the splits of one (sequence, kv-head) as one cluster.
+            // Used when the context asks for it, the merge scratch fits beside the ring, and the
+            // device can keep every cluster of the grid resident at once (so none waits for another).
+            MmaParams lp = mp;
+            constexpr int NH = (DT == VFKV_F8 || !ROWS2) ? 8 : 16;
+            constexpr bool kFits = (W * NH * (D + 1) + 2 * W * NH + NH * D + 2 * NH) * 4 <= S::RING_BYTES;
+            if (kFits && ctx->cluster_merge && mp.a.n_splits >= 2 && mp.a.n_splits <= 16) {
+                static int max_clusters[64][17] = {};      // per device and cluster size; 0 = not asked yet, -1 = no
+                int &known = max_clusters[ctx->device & 63][mp.a.n_splits];
+                cudaLaunchAttribute &ca = attr[n_attr];
+                ca.id = cudaLaunchAttributeClusterDimension;
+                ca.val.clusterDim.x = mp.a.n_splits; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = 1;
+                cfg.numAttrs = n_attr + 1;
+                if (known == 0) {
+                    known = -1;
+                    bool ok = true;
+                    if (mp.a.n_splits > 8)
+                        ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+                    int n = 0;
+                    if (ok && cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) known = n;
+                    cudaGetLastError();
+                }
+                const uint64_t clusters = uint64_t(mp.a.n_kv_heads) * mp.a.n_seqs;
+                if (known > 0 && clusters <= uint64_t(known)) lp.cluster = 1;
+                else cfg.numAttrs = n_attr;
+            }
+            cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tk, tv, lp);
             if (e != cudaSuccess) return check_cuda(ctx, e, "tensor-core attention launch");
         }
         ctx->launches++;
@@ -948,6 +1068,7 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     mp.counters = ws ? ws->counters : nullptr;
     mp.trace = ctx->d_trace;
     mp.pdl = ctx->pdl;
+    mp.cluster = 0;
     mp.k_new = a.k_new;
     mp.v_new = a.v_new;
     if ((reinterpret_cast<uintptr_t>(a.k_new) | reinterpret_cast<uintptr_t>(a.v_new)) % 16 != 0)
@@ -982,3 +1103,10 @@ bool encode_layer_maps(vfkv_ctx *ctx, const KvView &v, void *tm_k_out, void *tm_
 }
 
 }  // namespace vfkv
+
+extern "C" int32_t vfkv_ctx_set_cluster_merge(vfkv_ctx *ctx, uint32_t on)
+{
+    if (!ctx || on > 1) return VFKV_ERR_INVALID;
+    ctx->cluster_merge = on;
+    return VFKV_OK;
+}

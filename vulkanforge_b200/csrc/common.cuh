@@ -20,6 +20,7 @@ struct vfkv_ctx {
     uint32_t attn_impl = 0;            // 0 auto, 1 CUDA-core only, 2 tensor-core only
     uint32_t tune_warps = 0, tune_stages = 0;   // tensor-core kernel shape, 0 = choose
     uint32_t pdl = 0;                  // programmatic dependent launch mode of the attention kernel (0 / 1 / 2)
+    uint32_t cluster_merge = 0;        // 1: merge the splits inside a thread-block cluster where the device allows it
     uint64_t launches = 0;
     unsigned long long *d_trace = nullptr;   // caller-owned device buffer for kernel phase timestamps, or null
     void *encode_tiled = nullptr;      // cuTensorMapEncodeTiled, resolved at run time

@@ -121,6 +121,10 @@ class Context:
     def set_attn_impl(self, impl: int) -> None:
         self.check(self._lib.vfkv_ctx_set_attn_impl(self.handle, impl))
 
+    def set_cluster_merge(self, on: bool) -> None:
+        """Merge the splits of a (sequence, kv-head) inside a thread-block cluster where possible."""
+        self.check(self._lib.vfkv_ctx_set_cluster_merge(self.handle, int(on)))
+
     def launch_count(self) -> int:
         return int(self._lib.vfkv_ctx_launch_count(self.handle))
 
