@@ -79,6 +79,14 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def tensor_peak():
+    """Dense bf16 TFLOP/s of a library GEMM timed alone (MEASURED_PEAKS.json), else the fallback figure."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path)).get("bf16_tflops", 1590.0))
+    return 1590.0
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML while the timed region runs (read only)."""
 
@@ -357,6 +365,54 @@ def batch64_roofline(ctx, args, peak):
             job.close()
 
 
+def next_rows(ctx, args, peak, tensor_peak):
+    """The callers either side of the hot path, measured on their own: chunked-prefill causal
+    attention over the cache (a 512-token chunk ending at position 8192, FP8, 32 q / 8 kv / 128:
+    tensor-bound) and RoPE fused with the append of the same chunk (HBM-bound)."""
+    import torch
+    import vulkanforge_b200 as vf
+    hq, hkv, d, m, q_start = 32, 8, 128, 512, 7680
+    L = q_start + m
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for p in range(0, L, 4096):
+            kv = torch.randn(2, 4096, hkv * d, device="cuda", generator=g)
+            fwd.b_step_kv_write(0, kv[0], kv[1], 4096, p, 0)
+        q = torch.randn(m, hq, d, device="cuda", generator=g)
+        out = torch.zeros(m, hq, d, device="cuda")
+        kv = torch.randn(2, m, hkv * d, device="cuda", generator=g)
+
+        def timed(fn, reps):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e3 / reps
+
+        us_attn = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 10)
+        us_rope = timed(lambda: fwd.rope_kv_write(0, kv[0], kv[1], m, q_start, freq_base=500000.0), 20)
+        flops = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2)              # causal: query i sees q_start + i + 1 rows
+        rope_bytes = 2 * m * hkv * d * (4 + 1)                               # f32 in, one byte out, K and V
+        tf = flops / (us_attn * 1e-6) / 1e12
+        gbs = rope_bytes / (us_rope * 1e-6) / 1e9
+        return {"prefill_attention": {"workload": "512 queries at positions 7680..8191, FP8 cache, 32/8/128",
+                                      "us": us_attn, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
+                                      "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None,
+                                      "note": "m16n8k16 mma.sync kernel"},
+                "rope_append": {"workload": "512 tokens x 8 kv-heads x 128, FP8 cache, K rotated", "us": us_rope,
+                                "bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak,
+                                "note": "5 MiB per launch: launch latency, not bandwidth, sets the time"}}
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
 def run_ours(args, w, rank, world, local_rank):
     import torch
     dist = None
@@ -472,6 +528,7 @@ def run_ours(args, w, rank, world, local_rank):
                         "d2h_bytes_per_step": job.d2h_bytes()}}
         if world == 1 and not args.no_extra and args.workload == DEFAULT_WORKLOAD:
             line["roofline_batch64_ctx8192"] = batch64_roofline(job.ctx, args, peak)
+            line["next_rows"] = next_rows(job.ctx, args, peak, tensor_peak())
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_sample(w)
         print(json.dumps(line), flush=True)
