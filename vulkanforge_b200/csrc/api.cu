@@ -180,8 +180,9 @@ int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl)
 int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages)
 {
     if (!ctx) return VFKV_ERR_INVALID;
-    const bool ok = (warps == 0 && stages == 0) || (warps == 4 && (stages == 2 || stages == 3)) || (warps == 8 && stages == 3);
-    if (!ok) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_ctx_set_attn_tuning: warps x stages must be 0x0, 4x2, 4x3 or 8x3");
+    const bool ok = (warps == 0 && stages == 0) || (warps == 4 && stages >= 1 && stages <= 3) ||
+                    (warps == 8 && (stages == 1 || stages == 3));
+    if (!ok) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_ctx_set_attn_tuning: warps x stages must be 0x0, 4x1, 4x2, 4x3, 8x1 or 8x3");
     ctx->tune_warps = warps;
     ctx->tune_stages = stages;
     return VFKV_OK;

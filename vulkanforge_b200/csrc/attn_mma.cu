@@ -945,7 +945,10 @@ template <int DT, int D, bool ROWS2, int W, int NS, bool CAP>
 int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
     using S = Shape<DT, D, W, NS>;
-    if constexpr (S::SMEM_BYTES > 227 * 1024) {
+    constexpr int kNH = (DT == VFKV_F8 || !ROWS2) ? 8 : 16;
+    // the ring doubles as the scratch of the cross-warp merge: [W][NH][D + 1] + 2 [W][NH] floats
+    constexpr bool kMergeFits = (W * kNH * (D + 1) + 2 * W * kNH) * 4 <= S::RING_BYTES;
+    if constexpr (S::SMEM_BYTES > 227 * 1024 || !kMergeFits) {
         return set_error(ctx, VFKV_ERR_UNSUPPORTED, "tuning does not fit in shared memory for this shape");
     } else {
         auto kern = attn_split_mma_kernel<DT, D, ROWS2, W, NS, CAP>;
@@ -1016,11 +1019,21 @@ int32_t launch_c(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
     const uint64_t ctas = uint64_t(mp.a.n_splits) * mp.a.n_kv_heads * mp.a.n_seqs;
     uint32_t w = ctx->tune_warps, ns = ctx->tune_stages;
     if (w == 0) w = (kWide && ctas <= uint64_t(ctx->sm_count)) ? 8 : 4;
-    if (ns == 0) ns = 3;
+    // 4 warps: as many stages (up to 3) as still let two CTAs share an SM.  At head_dim 256 a stage
+    // is 16 KB, so that is one stage (64 KB per CTA): measured 5.5 TB/s against 3.9 TB/s with three
+    // stages and a single CTA of 4 warps per SM (F16, 8 sequences x 32768, windows 1024 / none).
+    constexpr int kTwoPerSm = 113 * 1024;
+    constexpr int kNH = (DT == VFKV_F8 || !ROWS2) ? 8 : 16;
+    constexpr int kMergeBytes = (4 * kNH * (D + 1) + 2 * 4 * kNH) * 4;       // cross-warp merge scratch, 4 warps
+    constexpr bool kOk2 = Shape<DT, D, 4, 2>::SMEM_BYTES <= kTwoPerSm && kMergeBytes <= Shape<DT, D, 4, 2>::RING_BYTES;
+    constexpr bool kOk1 = Shape<DT, D, 4, 1>::SMEM_BYTES <= kTwoPerSm && kMergeBytes <= Shape<DT, D, 4, 1>::RING_BYTES;
+    if (ns == 0) ns = (w == 8 || Shape<DT, D, 4, 3>::SMEM_BYTES <= kTwoPerSm) ? 3 : kOk2 ? 2 : kOk1 ? 1 : 3;
     if (w == 8 && ns == 3) return launch_k<DT, D, ROWS2, 8, 3, CAP>(ctx, tk, tv, mp, st);
     if (w == 4 && ns == 3) return launch_k<DT, D, ROWS2, 4, 3, CAP>(ctx, tk, tv, mp, st);
     if (w == 4 && ns == 2) return launch_k<DT, D, ROWS2, 4, 2, CAP>(ctx, tk, tv, mp, st);
-    return set_error(ctx, VFKV_ERR_INVALID, "attention tuning must be 4x2, 4x3 or 8x3 (warps x stages)");
+    if (w == 4 && ns == 1) return launch_k<DT, D, ROWS2, 4, 1, CAP>(ctx, tk, tv, mp, st);
+    if (w == 8 && ns == 1) return launch_k<DT, D, ROWS2, 8, 1, CAP>(ctx, tk, tv, mp, st);
+    return set_error(ctx, VFKV_ERR_INVALID, "attention tuning must be 4x1, 4x2, 4x3, 8x1 or 8x3 (warps x stages)");
 }
 
 template <int DT, int D, bool ROWS2>
