@@ -398,7 +398,8 @@ int32_t vfkv_stream_synchronize(vfkv_ctx *ctx, void *stream);
 /* ---------------------------------------------------------------------- */
 /* Selects the attention implementation for subsequent calls on this context:
  * 0 = automatic, 1 = CUDA-core kernel only, 2 = tensor-core kernel only
- * (VFKV_ERR_UNSUPPORTED from attend when the shape is outside it). */
+ * (VFKV_ERR_UNSUPPORTED from attend when the shape is outside it), 3 = automatic, but
+ * vfkv_attend_prefill takes its mma.sync kernel where it would take the tcgen05 one. */
 int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
 /* Shape of the tensor-core attention kernel for subsequent calls: warps per CTA x TMA stages per
  * warp; 4x2, 4x3 or 8x3, 0x0 = choose per call (4x2, or 8x3 when the grid has at most one CTA per

@@ -138,12 +138,47 @@ def test_prefill_attention_shapes(ctx, dtype, hq, hkv, d, m, q_start, kv_start, 
         got = out.cpu().numpy()
         assert np.isfinite(got).all()
         _check(got, want, dtype)
-        # the CUDA-core kernel agrees as well (independent implementation)
-        ctx.set_attn_impl(1)
-        out2 = torch.zeros(m, hq, d, device="cuda")
-        fwd.run_flash_attn_batch(1, to_dev(q), out2, m, q_start, n_kv, 1, kv_start, slot=1, window=window)
-        torch.cuda.synchronize()
-        _check(out2.cpu().numpy(), want, dtype)
+        # the other implementations agree as well: 1 = CUDA cores, 3 = mma.sync, 2 = tensor cores
+        # only, which for FP8 / head_dim 128 / g dividing 128 is the tcgen05 kernel whatever the
+        # chunk size (the automatic choice takes it only for chunks that fill the GPU)
+        tc5 = dtype == "F8" and d == 128 and 128 % (hq // hkv) == 0
+        for impl in (1, 3) + ((2,) if tc5 else ()):
+            ctx.set_attn_impl(impl)
+            out2 = torch.zeros(m, hq, d, device="cuda")
+            fwd.run_flash_attn_batch(1, to_dev(q), out2, m, q_start, n_kv, 1, kv_start, slot=1, window=window)
+            torch.cuda.synchronize()
+            _check(out2.cpu().numpy(), want, dtype)
+    finally:
+        ctx.set_attn_impl(0)
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+def test_prefill_large_chunk_takes_tcgen05_and_matches_mma(ctx):
+    """A chunk big enough that the automatic choice is the tcgen05 kernel (128-row blocks x kv-heads
+    >= SM count): compared with the mma.sync kernel everywhere and with the oracle on sampled queries."""
+    import torch
+    hq, hkv, d, m, q_start = 32, 8, 128, 640, 1500
+    L = q_start + m
+    rng = np.random.default_rng(21)
+    k, v = kv_values(rng, (L, hkv, d)), kv_values(rng, (L, hkv, d))
+    q = rng.standard_normal((m, hq, d), dtype=np.float32)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        _fill(fwd, k, v)
+        outs = {}
+        for impl in (0, 3):
+            ctx.set_attn_impl(impl)
+            out = torch.zeros(m, hq, d, device="cuda")
+            fwd.run_flash_attn_batch(0, to_dev(q), out, m, q_start, L, 0, 0)
+            torch.cuda.synchronize()
+            outs[impl] = out.cpu().numpy()
+        assert rel_err(outs[0], outs[3]) < 5e-3
+        kc, vc = encode_cache(k, oracle.F8), encode_cache(v, oracle.F8)
+        for i in (0, 1, 127, 128, 333, m - 1):
+            want = oracle.attention_ref(q[i], kc, vc, oracle.F8, hq, hkv, d, q_start + i + 1)
+            assert rel_err(outs[0][i], want) < 3e-2
     finally:
         ctx.set_attn_impl(0)
         fwd.workspace.destroy()

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libvfkv.so")
-SOURCES = ["api.cu", "append.cu", "attn_generic.cu", "attn_mma.cu", "attn_merge.cu", "exchange.cu", "attn_prefill.cu", "rope_append.cu", "routes.cpp", "noalloc.cu", "kv_cache.cpp"]
+SOURCES = ["api.cu", "append.cu", "attn_generic.cu", "attn_mma.cu", "attn_merge.cu", "exchange.cu", "attn_prefill.cu", "attn_prefill_tc5.cu", "rope_append.cu", "routes.cpp", "noalloc.cu", "kv_cache.cpp"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

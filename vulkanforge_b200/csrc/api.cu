@@ -172,7 +172,7 @@ int32_t vfkv_ctx_poll(vfkv_ctx *ctx, void *stream)
 
 int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl)
 {
-    if (!ctx || impl > 2) return VFKV_ERR_INVALID;
+    if (!ctx || impl > 3) return VFKV_ERR_INVALID;
     ctx->attn_impl = impl;
     return VFKV_OK;
 }

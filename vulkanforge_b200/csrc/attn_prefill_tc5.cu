@@ -1,0 +1,456 @@
+// Chunked-prefill causal attention over an FP8 cache on the 5th-generation tensor cores
+// (tcgen05.mma with accumulators in tensor memory).  Same function as prefill_mma_kernel in
+// attn_prefill.cu (flash_attn_batch.comp:105-208); used for head_dim 128 and FP8 caches.
+//
+// One CTA = 128 rows (128 / g consecutive queries x the g q-heads of one kv-head) x tiles of 128
+// positions.  Per tile:
+//   1. all threads fetch the K and V rows of the tile, widen the FP8 codes to half precision
+//      (exact; the kv_fp8_to_f16.comp step) and store them in the 128-byte-swizzled K-major /
+//      MN-major layouts the MMA descriptors describe;
+//   2. one thread issues S = Q K^T as 8 tcgen05.mma (M 128, N 128, K 16) into tensor memory;
+//   3. thread t owns row t: it reads its row of S from tensor memory (tcgen05.ld 32x32b), applies
+//      the causal / kv_start / window mask and the online softmax, and writes P in half
+//      precision into shared memory (over the K tile, which is dead by then);
+//   4. one thread issues O += P V as 8 tcgen05.mma into a second tensor-memory region, which holds
+//      the running output for the whole kernel.  The exponents of a row refer to a reference
+//      maximum that is moved (and O rescaled in tensor memory) only when the true maximum has
+//      outgrown it by more than 2^8, so most tiles cost no rescale at all.
+// Every wait on an MMA completion is bounded; a wait that runs out sets status bit 0, the CTA
+// leaves the tile loop, frees its tensor memory and returns.
+#include "../../include/vfkv_next.h"
+#include "common.cuh"
+#include "fp8_codec.cuh"
+
+namespace vfkv {
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int SLAB = 128 * 128;                 // bytes of one [128 rows][64 halves] slab
+constexpr int TILE = 2 * SLAB;                  // a [128][128] half-precision tile
+constexpr uint32_t TMEM_COLS = 256;             // S: columns 0..127, PV: columns 128..255
+
+struct Tc5Params {
+    const uint8_t *k, *v;              // rows of the slot: [pos][kv_head][128] FP8
+    const float *q;                    // [m][n_q_heads][128]
+    float *out;
+    uint64_t row_bytes;
+    uint32_t n_q_heads, n_kv_heads, group, m, q_start, n_kv, kv_start, window;
+    float scale, softcap;
+    uint32_t *status;
+};
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ uint64_t timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+// Bounded wait for the phase with the given parity; false after one second.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        // the timer is slow to read: look at it only now and then
+        if ((it & 255u) == 255u) {
+            if (t0 == 0) t0 = timer_ns();
+            else if (timer_ns() - t0 > 1000000000ull) return false;
+        }
+    }
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+// K-major: 8-row groups 1024 B apart (SBO), LBO unused.  MN-major: 64-element groups along
+// MN `lbo` bytes apart, 8-row groups along K 1024 B apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    return uint64_t((addr >> 4) & 0x3fffu) | (uint64_t((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           (uint64_t((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor of kind::f16: F32 accumulate, F16 x F16, M 128, N 128; bit 16 = B is MN-major.
+__host__ __device__ constexpr uint32_t idesc_f16(bool b_mn_major)
+{
+    return (1u << 4) | (uint32_t(b_mn_major) << 16) | (uint32_t(128 >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32])
+{
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// The same load without the wait, into 32 consecutive floats (wait once after a batch of loads).
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, float *v)
+{
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float *v)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 :: "r"(taddr),
+                    "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                    "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                    "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                    "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                    "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                    "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                    "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                    "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+}
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+{
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+// byte offset of 16-byte chunk c (0..15, 8 halves each) of row r in a [128][128] half tile
+__device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t c)
+{
+    return (c >> 3) * SLAB + r * 128 + (((c & 7u) ^ (r & 7u)) << 4);
+}
+
+__device__ __forceinline__ void query_range(const Tc5Params &p, uint32_t i, uint32_t *lo, uint32_t *hi)
+{
+    uint32_t c = p.q_start + i + 1u;
+    if (c > p.n_kv) c = p.n_kv;
+    uint32_t l = p.kv_start;
+    if (p.window != 0u && c > p.window && c - p.window > l) l = c - p.window;
+    if (l > c) l = c;
+    *lo = l; *hi = c;
+}
+
+template <bool CAP>
+__global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ uint32_t s_tmem, s_abort;
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;          // descriptors assume 1024-byte alignment
+    uint8_t *sm = smem_raw + (base - smem_addr(smem_raw));
+    const uint32_t q_sm = base, k_sm = base + TILE, v_sm = base + 2 * TILE;   // P reuses the K tile
+    const uint32_t bar_s = smem_addr(&s_bar[0]), bar_o = smem_addr(&s_bar[1]);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t kvh = blockIdx.y, g = p.group;
+    const uint32_t n_rows = p.m * g;
+    const uint32_t row0 = (gridDim.x - 1u - blockIdx.x) * BM;               // heaviest row blocks first
+
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0u;
+    }
+    if (warp == 0) {
+        __syncwarp();                      // the .sync.aligned instructions need the warp converged
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_addr(&s_tmem)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
+    // this thread's row
+    const uint32_t r = row0 + tid;
+    const bool r_ok = r < n_rows;
+    const uint32_t q_idx = r_ok ? r / g : 0u, hj = r_ok ? r % g : 0u;
+    uint32_t r_lo, r_hi;
+    query_range(p, q_idx, &r_lo, &r_hi);
+    if (!r_ok) { r_lo = 0u; r_hi = 0u; }
+    uint32_t c_lo, c_hi;
+    {
+        const uint32_t qa = row0 / g;
+        uint32_t qb = (row0 + BM - 1) / g;
+        if (qb >= p.m) qb = p.m - 1;
+        uint32_t lo_a, hi_a, lo_b, hi_b;
+        query_range(p, qa, &lo_a, &hi_a);
+        query_range(p, qb, &lo_b, &hi_b);
+        c_lo = lo_a / BN * BN;
+        c_hi = hi_b;
+    }
+    const uint32_t n_tiles = c_hi > c_lo ? (c_hi - c_lo + BN - 1) / BN : 0u;
+
+    // Q: f32 -> scaled half precision, K-major swizzled tile
+    for (uint32_t i = tid; i < uint32_t(BM * 16); i += 128) {
+        const uint32_t row = i >> 4, c = i & 15u;
+        const uint32_t rr = row0 + row;
+        uint4 hv = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < n_rows) {
+            const float *qp = p.q + (uint64_t(rr / g) * p.n_q_heads + kvh * g + rr % g) * HD + 8 * c;
+            const float4 a = *reinterpret_cast<const float4 *>(qp), b = *reinterpret_cast<const float4 *>(qp + 4);
+            hv = make_uint4(pack_half2(a.x * p.scale, a.y * p.scale), pack_half2(a.z * p.scale, a.w * p.scale),
+                            pack_half2(b.x * p.scale, b.y * p.scale), pack_half2(b.z * p.scale, b.w * p.scale));
+        }
+        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + tile_off(row, c)) = hv;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    const uint32_t t_lane = (warp * 32u) << 16;            // this warp's 32 lanes of tensor memory
+
+    float mref = kMaskedScore, lrow = 0.f;       // reference maximum of the exponents (log2 units), running sum
+    const uint8_t *kg = p.k + uint64_t(kvh) * HD, *vg = p.v + uint64_t(kvh) * HD;
+    uint32_t ph_s = 0, ph_o = 0;
+
+    for (uint32_t it = 0; it < n_tiles; ++it) {
+        const uint32_t t0 = c_lo + it * BN;
+        // ---- 1. K and V rows of this tile -> half precision in shared memory ---------------------
+        // The previous tile's P V product still reads P (in the K tile's place) and V: its loads are
+        // issued first, then the wait, then the stores.
+#pragma unroll 1
+        for (int w = 0; w < 2; ++w) {                      // K, then V: 8 loads in flight per thread
+            const uint8_t *src = w ? vg : kg;
+            uint8_t *dst = sm + ((w ? v_sm : k_sm) - base);
+            uint4 raw[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t idx = tid + 128 * i, pos = idx >> 3, c16 = idx & 7u;
+                const bool ok = t0 + pos < p.n_kv;
+                const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c16 * 16;
+                raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (w == 0 && it > 0) {
+                if (!mbar_wait(bar_o, ph_o)) atomicOr(&s_abort, 1u);
+                ph_o ^= 1u;
+                __syncwarp();
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t idx = tid + 128 * i, pos = idx >> 3, c16 = idx & 7u;
+                const uint4 x = raw[i];
+                __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
+                __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
+                __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
+                __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
+                *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
+                    make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                               *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
+                    make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
+                               *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the MMA
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        // ---- 2. S = Q K^T ----------------------------------------------------------------------------
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                umma_f16(tmem, smem_desc(q_sm + o, 16, 1024), smem_desc(k_sm + o, 16, 1024), idesc_f16(false), ks);
+            }
+            umma_commit(bar_s);
+        }
+        if (!mbar_wait(bar_s, ph_s)) atomicOr(&s_abort, 1u);
+        ph_s ^= 1u;
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+        // ---- 3. this thread's row of S: mask, softmax against the reference maximum ---------------
+        const bool full = t0 >= r_lo && t0 + BN <= r_hi;
+        // first pass over the row: its maximum (tensor-memory reads are cheap; keeping all 128
+        // scores in registers would cost the second CTA on the SM)
+        float mx = kMaskedScore;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float s[32];
+            tmem_ld32_nowait(tmem + t_lane + 32 * c, s);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                float x = s[j];
+                if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap);
+                if (!full) {
+                    const uint32_t pos = t0 + 32 * c + j;
+                    if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
+                }
+                mx = fmaxf(mx, x);
+            }
+        }
+        mx = mx > 0.5f * kMaskedScore ? mx * kLog2e : kMaskedScore;
+        // The accumulator O lives in tensor memory and is rescaled only when a row's maximum has
+        // grown by more than 2^8 over the reference its exponents use (so P stays below 256 in
+        // half precision); the decision is per warp because the tensor-memory accesses are.
+        const bool grow = mx > mref + 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+            const float mnew = grow ? mx : mref;
+            const float alpha = fast_exp2(mref - mnew);
+            lrow *= alpha;
+            mref = mnew;
+            if (it > 0) {                                      // O holds the sum of the earlier tiles
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float o[32];
+                    tmem_ld32_nowait(tmem + 128u + t_lane + 32 * c, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= alpha;
+                    tmem_st32(tmem + 128u + t_lane + 32 * c, o);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float s[32];
+            tmem_ld32_nowait(tmem + t_lane + 32 * c, s);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8) {                  // chunks of 8 positions
+                uint32_t h[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    float pr[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        float x = s[8 * q8 + j + e];
+                        if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap);
+                        const uint32_t pos = t0 + 32 * c + 8 * q8 + j + e;
+                        const bool ok = full || (pos >= r_lo && pos < r_hi);
+                        pr[e] = ok ? fast_exp2(fmaf(x, kLog2e, -mref)) : 0.f;
+                    }
+                    sum += pr[0] + pr[1];
+                    h[j >> 1] = pack_half2(pr[0], pr[1]);
+                }
+                // P is K-major over positions, in the K tile's place
+                *reinterpret_cast<uint4 *>(sm + (k_sm - base) + tile_off(tid, 4 * c + q8)) = make_uint4(h[0], h[1], h[2], h[3]);
+            }
+        }
+        lrow += sum;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        // ---- 4. O += P V -----------------------------------------------------------------------------------
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (uint32_t kk = 0; kk < BN / 16; ++kk) {
+                const uint32_t ao = (kk >> 2) * SLAB + (kk & 3u) * 32;            // P: K-major, 16 positions per step
+                umma_f16(tmem + 128u, smem_desc(k_sm + ao, 16, 1024), smem_desc(v_sm + kk * 2048, SLAB, 1024),
+                         idesc_f16(true), (it | kk) != 0u ? 1u : 0u);
+            }
+            umma_commit(bar_o);
+        }
+        if (s_abort) break;                                    // uniform: written before the last barrier at the latest
+    }
+    if (n_tiles > 0 && !s_abort) {
+        if (!mbar_wait(bar_o, ph_o)) atomicOr(&s_abort, 1u);
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    const bool failed = s_abort != 0u;
+    if (failed && tid == 0) atomicOr(p.status, 1u);
+
+    {
+        const float inv = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
+        float *o = p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float v[32];
+            if (n_tiles > 0) {
+                tmem_ld32_nowait(tmem + 128u + t_lane + 32 * c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+            if (r_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(o + 32 * c + j) =
+                        make_float4(inv > 0.f ? v[j] * inv : 0.f, inv > 0.f ? v[j + 1] * inv : 0.f,
+                                    inv > 0.f ? v[j + 2] * inv : 0.f, inv > 0.f ? v[j + 3] * inv : 0.f);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "n"(TMEM_COLS) : "memory");
+    }
+}
+
+constexpr int kSmemBytes = 3 * TILE + 1024;
+
+}  // namespace
+
+bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales)
+{
+    return dtype == VFKV_F8 && head_dim == 128 && !has_scales && group != 0 && BM % group == 0;
+}
+
+int32_t launch_prefill_tc5(vfkv_ctx *ctx, const uint8_t *k, const uint8_t *v, const float *q, float *out,
+                           uint64_t row_bytes, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
+                           uint32_t n_kv, uint32_t kv_start, uint32_t window, float scale, float softcap,
+                           cudaStream_t st)
+{
+    Tc5Params p{};
+    p.k = k; p.v = v; p.q = q; p.out = out; p.row_bytes = row_bytes;
+    p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
+    p.m = m; p.q_start = q_start; p.n_kv = n_kv; p.kv_start = kv_start; p.window = window;
+    p.scale = scale; p.softcap = softcap; p.status = ctx->d_status;
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tcgen05 prefill attention)");
+        configured[ctx->device & 63] = true;
+    }
+    const dim3 grid((m * p.group + BM - 1) / BM, n_kv_heads);
+    if (softcap > 0.f) prefill_tc5_kernel<true><<<grid, 128, kSmemBytes, st>>>(p);
+    else prefill_tc5_kernel<false><<<grid, 128, kSmemBytes, st>>>(p);
+    ctx->launches++;
+    return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
+}
+
+}  // namespace vfkv

@@ -17,7 +17,7 @@ struct vfkv_ctx {
     int sm_count = 0;
     std::string last_error;
     uint32_t *d_status = nullptr;      // device word written by bounded waits that give up
-    uint32_t attn_impl = 0;            // 0 auto, 1 CUDA-core only, 2 tensor-core only
+    uint32_t attn_impl = 0;            // 0 auto, 1 CUDA-core only, 2 tensor-core only, 3 as 0 but mma.sync instead of tcgen05 (prefill)
     uint32_t tune_warps = 0, tune_stages = 0;   // tensor-core kernel shape, 0 = choose
     uint32_t pdl = 0;                  // programmatic dependent launch mode of the attention kernel (0 / 1 / 2)
     uint32_t cluster_merge = 0;        // 1: merge the splits inside a thread-block cluster where the device allows it
@@ -166,6 +166,13 @@ int32_t launch_merge_partials(vfkv_ctx *ctx, const float *m, const float *l, con
 
 int32_t launch_merge_partials_packed(vfkv_ctx *ctx, const float *packed, uint32_t n_parts, uint32_t n_rows,
                                      uint32_t head_dim, float *out, cudaStream_t st);
+
+// prefill attention on tcgen05 (attn_prefill_tc5.cu); k / v point at the slot's rows of the layer
+bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales);
+int32_t launch_prefill_tc5(vfkv_ctx *ctx, const uint8_t *k, const uint8_t *v, const float *q, float *out,
+                           uint64_t row_bytes, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
+                           uint32_t n_kv, uint32_t kv_start, uint32_t window, float scale, float softcap,
+                           cudaStream_t st);
 
 // peer exchange of partials (exchange.cu)
 int32_t launch_fanout_push(vfkv_ctx *ctx, const PeerFanout &fan, const float *staging, uint32_t head_dim,
