@@ -367,11 +367,11 @@ def batch64_roofline(ctx, args, peak):
 
 def next_rows(ctx, args, peak, tensor_peak):
     """The callers either side of the hot path, measured on their own: chunked-prefill causal
-    attention over the cache (a 512-token chunk ending at position 8192, FP8, 32 q / 8 kv / 128:
-    tensor-bound) and RoPE fused with the append of the same chunk (HBM-bound)."""
+    attention over the cache (a 2048-token chunk ending at position 16384, FP8, 32 q / 8 kv / 128:
+    tensor-bound, takes the tcgen05 kernel) and RoPE fused with the append of a 512-token chunk."""
     import torch
     import vulkanforge_b200 as vf
-    hq, hkv, d, m, q_start = 32, 8, 128, 512, 7680
+    hq, hkv, d, m, q_start = 32, 8, 128, 2048, 14336
     L = q_start + m
     cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
     fwd = vf.CudaForward(ctx, cache, n_heads=hq)
@@ -382,7 +382,7 @@ def next_rows(ctx, args, peak, tensor_peak):
             fwd.b_step_kv_write(0, kv[0], kv[1], 4096, p, 0)
         q = torch.randn(m, hq, d, device="cuda", generator=g)
         out = torch.zeros(m, hq, d, device="cuda")
-        kv = torch.randn(2, m, hkv * d, device="cuda", generator=g)
+        kv = torch.randn(2, 512, hkv * d, device="cuda", generator=g)
 
         def timed(fn, reps):
             for _ in range(3):
@@ -396,21 +396,63 @@ def next_rows(ctx, args, peak, tensor_peak):
             return e0.elapsed_time(e1) * 1e3 / reps
 
         us_attn = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 10)
-        us_rope = timed(lambda: fwd.rope_kv_write(0, kv[0], kv[1], m, q_start, freq_base=500000.0), 20)
+        us_rope = timed(lambda: fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0), 20)
         flops = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2)              # causal: query i sees q_start + i + 1 rows
-        rope_bytes = 2 * m * hkv * d * (4 + 1)                               # f32 in, one byte out, K and V
+        rope_bytes = 2 * 512 * hkv * d * (4 + 1)                             # f32 in, one byte out, K and V
         tf = flops / (us_attn * 1e-6) / 1e12
         gbs = rope_bytes / (us_rope * 1e-6) / 1e9
-        return {"prefill_attention": {"workload": "512 queries at positions 7680..8191, FP8 cache, 32/8/128",
+        return {"prefill_attention": {"workload": "2048 queries at positions 14336..16383, FP8 cache, 32/8/128",
                                       "us": us_attn, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
                                       "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None,
-                                      "note": "m16n8k16 mma.sync kernel"},
+                                      "note": "tcgen05.mma kernel, S and O in tensor memory"},
                 "rope_append": {"workload": "512 tokens x 8 kv-heads x 128, FP8 cache, K rotated", "us": us_rope,
                                 "bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak,
                                 "note": "5 MiB per launch: launch latency, not bandwidth, sets the time"}}
     finally:
         fwd.workspace.destroy()
         cache.destroy()
+
+
+def run_probe(args):
+    """One kernel of the "next" rows on its own, for profiling: `--probe prefill` launches the
+    chunked-prefill attention `--steps` times (FP8, 32 q / 8 kv / 128, `--probe-m` queries ending
+    at position `--probe-ctx`); `--probe rope` the fused RoPE + append of a 512-token chunk."""
+    import torch
+    import vulkanforge_b200 as vf
+    ctx = vf.Context(0)
+    hq, hkv, d, m, L = 32, 8, 128, args.probe_m, args.probe_ctx
+    q_start = L - m
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for p in range(0, L, 4096):
+        n = min(4096, L - p)
+        kv = torch.randn(2, n, hkv * d, device="cuda", generator=g)
+        fwd.b_step_kv_write(0, kv[0], kv[1], n, p, 0)
+    q = torch.randn(m, hq, d, device="cuda", generator=g)
+    out = torch.zeros(m, hq, d, device="cuda")
+    kv = torch.randn(2, 512, hkv * d, device="cuda", generator=g)
+    if args.probe == "prefill":
+        fn = lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0)
+        work, unit = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2) / 1e12, "TFLOP/s"
+    else:
+        fn = lambda: fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0)
+        work, unit = 2 * 512 * hkv * d * 5 / 1e9, "GB/s"
+    for _ in range(args.warmup):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ctx.poll()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"probe": args.probe, "m": m, "context": L, "us_per_launch": us, "achieved": work / (us * 1e-6),
+                      "unit": unit, "steps": args.steps}), flush=True)
+    fwd.workspace.destroy()
+    cache.destroy()
+    ctx.destroy()
 
 
 def run_ours(args, w, rank, world, local_rank):
@@ -684,6 +726,10 @@ def main():
     ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch mode of the attention kernel (vfkv_ctx_set_dependent_launch)")
+    ap.add_argument("--probe", default=None, choices=["prefill", "rope"],
+                    help="run one kernel of the next rows on its own (for profiling) and exit")
+    ap.add_argument("--probe-m", type=int, default=2048)
+    ap.add_argument("--probe-ctx", type=int, default=16384)
     ap.add_argument("--cluster", type=int, default=0, choices=[0, 1],
                     help="merge the splits inside a thread-block cluster (vfkv_ctx_set_cluster_merge)")
     ap.add_argument("--tune", default=None, help="tensor-core kernel shape WxS (warps x stages), e.g. 4x3")
@@ -695,6 +741,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.probe:
+        run_probe(args)
+        return
     if args.impl == "reference":
         run_reference(args, w, rank, world)
         return

@@ -422,7 +422,11 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * every CTA stores 16 x uint64 nanosecond timestamps (globaltimer) at fixed phases -- 0 entry,
  * 1 range known, 2 barriers ready, 3 Q ready, 4 first tile landed, 5 stream done, 6 CTA joined,
  * 7 partial written, 8 ticket taken, 9 merged (last CTA only) -- at CTA index * 16.  The buffer
- * must hold 16 x 8 bytes per CTA of the largest grid.  NULL switches it off. */
+ * must hold 16 x 8 bytes per CTA of the largest grid.  NULL switches it off.
+ * The tcgen05 prefill kernel (vfkv_attend_prefill) uses the same buffer: thread 0 of each of its
+ * two warpgroups stores, at its 4th K/V tile, 0 tile start, 1 loads issued and previous P V
+ * complete, 2 K/V converted, 3 CTA barrier passed, 4 S issued, 5 S complete, 6 row maximum,
+ * 7 rescale decided, 8 P written, 9 P V issued -- at (CTA index * 2 + warpgroup) * 16. */
 /* Split merge inside a thread-block cluster (tensor-core kernel, 2..16 splits): the CTAs of one
  * (sequence, kv-head) exchange their partials through distributed shared memory instead of
  * global scratch and a ticket.  Taken only when every cluster of the grid can be resident at

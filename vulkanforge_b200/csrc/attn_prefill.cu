@@ -530,11 +530,11 @@ extern "C" int32_t vfkv_attend_prefill(vfkv_cache *cache, uint32_t layer, uint32
                         (dt == VFKV_F8 || dt == VFKV_F16) && (D == 64 || D == 128 || D == 256);
     if (ctx->attn_impl == 2 && !mma_ok)
         return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_attend_prefill: shape outside the tensor-core kernel");
-    // The tcgen05 kernel works on 128-row blocks, one CTA per SM: it pays once those fill the GPU;
-    // smaller chunks keep the 64-row mma.sync kernel (twice the CTAs).  attn_impl 2 forces it.
-    const uint64_t blocks128 = (uint64_t(m) * p.group + 127) / 128 * hkv;
+    // The tcgen05 kernel works on 256-row blocks, one CTA per SM: it pays once those fill most of
+    // the GPU; smaller chunks keep the 64-row mma.sync kernel (four times the CTAs).  attn_impl 2 forces it.
+    const uint64_t blocks256 = (uint64_t(m) * p.group + 255) / 256 * hkv;
     if (mma_ok && ctx->attn_impl != 3 && prefill_tc5_supported(dt, D, p.group, kv.k_scales != nullptr) &&
-        (blocks128 >= uint64_t(ctx->sm_count) || ctx->attn_impl == 2))
+        (blocks256 * 4 >= uint64_t(ctx->sm_count) * 3 || ctx->attn_impl == 2))
         return launch_prefill_tc5(ctx, p.k, p.v, d_q, d_out, p.row_bytes, n_q_heads, hkv, m, q_start, n_kv, kv_start,
                                   window, scale, softcap, st);
     if (mma_ok) {

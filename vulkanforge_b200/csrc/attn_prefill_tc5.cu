@@ -2,8 +2,9 @@
 // (tcgen05.mma with accumulators in tensor memory).  Same function as prefill_mma_kernel in
 // attn_prefill.cu (flash_attn_batch.comp:105-208); used for head_dim 128 and FP8 caches.
 //
-// One CTA = 128 rows (128 / g consecutive queries x the g q-heads of one kv-head) x tiles of 128
-// positions.  Per tile:
+// One CTA = two Q tiles of 128 rows (256 / g consecutive queries x the g q-heads of one kv-head),
+// one warpgroup per Q tile, x K/V tiles of 128 positions shared by both.  While one warpgroup does
+// the softmax of its tile the tensor core works for the other.  Per tile:
 //   1. all threads fetch the K and V rows of the tile, widen the FP8 codes to half precision
 //      (exact; the kv_fp8_to_f16.comp step) and store them in the 128-byte-swizzled K-major /
 //      MN-major layouts the MMA descriptors describe;
@@ -28,7 +29,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int SLAB = 128 * 128;                 // bytes of one [128 rows][64 halves] slab
 constexpr int TILE = 2 * SLAB;                  // a [128][128] half-precision tile
-constexpr uint32_t TMEM_COLS = 256;             // S: columns 0..127, PV: columns 128..255
+constexpr int CTA_ROWS = 2 * BM;                // two Q tiles per CTA, one per warpgroup
+constexpr uint32_t TMEM_COLS = 512;             // S of tile 0 and 1: columns 0..255; O of tile 0 and 1: 256..511
 
 struct Tc5Params {
     const uint8_t *k, *v;              // rows of the slot: [pos][kv_head][128] FP8
@@ -38,6 +40,7 @@ struct Tc5Params {
     uint32_t n_q_heads, n_kv_heads, group, m, q_start, n_kv, kv_start, window;
     float scale, softcap;
     uint32_t *status;
+    unsigned long long *trace;         // null, or 16 timestamps per warpgroup (phase analysis)
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -167,23 +170,25 @@ __device__ __forceinline__ void query_range(const Tc5Params &p, uint32_t i, uint
 }
 
 template <bool CAP>
-__global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
+__global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
 {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ __align__(8) uint64_t s_bar[4];
     __shared__ uint32_t s_tmem, s_abort;
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;          // descriptors assume 1024-byte alignment
     uint8_t *sm = smem_raw + (base - smem_addr(smem_raw));
-    const uint32_t q_sm = base, k_sm = base + TILE, v_sm = base + 2 * TILE;   // P reuses the K tile
-    const uint32_t bar_s = smem_addr(&s_bar[0]), bar_o = smem_addr(&s_bar[1]);
+    // shared memory: Q tile 0, Q tile 1, K, V, P of tile 0, P of tile 1
+    const uint32_t q_sm = base, k_sm = base + 2 * TILE, v_sm = base + 3 * TILE, p_sm = base + 4 * TILE;
     const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t wg = tid >> 7, t = tid & 127u;                           // warpgroup = Q tile, row inside it
+    const uint32_t bar_s = smem_addr(&s_bar[wg]), bar_o = smem_addr(&s_bar[2 + wg]);
     const uint32_t kvh = blockIdx.y, g = p.group;
     const uint32_t n_rows = p.m * g;
-    const uint32_t row0 = (gridDim.x - 1u - blockIdx.x) * BM;               // heaviest row blocks first
+    const uint32_t row0 = (gridDim.x - 1u - blockIdx.x) * CTA_ROWS;         // heaviest row blocks first
 
     if (tid == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mbar_init(smem_addr(&s_bar[i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0u;
     }
@@ -194,7 +199,7 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
     }
 
     // this thread's row
-    const uint32_t r = row0 + tid;
+    const uint32_t r = row0 + wg * BM + t;
     const bool r_ok = r < n_rows;
     const uint32_t q_idx = r_ok ? r / g : 0u, hj = r_ok ? r % g : 0u;
     uint32_t r_lo, r_hi;
@@ -203,7 +208,7 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
     uint32_t c_lo, c_hi;
     {
         const uint32_t qa = row0 / g;
-        uint32_t qb = (row0 + BM - 1) / g;
+        uint32_t qb = (row0 + CTA_ROWS - 1) / g;
         if (qb >= p.m) qb = p.m - 1;
         uint32_t lo_a, hi_a, lo_b, hi_b;
         query_range(p, qa, &lo_a, &hi_a);
@@ -213,8 +218,8 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
     }
     const uint32_t n_tiles = c_hi > c_lo ? (c_hi - c_lo + BN - 1) / BN : 0u;
 
-    // Q: f32 -> scaled half precision, K-major swizzled tile
-    for (uint32_t i = tid; i < uint32_t(BM * 16); i += 128) {
+    // Q: f32 -> scaled half precision, two K-major swizzled tiles
+    for (uint32_t i = tid; i < uint32_t(CTA_ROWS * 16); i += 256) {
         const uint32_t row = i >> 4, c = i & 15u;
         const uint32_t rr = row0 + row;
         uint4 hv = make_uint4(0u, 0u, 0u, 0u);
@@ -224,44 +229,51 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
             hv = make_uint4(pack_half2(a.x * p.scale, a.y * p.scale), pack_half2(a.z * p.scale, a.w * p.scale),
                             pack_half2(b.x * p.scale, b.y * p.scale), pack_half2(b.z * p.scale, b.w * p.scale));
         }
-        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + tile_off(row, c)) = hv;
+        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) = hv;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
-    const uint32_t t_lane = (warp * 32u) << 16;            // this warp's 32 lanes of tensor memory
+    const uint32_t t_lane = ((warp & 3u) * 32u) << 16;      // this warp's 32 lanes of tensor memory
+    const uint32_t tm_s = tmem + wg * 128u, tm_o = tmem + 256u + wg * 128u;   // S and O of this warpgroup's Q tile
+    const uint32_t my_p = p_sm + wg * TILE;
 
     float mref = kMaskedScore, lrow = 0.f;       // reference maximum of the exponents (log2 units), running sum
     const uint8_t *kg = p.k + uint64_t(kvh) * HD, *vg = p.v + uint64_t(kvh) * HD;
     uint32_t ph_s = 0, ph_o = 0;
 
+#define TC5_TRACE(i)                                                                                 \
+    do {                                                                                             \
+        if (p.trace != nullptr && t == 0 && it == 3)                                                 \
+            p.trace[((blockIdx.y * gridDim.x + blockIdx.x) * 2 + wg) * 16 + (i)] = timer_ns();       \
+    } while (0)
     for (uint32_t it = 0; it < n_tiles; ++it) {
         const uint32_t t0 = c_lo + it * BN;
-        // ---- 1. K and V rows of this tile -> half precision in shared memory ---------------------
-        // The previous tile's P V product still reads P (in the K tile's place) and V: its loads are
-        // issued first, then the wait, then the stores.
-#pragma unroll 1
-        for (int w = 0; w < 2; ++w) {                      // K, then V: 8 loads in flight per thread
-            const uint8_t *src = w ? vg : kg;
-            uint8_t *dst = sm + ((w ? v_sm : k_sm) - base);
-            uint4 raw[8];
+        // ---- 1. K and V rows of this tile -> half precision in shared memory (all 256 threads) --------
+        TC5_TRACE(0);
+        {
+            uint4 raw[8];                                  // 4 pieces of K, 4 of V
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint32_t idx = tid + 128 * i, pos = idx >> 3, c16 = idx & 7u;
+                const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
                 const bool ok = t0 + pos < p.n_kv;
                 const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c16 * 16;
-                raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
+                raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>((i < 4 ? kg : vg) + off)) : make_uint4(0u, 0u, 0u, 0u);
             }
-            if (w == 0 && it > 0) {
-                if (!mbar_wait(bar_o, ph_o)) atomicOr(&s_abort, 1u);
+            // V is still read by both P V products of the previous tile (K is free: both S products
+            // were waited for before the softmax)
+            if (it > 0) {
+                if (!mbar_wait(smem_addr(&s_bar[2]), ph_o) || !mbar_wait(smem_addr(&s_bar[3]), ph_o)) atomicOr(&s_abort, 1u);
                 ph_o ^= 1u;
                 __syncwarp();
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
+            TC5_TRACE(1);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const uint32_t idx = tid + 128 * i, pos = idx >> 3, c16 = idx & 7u;
+                const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
+                uint8_t *dst = sm + ((i < 4 ? k_sm : v_sm) - base);
                 const uint4 x = raw[i];
                 __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
                 __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
@@ -277,44 +289,54 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        TC5_TRACE(2);
         __syncthreads();
-        // ---- 2. S = Q K^T ----------------------------------------------------------------------------
+        TC5_TRACE(3);
+        if (s_abort) break;                                    // uniform: every writer passed a barrier since
+        // ---- 2. S = Q K^T for both Q tiles, back to back ---------------------------------------------
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (uint32_t ks = 0; ks < HD / 16; ++ks) {
-                const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
-                umma_f16(tmem, smem_desc(q_sm + o, 16, 1024), smem_desc(k_sm + o, 16, 1024), idesc_f16(false), ks);
+            for (uint32_t qt = 0; qt < 2; ++qt) {
+#pragma unroll
+                for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                    umma_f16(tmem + qt * 128u, smem_desc(q_sm + qt * TILE + o, 16, 1024), smem_desc(k_sm + o, 16, 1024),
+                             idesc_f16(false), ks);
+                }
+                umma_commit(smem_addr(&s_bar[qt]));
             }
-            umma_commit(bar_s);
         }
+        // ---- 3. per warpgroup: this thread's row of S: mask, softmax against the reference maximum ----
+        // While warpgroup 0 works on S0 the tensor core computes S1; while warpgroup 1 works on S1
+        // it computes O0 += P0 V.
+        TC5_TRACE(4);
         if (!mbar_wait(bar_s, ph_s)) atomicOr(&s_abort, 1u);
         ph_s ^= 1u;
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        TC5_TRACE(5);
 
-        // ---- 3. this thread's row of S: mask, softmax against the reference maximum ---------------
         const bool full = t0 >= r_lo && t0 + BN <= r_hi;
-        // first pass over the row: its maximum (tensor-memory reads are cheap; keeping all 128
-        // scores in registers would cost the second CTA on the SM)
+        // the whole row in registers (one CTA of 256 threads per SM: 255 registers each are there)
+        float s[BN];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tm_s + t_lane + 32 * c, &s[32 * c]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         float mx = kMaskedScore;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float s[32];
-            tmem_ld32_nowait(tmem + t_lane + 32 * c, s);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                float x = s[j];
-                if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap);
-                if (!full) {
-                    const uint32_t pos = t0 + 32 * c + j;
-                    if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
-                }
-                mx = fmaxf(mx, x);
+        for (int j = 0; j < BN; ++j) {
+            float x = s[j];
+            if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap);
+            x *= kLog2e;
+            if (!full) {
+                const uint32_t pos = t0 + j;
+                if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
             }
+            s[j] = x;
+            mx = fmaxf(mx, x);
         }
-        mx = mx > 0.5f * kMaskedScore ? mx * kLog2e : kMaskedScore;
+        TC5_TRACE(6);
         // The accumulator O lives in tensor memory and is rescaled only when a row's maximum has
         // grown by more than 2^8 over the reference its exponents use (so P stays below 256 in
         // half precision); the decision is per warp because the tensor-memory accesses are.
@@ -328,60 +350,52 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float o[32];
-                    tmem_ld32_nowait(tmem + 128u + t_lane + 32 * c, o);
+                    tmem_ld32_nowait(tm_o + t_lane + 32 * c, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int j = 0; j < 32; ++j) o[j] *= alpha;
-                    tmem_st32(tmem + 128u + t_lane + 32 * c, o);
+                    tmem_st32(tm_o + t_lane + 32 * c, o);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
         }
+        TC5_TRACE(7);
         float sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float s[32];
-            tmem_ld32_nowait(tmem + t_lane + 32 * c, s);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        for (int c = 0; c < BN / 8; ++c) {                    // 16 chunks of 8 positions
+            uint32_t h[4];
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8) {                  // chunks of 8 positions
-                uint32_t h[4];
-#pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                    float pr[2];
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        float x = s[8 * q8 + j + e];
-                        if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap);
-                        const uint32_t pos = t0 + 32 * c + 8 * q8 + j + e;
-                        const bool ok = full || (pos >= r_lo && pos < r_hi);
-                        pr[e] = ok ? fast_exp2(fmaf(x, kLog2e, -mref)) : 0.f;
-                    }
-                    sum += pr[0] + pr[1];
-                    h[j >> 1] = pack_half2(pr[0], pr[1]);
-                }
-                // P is K-major over positions, in the K tile's place
-                *reinterpret_cast<uint4 *>(sm + (k_sm - base) + tile_off(tid, 4 * c + q8)) = make_uint4(h[0], h[1], h[2], h[3]);
+            for (int j = 0; j < 8; j += 2) {
+                const float x0 = s[8 * c + j], x1 = s[8 * c + j + 1];
+                const float p0 = (full || x0 > 0.5f * kMaskedScore) ? fast_exp2(x0 - mref) : 0.f;
+                const float p1 = (full || x1 > 0.5f * kMaskedScore) ? fast_exp2(x1 - mref) : 0.f;
+                sum += p0 + p1;
+                h[j >> 1] = pack_half2(p0, p1);
             }
+            // P is K-major over positions
+            *reinterpret_cast<uint4 *>(sm + (my_p - base) + tile_off(t, c)) = make_uint4(h[0], h[1], h[2], h[3]);
         }
         lrow += sum;
+        TC5_TRACE(8);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-        // ---- 4. O += P V -----------------------------------------------------------------------------------
-        if (tid == 0) {
+        asm volatile("bar.sync %0, 128;" :: "r"(1u + wg) : "memory");      // this warpgroup only
+        // ---- 4. O += P V for this warpgroup's Q tile ----------------------------------------------------------
+        if (t == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (uint32_t kk = 0; kk < BN / 16; ++kk) {
                 const uint32_t ao = (kk >> 2) * SLAB + (kk & 3u) * 32;            // P: K-major, 16 positions per step
-                umma_f16(tmem + 128u, smem_desc(k_sm + ao, 16, 1024), smem_desc(v_sm + kk * 2048, SLAB, 1024),
+                umma_f16(tm_o, smem_desc(my_p + ao, 16, 1024), smem_desc(v_sm + kk * 2048, SLAB, 1024),
                          idesc_f16(true), (it | kk) != 0u ? 1u : 0u);
             }
             umma_commit(bar_o);
         }
-        if (s_abort) break;                                    // uniform: written before the last barrier at the latest
+        TC5_TRACE(9);
     }
-    if (n_tiles > 0 && !s_abort) {
+    __syncthreads();
+    const bool ran = n_tiles > 0 && s_abort == 0u;
+    if (ran) {
         if (!mbar_wait(bar_o, ph_o)) atomicOr(&s_abort, 1u);
         __syncwarp();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -396,8 +410,8 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             float v[32];
-            if (n_tiles > 0) {
-                tmem_ld32_nowait(tmem + 128u + t_lane + 32 * c, v);
+            if (ran) {
+                tmem_ld32_nowait(tm_o + t_lane + 32 * c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             } else {
 #pragma unroll
@@ -419,7 +433,7 @@ __global__ void __launch_bounds__(128, 2) prefill_tc5_kernel(const Tc5Params p)
     }
 }
 
-constexpr int kSmemBytes = 3 * TILE + 1024;
+constexpr int kSmemBytes = 6 * TILE + 1024;
 
 }  // namespace
 
@@ -438,6 +452,7 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, const uint8_t *k, const uint8_t *v, co
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
     p.m = m; p.q_start = q_start; p.n_kv = n_kv; p.kv_start = kv_start; p.window = window;
     p.scale = scale; p.softcap = softcap; p.status = ctx->d_status;
+    p.trace = ctx->d_trace;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -446,9 +461,9 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, const uint8_t *k, const uint8_t *v, co
         if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tcgen05 prefill attention)");
         configured[ctx->device & 63] = true;
     }
-    const dim3 grid((m * p.group + BM - 1) / BM, n_kv_heads);
-    if (softcap > 0.f) prefill_tc5_kernel<true><<<grid, 128, kSmemBytes, st>>>(p);
-    else prefill_tc5_kernel<false><<<grid, 128, kSmemBytes, st>>>(p);
+    const dim3 grid((m * p.group + CTA_ROWS - 1) / CTA_ROWS, n_kv_heads);
+    if (softcap > 0.f) prefill_tc5_kernel<true><<<grid, 256, kSmemBytes, st>>>(p);
+    else prefill_tc5_kernel<false><<<grid, 256, kSmemBytes, st>>>(p);
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
 }
