@@ -218,7 +218,9 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
     }
     const uint32_t n_tiles = c_hi > c_lo ? (c_hi - c_lo + BN - 1) / BN : 0u;
 
-    // Q: f32 -> scaled half precision, two K-major swizzled tiles
+    // Q: f32 -> scaled half precision, two K-major swizzled tiles.  Without a soft-cap the factor
+    // log2(e) of the exponentials is folded into the scale, so S arrives in log2 units.
+    const float qs = CAP ? p.scale : p.scale * kLog2e;
     for (uint32_t i = tid; i < uint32_t(CTA_ROWS * 16); i += 256) {
         const uint32_t row = i >> 4, c = i & 15u;
         const uint32_t rr = row0 + row;
@@ -226,8 +228,8 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
         if (rr < n_rows) {
             const float *qp = p.q + (uint64_t(rr / g) * p.n_q_heads + kvh * g + rr % g) * HD + 8 * c;
             const float4 a = *reinterpret_cast<const float4 *>(qp), b = *reinterpret_cast<const float4 *>(qp + 4);
-            hv = make_uint4(pack_half2(a.x * p.scale, a.y * p.scale), pack_half2(a.z * p.scale, a.w * p.scale),
-                            pack_half2(b.x * p.scale, b.y * p.scale), pack_half2(b.z * p.scale, b.w * p.scale));
+            hv = make_uint4(pack_half2(a.x * qs, a.y * qs), pack_half2(a.z * qs, a.w * qs),
+                            pack_half2(b.x * qs, b.y * qs), pack_half2(b.z * qs, b.w * qs));
         }
         *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) = hv;
     }
@@ -261,17 +263,7 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
                 const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c16 * 16;
                 raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>((i < 4 ? kg : vg) + off)) : make_uint4(0u, 0u, 0u, 0u);
             }
-            // V is still read by both P V products of the previous tile (K is free: both S products
-            // were waited for before the softmax)
-            if (it > 0) {
-                if (!mbar_wait(smem_addr(&s_bar[2]), ph_o) || !mbar_wait(smem_addr(&s_bar[3]), ph_o)) atomicOr(&s_abort, 1u);
-                ph_o ^= 1u;
-                __syncwarp();
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            }
-            TC5_TRACE(1);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            auto widen = [&](int i) {
                 const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
                 uint8_t *dst = sm + ((i < 4 ? k_sm : v_sm) - base);
                 const uint4 x = raw[i];
@@ -285,7 +277,24 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
                 *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
                     make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
                                *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+            };
+            // K is free already (both S products of the previous tile were waited for before its
+            // softmax): it is widened while the previous tile's P V products still run.  V and P
+            // are read by those products, so V waits for them.
+            // (this thread waited for its own warpgroup's S product only; the other one's is long
+            // complete, the wait makes that a guarantee)
+            if (it > 0 && !mbar_wait(smem_addr(&s_bar[wg ^ 1u]), ph_s ^ 1u)) atomicOr(&s_abort, 1u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) widen(i);
+            if (it > 0) {
+                if (!mbar_wait(smem_addr(&s_bar[2]), ph_o) || !mbar_wait(smem_addr(&s_bar[3]), ph_o)) atomicOr(&s_abort, 1u);
+                ph_o ^= 1u;
+                __syncwarp();
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
+            TC5_TRACE(1);
+#pragma unroll
+            for (int i = 4; i < 8; ++i) widen(i);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -293,7 +302,7 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
         __syncthreads();
         TC5_TRACE(3);
         if (s_abort) break;                                    // uniform: every writer passed a barrier since
-        // ---- 2. S = Q K^T for both Q tiles, back to back ---------------------------------------------
+        // ---- 2. S = Q K^T for both Q tiles ----------------------------------------------------------------
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -323,18 +332,24 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tm_s + t_lane + 32 * c, &s[32 * c]);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // tiles inside every row's range (all but the diagonal and window edges) need no mask
+        const bool warp_full = __all_sync(0xffffffffu, full);
         float mx = kMaskedScore;
+        if (warp_full && !CAP) {
 #pragma unroll
-        for (int j = 0; j < BN; ++j) {
-            float x = s[j];
-            if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap);
-            x *= kLog2e;
-            if (!full) {
-                const uint32_t pos = t0 + j;
-                if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
+            for (int j = 0; j < BN; j += 2) mx = fmaxf(mx, fmaxf(s[j], s[j + 1]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                float x = s[j];
+                if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap) * kLog2e;
+                if (!full) {
+                    const uint32_t pos = t0 + j;
+                    if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
+                }
+                s[j] = x;
+                mx = fmaxf(mx, x);
             }
-            s[j] = x;
-            mx = fmaxf(mx, x);
         }
         TC5_TRACE(6);
         // The accumulator O lives in tensor memory and is rescaled only when a row's maximum has
@@ -367,8 +382,11 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
 #pragma unroll
             for (int j = 0; j < 8; j += 2) {
                 const float x0 = s[8 * c + j], x1 = s[8 * c + j + 1];
-                const float p0 = (full || x0 > 0.5f * kMaskedScore) ? fast_exp2(x0 - mref) : 0.f;
-                const float p1 = (full || x1 > 0.5f * kMaskedScore) ? fast_exp2(x1 - mref) : 0.f;
+                float p0 = fast_exp2(x0 - mref), p1 = fast_exp2(x1 - mref);
+                if (!warp_full) {                              // a masked position contributes nothing
+                    p0 = x0 > 0.5f * kMaskedScore ? p0 : 0.f;
+                    p1 = x1 > 0.5f * kMaskedScore ? p1 : 0.f;
+                }
                 sum += p0 + p1;
                 h[j >> 1] = pack_half2(p0, p1);
             }
