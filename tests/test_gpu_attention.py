@@ -333,6 +333,41 @@ def test_decode_token_host_all_layers(ctx, impl):
         rig.close()
 
 
+def test_decode_token_host_replays_a_graph_over_several_tokens(ctx):
+    """On a real stream the host-buffer entry point captures one token's launches once and replays
+    them: successive tokens (positions advancing across a 1024 boundary, where the length hint and
+    so the graph change) must each append and attend correctly."""
+    import torch
+    hq, hkv, d, max_seq, n_layers, n_seqs = 32, 8, 128, 1100, 2, 2
+    rng = np.random.default_rng(62)
+    rig = Rig(ctx, vf.KvDtype.F8, hq, hkv, d, max_seq, n_layers=n_layers, n_slots=n_seqs)
+    stream = torch.cuda.Stream()
+    try:
+        k_all = kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d))
+        v_all = kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d))
+        kc, vc = encode_cache(k_all, oracle.F8), encode_cache(v_all, oracle.F8)
+        for l in range(n_layers):
+            for s in range(n_seqs):
+                rig.put(l, s, kc[l, s], vc[l, s])
+        rig.fwd.stream = stream.cuda_stream
+        n0 = ctx.launch_count()
+        for step, p0 in enumerate((1020, 1021, 1022, 1023, 1024, 1025)):
+            pos = np.array([p0, p0 - 500], np.uint32)
+            q = rng.standard_normal((n_layers, n_seqs, hq, d), dtype=np.float32)
+            kn = np.stack([np.stack([k_all[l, s, pos[s]] for s in range(n_seqs)]) for l in range(n_layers)])
+            vn = np.stack([np.stack([v_all[l, s, pos[s]] for s in range(n_seqs)]) for l in range(n_layers)])
+            out = np.zeros((n_layers, n_seqs, hq, d), np.float32)
+            rig.fwd.decode_token_host(q, kn, vn, out, pos, n_seqs)
+            for l in range(n_layers):
+                want = oracle.decode_step(q[l], kn[l], vn[l], kc[l].copy(), vc[l].copy(), oracle.F8, n_seqs, max_seq,
+                                          hq, hkv, d, pos + 1)
+                check(out[l], want, oracle.F8)
+        assert ctx.launch_count() - n0 == 6 * n_layers        # replays are counted like launches
+    finally:
+        rig.fwd.stream = None
+        rig.close()
+
+
 def test_attend_argument_errors(ctx):
     import torch
     rig = Rig(ctx, vf.KvDtype.F16, 32, 8, 128, 64)

@@ -472,6 +472,7 @@ int32_t vfkv_workspace_destroy(vfkv_workspace *ws)
     DeviceGuard g(ws->ctx->device);
     cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->counters);
     cudaFree(ws->stage_in); cudaFree(ws->stage_out);
+    if (ws->tok_graph) cudaGraphExecDestroy(ws->tok_graph);
     delete ws;
     return VFKV_OK;
 }
@@ -710,9 +711,55 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
     if (e == cudaSuccess && h_slot_ids) e = cudaMemcpyAsync(d_slots, h_slot_ids, n_seqs * 4, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host: H2D");
     {
-        int32_t rc = vfkv_decode_token(cache, ws, dq, dk, dv, ws->stage_out, n_q_heads, h_slot_ids ? d_slots : nullptr,
-                                       d_pos, n_seqs, max_pos + 1, windows, scale, softcap, n_splits, stream);
-        if (rc) return rc;
+        // The launches of one token depend on the host only through the configuration below
+        // (positions and slots are device-side inputs; the length hint is rounded up so that it
+        // changes rarely): capture them once, replay afterwards.
+        uint32_t hint = (max_pos + 1 + 1023u) / 1024u * 1024u;
+        if (hint > kv.config.max_seq_len) hint = kv.config.max_seq_len;
+        uint64_t wh = 1469598103934665603ull;
+        for (uint32_t l = 0; windows && l < L; ++l) wh = (wh ^ windows[l]) * 1099511628211ull;
+        uint32_t fs, fc;
+        memcpy(&fs, &scale, 4); memcpy(&fc, &softcap, 4);
+        const uint64_t key[8] = {reinterpret_cast<uint64_t>(cache), reinterpret_cast<uint64_t>(dq),
+                                 reinterpret_cast<uint64_t>(ws->stage_out),
+                                 uint64_t(n_q_heads) << 32 | n_seqs, uint64_t(hint) << 32 | n_splits,
+                                 uint64_t(fs) << 32 | fc, wh ^ (h_slot_ids ? 1u : 0u),
+                                 uint64_t(ctx->pdl) | uint64_t(ctx->tune_warps) << 8 | uint64_t(ctx->tune_stages) << 16 |
+                                     uint64_t(ctx->attn_impl) << 24 | uint64_t(ctx->cluster_merge) << 32 |
+                                     uint64_t(reinterpret_cast<uintptr_t>(st) & 0xffffffu) << 40};
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cap);
+        const bool graphable = cap == cudaStreamCaptureStatusNone && !ctx->profiling && !ctx->d_trace && st != nullptr;
+        if (graphable && (!ws->tok_graph || memcmp(key, ws->tok_key, sizeof(key)) != 0)) {
+            if (ws->tok_graph) { cudaGraphExecDestroy(ws->tok_graph); ws->tok_graph = nullptr; }
+            cudaGraph_t graph = nullptr;
+            if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                const uint64_t launches = ctx->launches;
+                int32_t rc = vfkv_decode_token(cache, ws, dq, dk, dv, ws->stage_out, n_q_heads,
+                                               h_slot_ids ? d_slots : nullptr, d_pos, n_seqs, hint, windows, scale,
+                                               softcap, n_splits, stream);
+                cudaError_t ce = cudaStreamEndCapture(st, &graph);
+                ctx->launches = launches;                       // recorded, not run
+                if (rc == VFKV_OK && ce == cudaSuccess && graph &&
+                    cudaGraphInstantiate(&ws->tok_graph, graph, 0) == cudaSuccess)
+                    memcpy(ws->tok_key, key, sizeof(key));
+                else
+                    ws->tok_graph = nullptr;
+                if (graph) cudaGraphDestroy(graph);
+                cudaGetLastError();
+                if (rc) return rc;
+            }
+        }
+        if (graphable && ws->tok_graph) {
+            e = cudaGraphLaunch(ws->tok_graph, st);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host: graph launch");
+            ctx->launches += L;
+        } else {
+            int32_t rc = vfkv_decode_token(cache, ws, dq, dk, dv, ws->stage_out, n_q_heads,
+                                           h_slot_ids ? d_slots : nullptr, d_pos, n_seqs, max_pos + 1, windows, scale,
+                                           softcap, n_splits, stream);
+            if (rc) return rc;
+        }
     }
     e = cudaMemcpyAsync(h_out, ws->stage_out, out_bytes, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);

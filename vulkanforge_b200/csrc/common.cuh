@@ -54,6 +54,10 @@ struct vfkv_workspace {
     float *stage_in = nullptr;
     float *stage_out = nullptr;
     uint64_t stage_in_bytes = 0, stage_out_bytes = 0;
+    // vfkv_decode_token_host: the kernel sequence of one token, captured once per configuration and
+    // replayed (the analogue of the reference's pre-recorded command buffers, forward/decode.rs:169-259)
+    cudaGraphExec_t tok_graph = nullptr;
+    uint64_t tok_key[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 };
 
 namespace vfkv {
