@@ -717,7 +717,12 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
         uint32_t hint = (max_pos + 1 + 1023u) / 1024u * 1024u;
         if (hint > kv.config.max_seq_len) hint = kv.config.max_seq_len;
         uint64_t wh = 1469598103934665603ull;
-        for (uint32_t l = 0; windows && l < L; ++l) wh = (wh ^ windows[l]) * 1099511628211ull;
+        auto mix = [&](uint64_t x) { wh = (wh ^ x) * 1099511628211ull; };
+        for (uint32_t l = 0; windows && l < L; ++l) mix(windows[l]);
+        // a cache object re-created at the same address must not find the old graph
+        mix(reinterpret_cast<uint64_t>(kv.k_buffer)); mix(reinterpret_cast<uint64_t>(kv.v_buffer));
+        mix(L); mix(D); mix(Hkv); mix(uint64_t(kv.kv_dtype)); mix(kv.config.max_seq_len); mix(kv.config.n_slots);
+        mix(reinterpret_cast<uint64_t>(ws->part_o)); mix(reinterpret_cast<uint64_t>(dk));
         uint32_t fs, fc;
         memcpy(&fs, &scale, 4); memcpy(&fc, &softcap, 4);
         const uint64_t key[8] = {reinterpret_cast<uint64_t>(cache), reinterpret_cast<uint64_t>(dq),
