@@ -139,9 +139,9 @@ def test_prefill_attention_shapes(ctx, dtype, hq, hkv, d, m, q_start, kv_start, 
         assert np.isfinite(got).all()
         _check(got, want, dtype)
         # the other implementations agree as well: 1 = CUDA cores, 3 = mma.sync, 2 = tensor cores
-        # only, which for FP8 / head_dim 128 / g dividing 128 is the tcgen05 kernel whatever the
-        # chunk size (the automatic choice takes it only for chunks that fill the GPU)
-        tc5 = dtype == "F8" and d == 128 and 128 % (hq // hkv) == 0
+        # only, which for FP8 or F16 / head_dim 128 / g dividing 128 is the tcgen05 kernel whatever
+        # the chunk size (the automatic choice takes it only for chunks that fill the GPU)
+        tc5 = dtype in ("F8", "F16") and d == 128 and 128 % (hq // hkv) == 0
         for impl in (1, 3) + ((2,) if tc5 else ()):
             ctx.set_attn_impl(impl)
             out2 = torch.zeros(m, hq, d, device="cuda")

@@ -9,6 +9,8 @@
 // (FP8 caches; the kv_fp8_to_f16.comp step) and consumed by m16n8k16 tensor-core MMAs with the
 // usual online softmax.  Shapes outside that kernel use a CUDA-core kernel with the reference's
 // work split (one CTA per (query, head)).
+#include <cmath>
+
 #include "../../include/vfkv_next.h"
 #include "common.cuh"
 #include "fp8_codec.cuh"
@@ -533,9 +535,14 @@ extern "C" int32_t vfkv_attend_prefill(vfkv_cache *cache, uint32_t layer, uint32
     // The tcgen05 kernel works on 256-row blocks, one CTA per SM: it pays once those fill most of
     // the GPU; smaller chunks keep the 64-row mma.sync kernel (four times the CTAs).  attn_impl 2 forces it.
     const uint64_t blocks256 = (uint64_t(m) * p.group + 255) / 256 * hkv;
-    if (mma_ok && ctx->attn_impl != 3 && prefill_tc5_supported(dt, D, p.group, kv.k_scales != nullptr) &&
+    // F16 caches carry the error budget of the reference's f32 shader (2e-3 absolute): the tcgen05
+    // kernel feeds Q as one half-precision value, which holds it (1e-4 .. 5e-4 measured) with the usual
+    // 1/sqrt(head_dim) scale but not with scale 1.0 (1e-2: the Gemma-4 rule); those keep the
+    // mma.sync kernel and its hi + lo split of Q.
+    const bool tc5_accurate = dt == VFKV_F8 || scale * sqrtf(float(D)) <= 1.5f;
+    if (mma_ok && ctx->attn_impl != 3 && prefill_tc5_supported(dt, D, p.group, kv.k_scales != nullptr) && tc5_accurate &&
         (blocks256 * 4 >= uint64_t(ctx->sm_count) * 3 || ctx->attn_impl == 2))
-        return launch_prefill_tc5(ctx, p.k, p.v, d_q, d_out, p.row_bytes, n_q_heads, hkv, m, q_start, n_kv, kv_start,
+        return launch_prefill_tc5(ctx, dt, p.k, p.v, d_q, d_out, p.row_bytes, n_q_heads, hkv, m, q_start, n_kv, kv_start,
                                   window, scale, softcap, st);
     if (mma_ok) {
         if (dt == VFKV_F8) {

@@ -1,6 +1,7 @@
-// Chunked-prefill causal attention over an FP8 cache on the 5th-generation tensor cores
+// Chunked-prefill causal attention over the cache on the 5th-generation tensor cores
 // (tcgen05.mma with accumulators in tensor memory).  Same function as prefill_mma_kernel in
-// attn_prefill.cu (flash_attn_batch.comp:105-208); used for head_dim 128 and FP8 caches.
+// attn_prefill.cu (flash_attn_batch.comp:105-208); used for head_dim 128, FP8 caches and, with the
+// usual attention scale, F16 caches.
 //
 // One CTA = two Q tiles of 128 rows (256 / g consecutive queries x the g q-heads of one kv-head),
 // one warpgroup per Q tile, x K/V tiles of 128 positions shared by both.  While one warpgroup does
@@ -169,7 +170,7 @@ __device__ __forceinline__ void query_range(const Tc5Params &p, uint32_t i, uint
     *lo = l; *hi = c;
 }
 
-template <bool CAP>
+template <int DT, bool CAP>
 __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -242,7 +243,8 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
     const uint32_t my_p = p_sm + wg * TILE;
 
     float mref = kMaskedScore, lrow = 0.f;       // reference maximum of the exponents (log2 units), running sum
-    const uint8_t *kg = p.k + uint64_t(kvh) * HD, *vg = p.v + uint64_t(kvh) * HD;
+    constexpr uint32_t ES = DT == VFKV_F8 ? 1u : 2u;           // bytes per cache element
+    const uint8_t *kg = p.k + uint64_t(kvh) * HD * ES, *vg = p.v + uint64_t(kvh) * HD * ES;
     uint32_t ph_s = 0, ph_o = 0;
 
 #define TC5_TRACE(i)                                                                                 \
@@ -254,38 +256,71 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
         const uint32_t t0 = c_lo + it * BN;
         // ---- 1. K and V rows of this tile -> half precision in shared memory (all 256 threads) --------
         TC5_TRACE(0);
-        {
-            uint4 raw[8];                                  // 4 pieces of K, 4 of V
+        if constexpr (DT == VFKV_F8) {
+                uint4 raw[8];                                  // 4 pieces of K, 4 of V
+    #pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
+                    const bool ok = t0 + pos < p.n_kv;
+                    const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c16 * 16;
+                    raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>((i < 4 ? kg : vg) + off)) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                auto widen = [&](int i) {
+                    const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
+                    uint8_t *dst = sm + ((i < 4 ? k_sm : v_sm) - base);
+                    const uint4 x = raw[i];
+                    __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
+                    __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
+                    __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
+                    __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
+                    *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
+                        make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                   *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                    *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
+                        make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
+                                   *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+                };
+                // K is free already (both S products of the previous tile were waited for before its
+                // softmax): it is widened while the previous tile's P V products still run.  V and P
+                // are read by those products, so V waits for them.
+                // (this thread waited for its own warpgroup's S product only; the other one's is long
+                // complete, the wait makes that a guarantee)
+                if (it > 0 && !mbar_wait(smem_addr(&s_bar[wg ^ 1u]), ph_s ^ 1u)) atomicOr(&s_abort, 1u);
+    #pragma unroll
+                for (int i = 0; i < 4; ++i) widen(i);
+                if (it > 0) {
+                    if (!mbar_wait(smem_addr(&s_bar[2]), ph_o) || !mbar_wait(smem_addr(&s_bar[3]), ph_o)) atomicOr(&s_abort, 1u);
+                    ph_o ^= 1u;
+                    __syncwarp();
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                }
+                TC5_TRACE(1);
+    #pragma unroll
+                for (int i = 4; i < 8; ++i) widen(i);
+        } else {
+            // F16 cache: the rows are half precision already; 16-byte pieces go straight to their
+            // swizzled places (8 pieces of K, then 8 of V, per thread)
+            uint4 raw[8];
+            auto fetch = [&](const uint8_t *src) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
-                const bool ok = t0 + pos < p.n_kv;
-                const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c16 * 16;
-                raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>((i < 4 ? kg : vg) + off)) : make_uint4(0u, 0u, 0u, 0u);
-            }
-            auto widen = [&](int i) {
-                const uint32_t idx = tid + 256 * (i & 3), pos = idx >> 3, c16 = idx & 7u;
-                uint8_t *dst = sm + ((i < 4 ? k_sm : v_sm) - base);
-                const uint4 x = raw[i];
-                __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
-                __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
-                __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
-                __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
-                *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
-                    make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
-                               *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
-                *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
-                    make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
-                               *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t idx = tid + 256 * i, pos = idx >> 4, c = idx & 15u;
+                    const bool ok = t0 + pos < p.n_kv;
+                    const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c * 16;
+                    raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
+                }
             };
-            // K is free already (both S products of the previous tile were waited for before its
-            // softmax): it is widened while the previous tile's P V products still run.  V and P
-            // are read by those products, so V waits for them.
-            // (this thread waited for its own warpgroup's S product only; the other one's is long
-            // complete, the wait makes that a guarantee)
-            if (it > 0 && !mbar_wait(smem_addr(&s_bar[wg ^ 1u]), ph_s ^ 1u)) atomicOr(&s_abort, 1u);
+            auto place = [&](uint32_t tile_sm) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) widen(i);
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t idx = tid + 256 * i, pos = idx >> 4, c = idx & 15u;
+                    *reinterpret_cast<uint4 *>(sm + (tile_sm - base) + tile_off(pos, c)) = raw[i];
+                }
+            };
+            fetch(kg);
+            if (it > 0 && !mbar_wait(smem_addr(&s_bar[wg ^ 1u]), ph_s ^ 1u)) atomicOr(&s_abort, 1u);
+            place(k_sm);
+            fetch(vg);
             if (it > 0) {
                 if (!mbar_wait(smem_addr(&s_bar[2]), ph_o) || !mbar_wait(smem_addr(&s_bar[3]), ph_o)) atomicOr(&s_abort, 1u);
                 ph_o ^= 1u;
@@ -293,8 +328,7 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
             TC5_TRACE(1);
-#pragma unroll
-            for (int i = 4; i < 8; ++i) widen(i);
+            place(v_sm);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the MMA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -457,10 +491,10 @@ constexpr int kSmemBytes = 6 * TILE + 1024;
 
 bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales)
 {
-    return dtype == VFKV_F8 && head_dim == 128 && !has_scales && group != 0 && BM % group == 0;
+    return (dtype == VFKV_F8 || dtype == VFKV_F16) && head_dim == 128 && !has_scales && group != 0 && BM % group == 0;
 }
 
-int32_t launch_prefill_tc5(vfkv_ctx *ctx, const uint8_t *k, const uint8_t *v, const float *q, float *out,
+int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, const uint8_t *v, const float *q, float *out,
                            uint64_t row_bytes, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
                            uint32_t n_kv, uint32_t kv_start, uint32_t window, float scale, float softcap,
                            cudaStream_t st)
@@ -473,15 +507,25 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, const uint8_t *k, const uint8_t *v, co
     p.trace = ctx->d_trace;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tcgen05 prefill attention)");
+        const void *kernels[4] = {reinterpret_cast<const void *>(prefill_tc5_kernel<VFKV_F8, false>),
+                                  reinterpret_cast<const void *>(prefill_tc5_kernel<VFKV_F8, true>),
+                                  reinterpret_cast<const void *>(prefill_tc5_kernel<VFKV_F16, false>),
+                                  reinterpret_cast<const void *>(prefill_tc5_kernel<VFKV_F16, true>)};
+        for (const void *kn : kernels) {
+            cudaError_t e = cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tcgen05 prefill attention)");
+        }
         configured[ctx->device & 63] = true;
     }
     const dim3 grid((m * p.group + CTA_ROWS - 1) / CTA_ROWS, n_kv_heads);
-    if (softcap > 0.f) prefill_tc5_kernel<true><<<grid, 256, kSmemBytes, st>>>(p);
-    else prefill_tc5_kernel<false><<<grid, 256, kSmemBytes, st>>>(p);
+    const bool cap = softcap > 0.f;
+    if (dtype == VFKV_F8) {
+        if (cap) prefill_tc5_kernel<VFKV_F8, true><<<grid, 256, kSmemBytes, st>>>(p);
+        else prefill_tc5_kernel<VFKV_F8, false><<<grid, 256, kSmemBytes, st>>>(p);
+    } else {
+        if (cap) prefill_tc5_kernel<VFKV_F16, true><<<grid, 256, kSmemBytes, st>>>(p);
+        else prefill_tc5_kernel<VFKV_F16, false><<<grid, 256, kSmemBytes, st>>>(p);
+    }
     ctx->launches++;
     return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
 }
