@@ -605,7 +605,7 @@ def run_position_sharded(args, w, rank, world, local_rank):
     g = torch.Generator(device="cuda").manual_seed(100 + rank)
     n_local = sh.local_len(L - 1, rank)
     n_layers = w["n_layers"]
-    ctx.check(ctx._lib.vfkv_ctx_set_dependent_launch(ctx.handle, 1 if args.pdl else 0))
+    ctx.check(ctx._lib.vfkv_ctx_set_dependent_launch(ctx.handle, args.pdl))
     for p in range(0, n_local, 4096):                      # this rank's pages of the 131071 earlier tokens
         m = min(4096, n_local - p)
         kv = torch.randn(2, m, hkv * d, device="cuda", generator=g)

@@ -417,7 +417,7 @@ def test_decode_token_kernel_shapes_dependent_launch_and_graph_replay(ctx, dtype
         dq, dk, dv, dpos = to_dev(q), to_dev(kn), to_dev(vn), to_dev(pos)
         out = torch.zeros(n_layers, n_seqs, hq, d, device="cuda")
         rig.fwd.stream = stream.cuda_stream
-        for tune in ((4, 2), (4, 3), (8, 3), (0, 0)):
+        for tune in ((4, 1), (4, 2), (4, 3), (8, 1), (8, 3), (0, 0)):
             for mode in (0, 1, 2):
                 ctx.check(L.vfkv_ctx_set_attn_tuning(ctx.handle, *tune))
                 ctx.check(L.vfkv_ctx_set_dependent_launch(ctx.handle, mode))
