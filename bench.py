@@ -184,7 +184,7 @@ def run_reference(args, w, rank, world):
             layer_step(s * per_step + i)
     dt_s = time.perf_counter() - t0
     us = dt_s * 1e6 / (args.steps * per_step * b)
-    cores = oracle.num_threads()
+    cores = oracle.use_all_host_threads()
     sample = (f"{args.steps} steps x {per_step} layer-steps of {b} sequence(s) at the workload's shapes "
               f"({w['dtype']} cache, context {slab}), {cores} OpenMP threads")
     line = {"metric": METRIC, "value": us, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
@@ -231,7 +231,7 @@ def cpu_baseline_sample(w, budget_s=12.0):
         el = time.perf_counter() - t0
         if el > budget_s or n >= 20000:
             break
-    cores = oracle.num_threads()
+    cores = oracle.use_all_host_threads()
     return {"value": el * 1e6 / (n * b), "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{n} layer-steps of {b} sequence(s), {w['dtype']} cache, context {slab}, "
                       f"{cores} OpenMP threads, {el:.1f} s"}

@@ -84,6 +84,7 @@ def _declare(L: C.CDLL) -> None:
     L.vfo_decode_step.restype = None
     L.vfo_decode_step.argtypes = [vp, vp, vp, vp, vp, u32, u32, u64, u32, u32, u32, vp, vp, f32, f32, vp]
     L.vfo_num_threads.restype, L.vfo_num_threads.argtypes = C.c_int, []
+    L.vfo_set_num_threads.restype, L.vfo_set_num_threads.argtypes = None, [C.c_int]
 
 
 def _p(a):
@@ -245,6 +246,15 @@ def decode_step(q, k_new, v_new, k_slabs, v_slabs, dtype, n_seqs, slab_positions
 
 def num_threads() -> int:
     return int(lib().vfo_num_threads())
+
+
+def use_all_host_threads() -> int:
+    """Sets the OpenMP thread count to the CPUs this process may run on (launchers export
+    OMP_NUM_THREADS=1) and returns it."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().vfo_set_num_threads(n)
+    return num_threads()
 
 
 def batch_attention_ref(q, k, v, dtype, n_heads, n_kv_heads, head_dim, m, q_start, n_kv, kv_start=0,

@@ -26,6 +26,17 @@ int vfo_num_threads(void)
 #endif
 }
 
+/* Launchers such as torch.distributed.run export OMP_NUM_THREADS=1; a timed CPU run sets
+ * the count it wants explicitly. */
+void vfo_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* ===================================================================== */
 /* E4M3 ("FN": no Inf, one NaN code, max 448)                             */
 /* ===================================================================== */

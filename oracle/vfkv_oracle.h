@@ -113,6 +113,7 @@ void vfo_decode_step(const float *q, const float *k_new, const float *v_new,
                      float scale, float softcap, float *out);
 
 int vfo_num_threads(void);
+void vfo_set_num_threads(int n);
 
 #ifdef __cplusplus
 }
