@@ -113,3 +113,54 @@ def test_all_gather_of_partials_over_gloo_world2(tmp_path, seq_len, page):
     for r in range(2):
         err = float(np.load(tmp_path / f"err{r}.npy")[0])
         assert err < 1e-4, err
+
+
+class _FakeForward:
+    """Records the calls ShardedSequenceDecoder makes (no GPU): enough to check which rank
+    appends, which local range it attends over, and what it hands to the exchange."""
+
+    class _Cfg:
+        head_dim = 64
+
+    class _Cache:
+        pass
+
+    def __init__(self, n_heads=8):
+        self.n_heads = n_heads
+        self.kv_cache = self._Cache()
+        self.kv_cache.config = self._Cfg()
+        self.calls = []
+
+    def step_kv_write(self, layer, k, v, pos, slot):
+        self.calls.append(("append", layer, pos, slot))
+
+    def attend_exchange(self, exchange, layer, q, lo, hi, out, k_new=None, v_new=None):
+        self.calls.append(("attend_exchange", layer, lo, hi, k_new is not None, v_new is not None))
+
+
+def test_sharded_decoder_owner_logic_with_peer_exchange(monkeypatch):
+    """decode(): every rank attends over its local rows [0, local_len(position + 1)); only the
+    owner of the new position passes the new K/V rows to the (fused) call."""
+    import sys
+    import types
+    from vulkanforge_b200.shard import ShardedSequenceDecoder
+    fake_torch = types.SimpleNamespace(zeros=lambda *a, **k: None, float32=None)
+    monkeypatch.setitem(sys.modules, "torch", fake_torch)      # the decoder only allocates its packed buffer
+    world, page = 4, 256
+    sh = PositionShards(world, page)
+    for position in (0, 255, 256, 1023, 1024, 5000):
+        owners = 0
+        total = 0
+        for rank in range(world):
+            fwd = _FakeForward()
+            dec = ShardedSequenceDecoder(fwd, sh, rank, exchange=object())
+            dec.decode(3, "q", "k", "v", "out", position)
+            (name, layer, lo, hi, has_k, has_v), = fwd.calls
+            assert (name, layer, lo) == ("attend_exchange", 3, 0)
+            assert hi == sh.local_len(position + 1, rank)
+            assert has_k == has_v == (sh.owner(position) == rank)
+            if has_k:
+                owners += 1
+                assert hi - 1 == sh.local_pos(position)        # the new row is the last local row of its owner
+            total += hi
+        assert owners == 1 and total == position + 1
