@@ -117,9 +117,12 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     // its own.  No CTA gets more than 8192 positions, 4096 once contexts beyond 8192 are possible
     // (measured: 64 sequences of 512..16384 tokens 5.0 / 5.5 / 6.1 TB/s with 1 / 2 / 4 splits;
     // 64 x 8192 uniform 6.3 / 6.0 / 5.9 TB/s).
+    // The rule is for batches that fill the GPU by themselves; a single long sequence is better off
+    // with its 16 splits on 8-warp CTAs, one per SM (131 072 positions, 8 kv-heads: 46.3 us with
+    // 16 splits of 8 warps, 51.1 us with 32 splits of 4 warps).
     const uint64_t per_cta = max_len > 8192 ? 4096 : 8192;
     const uint64_t by_len = (uint64_t(max_len) + per_cta - 1) / per_cta;
-    if (want < by_len) want = by_len;
+    if (want < by_len && base >= slots) want = by_len;
     if (want > cap) want = cap;
     if (want < 1) want = 1;
     return uint32_t(want);

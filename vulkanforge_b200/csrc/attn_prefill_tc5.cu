@@ -487,6 +487,303 @@ __global__ void __launch_bounds__(256) prefill_tc5_kernel(const Tc5Params p)
 
 constexpr int kSmemBytes = 6 * TILE + 1024;
 
+// ---- pipelined form ---------------------------------------------------------------------------------
+// Same tiles and the same arithmetic as prefill_tc5_kernel, with the two warpgroups running as two
+// independent pipelines over the shared K/V tiles:
+//   * P stays in tensor memory (half precision, two values per column, over the first 64 columns
+//     of the warpgroup's S region) and is the A operand of O += P V straight from there; the two P
+//     tiles leave shared memory, which pays for a second K buffer and a second V buffer;
+//   * the K/V rows of tile it + 1 are fetched and widened by all threads while S of tile `it` is
+//     on the tensor pipe; "tile ready" is an mbarrier with 256 arrivals per buffer, "buffer free"
+//     is the completion of both warpgroups' P V products of the tile that used it;
+//   * each warpgroup's first thread issues that warpgroup's MMAs, so while one warpgroup computes
+//     its softmax the tensor pipe works for the other.
+// Barriers: 0,1 S complete (per Q tile)   2,3 P V complete   4,5 K/V buffer 0 / 1 ready.
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" :: "r"(bar) : "memory");
+}
+
+template <int DT, bool CAP>
+__global__ void __launch_bounds__(256, 1) prefill_tc5p_kernel(const Tc5Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_bar[6];
+    __shared__ uint32_t s_tmem, s_abort[2];                      // one give-up flag per warpgroup
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - smem_addr(smem_raw));
+    // shared memory: Q tile 0, Q tile 1, K buffers 0 1, V buffers 0 1
+    const uint32_t q_sm = base, k_sm = base + 2 * TILE, v_sm = base + 4 * TILE;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t wg = tid >> 7, t = tid & 127u;
+    const uint32_t bar_s = smem_addr(&s_bar[wg]), bar_o = smem_addr(&s_bar[2 + wg]);
+    const uint32_t kvh = blockIdx.y, g = p.group;
+    const uint32_t n_rows = p.m * g;
+    const uint32_t row0 = (gridDim.x - 1u - blockIdx.x) * CTA_ROWS;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mbar_init(smem_addr(&s_bar[i]), 1);
+        mbar_init(smem_addr(&s_bar[4]), 256);
+        mbar_init(smem_addr(&s_bar[5]), 256);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort[0] = 0u; s_abort[1] = 0u;
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_addr(&s_tmem)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+
+    const uint32_t r = row0 + wg * BM + t;
+    const bool r_ok = r < n_rows;
+    const uint32_t q_idx = r_ok ? r / g : 0u, hj = r_ok ? r % g : 0u;
+    uint32_t r_lo, r_hi;
+    query_range(p, q_idx, &r_lo, &r_hi);
+    if (!r_ok) { r_lo = 0u; r_hi = 0u; }
+    uint32_t c_lo, c_hi;
+    {
+        const uint32_t qa = row0 / g;
+        uint32_t qb = (row0 + CTA_ROWS - 1) / g;
+        if (qb >= p.m) qb = p.m - 1;
+        uint32_t lo_a, hi_a, lo_b, hi_b;
+        query_range(p, qa, &lo_a, &hi_a);
+        query_range(p, qb, &lo_b, &hi_b);
+        c_lo = lo_a / BN * BN;
+        c_hi = hi_b;
+    }
+    const uint32_t n_tiles = c_hi > c_lo ? (c_hi - c_lo + BN - 1) / BN : 0u;
+
+    const float qs = CAP ? p.scale : p.scale * kLog2e;
+    for (uint32_t i = tid; i < uint32_t(CTA_ROWS * 16); i += 256) {
+        const uint32_t row = i >> 4, c = i & 15u;
+        const uint32_t rr = row0 + row;
+        uint4 hv = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < n_rows) {
+            const float *qp = p.q + (uint64_t(rr / g) * p.n_q_heads + kvh * g + rr % g) * HD + 8 * c;
+            const float4 a = *reinterpret_cast<const float4 *>(qp), b = *reinterpret_cast<const float4 *>(qp + 4);
+            hv = make_uint4(pack_half2(a.x * qs, a.y * qs), pack_half2(a.z * qs, a.w * qs),
+                            pack_half2(b.x * qs, b.y * qs), pack_half2(b.z * qs, b.w * qs));
+        }
+        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) = hv;
+    }
+
+    constexpr uint32_t ES = DT == VFKV_F8 ? 1u : 2u;
+    constexpr int NP = DT == VFKV_F8 ? 4 : 8;                 // 16-byte pieces of K (and of V) per thread and tile
+    const uint8_t *kg = p.k + uint64_t(kvh) * HD * ES, *vg = p.v + uint64_t(kvh) * HD * ES;
+    auto fetch = [&](const uint8_t *src, uint32_t t0, uint4 (&raw)[NP]) {
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const uint32_t idx = tid + 256 * i;
+            const uint32_t pos = DT == VFKV_F8 ? idx >> 3 : idx >> 4, c = DT == VFKV_F8 ? idx & 7u : idx & 15u;
+            const bool ok = t0 + pos < p.n_kv;
+            const uint64_t off = uint64_t(ok ? t0 + pos : 0u) * p.row_bytes + c * 16;
+            raw[i] = ok ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    auto place = [&](const uint4 (&raw)[NP], uint32_t tile_sm) {
+        uint8_t *dst = sm + (tile_sm - base);
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+            const uint32_t idx = tid + 256 * i;
+            if constexpr (DT == VFKV_F8) {
+                const uint32_t pos = idx >> 3, c16 = idx & 7u;
+                const uint4 x = raw[i];
+                __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
+                __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
+                __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
+                __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
+                *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
+                    make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                               *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
+                    make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
+                               *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+            } else {
+                *reinterpret_cast<uint4 *>(dst + tile_off(idx >> 4, idx & 15u)) = raw[i];
+            }
+        }
+    };
+
+    // tile 0 into buffer 0
+    if (n_tiles > 0) {
+        uint4 raw[NP];
+        fetch(kg, c_lo, raw);
+        place(raw, k_sm);
+        fetch(vg, c_lo, raw);
+        place(raw, v_sm);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(smem_addr(&s_bar[4]));
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    const uint32_t t_lane = ((warp & 3u) * 32u) << 16;
+    const uint32_t tm_s = tmem + wg * 128u, tm_o = tmem + 256u + wg * 128u;
+    volatile uint32_t *abort_flag = &s_abort[wg];            // written and read by this warpgroup only
+
+    float mref = kMaskedScore, lrow = 0.f;
+    bool gave_up = false;
+    for (uint32_t it = 0; it < n_tiles; ++it) {
+        const uint32_t t0 = c_lo + it * BN, b = it & 1u, par = it & 1u;
+        const bool more = it + 1 < n_tiles;
+        // ---- 1. S = Q K^T of this warpgroup's Q tile.  Its region of tensor memory still holds
+        //         P of the previous tile until that tile's P V product is complete.
+        TC5_TRACE(0);
+        if (it > 0 && !mbar_wait(bar_o, par ^ 1u)) gave_up = true;
+        TC5_TRACE(1);
+        if (t == 0) {
+            if (!mbar_wait(smem_addr(&s_bar[4 + b]), (it >> 1) & 1u)) gave_up = true;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                umma_f16(tm_s, smem_desc(q_sm + wg * TILE + o, 16, 1024), smem_desc(k_sm + b * TILE + o, 16, 1024),
+                         idesc_f16(false), ks);
+            }
+            umma_commit(bar_s);
+        }
+        TC5_TRACE(2);
+        // ---- 2. K/V rows of the next tile into the other buffer, free once both warpgroups' P V
+        //         products of tile it - 1 are complete (this warpgroup's was waited for above).
+        if (more) {
+            uint4 raw[NP];
+            fetch(kg, t0 + BN, raw);
+            if (it > 0 && !mbar_wait(smem_addr(&s_bar[2 + (wg ^ 1u)]), par ^ 1u)) gave_up = true;
+            place(raw, k_sm + (b ^ 1u) * TILE);
+            fetch(vg, t0 + BN, raw);
+            place(raw, v_sm + (b ^ 1u) * TILE);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_addr(&s_bar[4 + (b ^ 1u)]));
+        }
+        TC5_TRACE(3);
+        // ---- 3. this thread's row of S: mask, softmax against the reference maximum, P -> tensor memory
+        if (!mbar_wait(bar_s, par)) gave_up = true;
+        TC5_TRACE(4);
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool full = t0 >= r_lo && t0 + BN <= r_hi;
+        float s[BN];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32_nowait(tm_s + t_lane + 32 * c, &s[32 * c]);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const bool warp_full = __all_sync(0xffffffffu, full);
+        float mx = kMaskedScore;
+        if (warp_full && !CAP) {
+#pragma unroll
+            for (int j = 0; j < BN; j += 2) mx = fmaxf(mx, fmaxf(s[j], s[j + 1]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < BN; ++j) {
+                float x = s[j];
+                if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap) * kLog2e;
+                if (!full) {
+                    const uint32_t pos = t0 + j;
+                    if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
+                }
+                s[j] = x;
+                mx = fmaxf(mx, x);
+            }
+        }
+        const bool grow = mx > mref + 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+            const float mnew = grow ? mx : mref;
+            const float alpha = fast_exp2(mref - mnew);
+            lrow *= alpha;
+            mref = mnew;
+            if (it > 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float o[32];
+                    tmem_ld32_nowait(tm_o + t_lane + 32 * c, o);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= alpha;
+                    tmem_st32(tm_o + t_lane + 32 * c, o);
+                }
+            }
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {                         // 64 positions = 32 packed columns per store
+            float pk[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float x0 = s[64 * c + 2 * j], x1 = s[64 * c + 2 * j + 1];
+                float p0 = fast_exp2(x0 - mref), p1 = fast_exp2(x1 - mref);
+                if (!warp_full) {
+                    p0 = x0 > 0.5f * kMaskedScore ? p0 : 0.f;
+                    p1 = x1 > 0.5f * kMaskedScore ? p1 : 0.f;
+                }
+                sum += p0 + p1;
+                pk[j] = __uint_as_float(pack_half2(p0, p1));   // position 2j in the low half
+            }
+            tmem_st32(tm_s + t_lane + 32 * c, pk);
+        }
+        lrow += sum;
+        TC5_TRACE(5);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (gave_up) *abort_flag = 1u;
+        asm volatile("bar.sync %0, 128;" :: "r"(1u + wg) : "memory");      // this warpgroup only
+        TC5_TRACE(6);
+        if (*abort_flag) break;                                            // the same value for the whole warpgroup
+        // ---- 4. O += P V: A from tensor memory (16 positions = 8 columns per step), B = V rows (MN-major)
+        if (t == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (uint32_t kk = 0; kk < BN / 16; ++kk)
+                umma_f16_ts(tm_o, tm_s + kk * 8u, smem_desc(v_sm + b * TILE + kk * 2048, SLAB, 1024), idesc_f16(true),
+                            (it | kk) != 0u ? 1u : 0u);
+            umma_commit(bar_o);
+        }
+        TC5_TRACE(7);
+    }
+    const bool ran = n_tiles > 0 && *abort_flag == 0u;
+    if (ran) {
+        if (!mbar_wait(bar_o, (n_tiles - 1u) & 1u)) *abort_flag = 1u;
+        __syncwarp();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    const bool failed = (s_abort[0] | s_abort[1]) != 0u;
+    if (failed && tid == 0) atomicOr(p.status, 1u);
+    {
+        const float inv = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
+        float *o = p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float v[32];
+            if (ran && !failed) {
+                tmem_ld32_nowait(tm_o + t_lane + 32 * c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            }
+            if (r_ok) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(o + 32 * c + j) =
+                        make_float4(inv > 0.f ? v[j] * inv : 0.f, inv > 0.f ? v[j + 1] * inv : 0.f,
+                                    inv > 0.f ? v[j + 2] * inv : 0.f, inv > 0.f ? v[j + 3] * inv : 0.f);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "n"(TMEM_COLS) : "memory");
+    }
+}
+
 }  // namespace
 
 bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales)
@@ -519,6 +816,29 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
     }
     const dim3 grid((m * p.group + CTA_ROWS - 1) / CTA_ROWS, n_kv_heads);
     const bool cap = softcap > 0.f;
+    if (ctx->tune_stages != 1) {          // the pipelined form; vfkv_ctx_set_attn_tuning(ctx, 4, 1) keeps the simple one
+        static bool configured_p[64] = {};
+        if (!configured_p[ctx->device & 63]) {
+            const void *kernels[4] = {reinterpret_cast<const void *>(prefill_tc5p_kernel<VFKV_F8, false>),
+                                      reinterpret_cast<const void *>(prefill_tc5p_kernel<VFKV_F8, true>),
+                                      reinterpret_cast<const void *>(prefill_tc5p_kernel<VFKV_F16, false>),
+                                      reinterpret_cast<const void *>(prefill_tc5p_kernel<VFKV_F16, true>)};
+            for (const void *kn : kernels) {
+                cudaError_t e = cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+                if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tcgen05 prefill attention)");
+            }
+            configured_p[ctx->device & 63] = true;
+        }
+        if (dtype == VFKV_F8) {
+            if (cap) prefill_tc5p_kernel<VFKV_F8, true><<<grid, 256, kSmemBytes, st>>>(p);
+            else prefill_tc5p_kernel<VFKV_F8, false><<<grid, 256, kSmemBytes, st>>>(p);
+        } else {
+            if (cap) prefill_tc5p_kernel<VFKV_F16, true><<<grid, 256, kSmemBytes, st>>>(p);
+            else prefill_tc5p_kernel<VFKV_F16, false><<<grid, 256, kSmemBytes, st>>>(p);
+        }
+        ctx->launches++;
+        return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
+    }
     if (dtype == VFKV_F8) {
         if (cap) prefill_tc5_kernel<VFKV_F8, true><<<grid, 256, kSmemBytes, st>>>(p);
         else prefill_tc5_kernel<VFKV_F8, false><<<grid, 256, kSmemBytes, st>>>(p);
