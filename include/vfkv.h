@@ -302,7 +302,11 @@ int32_t vfkv_decode_token(vfkv_cache *cache, vfkv_workspace *ws, const float *d_
  * h_positions / h_slot_ids (NULL = identity) are host arrays of n_seqs.
  * windows: NULL, or n_layers entries (0 = global layer).  This is the
  * forward_token boundary (src/backend/vulkan/forward/decode.rs:567-626) reduced
- * to the hot path. */
+ * to the hot path.  On a non-default stream the layers run as up to four cached
+ * CUDA graphs, and a second stream owned by the workspace copies the next
+ * group's inputs and the previous group's outputs while a group computes; the
+ * call returns when h_out is complete.  Pinned host buffers make the copies
+ * asynchronous. */
 int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const float *h_q,
                                const float *h_k, const float *h_v, float *h_out,
                                uint32_t n_q_heads, const uint32_t *h_slot_ids,

@@ -472,7 +472,11 @@ int32_t vfkv_workspace_destroy(vfkv_workspace *ws)
     DeviceGuard g(ws->ctx->device);
     cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->counters);
     cudaFree(ws->stage_in); cudaFree(ws->stage_out);
-    if (ws->tok_graph) cudaGraphExecDestroy(ws->tok_graph);
+    for (auto gexec : ws->tok_graphs)
+        if (gexec) cudaGraphExecDestroy(gexec);
+    for (auto ev : ws->tok_events)
+        if (ev) cudaEventDestroy(ev);
+    if (ws->copy_stream) cudaStreamDestroy(ws->copy_stream);
     delete ws;
     return VFKV_OK;
 }
@@ -704,68 +708,117 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
     }
     float *dq = ws->stage_in, *dk = dq + q_elems, *dv = dk + kv_elems;
     uint32_t *d_pos = ws->d_u32, *d_slots = ws->d_u32 + ws->max_seqs;
-    cudaError_t e = cudaMemcpyAsync(dq, h_q, q_elems * 4, cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dk, h_k, kv_elems * 4, cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dv, h_v, kv_elems * 4, cudaMemcpyHostToDevice, st);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(d_pos, h_positions, n_seqs * 4, cudaMemcpyHostToDevice, st);
+    cudaError_t e = cudaMemcpyAsync(d_pos, h_positions, n_seqs * 4, cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess && h_slot_ids) e = cudaMemcpyAsync(d_slots, h_slot_ids, n_seqs * 4, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host: H2D");
-    {
-        // The launches of one token depend on the host only through the configuration below
-        // (positions and slots are device-side inputs; the length hint is rounded up so that it
-        // changes rarely): capture them once, replay afterwards.
-        uint32_t hint = (max_pos + 1 + 1023u) / 1024u * 1024u;
-        if (hint > kv.config.max_seq_len) hint = kv.config.max_seq_len;
-        uint64_t wh = 1469598103934665603ull;
-        auto mix = [&](uint64_t x) { wh = (wh ^ x) * 1099511628211ull; };
-        for (uint32_t l = 0; windows && l < L; ++l) mix(windows[l]);
-        // a cache object re-created at the same address must not find the old graph
-        mix(reinterpret_cast<uint64_t>(kv.k_buffer)); mix(reinterpret_cast<uint64_t>(kv.v_buffer));
-        mix(L); mix(D); mix(Hkv); mix(uint64_t(kv.kv_dtype)); mix(kv.config.max_seq_len); mix(kv.config.n_slots);
-        mix(reinterpret_cast<uint64_t>(ws->part_o)); mix(reinterpret_cast<uint64_t>(dk));
-        uint32_t fs, fc;
-        memcpy(&fs, &scale, 4); memcpy(&fc, &softcap, 4);
-        const uint64_t key[8] = {reinterpret_cast<uint64_t>(cache), reinterpret_cast<uint64_t>(dq),
-                                 reinterpret_cast<uint64_t>(ws->stage_out),
-                                 uint64_t(n_q_heads) << 32 | n_seqs, uint64_t(hint) << 32 | n_splits,
-                                 uint64_t(fs) << 32 | fc, wh ^ (h_slot_ids ? 1u : 0u),
-                                 uint64_t(ctx->pdl) | uint64_t(ctx->tune_warps) << 8 | uint64_t(ctx->tune_stages) << 16 |
-                                     uint64_t(ctx->attn_impl) << 24 | uint64_t(ctx->cluster_merge) << 32 |
-                                     uint64_t(reinterpret_cast<uintptr_t>(st) & 0xffffffu) << 40};
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(st, &cap);
-        const bool graphable = cap == cudaStreamCaptureStatusNone && !ctx->profiling && !ctx->d_trace && st != nullptr;
-        if (graphable && (!ws->tok_graph || memcmp(key, ws->tok_key, sizeof(key)) != 0)) {
-            if (ws->tok_graph) { cudaGraphExecDestroy(ws->tok_graph); ws->tok_graph = nullptr; }
-            cudaGraph_t graph = nullptr;
-            if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-                const uint64_t launches = ctx->launches;
-                int32_t rc = vfkv_decode_token(cache, ws, dq, dk, dv, ws->stage_out, n_q_heads,
-                                               h_slot_ids ? d_slots : nullptr, d_pos, n_seqs, hint, windows, scale,
-                                               softcap, n_splits, stream);
-                cudaError_t ce = cudaStreamEndCapture(st, &graph);
-                ctx->launches = launches;                       // recorded, not run
-                if (rc == VFKV_OK && ce == cudaSuccess && graph &&
-                    cudaGraphInstantiate(&ws->tok_graph, graph, 0) == cudaSuccess)
-                    memcpy(ws->tok_key, key, sizeof(key));
-                else
-                    ws->tok_graph = nullptr;
-                if (graph) cudaGraphDestroy(graph);
-                cudaGetLastError();
-                if (rc) return rc;
-            }
-        }
-        if (graphable && ws->tok_graph) {
-            e = cudaGraphLaunch(ws->tok_graph, st);
-            if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host: graph launch");
-            ctx->launches += L;
-        } else {
-            int32_t rc = vfkv_decode_token(cache, ws, dq, dk, dv, ws->stage_out, n_q_heads,
-                                           h_slot_ids ? d_slots : nullptr, d_pos, n_seqs, max_pos + 1, windows, scale,
-                                           softcap, n_splits, stream);
+    const uint64_t q_stride = uint64_t(n_seqs) * n_q_heads * D, kv_stride = uint64_t(n_seqs) * Hkv * D;
+    // The launches of one token depend on the host only through the configuration below
+    // (positions and slots are device-side inputs; the length hint is rounded up so that it
+    // changes rarely): capture them once, replay afterwards.
+    uint32_t hint = (max_pos + 1 + 1023u) / 1024u * 1024u;
+    if (hint > kv.config.max_seq_len) hint = kv.config.max_seq_len;
+    uint64_t wh = 1469598103934665603ull;
+    auto mix = [&](uint64_t x) { wh = (wh ^ x) * 1099511628211ull; };
+    for (uint32_t l = 0; windows && l < L; ++l) mix(windows[l]);
+    // a cache object re-created at the same address must not find the old graphs
+    mix(reinterpret_cast<uint64_t>(kv.k_buffer)); mix(reinterpret_cast<uint64_t>(kv.v_buffer));
+    mix(L); mix(D); mix(Hkv); mix(uint64_t(kv.kv_dtype)); mix(kv.config.max_seq_len); mix(kv.config.n_slots);
+    mix(reinterpret_cast<uint64_t>(ws->part_o)); mix(reinterpret_cast<uint64_t>(dk));
+    uint32_t fs, fc;
+    memcpy(&fs, &scale, 4); memcpy(&fc, &softcap, 4);
+    const uint64_t key[8] = {reinterpret_cast<uint64_t>(cache), reinterpret_cast<uint64_t>(dq),
+                             reinterpret_cast<uint64_t>(ws->stage_out),
+                             uint64_t(n_q_heads) << 32 | n_seqs, uint64_t(hint) << 32 | n_splits,
+                             uint64_t(fs) << 32 | fc, wh ^ (h_slot_ids ? 1u : 0u),
+                             uint64_t(ctx->pdl) | uint64_t(ctx->tune_warps) << 8 | uint64_t(ctx->tune_stages) << 16 |
+                                 uint64_t(ctx->attn_impl) << 24 | uint64_t(ctx->cluster_merge) << 32 |
+                                 uint64_t(reinterpret_cast<uintptr_t>(st) & 0xffffffu) << 40};
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cap);
+    bool graphable = cap == cudaStreamCaptureStatusNone && !ctx->profiling && !ctx->d_trace && st != nullptr;
+    // The layers are cut into up to four groups, one graph each: the inputs of group c + 1 cross
+    // the bus on a second stream while group c computes, and the outputs of group c go back while
+    // group c + 1 computes.  Only the first group's inputs and the last group's outputs are exposed.
+    const uint32_t n_chunks = L < vfkv_workspace::kTokChunks ? L : vfkv_workspace::kTokChunks;
+    auto chunk_begin = [&](uint32_t c) { return uint32_t(uint64_t(L) * c / n_chunks); };
+    auto run_layers = [&](uint32_t l0, uint32_t l1, uint32_t len_hint) -> int32_t {
+        for (uint32_t l = l0; l < l1; ++l) {
+            int32_t rc = vfkv_decode_step(cache, ws, l, dq + l * q_stride, dk + l * kv_stride, dv + l * kv_stride,
+                                          ws->stage_out + l * q_stride, n_q_heads, h_slot_ids ? d_slots : nullptr,
+                                          d_pos, n_seqs, len_hint, windows ? windows[l] : 0, scale, softcap,
+                                          n_splits, stream);
             if (rc) return rc;
         }
+        return VFKV_OK;
+    };
+    if (graphable && !ws->copy_stream) {
+        bool ok = cudaStreamCreateWithFlags(&ws->copy_stream, cudaStreamNonBlocking) == cudaSuccess;
+        for (uint32_t i = 0; ok && i < 2 * vfkv_workspace::kTokChunks + 2; ++i)
+            ok = cudaEventCreateWithFlags(&ws->tok_events[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) { cudaGetLastError(); graphable = false; }
     }
+    if (graphable && (!ws->tok_graphs[0] || memcmp(key, ws->tok_key, sizeof(key)) != 0)) {
+        for (auto &gexec : ws->tok_graphs)
+            if (gexec) { cudaGraphExecDestroy(gexec); gexec = nullptr; }
+        for (uint32_t c = 0; c < n_chunks; ++c) {
+            cudaGraph_t graph = nullptr;
+            if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); break; }
+            const uint64_t launches = ctx->launches;
+            int32_t rc = run_layers(chunk_begin(c), chunk_begin(c + 1), hint);
+            cudaError_t ce = cudaStreamEndCapture(st, &graph);
+            ctx->launches = launches;                           // recorded, not run
+            const bool ok = rc == VFKV_OK && ce == cudaSuccess && graph &&
+                            cudaGraphInstantiate(&ws->tok_graphs[c], graph, 0) == cudaSuccess;
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            if (rc) return rc;
+            if (!ok) { ws->tok_graphs[c] = nullptr; break; }
+        }
+        bool all = true;
+        for (uint32_t c = 0; c < n_chunks; ++c) all = all && ws->tok_graphs[c];
+        if (all) memcpy(ws->tok_key, key, sizeof(key));
+        else {
+            for (auto &gexec : ws->tok_graphs)
+                if (gexec) { cudaGraphExecDestroy(gexec); gexec = nullptr; }
+        }
+    }
+    if (graphable && ws->tok_graphs[0]) {
+        cudaStream_t cs = ws->copy_stream;
+        cudaEvent_t *ev_in = ws->tok_events, *ev_done = ws->tok_events + vfkv_workspace::kTokChunks;
+        cudaEvent_t ev_start = ws->tok_events[2 * vfkv_workspace::kTokChunks], ev_end = ws->tok_events[2 * vfkv_workspace::kTokChunks + 1];
+        // the copies start behind whatever the caller queued on its stream
+        e = cudaEventRecord(ev_start, st);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, ev_start, 0);
+        for (uint32_t c = 0; c < n_chunks && e == cudaSuccess; ++c) {
+            const uint32_t l0 = chunk_begin(c), nl = chunk_begin(c + 1) - l0;
+            e = cudaMemcpyAsync(dq + l0 * q_stride, h_q + l0 * q_stride, nl * q_stride * 4, cudaMemcpyHostToDevice, cs);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(dk + l0 * kv_stride, h_k + l0 * kv_stride, nl * kv_stride * 4, cudaMemcpyHostToDevice, cs);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(dv + l0 * kv_stride, h_v + l0 * kv_stride, nl * kv_stride * 4, cudaMemcpyHostToDevice, cs);
+            if (e == cudaSuccess) e = cudaEventRecord(ev_in[c], cs);
+        }
+        for (uint32_t c = 0; c < n_chunks && e == cudaSuccess; ++c) {
+            const uint32_t l0 = chunk_begin(c), nl = chunk_begin(c + 1) - l0;
+            e = cudaStreamWaitEvent(st, ev_in[c], 0);
+            if (e == cudaSuccess) e = cudaGraphLaunch(ws->tok_graphs[c], st);
+            if (e == cudaSuccess) e = cudaEventRecord(ev_done[c], st);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, ev_done[c], 0);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h_out + l0 * q_stride, ws->stage_out + l0 * q_stride, nl * q_stride * 4, cudaMemcpyDeviceToHost, cs);
+            if (e == cudaSuccess) ctx->launches += nl;
+        }
+        // both streams are joined and drained even after an error, so that nothing is left in flight
+        cudaError_t e2 = cudaEventRecord(ev_end, cs);
+        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, ev_end, 0);
+        cudaError_t e3 = cudaStreamSynchronize(st);
+        if (e2 != cudaSuccess) cudaStreamSynchronize(cs);
+        if (e == cudaSuccess) e = e2 != cudaSuccess ? e2 : e3;
+        return check_cuda(ctx, e, "vfkv_decode_token_host: pipelined step");
+    }
+    // stream order only (inside a capture, under the profiler or with the phase trace on)
+    e = cudaMemcpyAsync(dq, h_q, q_elems * 4, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dk, h_k, kv_elems * 4, cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dv, h_v, kv_elems * 4, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host: H2D");
+    if (int32_t rc = run_layers(0, L, max_pos + 1)) return rc;
     e = cudaMemcpyAsync(h_out, ws->stage_out, out_bytes, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     return check_cuda(ctx, e, "vfkv_decode_token_host: D2H");

@@ -56,8 +56,13 @@ struct vfkv_workspace {
     uint64_t stage_in_bytes = 0, stage_out_bytes = 0;
     // vfkv_decode_token_host: the kernel sequence of one token, captured once per configuration and
     // replayed (the analogue of the reference's pre-recorded command buffers, forward/decode.rs:169-259)
-    cudaGraphExec_t tok_graph = nullptr;
+    // The layers form up to kTokChunks groups with one graph each, so that a second stream moves the
+    // next group's inputs and the previous group's outputs while a group computes.
+    static constexpr uint32_t kTokChunks = 4;
+    cudaGraphExec_t tok_graphs[kTokChunks] = {nullptr, nullptr, nullptr, nullptr};
     uint64_t tok_key[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t tok_events[2 * kTokChunks + 2] = {};     // inputs there / group done, per group; start; copies done
 };
 
 namespace vfkv {
