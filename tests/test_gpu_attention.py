@@ -333,12 +333,14 @@ def test_decode_token_host_all_layers(ctx, impl):
         rig.close()
 
 
-def test_decode_token_host_replays_a_graph_over_several_tokens(ctx):
+@pytest.mark.parametrize("n_layers", [2, 9])
+def test_decode_token_host_replays_a_graph_over_several_tokens(ctx, n_layers):
     """On a real stream the host-buffer entry point captures one token's launches once and replays
     them: successive tokens (positions advancing across a 1024 boundary, where the length hint and
-    so the graph change) must each append and attend correctly."""
+    so the graphs change) must each append and attend correctly.  Nine layers form four uneven
+    groups (2, 2, 2, 3) whose copies run on the workspace's second stream."""
     import torch
-    hq, hkv, d, max_seq, n_layers, n_seqs = 32, 8, 128, 1100, 2, 2
+    hq, hkv, d, max_seq, n_seqs = 32, 8, 128, 1100, 2
     rng = np.random.default_rng(62)
     rig = Rig(ctx, vf.KvDtype.F8, hq, hkv, d, max_seq, n_layers=n_layers, n_slots=n_seqs)
     stream = torch.cuda.Stream()
