@@ -397,17 +397,31 @@ def next_rows(ctx, args, peak, tensor_peak):
 
         us_attn = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 10)
         us_rope = timed(lambda: fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0), 20)
+        # the same launches replayed from a CUDA graph: device time without the host's call overhead
+        side = torch.cuda.Stream()
+        fwd.stream = side.cuda_stream
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(20):
+                fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0)
+        fwd.stream = None
+        us_rope_graph = timed(graph.replay, 5) / 20
         flops = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2)              # causal: query i sees q_start + i + 1 rows
         rope_bytes = 2 * 512 * hkv * d * (4 + 1)                             # f32 in, one byte out, K and V
         tf = flops / (us_attn * 1e-6) / 1e12
-        gbs = rope_bytes / (us_rope * 1e-6) / 1e9
+        gbs = rope_bytes / (us_rope_graph * 1e-6) / 1e9                      # device time: the graph replay
         return {"prefill_attention": {"workload": "2048 queries at positions 14336..16383, FP8 cache, 32/8/128",
                                       "us": us_attn, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
                                       "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None,
                                       "note": "tcgen05.mma kernel, S and O in tensor memory"},
                 "rope_append": {"workload": "512 tokens x 8 kv-heads x 128, FP8 cache, K rotated", "us": us_rope,
+                                "us_in_graph": us_rope_graph,
                                 "bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak,
-                                "note": "5 MiB per launch: launch latency, not bandwidth, sets the time"}}
+                                "note": "5 MiB per launch: launch latency, not bandwidth, sets the time; "
+                                        "us = one library call per launch from Python, us_in_graph = graph replay"}}
     finally:
         fwd.workspace.destroy()
         cache.destroy()

@@ -68,6 +68,15 @@ __device__ __forceinline__ void rotate_piece(const float *__restrict__ x, uint32
     }
     const bool upper = d0 >= half;
     const uint32_t i0 = upper ? d0 - half : d0;
+    // both halves of the pairs as 16-byte loads (x, i0 and half are multiples of four elements)
+    float lo[E], hi[E];
+#pragma unroll
+    for (int j = 0; j < E; j += 4) {
+        const float4 u = __ldg(reinterpret_cast<const float4 *>(x + i0 + j));
+        const float4 w = __ldg(reinterpret_cast<const float4 *>(x + i0 + half + j));
+        lo[j] = u.x; lo[j + 1] = u.y; lo[j + 2] = u.z; lo[j + 3] = u.w;
+        hi[j] = w.x; hi[j + 1] = w.y; hi[j + 2] = w.z; hi[j + 3] = w.w;
+    }
     float freq = 1.0f;
     for (uint32_t i = 0; i < i0; ++i) freq = __fmul_rn(freq, theta_scale);
 #pragma unroll
@@ -75,7 +84,7 @@ __device__ __forceinline__ void rotate_piece(const float *__restrict__ x, uint32
         const float theta = __fmul_rn(pos_f, freq);
         float s, c;
         sincosf(theta, &s, &c);
-        const float a = x[i0 + j], b = x[i0 + j + half];
+        const float a = lo[j], b = hi[j];
         // (x_i, x_{i+half}) <- (a c - b s, a s + b c), products rounded separately as on the CPU
         out[j] = upper ? __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c)) : __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
         freq = __fmul_rn(freq, theta_scale);
