@@ -753,7 +753,7 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
     };
     if (graphable && !ws->copy_stream) {
         bool ok = cudaStreamCreateWithFlags(&ws->copy_stream, cudaStreamNonBlocking) == cudaSuccess;
-        for (uint32_t i = 0; ok && i < 2 * vfkv_workspace::kTokChunks + 2; ++i)
+        for (uint32_t i = 0; ok && i < 2 * vfkv_workspace::kTokChunks; ++i)
             ok = cudaEventCreateWithFlags(&ws->tok_events[i], cudaEventDisableTiming) == cudaSuccess;
         if (!ok) { cudaGetLastError(); graphable = false; }
     }
@@ -785,31 +785,35 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
     if (graphable && ws->tok_graphs[0]) {
         cudaStream_t cs = ws->copy_stream;
         cudaEvent_t *ev_in = ws->tok_events, *ev_done = ws->tok_events + vfkv_workspace::kTokChunks;
-        cudaEvent_t ev_start = ws->tok_events[2 * vfkv_workspace::kTokChunks], ev_end = ws->tok_events[2 * vfkv_workspace::kTokChunks + 1];
-        // the copies start behind whatever the caller queued on its stream
-        e = cudaEventRecord(ev_start, st);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, ev_start, 0);
-        for (uint32_t c = 0; c < n_chunks && e == cudaSuccess; ++c) {
+        // The staging buffers belong to the workspace and every earlier call drained both streams,
+        // so the first copies need not wait for the caller's stream.  Each group's launch is issued
+        // as soon as its own copies are queued: the host calls for the later groups then run while
+        // the first group computes.  On the copy stream the order is in(0) in(1) out(0) in(2) out(1)
+        // ..., so an input copy never waits for a group that has not started.
+        auto copy_in = [&](uint32_t c) {
             const uint32_t l0 = chunk_begin(c), nl = chunk_begin(c + 1) - l0;
-            e = cudaMemcpyAsync(dq + l0 * q_stride, h_q + l0 * q_stride, nl * q_stride * 4, cudaMemcpyHostToDevice, cs);
-            if (e == cudaSuccess) e = cudaMemcpyAsync(dk + l0 * kv_stride, h_k + l0 * kv_stride, nl * kv_stride * 4, cudaMemcpyHostToDevice, cs);
-            if (e == cudaSuccess) e = cudaMemcpyAsync(dv + l0 * kv_stride, h_v + l0 * kv_stride, nl * kv_stride * 4, cudaMemcpyHostToDevice, cs);
-            if (e == cudaSuccess) e = cudaEventRecord(ev_in[c], cs);
-        }
+            cudaError_t ce = cudaMemcpyAsync(dq + l0 * q_stride, h_q + l0 * q_stride, nl * q_stride * 4, cudaMemcpyHostToDevice, cs);
+            if (ce == cudaSuccess) ce = cudaMemcpyAsync(dk + l0 * kv_stride, h_k + l0 * kv_stride, nl * kv_stride * 4, cudaMemcpyHostToDevice, cs);
+            if (ce == cudaSuccess) ce = cudaMemcpyAsync(dv + l0 * kv_stride, h_v + l0 * kv_stride, nl * kv_stride * 4, cudaMemcpyHostToDevice, cs);
+            if (ce == cudaSuccess) ce = cudaEventRecord(ev_in[c], cs);
+            return ce;
+        };
+        e = copy_in(0);
         for (uint32_t c = 0; c < n_chunks && e == cudaSuccess; ++c) {
             const uint32_t l0 = chunk_begin(c), nl = chunk_begin(c + 1) - l0;
             e = cudaStreamWaitEvent(st, ev_in[c], 0);
             if (e == cudaSuccess) e = cudaGraphLaunch(ws->tok_graphs[c], st);
             if (e == cudaSuccess) e = cudaEventRecord(ev_done[c], st);
+            if (e == cudaSuccess) ctx->launches += nl;
+            if (e == cudaSuccess && c + 1 < n_chunks) e = copy_in(c + 1);
             if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, ev_done[c], 0);
             if (e == cudaSuccess) e = cudaMemcpyAsync(h_out + l0 * q_stride, ws->stage_out + l0 * q_stride, nl * q_stride * 4, cudaMemcpyDeviceToHost, cs);
-            if (e == cudaSuccess) ctx->launches += nl;
         }
-        // both streams are joined and drained even after an error, so that nothing is left in flight
-        cudaError_t e2 = cudaEventRecord(ev_end, cs);
-        if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(st, ev_end, 0);
+        // The last output copy follows the last group, so the copy stream finishing means the step
+        // is complete; the caller's stream is drained as well, also after an error, so that
+        // nothing of this call is left in flight.
+        cudaError_t e2 = cudaStreamSynchronize(cs);
         cudaError_t e3 = cudaStreamSynchronize(st);
-        if (e2 != cudaSuccess) cudaStreamSynchronize(cs);
         if (e == cudaSuccess) e = e2 != cudaSuccess ? e2 : e3;
         return check_cuda(ctx, e, "vfkv_decode_token_host: pipelined step");
     }

@@ -62,7 +62,7 @@ struct vfkv_workspace {
     cudaGraphExec_t tok_graphs[kTokChunks] = {nullptr, nullptr, nullptr, nullptr};
     uint64_t tok_key[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     cudaStream_t copy_stream = nullptr;
-    cudaEvent_t tok_events[2 * kTokChunks + 2] = {};     // inputs there / group done, per group; start; copies done
+    cudaEvent_t tok_events[2 * kTokChunks] = {};         // inputs there / group done, per group
 };
 
 namespace vfkv {
