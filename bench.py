@@ -147,6 +147,7 @@ def run_reference(args, w, rank, world):
     if rank != 0:
         return
     import oracle
+    cores = oracle.use_all_host_threads()           # before anything is timed: launchers export OMP_NUM_THREADS=1
     dt = DT[w["dtype"]]
     rng = np.random.default_rng(1234)
     lens = make_lens(w, rng)
@@ -184,7 +185,6 @@ def run_reference(args, w, rank, world):
             layer_step(s * per_step + i)
     dt_s = time.perf_counter() - t0
     us = dt_s * 1e6 / (args.steps * per_step * b)
-    cores = oracle.use_all_host_threads()
     sample = (f"{args.steps} steps x {per_step} layer-steps of {b} sequence(s) at the workload's shapes "
               f"({w['dtype']} cache, context {slab}), {cores} OpenMP threads")
     line = {"metric": METRIC, "value": us, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
@@ -207,6 +207,7 @@ def make_lens(w, rng):
 def cpu_baseline_sample(w, budget_s=12.0):
     """Oracle timing on the host cores for the JSON line's cpu_baseline object."""
     import oracle
+    cores = oracle.use_all_host_threads()           # before anything is timed
     dt = DT[w["dtype"]]
     rng = np.random.default_rng(99)
     b = min(w["batch"], 4)
@@ -231,7 +232,6 @@ def cpu_baseline_sample(w, budget_s=12.0):
         el = time.perf_counter() - t0
         if el > budget_s or n >= 20000:
             break
-    cores = oracle.use_all_host_threads()
     return {"value": el * 1e6 / (n * b), "unit": UNIT, "cores": cores, "kind": "port",
             "sample": f"{n} layer-steps of {b} sequence(s), {w['dtype']} cache, context {slab}, "
                       f"{cores} OpenMP threads, {el:.1f} s"}
