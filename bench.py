@@ -657,14 +657,6 @@ def run_position_sharded(args, w, rank, world, local_rank):
         with torch.cuda.graph(graph, stream=stream):
             step()
         run, launch_kind = graph.replay, "one CUDA graph replay per token"
-    elif args.graph_collective:
-        try:                                               # the whole step, collective included, as one graph
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step()
-            run, launch_kind = graph.replay, "one CUDA graph replay per token (NCCL all-gather captured)"
-        except Exception as exc:                           # capture of the collective refused: plain launches
-            launch_kind = f"stream launches (graph capture failed: {type(exc).__name__})"
     barrier()
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
@@ -734,9 +726,6 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="position-sharded mode: how the per-GPU partials travel (peer stores fused into the "
                          "attention kernel, or an NCCL all-gather)")
-    ap.add_argument("--graph-collective", action="store_true",
-                    help="position-sharded mode: capture the step, NCCL all-gather included, in one CUDA graph "
-                         "(off by default: a 2-GPU run with it did not finish)")
     ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch mode of the attention kernel (vfkv_ctx_set_dependent_launch)")

@@ -4,8 +4,8 @@
  * split-K GQA decode attention with its log-sum-exp merge.
  *
  * Each entry point cites the VulkanForge interface it stands in for, by the
- * file's path inside that project.  A reference-side binding (Rust `extern "C"`
- * block plus a `src/backend/cuda` module) is shown in INTEGRATION.md.
+ * file's path inside that project.  The reference-side binding (Rust `extern "C"`
+ * block plus a `src/backend/cuda` module) lives under rust/ in this source tree.
  *
  * Conventions
  *   - Every function returns a vfkv_status (0 = OK) and never aborts; the text
@@ -223,6 +223,15 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
                               uint32_t head_dim, uint32_t max_splits, vfkv_workspace **out);
 int32_t vfkv_workspace_destroy(vfkv_workspace *ws);
 uint64_t vfkv_workspace_bytes(const vfkv_workspace *ws);
+/* The tensor-core attention kernel merges its splits through the workspace without a second
+ * launch: every CTA of a (sequence, kv-head) draws a ticket from a 64-bit word {launch number << 8
+ * | CTAs drawn} when it starts, the last drawer is the one that will merge, and the partials are
+ * 8-byte words {f32 value, u32 launch number + 1} that the merging CTA polls (at most the time set
+ * with vfkv_ctx_set_merge_wait_ms; a wait that runs out raises bit 1 of the status word).  A
+ * launch always leaves its ticket words complete, so an error needs no clean-up; after a kernel
+ * was killed from outside (a debugger, a reset from another process) vfkv_workspace_reset puts
+ * tickets and tags back to zero, in stream order. */
+int32_t vfkv_workspace_reset(vfkv_workspace *ws, void *stream);
 
 /* ---------------------------------------------------------------------- */
 /* cache-level ops: what the forward pass calls                             */
@@ -342,13 +351,18 @@ int32_t vfkv_merge_partials_packed(vfkv_ctx *ctx, const float *d_packed, uint32_
  * No counterpart in the reference.  Each GPU of the group owns one exchange buffer of 8-byte words
  * {f32 value, u32 tag}.  The attention kernel of vfkv_attend_push stores this GPU's (m, l, o)
  * block into the buffer of EVERY rank with plain peer stores, each word tagged with the number of
- * the exchange (one 8-byte store per word, so a reader that finds the tag has the value: no
- * flags, no fences).  vfkv_exchange_merge polls the words of all ranks in its own buffer -- at
- * most the time set with vfkv_exchange_set_timeout_ms (default 1000 ms); a wait that runs out
- * sets bit 8 of the status word read by vfkv_ctx_poll and writes zeros -- and applies the
+ * the exchange (8-byte accesses are single-copy atomic, so a reader that finds the tag has the
+ * value: no flags, no fences).  vfkv_exchange_merge polls the words of all ranks in its own
+ * buffer -- at most the time set with vfkv_exchange_set_timeout_ms (default 1000 ms); a wait that
+ * runs out sets bit 8 of the status word read by vfkv_ctx_poll and writes zeros -- and applies the
  * flash_attn_reduce.comp:51-80 merge.  Blocks are double-buffered by the parity of a device-side
- * exchange counter, so both calls can be captured in a CUDA graph and replayed.  Every rank must
- * make the same sequence of push / merge calls, one merge per push.
+ * exchange counter, so the calls can be captured in a CUDA graph and replayed.  Every rank must
+ * make the same sequence of exchanges: one vfkv_exchange_merge per vfkv_attend_push, or
+ * vfkv_attend_exchange alone.  vfkv_attend_exchange does both steps in ONE launch where the
+ * tensor-core kernel covers the shape: the CTA that has merged a kv-head's splits stores the block
+ * to every rank, then polls its own buffer for the other ranks' words of the same rows and writes
+ * the final rows.  That needs the ranks' kernels to run at the same time, i.e. one GPU per rank;
+ * ranks that share a GPU (tests) use the two-call form, whose producers all run first.
  *
  * Set-up: create on every rank with the same shape; make each rank's buffer known to the others,
  * either through vfkv_exchange_export / vfkv_exchange_import (CUDA IPC handles, one process per
@@ -378,7 +392,8 @@ int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *e
                          uint32_t n_splits, void *stream);
 /* Waits for all ranks' blocks of the current exchange and writes d_out [n_rows][head_dim]. */
 int32_t vfkv_exchange_merge(vfkv_exchange *ex, float *d_out, void *stream);
-/* vfkv_attend_push followed by vfkv_exchange_merge. */
+/* vfkv_attend_push and vfkv_exchange_merge as one step (one launch where the tensor-core kernel
+ * covers the shape and d_out is 16-byte aligned, else the two calls in a row). */
 int32_t vfkv_attend_exchange(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex,
                              uint32_t layer, uint32_t kv_layer, const float *d_q,
                              const float *d_k_new, const float *d_v_new, uint32_t n_q_heads,
@@ -420,12 +435,17 @@ int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages)
  *      that wait.  The caller promises that the kernel enqueued immediately before on the stream
  *      writes neither those arrays nor this layer's cache rows (true for consecutive layers of a
  *      decode step, and for a forward pass whose preceding kernel is a projection or RoPE).
+ *      Only that one kernel matters: a mode-2 kernel releases its successor after its own wait,
+ *      so an early prefetch never overlaps anything older than the direct predecessor.  When the
+ *      direct predecessor was launched through this context and wrote rows of the slab this call
+ *      reads (the same layer twice in a row, a subscriber layer right after its publisher's
+ *      append, any raw store), the library itself falls back to mode 1 for that launch.
  *      Q, the token to append and all outputs are still touched only after the wait. */
 int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
 /* Latency analysis of the tensor-core attention kernel: while d_buffer is non-NULL, thread 0 of
  * every CTA stores 16 x uint64 nanosecond timestamps (globaltimer) at fixed phases -- 0 entry,
  * 1 range known, 2 barriers ready, 3 Q ready, 4 first tile landed, 5 stream done, 6 CTA joined,
- * 7 partial written, 8 ticket taken, 9 merged (last CTA only) -- at CTA index * 16.  The buffer
+ * 7 partial stored, 8 splits merged (merging CTA only), 9 rows written -- at CTA index * 16.  The buffer
  * must hold 16 x 8 bytes per CTA of the largest grid.  NULL switches it off.
  * The tcgen05 prefill kernel (vfkv_attend_prefill) uses the same buffer: thread 0 of each of its
  * two warpgroups stores, at its 4th K/V tile, 0 tile start, 1 loads issued and previous P V
@@ -436,6 +456,13 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * global scratch and a ticket.  Taken only when every cluster of the grid can be resident at
  * once; otherwise the call falls back to the scratch + ticket form.  0 = off (default), 1 = on. */
 int32_t vfkv_ctx_set_cluster_merge(vfkv_ctx *ctx, uint32_t on);
+/* Time limit of the merging CTA's wait for the other splits' partials (1..10000 ms, default 1000). */
+int32_t vfkv_ctx_set_merge_wait_ms(vfkv_ctx *ctx, uint32_t ms);
+/* Host-side failure injection for tests of the bounded waits: in later launches of the tensor-core
+ * attention kernel the CTA of (sequence 0, kv-head 0, split `split`) behaves as if its wait for a
+ * TMA tile had run out -- it raises bit 1 of the status word and publishes no partial -- so the
+ * merging CTA's own wait runs out as well.  Nothing faults or hangs.  0xFFFFFFFF = off (default). */
+int32_t vfkv_ctx_debug_fail_split(vfkv_ctx *ctx, uint32_t split);
 int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer);
 /* Kernels this context has launched since creation (for launch accounting). */
 uint64_t vfkv_ctx_launch_count(const vfkv_ctx *ctx);

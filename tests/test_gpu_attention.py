@@ -1,9 +1,16 @@
 """Split-K GQA decode attention on the GPU, through the C ABI, against the CPU oracle
 (the restatement of the reference's cpu_attention_reference, tests/correctness.rs:2567-2617).
 
-Tolerances: F32 / F16 cache: max-abs error below 1e-3 (the reference's own threshold for
-split+reduce, tests/correctness.rs:2875-2894; the build's gate is 2e-3).  FP8 cache: error
-relative to the output's max below 3e-2 against the oracle reading the same E4M3 bytes."""
+Two gates per comparison.  Acceptance gate: F32 / F16 cache max-abs error below 1e-3 (the
+reference's own threshold for split+reduce, tests/correctness.rs:2875-2894; the stated limit is
+2e-3), FP8 cache error relative to the output's max below 3e-2 against the oracle reading the same
+E4M3 bytes (the reference's class for half-precision operands is 2e-3 / 2e-2,
+tests/coopmat_fa_gemma.rs:260,330).  Regression gate: what the kernels deliver by design -- f32
+accumulation, and on the tensor cores Q and P carried as a high plus a low half-precision term --
+is f32-grade, so F32 / F16 results must stay within 2e-5 and FP8 results within 1e-4 relative; a
+change that dropped the low terms (operand rounding 2^-11) fails it.  The one path that feeds
+single half-precision operands (F16 cache, more than 8 q-heads per kv-head on the tensor cores)
+is held to the acceptance gate only."""
 import os
 
 import numpy as np
@@ -18,15 +25,25 @@ pytestmark = pytest.mark.gpu
 
 ABS_TOL = 1e-3
 FP8_REL_TOL = 3e-2
+REGRESSION_ABS_TOL = 2e-5
+REGRESSION_FP8_REL_TOL = 1e-4
 
 
-def check(got, want, dtype):
+def single_term_path(impl, dtype, hq, hkv, d):
+    """True where the tensor-core kernel runs without the high + low operand split."""
+    return impl != 1 and int(dtype) == oracle.F16 and hq // hkv > 8 and d in (64, 128, 256)
+
+
+def check(got, want, dtype, single_term=False):
     assert np.isfinite(got).all()
     if int(dtype) == oracle.F8:
-        assert rel_err(got, want) < FP8_REL_TOL, rel_err(got, want)
+        err = rel_err(got, want)
+        assert err < FP8_REL_TOL, err
+        assert single_term or err < REGRESSION_FP8_REL_TOL, ("regression gate", err)
     else:
         err = float(np.max(np.abs(got - want)))
         assert err < ABS_TOL, err
+        assert single_term or err < REGRESSION_ABS_TOL, ("regression gate", err)
 
 
 class Rig:
@@ -153,7 +170,7 @@ def test_shapes_lengths_and_starts(ctx, impl, dtype, hq, hkv, d):
                                    (257, 3, 64)]:
             got = rig.attend(q, 0, L, kv_start=start, n_splits=n_splits)
             want = oracle.attention_ref(q, kc, vc, int(dtype), hq, hkv, d, L, start)
-            check(got, want, dtype)
+            check(got, want, dtype, single_term_path(impl, dtype, hq, hkv, d))
     finally:
         rig.close()
 
@@ -450,4 +467,80 @@ def test_decode_token_kernel_shapes_dependent_launch_and_graph_replay(ctx, dtype
     finally:
         ctx.check(L.vfkv_ctx_set_attn_tuning(ctx.handle, 0, 0))
         ctx.check(L.vfkv_ctx_set_dependent_launch(ctx.handle, 0))
+        rig.close()
+
+
+def test_split_that_gives_up_is_reported_and_the_next_launch_is_clean(ctx):
+    """A CTA whose bounded wait runs out (injected on the host: one split of kv-head 0 acts as if its
+    tile never arrived) publishes no partial.  The merging CTA's wait for it is bounded too, the
+    status word reports the failure, and -- because every CTA draws its split ticket before it can
+    give up -- the workspace needs no repair: the very next launch on it is correct."""
+    import torch
+    hq, hkv, d, L = 32, 8, 128, 1500
+    rng = np.random.default_rng(91)
+    kc, vc = encode_cache(kv_values(rng, (L, hkv, d)), oracle.F8), encode_cache(kv_values(rng, (L, hkv, d)), oracle.F8)
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    want = oracle.attention_ref(q, kc, vc, oracle.F8, hq, hkv, d, L)
+    rig = Rig(ctx, vf.KvDtype.F8, hq, hkv, d, L)
+    try:
+        rig.put(0, 0, kc, vc)
+        ctx.set_merge_wait_ms(20)
+        for failing in (0, 3):
+            ctx.debug_fail_split(failing)
+            rig.attend(q, 0, L, n_splits=4)
+            with pytest.raises(vf.VfkvError) as err:
+                ctx.poll()
+            assert err.value.status == vf.kv_cache.ERR_TIMEOUT
+            ctx.debug_fail_split(None)
+            for n_splits in (4, 7):                      # no reset in between
+                got = rig.attend(q, 0, L, n_splits=n_splits)
+                ctx.poll()
+                check(got, want, oracle.F8)
+        rig.fwd.workspace.reset()                        # the explicit repair call is harmless too
+        check(rig.attend(q, 0, L, n_splits=4), want, oracle.F8)
+        ctx.poll()
+    finally:
+        ctx.debug_fail_split(None)
+        ctx.set_merge_wait_ms(1000)
+        rig.close()
+
+
+@pytest.mark.parametrize("dtype", [vf.KvDtype.F8, vf.KvDtype.F16])
+def test_dependent_launch_mode2_on_one_layer_with_advancing_positions(ctx, dtype):
+    """Mode 2 prefetches K/V before it waits for the kernel in front of it.  On a one-layer cache
+    every decode step reads the slab the step before it appended to; the library must notice that
+    and wait first.  Eight tokens are enqueued back to back without a host synchronisation; token
+    t attends over the rows tokens 0..t-1 appended."""
+    import torch
+    hq, hkv, d, max_seq, base, steps = 32, 8, 128, 700, 600, 8
+    rng = np.random.default_rng(17)
+    fp8 = dtype == vf.KvDtype.F8
+    kc = encode_cache(kv_values(rng, (1, max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0), int(dtype))
+    vc = encode_cache(kv_values(rng, (1, max_seq, hkv, d), outlier_frac=0.01 if fp8 else 0.0), int(dtype))
+    q = rng.standard_normal((steps, 1, hq, d), dtype=np.float32)
+    kn = kv_values(rng, (steps, 1, hkv, d), outlier_frac=0.0)
+    vn = kv_values(rng, (steps, 1, hkv, d), outlier_frac=0.0)
+    kk, vv = kc.copy(), vc.copy()
+    want = [oracle.decode_step(q[t], kn[t], vn[t], kk, vv, int(dtype), 1, max_seq, hq, hkv, d,
+                               np.array([base + t + 1], np.uint32)) for t in range(steps)]
+    stream = torch.cuda.Stream()
+    rig = Rig(ctx, dtype, hq, hkv, d, max_seq, n_splits=4)
+    try:
+        rig.put(0, 0, kc[0], vc[0])
+        dq, dk, dv = to_dev(q), to_dev(kn), to_dev(vn)
+        dpos = to_dev(np.arange(base, base + steps, dtype=np.uint32))
+        out = torch.zeros(steps, 1, hq, d, device="cuda")
+        rig.fwd.stream = stream.cuda_stream
+        ctx.set_dependent_launch(2)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            for t in range(steps):
+                rig.fwd.decode_step(0, dq[t], dk[t], dv[t], out[t], None, dpos[t:t + 1], 1, max_seq)
+        stream.synchronize()
+        ctx.poll()
+        got = out.cpu().numpy()
+        for t in range(steps):
+            check(got[t], want[t], dtype)
+    finally:
+        ctx.set_dependent_launch(0)
         rig.close()

@@ -187,6 +187,93 @@ def test_peer_exchange_wait_runs_out_and_context_survives(ctx):
         _destroy_group(ranks)
 
 
+@pytest.mark.parametrize("world,seq_len,n_splits", [(2, 3000, 0), (2, 900, 1), (1, 2500, 0), (4, 6000, 5)])
+def test_one_launch_exchange_with_the_other_ranks_already_there(ctx, world, seq_len, n_splits):
+    """vfkv_attend_exchange on the tensor-core path is ONE launch: attention, fan-out of the block
+    to every rank, wait for the other ranks' blocks in this GPU's own buffer, final rows.  The
+    waiting kernel needs the other ranks' kernels to run beside it, which one GPU cannot offer, so
+    here ranks 1.. push first (two-call form) and rank 0 then runs the one-launch form: its waits
+    are real polls that find the words there.  Several steps in a row cover the parity
+    double-buffering and the exchange counter advanced by the kernel itself."""
+    import torch
+    hq, hkv, d = HQ, HKV, D
+    rng = np.random.default_rng(world * 31 + seq_len)
+    steps = 4
+    k = kv_values(rng, (seq_len + steps, hkv, d))
+    v = kv_values(rng, (seq_len + steps, hkv, d))
+    sh, ranks = _emulated_group(ctx, world, seq_len, vf.KvDtype.F8)
+    try:
+        dk, dv = to_dev(k), to_dev(v)
+        for _, fwd, dec, _ in ranks:
+            fwd.n_splits = n_splits
+            dec.prefill(0, dk[:seq_len], dv[:seq_len], 0, seq_len)
+        outs = [torch.zeros(hq, d, device="cuda") for _ in ranks]
+        for t in range(steps):
+            L = seq_len + t + 1
+            q = rng.standard_normal((hq, d), dtype=np.float32)
+            dq = to_dev(q)
+            new = lambda r: dict(k_new=dk[L - 1], v_new=dv[L - 1]) if sh.owner(L - 1) == r else {}
+            for r in range(1, world):
+                _, fwd, _, ex = ranks[r]
+                fwd.attend_push(ex, 0, dq, 0, sh.local_len(L, r), **new(r))
+            n0 = ctx.launch_count()
+            _, fwd0, _, ex0 = ranks[0]
+            fwd0.attend_exchange(ex0, 0, dq, 0, sh.local_len(L, 0), outs[0], **new(0))
+            assert ctx.launch_count() - n0 == 1
+            for r in range(1, world):
+                _, fwd, _, ex = ranks[r]
+                fwd.exchange_merge(ex, outs[r])
+            torch.cuda.synchronize()
+            ctx.poll()
+            kc, vc = encode_cache(k[:L], oracle.F8), encode_cache(v[:L], oracle.F8)
+            want = oracle.attention_ref(q, kc, vc, oracle.F8, hq, hkv, d, L)
+            for r in range(world):
+                assert rel_err(outs[r].cpu().numpy(), want) < 1e-4, (t, r)
+    finally:
+        _destroy_group(ranks)
+
+
+def test_one_launch_exchange_wait_runs_out_and_context_survives(ctx):
+    """The one-launch form with a peer that never stores: the kernel's wait is bounded, the status
+    word says so, the rows are zeros, and the next exchanges work."""
+    import torch
+    world, seq_len = 2, 800
+    rng = np.random.default_rng(6)
+    k = kv_values(rng, (seq_len, HKV, D))
+    v = kv_values(rng, (seq_len, HKV, D))
+    q = rng.standard_normal((HQ, D), dtype=np.float32)
+    sh, ranks = _emulated_group(ctx, world, seq_len, vf.KvDtype.F8)
+    try:
+        dk, dv, dq = to_dev(k), to_dev(v), to_dev(q)
+        for _, _, dec, ex in ranks:
+            dec.prefill(0, dk, dv, 0, seq_len)
+            ex.set_timeout_ms(20)
+        outs = [torch.ones(HQ, D, device="cuda") for _ in ranks]
+        (_, f0, _, e0), (_, f1, _, e1) = ranks
+        f0.attend_exchange(e0, 0, dq, 0, sh.local_len(seq_len, 0), outs[0])      # rank 1 has not pushed
+        torch.cuda.synchronize()
+        with pytest.raises(vf.VfkvError) as err:
+            ctx.poll()
+        assert err.value.status == vf.kv_cache.ERR_TIMEOUT
+        assert float(outs[0].abs().max()) == 0.0
+        f1.attend_push(e1, 0, dq, 0, sh.local_len(seq_len, 1))                   # exchange 1 of rank 1
+        f1.exchange_merge(e1, outs[1])
+        torch.cuda.synchronize()
+        ctx.poll()
+        kc, vc = encode_cache(k, oracle.F8), encode_cache(v, oracle.F8)
+        want = oracle.attention_ref(q, kc, vc, oracle.F8, HQ, HKV, D, seq_len)
+        assert rel_err(outs[1].cpu().numpy(), want) < 1e-4
+        f1.attend_push(e1, 0, dq, 0, sh.local_len(seq_len, 1))                   # exchange 2 on both
+        f0.attend_exchange(e0, 0, dq, 0, sh.local_len(seq_len, 0), outs[0])
+        f1.exchange_merge(e1, outs[1])
+        torch.cuda.synchronize()
+        ctx.poll()
+        for r in range(world):
+            assert rel_err(outs[r].cpu().numpy(), want) < 1e-4
+    finally:
+        _destroy_group(ranks)
+
+
 def _nccl_rank(rank, world, port, seq_len, result_dir):
     import torch
     import torch.distributed as dist

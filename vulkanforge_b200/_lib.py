@@ -74,6 +74,7 @@ SIGNATURES = {
     "vfkv_workspace_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
     "vfkv_workspace_destroy": (i32, [vp]),
     "vfkv_workspace_bytes": (u64, [vp]),
+    "vfkv_workspace_reset": (i32, [vp, vp]),
     "vfkv_append": (i32, [vp, u32, vp, vp, u32, u32, u32, vp]),
     "vfkv_append_batch": (i32, [vp, u32, vp, vp, vp, vp, u32, vp]),
     "vfkv_fp8_to_f16": (i32, [vp, u32, u32, u32, vp, vp, vp]),
@@ -122,6 +123,8 @@ SIGNATURES = {
     "vfkv_ctx_set_attn_tuning": (i32, [vp, u32, u32]),
     "vfkv_ctx_set_dependent_launch": (i32, [vp, u32]),
     "vfkv_ctx_set_cluster_merge": (i32, [vp, u32]),
+    "vfkv_ctx_set_merge_wait_ms": (i32, [vp, u32]),
+    "vfkv_ctx_debug_fail_split": (i32, [vp, u32]),
     "vfkv_ctx_set_trace_buffer": (i32, [vp, vp]),
     "vfkv_ctx_launch_count": (u64, [vp]),
     "vfkv_profile_enable": (i32, [vp, i32]),

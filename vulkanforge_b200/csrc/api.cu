@@ -195,6 +195,20 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode)
     return VFKV_OK;
 }
 
+int32_t vfkv_ctx_set_merge_wait_ms(vfkv_ctx *ctx, uint32_t ms)
+{
+    if (!ctx || ms == 0 || ms > 10000) return VFKV_ERR_INVALID;
+    ctx->merge_wait_ns = uint64_t(ms) * 1000000ull;
+    return VFKV_OK;
+}
+
+int32_t vfkv_ctx_debug_fail_split(vfkv_ctx *ctx, uint32_t split)
+{
+    if (!ctx) return VFKV_ERR_INVALID;
+    ctx->debug_fail_split = split;
+    return VFKV_OK;
+}
+
 int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer)
 {
     if (!ctx) return VFKV_ERR_INVALID;
@@ -453,15 +467,20 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->part_l), parts * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->d_u32), u32_bytes);
     ws->n_counters = rows;
-    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->counters), rows * 4);
-    if (e == cudaSuccess) e = cudaMemset(ws->counters, 0, rows * 4);
+    ws->tag_words = parts * (uint64_t(head_dim) + 4);     // o, {m, l} and one decision pair per CTA (kv-heads <= q-heads)
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->tickets), rows * 8);
+    if (e == cudaSuccess) e = cudaMemset(ws->tickets, 0, rows * 8);
+    // tag 0 is never used by a launch, so zeroed words read as "not there yet"
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->tag_part), ws->tag_words * 8);
+    if (e == cudaSuccess) e = cudaMemset(ws->tag_part, 0, ws->tag_words * 8);
     if (e != cudaSuccess) {
-        cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->counters);
+        cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->tickets);
+        cudaFree(ws->tag_part);
         cudaGetLastError();
         delete ws;
         return check_cuda(ctx, e, "vfkv_workspace_create: cudaMalloc");
     }
-    ws->bytes = ofl + parts * 8 + u32_bytes + rows * 4;
+    ws->bytes = ofl + parts * 8 + u32_bytes + rows * 8 + ws->tag_words * 8;
     *out = ws;
     return VFKV_OK;
 }
@@ -470,7 +489,8 @@ int32_t vfkv_workspace_destroy(vfkv_workspace *ws)
 {
     if (!ws) return VFKV_OK;
     DeviceGuard g(ws->ctx->device);
-    cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->counters);
+    cudaFree(ws->part_o); cudaFree(ws->part_m); cudaFree(ws->part_l); cudaFree(ws->d_u32); cudaFree(ws->tickets);
+    cudaFree(ws->tag_part);
     cudaFree(ws->stage_in); cudaFree(ws->stage_out);
     for (auto gexec : ws->tok_graphs)
         if (gexec) cudaGraphExecDestroy(gexec);
@@ -479,6 +499,15 @@ int32_t vfkv_workspace_destroy(vfkv_workspace *ws)
     if (ws->copy_stream) cudaStreamDestroy(ws->copy_stream);
     delete ws;
     return VFKV_OK;
+}
+
+int32_t vfkv_workspace_reset(vfkv_workspace *ws, void *stream)
+{
+    if (!ws) return VFKV_ERR_INVALID;
+    DeviceGuard g(ws->ctx->device);
+    cudaError_t e = cudaMemsetAsync(ws->tickets, 0, ws->n_counters * 8, as_stream(stream));
+    if (e == cudaSuccess) e = cudaMemsetAsync(ws->tag_part, 0, ws->tag_words * 8, as_stream(stream));
+    return check_cuda(ws->ctx, e, "vfkv_workspace_reset");
 }
 
 uint64_t vfkv_workspace_bytes(const vfkv_workspace *ws) { return ws ? ws->bytes + ws->stage_in_bytes + ws->stage_out_bytes : 0; }
@@ -850,28 +879,32 @@ int32_t vfkv_attend_partial(vfkv_cache *cache, vfkv_workspace *ws, uint32_t laye
     return launch_attention(ctx, ws, a, as_stream(stream));
 }
 
-int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer, uint32_t kv_layer,
-                         const float *d_q, const float *d_k_new, const float *d_v_new, uint32_t n_q_heads,
-                         uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale, float softcap,
-                         uint32_t n_splits, void *stream)
+// Shared by vfkv_attend_push (fused = false) and vfkv_attend_exchange (fused = true).
+static int32_t attend_push_impl(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer,
+                                uint32_t kv_layer, const float *d_q, const float *d_k_new, const float *d_v_new,
+                                uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale,
+                                float softcap, uint32_t n_splits, float *d_out, bool fused, bool *did_fuse,
+                                void *stream, const char *fn)
 {
-    int32_t rc = attend_common(cache, layer, kv_layer, n_q_heads, "vfkv_attend_push");
+    if (did_fuse) *did_fuse = false;
+    int32_t rc = attend_common(cache, layer, kv_layer, n_q_heads, fn);
     if (rc) return rc;
     vfkv_ctx *ctx = cache->ctx;
-    if (!d_q || !ex) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: null argument");
-    if (ex->ctx != ctx) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: exchange belongs to another context");
-    if (!vfkv_exchange_ready(ex)) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: not every rank's buffer is set");
+    const std::string name(fn);
+    if (!d_q || !ex) return set_error(ctx, VFKV_ERR_INVALID, name + ": null argument");
+    if (ex->ctx != ctx) return set_error(ctx, VFKV_ERR_INVALID, name + ": exchange belongs to another context");
+    if (!vfkv_exchange_ready(ex)) return set_error(ctx, VFKV_ERR_INVALID, name + ": not every rank's buffer is set");
     if (slot >= cache->kv.config.n_slots || pos_end > cache->kv.config.max_seq_len || pos_begin > pos_end)
-        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: slot or position range out of bounds");
+        return set_error(ctx, VFKV_ERR_INVALID, name + ": slot or position range out of bounds");
     const bool has_new = d_k_new || d_v_new;
     if (has_new && (!d_k_new || !d_v_new || pos_end == 0 || pos_begin == pos_end || kv_layer != layer))
-        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: a new token needs both K and V, a non-empty range and kv_layer == layer");
+        return set_error(ctx, VFKV_ERR_INVALID, name + ": a new token needs both K and V, a non-empty range and kv_layer == layer");
     if ((reinterpret_cast<uintptr_t>(d_k_new) | reinterpret_cast<uintptr_t>(d_v_new)) % 16 != 0)
-        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: K and V inputs must be 16-byte aligned");
+        return set_error(ctx, VFKV_ERR_INVALID, name + ": K and V inputs must be 16-byte aligned");
     AttnArgs a;
     a.kv = make_view(cache, kv_layer);
     if (ex->fan.n_rows != n_q_heads || ex->head_dim != a.kv.head_dim)
-        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_push: exchange was created for another shape");
+        return set_error(ctx, VFKV_ERR_INVALID, name + ": exchange was created for another shape");
     a.seq.n_seqs = 1; a.seq.slot0 = slot; a.seq.seq_len_scalar = pos_end; a.seq.kv_start_scalar = pos_begin;
     a.q = d_q; a.n_q_heads = n_q_heads; a.scale = scale; a.softcap = softcap; a.n_splits = n_splits;
     // the staged block has the layout of one exchange block, in plain floats
@@ -883,6 +916,12 @@ int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *e
         a.fan = ex->d_fan;                              // and writes the new token's cache row as well
         a.k_new = d_k_new;
         a.v_new = d_v_new;
+        if (fused && reinterpret_cast<uintptr_t>(d_out) % 16 == 0) {
+            // one launch per layer: the same kernel waits for the other ranks' blocks and writes the rows
+            a.out = d_out;
+            a.fan_merge = true;
+            if (did_fuse) *did_fuse = true;
+        }
         DeviceGuard g(ctx->device);
         return launch_attention(ctx, ws, a, as_stream(stream));
     }
@@ -896,14 +935,26 @@ int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *e
     return launch_fanout_push(ctx, ex->fan, ex->staging, ex->head_dim, as_stream(stream));
 }
 
+int32_t vfkv_attend_push(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer, uint32_t kv_layer,
+                         const float *d_q, const float *d_k_new, const float *d_v_new, uint32_t n_q_heads,
+                         uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale, float softcap,
+                         uint32_t n_splits, void *stream)
+{
+    return attend_push_impl(cache, ws, ex, layer, kv_layer, d_q, d_k_new, d_v_new, n_q_heads, slot, pos_begin, pos_end,
+                            scale, softcap, n_splits, nullptr, false, nullptr, stream, "vfkv_attend_push");
+}
+
 int32_t vfkv_attend_exchange(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exchange *ex, uint32_t layer,
                              uint32_t kv_layer, const float *d_q, const float *d_k_new, const float *d_v_new,
                              uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale,
                              float softcap, uint32_t n_splits, float *d_out, void *stream)
 {
-    int32_t rc = vfkv_attend_push(cache, ws, ex, layer, kv_layer, d_q, d_k_new, d_v_new, n_q_heads, slot, pos_begin,
-                                  pos_end, scale, softcap, n_splits, stream);
-    if (rc) return rc;
+    if (!d_out) return VFKV_ERR_INVALID;
+    bool fused = false;
+    int32_t rc = attend_push_impl(cache, ws, ex, layer, kv_layer, d_q, d_k_new, d_v_new, n_q_heads, slot, pos_begin,
+                                  pos_end, scale, softcap, n_splits, d_out, true, &fused, stream,
+                                  "vfkv_attend_exchange");
+    if (rc || fused) return rc;
     return vfkv_exchange_merge(ex, d_out, stream);
 }
 

@@ -106,6 +106,7 @@ static int32_t launch_store_t(vfkv_ctx *ctx, const float *src, void *dst, uint64
             src, static_cast<uint32_t *>(dst), done, n);
         ctx->launches++;
     }
+    ctx->last_written_slab = vfkv::kAnySlab;        // a raw destination may lie in any layer
     return check_cuda(ctx, cudaGetLastError(), "store kernel launch");
 }
 
@@ -236,6 +237,7 @@ int32_t launch_append(vfkv_ctx *ctx, const AppendArgs &a, cudaStream_t st)
             append_scaled_kernel<<<dim3(unsigned(blocks), 2), 256, 0, st>>>(p);
         }
         ctx->launches++;
+        ctx->last_written_slab = a.k_dst;
         return check_cuda(ctx, cudaGetLastError(), "append_scaled launch");
     }
     const int E = a.dtype == VFKV_F8 ? 16 : a.dtype == VFKV_F16 ? 8 : 4;
@@ -252,6 +254,7 @@ int32_t launch_append(vfkv_ctx *ctx, const AppendArgs &a, cudaStream_t st)
     default: return set_error(ctx, VFKV_ERR_INVALID, "unknown dtype");
     }
     ctx->launches++;
+    ctx->last_written_slab = a.k_dst;
     return check_cuda(ctx, cudaGetLastError(), "append launch");
 }
 

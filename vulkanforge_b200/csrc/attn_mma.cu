@@ -32,6 +32,8 @@
 // context's status word and returns without touching the output.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "attn_params.cuh"
 #include "fp8_codec.cuh"
 
@@ -148,11 +150,17 @@ __device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t &hi, ui
 
 struct MmaParams {
     AttnParams a;
-    uint32_t *counters;     // one ticket per (sequence, kv-head); zero between launches
+    // Split merge (n_splits > 1): one 64-bit ticket word per (sequence, kv-head), {launch number << 8 |
+    // CTAs of this launch that have drawn}, and the partials as tagged 8-byte words (see vfkv_workspace).
+    unsigned long long *tickets;
+    uint64_t *tag_part;
+    uint64_t merge_wait_ns;       // limit of the merging CTA's wait for the other splits' partials
     const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
     unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0
     uint32_t pdl;                 // 0 plain launch, 1 dependent launch, 2 dependent launch with early K/V prefetch
     uint32_t cluster;             // 1: the splits of a (sequence, kv-head) are one thread-block cluster
+    uint32_t fan_merge;           // with a.fan: also wait for the other ranks' blocks and write the final rows
+    uint32_t fail_split;          // test hook: this split of (sequence 0, kv-head 0) acts as if a TMA wait ran out
 };
 
 // Phase timestamps for latency analysis; costs one predicated branch when tracing is off.
@@ -298,7 +306,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
     const uint32_t bars = ring + S::RING_BYTES;           // kWarps*kStages mbarriers, 8 bytes each
-    __shared__ uint32_t s_flag, s_epoch;
+    __shared__ uint32_t s_flag, s_epoch, s_tag, s_merger, s_safe, s_nlist;
+    __shared__ uint8_t s_take[256];       // slices the last drawer takes over (n_splits <= 255)
     __shared__ PeerFanout s_fan;          // the group's fan-out table (position-sharded calls only)
 
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
@@ -306,18 +315,39 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t gid = lane >> 2, tig = lane & 3;
     const uint32_t g = p.group;
 
+    // ---- split ticket, drawn before anything else ----------------------------------------------
+    // The CTA of a (sequence, kv-head) that draws the last ticket of a launch will merge the splits;
+    // the launch number in the word's upper bits is the tag of this launch's partials.  The last
+    // drawer also rolls the word over to the next launch.  Nothing waits on a ticket, and a CTA
+    // draws before its first bounded wait, so the word is always complete at the end of a launch.
+    // The tickets belong to the workspace and are only touched here, at the start of CTAs; a
+    // dependent launch lets its successor start only after every CTA has passed the barrier
+    // below, so launches never interleave their tickets.
+    if (threadIdx.x == 32) {
+        uint32_t tag = 0u, merger = 0u;
+        if (p.n_splits > 1u && mp.cluster == 0u) {
+            unsigned long long *tk = mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh);
+            const unsigned long long old = atomicAdd(tk, 1ull);
+            tag = uint32_t(old >> 8) + 1u;
+            merger = uint32_t(old & 0xFFull) == p.n_splits - 1u ? 1u : 0u;
+            if (merger) atomicAdd(tk, 256ull - p.n_splits);
+        }
+        s_tag = tag; s_merger = merger;
+    }
+
     // Q is fetched first: its address depends on the block index only, so these loads overlap the
     // (dependent) read of the sequence's position and the first TMA round trip.
     // element layout this thread needs: FP8  d = 32ks + 4tig + i  and  32ks + 16 + 4tig + i   (i < 4)
     //                                   F16  d = 16ks + 2tig + i  and  16ks + 8 + 2tig + i    (i < 2)
     float qv[RS][KSTEPS][4], qv2[RS][KSTEPS][4];
-    // Programmatic dependent launch: this grid lets its successor in the stream begin as soon as
-    // all of this grid's CTAs are running, and itself waits for its predecessor before it touches
-    // anything the predecessor may have produced.  mp.pdl == 2 is the caller's promise that the
-    // predecessor writes neither the position / slot arrays nor this layer's cache rows, so the
-    // K/V prefetch may start before the wait; Q, the new token and every store come after it.
+    // Programmatic dependent launch: this grid lets its successor in the stream begin once every CTA
+    // has drawn its ticket (and, in mode 2, has seen its predecessor complete), and itself waits for
+    // its predecessor before it touches anything the predecessor may have produced.  mp.pdl == 2 is
+    // the caller's promise that the kernel directly before this one writes neither the position /
+    // slot arrays nor this layer's cache rows, so the K/V prefetch may start before the wait; Q, the
+    // new token and every store come after it.  Because the successor is released only after this
+    // grid's own wait, the early prefetch can only ever overlap the direct predecessor.
     // Both instructions do nothing in a launch without the attribute.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (mp.pdl != 2u) asm volatile("griddepcontrol.wait;" ::: "memory");
     auto load_q = [&]() {
 #pragma unroll
@@ -341,10 +371,26 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     }
     };
-    // exchange number of a position-sharded call (written by the merge kernel of the previous
-    // exchange): fetched right after the wait so that the epilogue finds it in shared memory
+    // Exchange number of a position-sharded call: read after the wait (the kernel that closed the
+    // previous exchange wrote it), kept in shared memory for the epilogue.  When this kernel also
+    // closes the exchange (fan_merge), the CTA that draws the last exchange ticket advances the
+    // number at once: every CTA reads the number before it draws (the ticket's operand depends on
+    // the value read), so the last drawer knows that all of them hold the old number.
     auto load_epoch = [&]() {
-        if (threadIdx.x == 32 && p.fan != nullptr) { s_fan = *p.fan; s_epoch = *s_fan.epoch; }
+        if (threadIdx.x == 32 && p.fan != nullptr) {
+            s_fan = *p.fan;
+            const uint32_t e = *reinterpret_cast<const volatile uint32_t *>(s_fan.epoch);
+            s_epoch = e;
+            if (mp.fan_merge != 0u) {
+                uint32_t one;
+                asm volatile("sub.u32 %0, %1, %2;" : "=r"(one) : "r"(e + 1u), "r"(e));
+                const uint32_t total = gridDim.x * gridDim.y * gridDim.z;
+                if (atomicAdd(&s_fan.ctl[1], one) == total - 1u) {
+                    s_fan.ctl[1] = 0u;
+                    *reinterpret_cast<volatile uint32_t *>(&s_fan.ctl[0]) = e + 1u;
+                }
+            }
+        }
     };
     if (mp.pdl != 2u) { load_q(); load_epoch(); }
 
@@ -363,6 +409,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     __syncthreads();
     VFKV_TRACE(2);
+    if (mp.pdl != 2u) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- this warp's pipeline -------------------------------------------------------------
     const uint32_t my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
@@ -389,6 +436,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     if (mp.pdl == 2u) {       // the prefetch is in flight; now wait for the predecessor, then read Q
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         load_q();
         load_epoch();
     }
@@ -480,6 +528,12 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
     for (int nb = 0; nb < NDB; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f; }
     bool timed_out = false;
+    // Has every CTA of this (sequence, kv-head) started?  Asked now, used after the stream: the
+    // answer decides whether this CTA may wait for the others' partials (see the merge below).
+    unsigned long long ticket_now = 0ull;
+    if (threadIdx.x == 0 && p.n_splits > 1u && mp.cluster == 0u)
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(ticket_now)
+                     : "l"(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh)) : "memory");
     VFKV_TRACE(3);
 
     // Lane-constant parts of the swizzled shared-memory addresses (tile_addr with the tile base
@@ -648,9 +702,14 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     }
 
     VFKV_TRACE(5);
+    // host-side failure injection (tests): after its tiles have all landed, so that no copy is still
+    // in flight, this CTA reports a wait that ran out and publishes nothing
+    if (split == mp.fail_split && kvh == 0u && s == 0u) timed_out = true;
     if (timed_out) {
         if (lane == 0) { atomicOr(p.status, 1u); s_flag = 1; }
     }
+    if (threadIdx.x == 0)     // the word has moved on to the next launch, or counts all of this launch's CTAs
+        s_safe = (uint32_t(ticket_now >> 8) + 1u != s_tag || uint32_t(ticket_now & 0xFFull) >= p.n_splits) ? 1u : 0u;
     __syncthreads();          // all tiles consumed (or abandoned): the ring is free for the merge
     VFKV_TRACE(6);
     const bool gave_up = s_flag != 0u;
@@ -784,141 +843,245 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         return;
     }
-    for (uint32_t idx = threadIdx.x; idx < g * D; idx += blockDim.x) {
-        const uint32_t j = idx / D, d = idx % D;
+    // ---- this CTA's partial: the warps' partials merged, two dims per thread ----------------------
+    const uint32_t HD2 = D / 2;
+    const uint32_t n_pairs = g * HD2;                          // pairs of output values of this (sequence, kv-head)
+    auto cta_partial = [&](uint32_t j, uint32_t d, float &O0, float &O1, float &Mn, float &L) {
         float M = kMaskedScore;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) M = fmaxf(M, sm_m[w * NH + j]);
-        float L = 0.f, O = 0.f;
+        L = 0.f; O0 = 0.f; O1 = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
             const float f = fast_exp2(sm_m[w * NH + j] - M);
             L = fmaf(sm_l[w * NH + j], f, L);
-            O = fmaf(sm_o[(w * NH + j) * DP + d], f, O);
+            O0 = fmaf(sm_o[(w * NH + j) * DP + d], f, O0);
+            O1 = fmaf(sm_o[(w * NH + j) * DP + d + 1], f, O1);
         }
+        Mn = M * kLn2;                                         // partials carry natural-log maxima
+    };
+    // Final values of one output pair: the caller's buffers and, in a position-sharded call, every
+    // GPU's exchange buffer.
+    auto emit = [&](uint32_t idx, float a0, float a1, float gmax, float gsum) {
+        const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
         const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
-        const float m_nat = M * kLn2;                          // partials carry natural-log maxima
-        if (direct) {
-            if (p.out) p.out[row * D + d] = L > 0.f ? O * (1.0f / L) : 0.f;
-            if (p.out_o) {
-                p.out_o[row * D + d] = O;
-                if (d == 0) { p.out_m[row] = m_nat; p.out_l[row] = L; }
-            }
-            if (fan) {
-#pragma unroll
-                for (uint32_t r = 0; r < 8; ++r) {
-                    if (r < s_fan.world) {
-                        uint64_t *dst = s_fan.base[r];
-                        fanout_store(dst + fs.o + row * D + d, O, fs.epoch);
-                        if (d == 0) {
-                            fanout_store(dst + fs.m + row, m_nat, fs.epoch);
-                            fanout_store(dst + fs.m + s_fan.n_rows + row, L, fs.epoch);
-                        }
-                    }
-                }
-            }
-        } else {
-            const uint64_t pi = row * p.n_splits + split;
-            p.part_o[pi * D + d] = O;
-            if (d == 0) { p.part_m[pi] = m_nat; p.part_l[pi] = L; }
-        }
-    }
-    VFKV_TRACE(7);
-    if (direct) return;
-
-    // ---- the last CTA of this (sequence, kv-head) merges the splits ---------------------------------
-    // The barrier orders every thread's partial stores before thread 0's ticket; the ticket is an
-    // acq_rel atomic at GPU scope, so it publishes them (release) and, for the CTA that draws the
-    // last ticket, makes the other CTAs' partials visible (acquire).  One round trip, no fences.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t ticket;
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;"
-                     : "=r"(ticket) : "l"(mp.counters + s * p.n_kv_heads + kvh), "r"(1u) : "memory");
-        s_flag = ticket == p.n_splits - 1 ? 2u : 0u;
-    }
-    __syncthreads();
-    VFKV_TRACE(8);
-    if (s_flag != 2u) return;
-    // flash_attn_reduce.comp:57-75 with the maximum taken first.  Everything the merge of up to 16
-    // splits needs is requested in one batch, so it costs a single L2 round trip.
-    for (uint32_t idx = threadIdx.x; idx < g * (D / 4); idx += blockDim.x) {
-        const uint32_t j = idx / (D / 4), d = 4 * (idx % (D / 4));
-        const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
-        const float *pm = p.part_m + row * p.n_splits, *pl = p.part_l + row * p.n_splits;
-        const float4 *po = reinterpret_cast<const float4 *>(p.part_o + row * p.n_splits * D + d);
-        constexpr uint32_t CH = 16;
-        float gmax = kMaskedScore, gsum = 0.f;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        {   // the first 16 splits: everything is requested in one batch, a single L2 round trip
-            float4 o[CH];
-            float mm[CH], ll[CH];
-#pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) {
-                const bool in = i < p.n_splits;
-                o[i] = in ? __ldcg(po + uint64_t(i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                mm[i] = in ? __ldcg(pm + i) : kMaskedScore;
-                ll[i] = in ? __ldcg(pl + i) : 0.f;
-            }
-#pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) gmax = fmaxf(gmax, mm[i]);
-#pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) {
-                const float kn = __expf(mm[i] - gmax);            // absent splits: l = 0 and o = 0
-                gsum = fmaf(ll[i], kn, gsum);
-                a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
-                a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
-            }
-        }
-        for (uint32_t c0 = CH; c0 < p.n_splits; c0 += CH) {       // further splits: one round trip per 16
-            float4 o[CH];
-            float mm[CH], ll[CH];
-#pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) {
-                const bool in = c0 + i < p.n_splits;
-                o[i] = in ? __ldcg(po + uint64_t(c0 + i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                mm[i] = in ? __ldcg(pm + c0 + i) : kMaskedScore;
-                ll[i] = in ? __ldcg(pl + c0 + i) : 0.f;
-            }
-            float nmax = gmax;
-#pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) nmax = fmaxf(nmax, mm[i]);
-            const float ko = __expf(gmax - nmax);                 // running update of flash_attn_reduce.comp:57-75
-            gsum *= ko; a.x *= ko; a.y *= ko; a.z *= ko; a.w *= ko;
-            gmax = nmax;
-#pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) {
-                const float kn = __expf(mm[i] - gmax);
-                gsum = fmaf(ll[i], kn, gsum);
-                a.x = fmaf(o[i].x, kn, a.x); a.y = fmaf(o[i].y, kn, a.y);
-                a.z = fmaf(o[i].z, kn, a.z); a.w = fmaf(o[i].w, kn, a.w);
-            }
-        }
-        if (p.out) {
+        if (p.out && mp.fan_merge == 0u) {
             const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;
-            *reinterpret_cast<float4 *>(p.out + row * D + d) = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+            *reinterpret_cast<float2 *>(p.out + row * D + d) = make_float2(a0 * inv, a1 * inv);
         }
         if (p.out_o) {
-            *reinterpret_cast<float4 *>(p.out_o + row * D + d) = a;
+            *reinterpret_cast<float2 *>(p.out_o + row * D + d) = make_float2(a0, a1);
             if (d == 0) { p.out_m[row] = gmax; p.out_l[row] = gsum; }
         }
-        if (fan) {            // the merged partial goes straight into every GPU's exchange buffer
-#pragma unroll
-            for (uint32_t r = 0; r < 8; ++r) {
-                if (r < s_fan.world) {
-                    uint64_t *dst = s_fan.base[r];
-                    fanout_store4(dst + fs.o + row * D + d, a, fs.epoch);
-                    if (d == 0) {
-                        fanout_store(dst + fs.m + row, gmax, fs.epoch);
-                        fanout_store(dst + fs.m + s_fan.n_rows + row, gsum, fs.epoch);
-                    }
+        if (fan) {
+            for (uint32_t r = 0; r < s_fan.world; ++r) {
+                uint64_t *dst = s_fan.base[r];
+                fanout_store2(dst + fs.o + row * D + d, a0, a1, fs.epoch);
+                if (d == 0) {
+                    fanout_store(dst + fs.m + row, gmax, fs.epoch);
+                    fanout_store(dst + fs.m + s_fan.n_rows + row, gsum, fs.epoch);
+                }
+            }
+        }
+    };
+
+    // ---- several splits: publish the partial, then every CTA merges one slice of the rows ----------
+    // The partial goes to the workspace as tagged words (one 16-byte store = two {value, tag}
+    // words); no fence and no flag follow, readers poll the words themselves until each carries
+    // this launch's tag.  The n_pairs output pairs are cut into n_splits slices and CTA i merges
+    // slice i over all splits (flash_attn_reduce.comp:51-80): one load round trip of a few KB per CTA
+    // instead of one CTA reading everything.  A CTA may only wait for CTAs that have started: it
+    // claims its slice if the ticket word showed, when it began to stream, that every CTA of the
+    // group had drawn (always true for the last drawer); otherwise it leaves the slice to the last
+    // drawer, which therefore never waits for a CTA that is not yet running.  Each CTA publishes
+    // that decision as one more tagged word.
+    // The loops below are deliberately rolled and spread over all threads (one (pair, split) item
+    // per thread, staged through shared memory): this code runs once per CTA from a cold
+    // instruction cache, where straight-line code costs more than the loads it issues.
+    const uint32_t tag = s_tag;
+    const bool merger = s_merger != 0u;
+    const uint64_t grp = uint64_t(s) * p.n_kv_heads + kvh;
+    const uint64_t pwords = uint64_t(g) * (D + 2) + 2;        // words of one CTA's partial: o[g][D], {m, l}[g], decision
+    uint64_t *const gp = mp.tag_part + grp * p.n_splits * pwords;
+    const uint32_t per = (n_pairs + p.n_splits - 1) / p.n_splits;
+    if (!direct) {
+        const bool claimed = merger || s_safe != 0u;
+        uint64_t *mine = gp + uint64_t(split) * pwords;
+        for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+            const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
+            float O0, O1, Mn, L;
+            cta_partial(j, d, O0, O1, Mn, L);
+            tagged_store2(mine + uint64_t(j) * D + d, O0, O1, tag);
+            if (d == 0) tagged_store2(mine + uint64_t(g) * D + 2 * j, Mn, L, tag);
+        }
+        if (threadIdx.x == 0) tagged_store2(mine + uint64_t(g) * (D + 2), claimed ? 1.0f : 0.0f, 0.f, tag);
+        VFKV_TRACE(7);
+        if (!claimed) return;
+        // the last drawer's last warp collects the other CTAs' decisions while the rest merge
+        if (merger && warp == uint32_t(kWarps) - 1u) {
+            for (uint32_t i = lane; i < p.n_splits; i += 32) {
+                const uint64_t *pd = gp + uint64_t(i) * pwords + uint64_t(g) * (D + 2);
+                uint64_t t0 = 0;
+                for (;;) {
+                    const ulonglong2 w = tagged_load2(pd);
+                    if (tags_are(w, tag)) { s_take[i] = (i != split && tagged_value(w.x) == 0.f) ? 1 : 0; break; }
+                    const uint64_t now = global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; s_take[i] = 0; break; }
+                    else __nanosleep(40);
                 }
             }
         }
     }
+    if (direct) {             // a single split: this CTA's partial is the local result
+        for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+            float a0, a1, gmax, gsum;
+            cta_partial(idx / HD2, 2 * (idx % HD2), a0, a1, gmax, gsum);
+            emit(idx, a0, a1, gmax, gsum);
+        }
+        VFKV_TRACE(8);
+        if (!(fan && mp.fan_merge != 0u)) { VFKV_TRACE(9); return; }
+    }
+    __syncthreads();          // the warps' partials are dead: the ring becomes the staging area
+
+    const bool xrank = fan && mp.fan_merge != 0u;
+    float4 *stg = reinterpret_cast<float4 *>(ring_ptr);          // items {o0, o1, m, l}
+    constexpr uint32_t kStageItems = S::RING_BYTES / 16;
+    // Pass 0: this CTA's slice (every pair when there is a single split).  Pass 1, last drawer only:
+    // the slices their owners left behind.
+    for (uint32_t pass = 0; pass < 2u; ++pass) {
+        uint32_t n_list = 1;
+        if (pass == 1u) {
+            if (direct || !merger) break;
+            if (threadIdx.x == 0) {
+                uint32_t n = 0;
+                for (uint32_t i = 0; i < p.n_splits; ++i)
+                    if (s_take[i]) s_take[n++] = uint8_t(i);          // compacted in place: n <= i
+                s_nlist = n;
+            }
+            __syncthreads();
+            n_list = s_nlist;
+            if (n_list == 0) break;
+        }
+        const uint32_t total_v = direct ? n_pairs : n_list * per;
+        const uint32_t parts_here = direct ? 1u : p.n_splits;
+        const uint32_t world_here = xrank ? s_fan.world : 1u;
+        const uint32_t chunk_v = max(1u, kStageItems / max(parts_here, world_here));
+        for (uint32_t v0 = 0; v0 < total_v; v0 += chunk_v) {
+            const uint32_t nv = min(chunk_v, total_v - v0);
+            // virtual index -> output pair (0xFFFFFFFF: beyond the last pair)
+            auto pair_of = [&](uint32_t v) -> uint32_t {
+                if (direct) return v;
+                const uint32_t sl = pass == 0u ? split : uint32_t(s_take[v / per]);
+                const uint32_t idx = sl * per + v % per;
+                return idx < n_pairs ? idx : 0xFFFFFFFFu;
+            };
+            if (!direct) {
+                // every thread fetches one (pair, split) item at a time; consecutive threads, consecutive pairs
+                for (uint32_t w = threadIdx.x; w < nv * p.n_splits; w += blockDim.x) {
+                    const uint32_t i = w / nv, vi = w % nv;
+                    const uint32_t idx = pair_of(v0 + vi);
+                    if (idx == 0xFFFFFFFFu) continue;
+                    const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
+                    const uint64_t *a_o = gp + uint64_t(i) * pwords + uint64_t(j) * D + d;
+                    const uint64_t *a_m = gp + uint64_t(i) * pwords + uint64_t(g) * D + 2 * j;
+                    ulonglong2 ow, mw;
+                    uint64_t t0 = 0;
+                    for (;;) {
+                        ow = tagged_load2(a_o);
+                        mw = tagged_load2(a_m);
+                        if (tags_are(ow, tag) && tags_are(mw, tag)) break;
+                        const uint64_t now = global_timer_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; break; }
+                        else __nanosleep(40);
+                    }
+                    stg[i * nv + vi] = make_float4(tagged_value(ow.x), tagged_value(ow.y), tagged_value(mw.x), tagged_value(mw.y));
+                }
+                __syncthreads();
+                if (s_flag == 3u) break;           // a partial of this launch never arrived (uniform: read after the barrier)
+            }
+            for (uint32_t vi = threadIdx.x; vi < nv && !direct; vi += blockDim.x) {
+                const uint32_t idx = pair_of(v0 + vi);
+                if (idx == 0xFFFFFFFFu) continue;
+                float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
+                for (uint32_t i = 0; i < p.n_splits; ++i) gmax = fmaxf(gmax, stg[i * nv + vi].z);
+                for (uint32_t i = 0; i < p.n_splits; ++i) {
+                    const float4 t = stg[i * nv + vi];
+                    const float kn = __expf(t.z - gmax);
+                    gsum = fmaf(t.w, kn, gsum);
+                    a0 = fmaf(t.x, kn, a0);
+                    a1 = fmaf(t.y, kn, a1);
+                }
+                emit(idx, a0, a1, gmax, gsum);
+            }
+            if (pass == 0u && v0 == 0 && !direct) VFKV_TRACE(8);
+            __syncthreads();                       // the staged items have been consumed
+            if (!xrank) continue;
+
+            // ---- position-sharded call: merge the blocks of all ranks for the same pairs ---------------
+            // Every rank's kernel stores its block of these rows into this GPU's buffer, this rank's
+            // own block included (emit above).  The words are polled, with the exchange's time limit,
+            // until they carry the exchange number; then the same merge runs over one part per rank.
+            // Loads touch this GPU's memory only.
+            {
+                const uint64_t *local = s_fan.base[s_fan.rank];
+                const uint32_t e = fs.epoch, world = s_fan.world;
+                for (uint32_t w = threadIdx.x; w < nv * world; w += blockDim.x) {
+                    const uint32_t r = w / nv, vi = w % nv;
+                    const uint32_t idx = pair_of(v0 + vi);
+                    if (idx == 0xFFFFFFFFu) continue;
+                    const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
+                    const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
+                    const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
+                    ulonglong2 ow;
+                    uint64_t mw, lw;
+                    uint64_t t0 = 0;
+                    for (;;) {
+                        ow = tagged_load2_sys(local + rs.o + row * D + d);
+                        mw = tagged_load1_sys(local + rs.m + row);
+                        lw = tagged_load1_sys(local + rs.m + s_fan.n_rows + row);
+                        if (tags_are(ow, e) && uint32_t(mw >> 32) == e && uint32_t(lw >> 32) == e) break;
+                        const uint64_t now = global_timer_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > s_fan.wait_ns || *reinterpret_cast<volatile uint32_t *>(&s_flag) == 4u) { s_flag = 4u; ow.x = ow.y = 0ull; mw = fanout_word(kMaskedScore, e); lw = 0ull; break; }
+                        else __nanosleep(40);
+                    }
+                    stg[r * nv + vi] = make_float4(tagged_value(ow.x), tagged_value(ow.y), tagged_value(mw), tagged_value(lw));
+                }
+                __syncthreads();
+                const bool late = s_flag == 4u;
+                for (uint32_t vi = threadIdx.x; vi < nv; vi += blockDim.x) {
+                    const uint32_t idx = pair_of(v0 + vi);
+                    if (idx == 0xFFFFFFFFu) continue;
+                    const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
+                    const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
+                    float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
+                    if (!late) {
+                        for (uint32_t r = 0; r < world; ++r) gmax = fmaxf(gmax, stg[r * nv + vi].z);
+                        for (uint32_t r = 0; r < world; ++r) {
+                            const float4 t = stg[r * nv + vi];
+                            const float kn = __expf(t.z - gmax);
+                            gsum = fmaf(t.w, kn, gsum);
+                            a0 = fmaf(t.x, kn, a0);
+                            a1 = fmaf(t.y, kn, a1);
+                        }
+                    }
+                    const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;   // a rank that never answered: zeros, not garbage
+                    if (p.out) *reinterpret_cast<float2 *>(p.out + row * D + d) = make_float2(a0 * inv, a1 * inv);
+                }
+                __syncthreads();
+            }
+        }
+        if (direct || s_flag == 3u) break;
+    }
+    if (threadIdx.x == 0) {
+        if (s_flag == 3u) atomicOr(p.status, 1u);     // a partial of this launch never arrived; those rows keep their old contents
+        if (s_flag == 4u) atomicOr(p.status, 8u);     // a rank's block did not arrive in time; those rows are zeros
+    }
     VFKV_TRACE(9);
-    if (threadIdx.x == 0) mp.counters[s * p.n_kv_heads + kvh] = 0u;   // ready for the next launch
 }
+
 
 // ---- host side -------------------------------------------------------------------------------------
 
@@ -952,11 +1115,13 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
         return set_error(ctx, VFKV_ERR_UNSUPPORTED, "tuning does not fit in shared memory for this shape");
     } else {
         auto kern = attn_split_mma_kernel<DT, D, ROWS2, W, NS, CAP>;
-        static bool configured[64] = {};
-        if (!configured[ctx->device & 63]) {
+        // per device, shared by every context and thread: setting the attribute twice is harmless,
+        // the flag only saves the call
+        static std::atomic<bool> configured[64];
+        if (!configured[ctx->device & 63].load(std::memory_order_acquire)) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM_BYTES);
             if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tensor-core attention)");
-            configured[ctx->device & 63] = true;
+            configured[ctx->device & 63].store(true, std::memory_order_release);
         }
         dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
         {
@@ -981,9 +1146,10 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
             MmaParams lp = mp;
             constexpr int NH = (DT == VFKV_F8 || !ROWS2) ? 8 : 16;
             constexpr bool kFits = (W * NH * (D + 1) + 2 * W * NH + NH * D + 2 * NH) * 4 <= S::RING_BYTES;
-            if (kFits && ctx->cluster_merge && mp.a.n_splits >= 2 && mp.a.n_splits <= 16) {
-                static int max_clusters[64][17] = {};      // per device and cluster size; 0 = not asked yet, -1 = no
-                int &known = max_clusters[ctx->device & 63][mp.a.n_splits];
+            if (kFits && ctx->cluster_merge && mp.fan_merge == 0u && mp.a.n_splits >= 2 && mp.a.n_splits <= 16) {
+                static std::atomic<int> max_clusters[64][17];   // per device and cluster size; 0 = not asked yet, -1 = no
+                std::atomic<int> &slot_known = max_clusters[ctx->device & 63][mp.a.n_splits];
+                int known = slot_known.load(std::memory_order_acquire);
                 cudaLaunchAttribute &ca = attr[n_attr];
                 ca.id = cudaLaunchAttributeClusterDimension;
                 ca.val.clusterDim.x = mp.a.n_splits; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = 1;
@@ -996,6 +1162,7 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
                     int n = 0;
                     if (ok && cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) known = n;
                     cudaGetLastError();
+                    slot_known.store(known, std::memory_order_release);
                 }
                 const uint64_t clusters = uint64_t(mp.a.n_kv_heads) * mp.a.n_seqs;
                 if (known > 0 && clusters <= uint64_t(known)) lp.cluster = 1;
@@ -1078,28 +1245,44 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     }
     MmaParams mp;
     mp.a = make_params(ctx, ws, a, n_splits);
-    mp.counters = ws ? ws->counters : nullptr;
+    mp.tickets = ws ? ws->tickets : nullptr;
+    mp.tag_part = ws ? ws->tag_part : nullptr;
+    mp.merge_wait_ns = ctx->merge_wait_ns;
     mp.trace = ctx->d_trace;
-    mp.pdl = ctx->pdl;
+    // Mode 2 prefetches K/V before it waits for the kernel in front of it.  When that kernel was
+    // launched through this context and wrote rows of the very slab this call reads (the same layer
+    // twice in a row, or a layer that reads its publisher's slab right after the publisher's
+    // append), the prefetch has to wait as well.
+    mp.pdl = (ctx->pdl == 2u && (ctx->last_written_slab == a.kv.k || ctx->last_written_slab == kAnySlab)) ? 1u : ctx->pdl;
     mp.cluster = 0;
+    mp.fan_merge = (a.fan && a.fan_merge) ? 1u : 0u;
+    mp.fail_split = ctx->debug_fail_split;
     mp.k_new = a.k_new;
     mp.v_new = a.v_new;
     if ((reinterpret_cast<uintptr_t>(a.k_new) | reinterpret_cast<uintptr_t>(a.v_new)) % 16 != 0)
         return set_error(ctx, VFKV_ERR_INVALID, "new K/V rows must be 16-byte aligned");
-    if (n_splits > 1 && !mp.counters) return set_error(ctx, VFKV_ERR_INVALID, "workspace has no ticket counters");
+    if (n_splits > 1 && (!mp.tickets || !mp.tag_part)) return set_error(ctx, VFKV_ERR_INVALID, "workspace has no split-merge storage");
+    if (n_splits > 255) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "the tensor-core attention kernel merges at most 255 splits");
+    if (n_splits > 1 && uint64_t(a.seq.n_seqs) * n_splits * (a.n_q_heads * (uint64_t(D) + 2) + 2ull * a.kv.n_kv_heads) > ws->tag_words)
+        return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
     if (n_splits > 1 && uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads > ws->n_counters)
         return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
     const uint32_t g = a.n_q_heads / a.kv.n_kv_heads;
-    if (a.kv.dtype == VFKV_F8) {
-        if (D == 128) return launch_t<VFKV_F8, 128, false>(ctx, tk, tv, mp, st);
-        if (D == 256) return launch_t<VFKV_F8, 256, false>(ctx, tk, tv, mp, st);
-    } else {
-        const bool r2 = g > 8;
-        if (D == 64) return r2 ? launch_t<VFKV_F16, 64, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 64, false>(ctx, tk, tv, mp, st);
-        if (D == 128) return r2 ? launch_t<VFKV_F16, 128, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 128, false>(ctx, tk, tv, mp, st);
-        if (D == 256) return r2 ? launch_t<VFKV_F16, 256, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 256, false>(ctx, tk, tv, mp, st);
-    }
-    return set_error(ctx, VFKV_ERR_UNSUPPORTED, "shape outside the tensor-core attention kernel");
+    auto run = [&]() -> int32_t {
+        if (a.kv.dtype == VFKV_F8) {
+            if (D == 128) return launch_t<VFKV_F8, 128, false>(ctx, tk, tv, mp, st);
+            if (D == 256) return launch_t<VFKV_F8, 256, false>(ctx, tk, tv, mp, st);
+        } else {
+            const bool r2 = g > 8;
+            if (D == 64) return r2 ? launch_t<VFKV_F16, 64, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 64, false>(ctx, tk, tv, mp, st);
+            if (D == 128) return r2 ? launch_t<VFKV_F16, 128, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 128, false>(ctx, tk, tv, mp, st);
+            if (D == 256) return r2 ? launch_t<VFKV_F16, 256, true>(ctx, tk, tv, mp, st) : launch_t<VFKV_F16, 256, false>(ctx, tk, tv, mp, st);
+        }
+        return set_error(ctx, VFKV_ERR_UNSUPPORTED, "shape outside the tensor-core attention kernel");
+    };
+    const int32_t rc = run();
+    if (rc == VFKV_OK) ctx->last_written_slab = a.k_new ? a.kv.k : nullptr;
+    return rc;
 }
 
 // Pre-encodes the two tensor maps of one layer of a cache (host memory; reused by every call).

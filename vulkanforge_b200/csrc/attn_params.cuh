@@ -118,12 +118,47 @@ __device__ __forceinline__ void fanout_store(uint64_t *dst, float v, uint32_t ta
 {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(dst), "l"(fanout_word(v, tag)) : "memory");
 }
+// Two consecutive values as one 16-byte store of two tagged words (dst 16-byte aligned).  The vector
+// store is performed as two 8-byte accesses, each single-copy atomic, which is all a reader relies
+// on: it checks the tag of every word it uses.  System scope: the destination may be a peer GPU.
+__device__ __forceinline__ void fanout_store2(uint64_t *dst, float v0, float v1, uint32_t tag)
+{
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" :: "l"(dst), "l"(fanout_word(v0, tag)), "l"(fanout_word(v1, tag)) : "memory");
+}
 // four consecutive values (dst 16-byte aligned) as two 16-byte stores
 __device__ __forceinline__ void fanout_store4(uint64_t *dst, float4 v, uint32_t tag)
 {
-    asm volatile("st.global.v2.u64 [%0], {%1, %2};" :: "l"(dst), "l"(fanout_word(v.x, tag)), "l"(fanout_word(v.y, tag)) : "memory");
-    asm volatile("st.global.v2.u64 [%0], {%1, %2};" :: "l"(dst + 2), "l"(fanout_word(v.z, tag)), "l"(fanout_word(v.w, tag)) : "memory");
+    fanout_store2(dst, v.x, v.y, tag);
+    fanout_store2(dst + 2, v.z, v.w, tag);
 }
+// The same pair of tagged words inside this GPU's own memory (split partials of the workspace).
+__device__ __forceinline__ void tagged_store2(uint64_t *dst, float v0, float v1, uint32_t tag)
+{
+    asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" :: "l"(dst), "l"(fanout_word(v0, tag)), "l"(fanout_word(v1, tag)) : "memory");
+}
+__device__ __forceinline__ ulonglong2 tagged_load2(const uint64_t *src)
+{
+    ulonglong2 w;
+    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w.x), "=l"(w.y) : "l"(src) : "memory");
+    return w;
+}
+__device__ __forceinline__ ulonglong2 tagged_load2_sys(const uint64_t *src)
+{
+    ulonglong2 w;
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w.x), "=l"(w.y) : "l"(src) : "memory");
+    return w;
+}
+__device__ __forceinline__ uint64_t tagged_load1_sys(const uint64_t *src)
+{
+    uint64_t w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+    return w;
+}
+__device__ __forceinline__ bool tags_are(ulonglong2 w, uint32_t tag)
+{
+    return uint32_t(w.x >> 32) == tag && uint32_t(w.y >> 32) == tag;
+}
+__device__ __forceinline__ float tagged_value(uint64_t w) { return __uint_as_float(uint32_t(w)); }
 
 __device__ __forceinline__ float apply_softcap(float s, float cap)
 {

@@ -20,6 +20,11 @@ struct vfkv_ctx {
     uint32_t attn_impl = 0;            // 0 auto, 1 CUDA-core only, 2 tensor-core only, 3 as 0 but mma.sync instead of tcgen05 (prefill)
     uint32_t tune_warps = 0, tune_stages = 0;   // tensor-core kernel shape, 0 = choose
     uint32_t pdl = 0;                  // programmatic dependent launch mode of the attention kernel (0 / 1 / 2)
+    // Layer slab (K base address) that the last launch on this context wrote cache rows into, or
+    // null: a mode-2 launch that reads the same slab next waits before its K/V prefetch (mode 1).
+    const void *last_written_slab = nullptr;
+    uint64_t merge_wait_ns = 1000000000ull;   // limit of the merging CTA's wait for the other splits' partials
+    uint32_t debug_fail_split = 0xFFFFFFFFu;  // failure injection for tests (vfkv_ctx_debug_fail_split)
     uint32_t cluster_merge = 0;        // 1: merge the splits inside a thread-block cluster where the device allows it
     uint64_t launches = 0;
     unsigned long long *d_trace = nullptr;   // caller-owned device buffer for kernel phase timestamps, or null
@@ -47,8 +52,13 @@ struct vfkv_workspace {
     float *part_m = nullptr;    // [seq][q_head][split]
     float *part_l = nullptr;    // [seq][q_head][split]
     uint32_t *d_u32 = nullptr;  // staging for scalar-call slot/len/start and host-step arrays
-    uint32_t *counters = nullptr;   // split tickets of the fused merge, one per (sequence, kv-head); zero at rest
+    // Tensor-core kernel's split merge: one 64-bit ticket per (sequence, kv-head), {launch number << 8 |
+    // CTAs that have drawn}, never reset; and the split partials as 8-byte words {f32 value, u32 tag},
+    // tag = launch number + 1, so that a reader that finds the tag has the value.
+    unsigned long long *tickets = nullptr;
     uint64_t n_counters = 0;
+    uint64_t *tag_part = nullptr;   // [seq * kv_head][split][ o[g][head_dim] | {m, l}[g] | decision pair ] words
+    uint64_t tag_words = 0;
     uint64_t bytes = 0;
     // staging for vfkv_decode_token_host, grown on first use
     float *stage_in = nullptr;
@@ -113,6 +123,9 @@ struct PeerFanout {
     uint32_t world = 0;                // 0 = no fan-out
     uint32_t rank = 0;
     uint32_t n_rows = 0;               // sequences * q-heads
+    uint32_t pad = 0;
+    uint32_t *ctl = nullptr;           // [0] completed exchanges (== epoch), [1] ticket of the kernels that close an exchange
+    uint64_t wait_ns = 1000000000ull;  // limit of a wait for the other ranks' words
 };
 
 struct AttnArgs {
@@ -132,6 +145,9 @@ struct AttnArgs {
     const float *k_new = nullptr;
     const float *v_new = nullptr;
     const PeerFanout *fan = nullptr;   // device copy of the group's fan-out table, or null (tensor-core kernel only)
+    // with fan: the attention kernel also waits for the other ranks' blocks in its own buffer, merges
+    // them and writes the final rows to `out` (one launch per layer); otherwise vfkv_exchange_merge does
+    bool fan_merge = false;
 };
 
 // Brackets one kernel launch with a pair of events on its stream while profiling is on.
@@ -198,6 +214,9 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
 // merges ws partials [seq][head][split] into a.out (normalised) or a.out_{m,l,o}
 int32_t launch_merge_ws(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, uint32_t n_splits,
                         cudaStream_t st);
+
+// vfkv_ctx::last_written_slab after a store whose destination is a raw pointer.
+static const void *const kAnySlab = reinterpret_cast<const void *>(~uintptr_t(0));
 
 // Sentinel of vk_shaders/flash_attn_split.comp:104 for masked scores.
 constexpr float kMaskedScore = -1e30f;

@@ -194,6 +194,8 @@ int32_t vfkv_exchange_create(vfkv_ctx *ctx, uint32_t world, uint32_t rank, uint3
     }
     ex->fan.world = world; ex->fan.rank = rank; ex->fan.n_rows = n_rows;
     ex->fan.epoch = ex->ctl;
+    ex->fan.ctl = ex->ctl;
+    ex->fan.wait_ns = ex->wait_ns;
     ex->fan.base[rank] = ex->local;
     if (cudaMalloc(&ex->d_fan, sizeof(PeerFanout)) != cudaSuccess ||
         cudaMemcpy(ex->d_fan, &ex->fan, sizeof(PeerFanout), cudaMemcpyHostToDevice) != cudaSuccess) {
@@ -269,7 +271,10 @@ int32_t vfkv_exchange_set_timeout_ms(vfkv_exchange *ex, uint32_t ms)
 {
     if (!ex || ms == 0 || ms > 10000) return VFKV_ERR_INVALID;
     ex->wait_ns = uint64_t(ms) * 1000000ull;
-    return VFKV_OK;
+    ex->fan.wait_ns = ex->wait_ns;
+    Guard g(ex->ctx->device);
+    return check_cuda(ex->ctx, cudaMemcpy(ex->d_fan, &ex->fan, sizeof(PeerFanout), cudaMemcpyHostToDevice),
+                      "vfkv_exchange_set_timeout_ms");
 }
 
 uint32_t vfkv_exchange_ready(const vfkv_exchange *ex)

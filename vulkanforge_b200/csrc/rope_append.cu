@@ -170,6 +170,7 @@ static int32_t launch_rope_append_t(vfkv_ctx *ctx, const RopeAppendParams &p, cu
     ProfScope ps(ctx, VFKV_PROF_KV_STORE, st);
     rope_append_kernel<DT><<<dim3(unsigned(blocks), 2), 256, 0, st>>>(p);
     ctx->launches++;
+    ctx->last_written_slab = p.k_dst;
     return check_cuda(ctx, cudaGetLastError(), "rope_append launch");
 }
 

@@ -125,6 +125,20 @@ class Context:
         """Merge the splits of a (sequence, kv-head) inside a thread-block cluster where possible."""
         self.check(self._lib.vfkv_ctx_set_cluster_merge(self.handle, int(on)))
 
+    def set_dependent_launch(self, mode: int) -> None:
+        self.check(self._lib.vfkv_ctx_set_dependent_launch(self.handle, mode))
+
+    def set_attn_tuning(self, warps: int, stages: int) -> None:
+        self.check(self._lib.vfkv_ctx_set_attn_tuning(self.handle, warps, stages))
+
+    def set_merge_wait_ms(self, ms: int) -> None:
+        """Time limit of the merging CTA's wait for the other splits' partials."""
+        self.check(self._lib.vfkv_ctx_set_merge_wait_ms(self.handle, ms))
+
+    def debug_fail_split(self, split=None) -> None:
+        """Test hook: one CTA of later attention launches acts as if its TMA wait had run out."""
+        self.check(self._lib.vfkv_ctx_debug_fail_split(self.handle, 0xFFFFFFFF if split is None else split))
+
     def launch_count(self) -> int:
         return int(self._lib.vfkv_ctx_launch_count(self.handle))
 
@@ -146,6 +160,10 @@ class Workspace:
 
     def bytes(self) -> int:
         return int(self.ctx._lib.vfkv_workspace_bytes(self.handle))
+
+    def reset(self, stream=None) -> None:
+        """Zeroes the split tickets and partial tags (stream-ordered)."""
+        self.ctx.check(self.ctx._lib.vfkv_workspace_reset(self.handle, stream))
 
     def destroy(self) -> None:
         if self.handle:
