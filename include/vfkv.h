@@ -464,6 +464,11 @@ int32_t vfkv_ctx_set_merge_wait_ms(vfkv_ctx *ctx, uint32_t ms);
  * merging CTA's own wait runs out as well.  Nothing faults or hangs.  0xFFFFFFFF = off (default). */
 int32_t vfkv_ctx_debug_fail_split(vfkv_ctx *ctx, uint32_t split);
 int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer);
+/* With n_blocks > 1 the k-th launch of the decode attention kernel after this call (or after the
+ * buffer was set) writes block k % n_blocks of the buffer, a block being 16 x 8 bytes per CTA of
+ * that launch's grid: the phases of consecutive layers of one token side by side, on the GPU's
+ * common nanosecond clock.  The blocks of one ring must belong to launches with equal grids. */
+int32_t vfkv_ctx_set_trace_ring(vfkv_ctx *ctx, uint32_t n_blocks);
 /* Kernels this context has launched since creation (for launch accounting). */
 uint64_t vfkv_ctx_launch_count(const vfkv_ctx *ctx);
 

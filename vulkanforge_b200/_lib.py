@@ -126,6 +126,7 @@ SIGNATURES = {
     "vfkv_ctx_set_merge_wait_ms": (i32, [vp, u32]),
     "vfkv_ctx_debug_fail_split": (i32, [vp, u32]),
     "vfkv_ctx_set_trace_buffer": (i32, [vp, vp]),
+    "vfkv_ctx_set_trace_ring": (i32, [vp, u32]),
     "vfkv_ctx_launch_count": (u64, [vp]),
     "vfkv_profile_enable": (i32, [vp, i32]),
     "vfkv_profile_collect": (i32, [vp, u32, C.POINTER(u64), C.POINTER(C.c_double), C.POINTER(C.c_double), i32]),

@@ -213,6 +213,15 @@ int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer)
 {
     if (!ctx) return VFKV_ERR_INVALID;
     ctx->d_trace = static_cast<unsigned long long *>(d_buffer);
+    ctx->trace_seq = 0;
+    return VFKV_OK;
+}
+
+int32_t vfkv_ctx_set_trace_ring(vfkv_ctx *ctx, uint32_t n_blocks)
+{
+    if (!ctx || n_blocks == 0) return VFKV_ERR_INVALID;
+    ctx->trace_ring = n_blocks;
+    ctx->trace_seq = 0;
     return VFKV_OK;
 }
 
@@ -468,8 +477,8 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->d_u32), u32_bytes);
     ws->n_counters = rows;
     ws->tag_words = parts * (uint64_t(head_dim) + 4);     // o, {m, l} and one decision pair per CTA (kv-heads <= q-heads)
-    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->tickets), rows * 8);
-    if (e == cudaSuccess) e = cudaMemset(ws->tickets, 0, rows * 8);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->tickets), rows * 256 * 8);
+    if (e == cudaSuccess) e = cudaMemset(ws->tickets, 0, rows * 256 * 8);
     // tag 0 is never used by a launch, so zeroed words read as "not there yet"
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->tag_part), ws->tag_words * 8);
     if (e == cudaSuccess) e = cudaMemset(ws->tag_part, 0, ws->tag_words * 8);
@@ -480,7 +489,7 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
         delete ws;
         return check_cuda(ctx, e, "vfkv_workspace_create: cudaMalloc");
     }
-    ws->bytes = ofl + parts * 8 + u32_bytes + rows * 8 + ws->tag_words * 8;
+    ws->bytes = ofl + parts * 8 + u32_bytes + rows * 256 * 8 + ws->tag_words * 8;
     *out = ws;
     return VFKV_OK;
 }
@@ -505,7 +514,7 @@ int32_t vfkv_workspace_reset(vfkv_workspace *ws, void *stream)
 {
     if (!ws) return VFKV_ERR_INVALID;
     DeviceGuard g(ws->ctx->device);
-    cudaError_t e = cudaMemsetAsync(ws->tickets, 0, ws->n_counters * 8, as_stream(stream));
+    cudaError_t e = cudaMemsetAsync(ws->tickets, 0, ws->n_counters * 256 * 8, as_stream(stream));
     if (e == cudaSuccess) e = cudaMemsetAsync(ws->tag_part, 0, ws->tag_words * 8, as_stream(stream));
     return check_cuda(ws->ctx, e, "vfkv_workspace_reset");
 }

@@ -150,13 +150,14 @@ __device__ __forceinline__ void split_f16x2(float x0, float x1, uint32_t &hi, ui
 
 struct MmaParams {
     AttnParams a;
-    // Split merge (n_splits > 1): one 64-bit ticket word per (sequence, kv-head), {launch number << 8 |
-    // CTAs of this launch that have drawn}, and the partials as tagged 8-byte words (see vfkv_workspace).
+    // Split merge (n_splits > 1): 256 64-bit ticket words per (sequence, kv-head), one per split count,
+    // and the partials as tagged 8-byte words (see vfkv_workspace).
     unsigned long long *tickets;
     uint64_t *tag_part;
     uint64_t merge_wait_ns;       // limit of the merging CTA's wait for the other splits' partials
+    uint32_t launch_seq;          // host-side count of split launches on this workspace (part of the tag)
     const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
-    unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0
+    unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0 (this launch's block of the buffer)
     uint32_t pdl;                 // 0 plain launch, 1 dependent launch, 2 dependent launch with early K/V prefetch
     uint32_t cluster;             // 1: the splits of a (sequence, kv-head) are one thread-block cluster
     uint32_t fan_merge;           // with a.fan: also wait for the other ranks' blocks and write the final rows
@@ -306,8 +307,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
     const uint32_t bars = ring + S::RING_BYTES;           // kWarps*kStages mbarriers, 8 bytes each
-    __shared__ uint32_t s_flag, s_epoch, s_tag, s_merger, s_safe, s_nlist;
-    __shared__ uint8_t s_take[256];       // slices the last drawer takes over (n_splits <= 255)
+    __shared__ uint32_t s_flag, s_epoch, s_tag, s_merger, s_safe, s_nlist, s_late, s_launch_no;
+    __shared__ uint8_t s_list[256];       // slices the last drawer takes over (n_splits <= 255)
     __shared__ PeerFanout s_fan;          // the group's fan-out table (position-sharded calls only)
 
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
@@ -316,23 +317,27 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t g = p.group;
 
     // ---- split ticket, drawn before anything else ----------------------------------------------
-    // The CTA of a (sequence, kv-head) that draws the last ticket of a launch will merge the splits;
-    // the launch number in the word's upper bits is the tag of this launch's partials.  The last
-    // drawer also rolls the word over to the next launch.  Nothing waits on a ticket, and a CTA
-    // draws before its first bounded wait, so the word is always complete at the end of a launch.
-    // The tickets belong to the workspace and are only touched here, at the start of CTAs; a
-    // dependent launch lets its successor start only after every CTA has passed the barrier
-    // below, so launches never interleave their tickets.
+    // Every CTA of a (sequence, kv-head) draws a ticket from a 64-bit word that only ever counts up;
+    // there is one word per split count, so ticket / n_splits is the number of the launch among
+    // those that used this word and ticket % n_splits the CTA's place in the draw.  The last
+    // drawer is the one CTA that never has to wonder whether the others have started.  The launch
+    // number, together with the host's count of launches on this workspace, is the tag of this
+    // launch's partials.  Nothing waits on a ticket and nothing resets one, and a CTA draws before
+    // its first bounded wait, so the words are always consistent.  The result is published to the
+    // CTA before the barrier below; only after that barrier may a dependent launch start, so two
+    // launches never interleave their draws.
     if (threadIdx.x == 32) {
-        uint32_t tag = 0u, merger = 0u;
+        uint32_t tag = 0u, merger = 0u, launch_no = 0u;
         if (p.n_splits > 1u && mp.cluster == 0u) {
-            unsigned long long *tk = mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh);
-            const unsigned long long old = atomicAdd(tk, 1ull);
-            tag = uint32_t(old >> 8) + 1u;
-            merger = uint32_t(old & 0xFFull) == p.n_splits - 1u ? 1u : 0u;
-            if (merger) atomicAdd(tk, 256ull - p.n_splits);
+            const unsigned long long old =
+                atomicAdd(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh) * 256u + p.n_splits, 1ull);
+            launch_no = uint32_t(old / p.n_splits);
+            merger = uint32_t(old % p.n_splits) == p.n_splits - 1u ? 1u : 0u;
+            // never 0, the value of a cleared workspace; launches that share a host count are replays
+            // of one graph node (same addresses), which the device-side number tells apart
+            tag = 0x80000000u | ((mp.launch_seq & 0x7FFFu) << 16) | (launch_no & 0xFFFFu);
         }
-        s_tag = tag; s_merger = merger;
+        s_tag = tag; s_merger = merger; s_launch_no = launch_no;
     }
 
     // Q is fetched first: its address depends on the block index only, so these loads overlap the
@@ -405,6 +410,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         for (int i = 0; i < kWarps * kStages; ++i) mbar_init(bars + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_flag = 0;
+        s_late = 0;
+        s_nlist = 0;
     }
 
     __syncthreads();
@@ -533,7 +540,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     unsigned long long ticket_now = 0ull;
     if (threadIdx.x == 0 && p.n_splits > 1u && mp.cluster == 0u)
         asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(ticket_now)
-                     : "l"(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh)) : "memory");
+                     : "l"(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh) * 256u + p.n_splits) : "memory");
     VFKV_TRACE(3);
 
     // Lane-constant parts of the swizzled shared-memory addresses (tile_addr with the tile base
@@ -708,8 +715,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (timed_out) {
         if (lane == 0) { atomicOr(p.status, 1u); s_flag = 1; }
     }
-    if (threadIdx.x == 0)     // the word has moved on to the next launch, or counts all of this launch's CTAs
-        s_safe = (uint32_t(ticket_now >> 8) + 1u != s_tag || uint32_t(ticket_now & 0xFFull) >= p.n_splits) ? 1u : 0u;
+    if (threadIdx.x == 0)     // had every CTA of this launch drawn when this CTA began to stream?
+        s_safe = ticket_now >= (uint64_t(s_launch_no) + 1u) * p.n_splits ? 1u : 0u;
     __syncthreads();          // all tiles consumed (or abandoned): the ring is free for the merge
     VFKV_TRACE(6);
     const bool gave_up = s_flag != 0u;
@@ -895,9 +902,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // group had drawn (always true for the last drawer); otherwise it leaves the slice to the last
     // drawer, which therefore never waits for a CTA that is not yet running.  Each CTA publishes
     // that decision as one more tagged word.
-    // The loops below are deliberately rolled and spread over all threads (one (pair, split) item
-    // per thread, staged through shared memory): this code runs once per CTA from a cold
-    // instruction cache, where straight-line code costs more than the loads it issues.
+    // The work is spread over all threads, one (pair, split) item each, and combined with shuffles:
+    // this tail runs once per CTA with nothing to overlap it, so its cost is the length of its
+    // longest dependent chain (a thread that walks 16 splits by itself costs about 1 us more than
+    // 16 lanes that fetch one split each).
     const uint32_t tag = s_tag;
     const bool merger = s_merger != 0u;
     const uint64_t grp = uint64_t(s) * p.n_kv_heads + kvh;
@@ -917,20 +925,30 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         if (threadIdx.x == 0) tagged_store2(mine + uint64_t(g) * (D + 2), claimed ? 1.0f : 0.0f, 0.f, tag);
         VFKV_TRACE(7);
         if (!claimed) return;
-        // the last drawer's last warp collects the other CTAs' decisions while the rest merge
+        // The last drawer's last warp collects the other CTAs' decisions while the rest merge, and
+        // leaves the list of slices nobody claimed (usually empty) in shared memory.
         if (merger && warp == uint32_t(kWarps) - 1u) {
-            for (uint32_t i = lane; i < p.n_splits; i += 32) {
-                const uint64_t *pd = gp + uint64_t(i) * pwords + uint64_t(g) * (D + 2);
-                uint64_t t0 = 0;
-                for (;;) {
-                    const ulonglong2 w = tagged_load2(pd);
-                    if (tags_are(w, tag)) { s_take[i] = (i != split && tagged_value(w.x) == 0.f) ? 1 : 0; break; }
-                    const uint64_t now = global_timer_ns();
-                    if (t0 == 0) t0 = now;
-                    else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; s_take[i] = 0; break; }
-                    else __nanosleep(40);
+            uint32_t n = 0;
+            for (uint32_t c = 0; c < p.n_splits; c += 32) {
+                const uint32_t i = c + lane;
+                bool orphan = false;
+                if (i < p.n_splits) {
+                    const uint64_t *pd = gp + uint64_t(i) * pwords + uint64_t(g) * (D + 2);
+                    uint64_t t0 = 0;
+                    for (;;) {
+                        const ulonglong2 w = tagged_load2(pd);
+                        if (tags_are(w, tag)) { orphan = i != split && tagged_value(w.x) == 0.f; break; }
+                        const uint64_t now = global_timer_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; break; }
+                        else __nanosleep(40);
+                    }
                 }
+                const uint32_t mask = __ballot_sync(0xffffffffu, orphan);
+                if (orphan) s_list[n + __popc(mask & ((1u << lane) - 1u))] = uint8_t(i);
+                n += __popc(mask);
             }
+            if (lane == 0) s_nlist = n;
         }
     }
     if (direct) {             // a single split: this CTA's partial is the local result
@@ -947,20 +965,31 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const bool xrank = fan && mp.fan_merge != 0u;
     float4 *stg = reinterpret_cast<float4 *>(ring_ptr);          // items {o0, o1, m, l}
     constexpr uint32_t kStageItems = S::RING_BYTES / 16;
+    // Merge of up to 32 parts per output pair without shared memory: the parts of a pair sit in
+    // neighbouring lanes (groups of P lanes, P a power of two), which combine them with shuffles:
+    // the maximum first, then the weighted sums (flash_attn_reduce.comp:57-75).  Lane 0 of a group
+    // ends up with the pair's merged (o0, o1, m, l).  Lanes without a part pass m = -1e30, l = 0.
+    auto group_merge = [&](uint32_t P, float &o0, float &o1, float &m, float &l) {
+        float gm = m;
+        for (uint32_t off = P >> 1; off != 0; off >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, off));
+        const float kn = __expf(m - gm);
+        o0 *= kn; o1 *= kn; l *= kn;
+        for (uint32_t off = P >> 1; off != 0; off >>= 1) {
+            o0 += __shfl_xor_sync(0xffffffffu, o0, off);
+            o1 += __shfl_xor_sync(0xffffffffu, o1, off);
+            l += __shfl_xor_sync(0xffffffffu, l, off);
+        }
+        m = gm;
+    };
+    auto pow2_at_least = [](uint32_t n) { uint32_t q = 1; while (q < n) q <<= 1; return q; };
+
     // Pass 0: this CTA's slice (every pair when there is a single split).  Pass 1, last drawer only:
     // the slices their owners left behind.
     for (uint32_t pass = 0; pass < 2u; ++pass) {
         uint32_t n_list = 1;
         if (pass == 1u) {
             if (direct || !merger) break;
-            if (threadIdx.x == 0) {
-                uint32_t n = 0;
-                for (uint32_t i = 0; i < p.n_splits; ++i)
-                    if (s_take[i]) s_take[n++] = uint8_t(i);          // compacted in place: n <= i
-                s_nlist = n;
-            }
-            __syncthreads();
-            n_list = s_nlist;
+            n_list = s_nlist;                      // written before the barrier above
             if (n_list == 0) break;
         }
         const uint32_t total_v = direct ? n_pairs : n_list * per;
@@ -972,112 +1001,125 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             // virtual index -> output pair (0xFFFFFFFF: beyond the last pair)
             auto pair_of = [&](uint32_t v) -> uint32_t {
                 if (direct) return v;
-                const uint32_t sl = pass == 0u ? split : uint32_t(s_take[v / per]);
+                const uint32_t sl = pass == 0u ? split : uint32_t(s_list[v / per]);
                 const uint32_t idx = sl * per + v % per;
                 return idx < n_pairs ? idx : 0xFFFFFFFFu;
             };
-            if (!direct) {
-                // every thread fetches one (pair, split) item at a time; consecutive threads, consecutive pairs
+            // one (pair, split) item: poll its words until they carry this launch's tag
+            auto fetch_part = [&](uint32_t idx, uint32_t i, float &o0, float &o1, float &m, float &l) {
+                const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
+                const uint64_t *a_o = gp + uint64_t(i) * pwords + uint64_t(j) * D + d;
+                const uint64_t *a_m = gp + uint64_t(i) * pwords + uint64_t(g) * D + 2 * j;
+                uint64_t t0 = 0;
+                for (;;) {
+                    // two requests a quarter of a round trip apart: the CTAs of a group finish within
+                    // a few hundred ns of one another, so the second often finds what the first missed
+                    ulonglong2 ow = tagged_load2(a_o), mw = tagged_load2(a_m);
+                    __nanosleep(200);
+                    const ulonglong2 ow2 = tagged_load2(a_o), mw2 = tagged_load2(a_m);
+                    if (!(tags_are(ow, tag) && tags_are(mw, tag))) { ow = ow2; mw = mw2; }
+                    if (tags_are(ow, tag) && tags_are(mw, tag)) {
+                        o0 = tagged_value(ow.x); o1 = tagged_value(ow.y); m = tagged_value(mw.x); l = tagged_value(mw.y);
+                        return;
+                    }
+                    const uint64_t now = global_timer_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; return; }
+                    else __nanosleep(40);
+                }
+            };
+            if (!direct && p.n_splits <= 32u) {
+                const uint32_t P = pow2_at_least(p.n_splits), ppw = 32u / P;       // pairs per warp and step
+                for (uint32_t b = warp * ppw; b < nv; b += uint32_t(kWarps) * ppw) {
+                    const uint32_t vi = b + lane / P, i = lane % P;
+                    const uint32_t idx = vi < nv ? pair_of(v0 + vi) : 0xFFFFFFFFu;
+                    const bool active = idx != 0xFFFFFFFFu && i < p.n_splits;
+                    float o0 = 0.f, o1 = 0.f, m = kMaskedScore, l = 0.f;
+                    if (active) fetch_part(idx, i, o0, o1, m, l);
+                    group_merge(P, o0, o1, m, l);
+                    if (active && i == 0u) emit(idx, o0, o1, m, l);
+                }
+            } else if (!direct) {
+                // more than 32 splits: the items of a chunk are staged in shared memory
                 for (uint32_t w = threadIdx.x; w < nv * p.n_splits; w += blockDim.x) {
                     const uint32_t i = w / nv, vi = w % nv;
                     const uint32_t idx = pair_of(v0 + vi);
                     if (idx == 0xFFFFFFFFu) continue;
-                    const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
-                    const uint64_t *a_o = gp + uint64_t(i) * pwords + uint64_t(j) * D + d;
-                    const uint64_t *a_m = gp + uint64_t(i) * pwords + uint64_t(g) * D + 2 * j;
-                    ulonglong2 ow, mw;
-                    uint64_t t0 = 0;
-                    for (;;) {
-                        ow = tagged_load2(a_o);
-                        mw = tagged_load2(a_m);
-                        if (tags_are(ow, tag) && tags_are(mw, tag)) break;
-                        const uint64_t now = global_timer_ns();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; break; }
-                        else __nanosleep(40);
-                    }
-                    stg[i * nv + vi] = make_float4(tagged_value(ow.x), tagged_value(ow.y), tagged_value(mw.x), tagged_value(mw.y));
+                    float o0 = 0.f, o1 = 0.f, m = kMaskedScore, l = 0.f;
+                    fetch_part(idx, i, o0, o1, m, l);
+                    stg[i * nv + vi] = make_float4(o0, o1, m, l);
                 }
                 __syncthreads();
-                if (s_flag == 3u) break;           // a partial of this launch never arrived (uniform: read after the barrier)
-            }
-            for (uint32_t vi = threadIdx.x; vi < nv && !direct; vi += blockDim.x) {
-                const uint32_t idx = pair_of(v0 + vi);
-                if (idx == 0xFFFFFFFFu) continue;
-                float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
-                for (uint32_t i = 0; i < p.n_splits; ++i) gmax = fmaxf(gmax, stg[i * nv + vi].z);
-                for (uint32_t i = 0; i < p.n_splits; ++i) {
-                    const float4 t = stg[i * nv + vi];
-                    const float kn = __expf(t.z - gmax);
-                    gsum = fmaf(t.w, kn, gsum);
-                    a0 = fmaf(t.x, kn, a0);
-                    a1 = fmaf(t.y, kn, a1);
+                for (uint32_t vi = threadIdx.x; vi < nv; vi += blockDim.x) {
+                    const uint32_t idx = pair_of(v0 + vi);
+                    if (idx == 0xFFFFFFFFu) continue;
+                    float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+                    for (uint32_t i = 0; i < p.n_splits; ++i) gmax = fmaxf(gmax, stg[i * nv + vi].z);
+#pragma unroll 4
+                    for (uint32_t i = 0; i < p.n_splits; ++i) {
+                        const float4 t = stg[i * nv + vi];
+                        const float kn = __expf(t.z - gmax);
+                        gsum = fmaf(t.w, kn, gsum);
+                        a0 = fmaf(t.x, kn, a0);
+                        a1 = fmaf(t.y, kn, a1);
+                    }
+                    emit(idx, a0, a1, gmax, gsum);
                 }
-                emit(idx, a0, a1, gmax, gsum);
+                __syncthreads();                   // the staged items have been consumed
             }
             if (pass == 0u && v0 == 0 && !direct) VFKV_TRACE(8);
-            __syncthreads();                       // the staged items have been consumed
             if (!xrank) continue;
 
             // ---- position-sharded call: merge the blocks of all ranks for the same pairs ---------------
             // Every rank's kernel stores its block of these rows into this GPU's buffer, this rank's
             // own block included (emit above).  The words are polled, with the exchange's time limit,
-            // until they carry the exchange number; then the same merge runs over one part per rank.
-            // Loads touch this GPU's memory only.
+            // until they carry the exchange number; then the same merge runs over one part per rank
+            // (at most 8, so a group of lanes holds them).  Loads touch this GPU's memory only.
             {
                 const uint64_t *local = s_fan.base[s_fan.rank];
                 const uint32_t e = fs.epoch, world = s_fan.world;
-                for (uint32_t w = threadIdx.x; w < nv * world; w += blockDim.x) {
-                    const uint32_t r = w / nv, vi = w % nv;
-                    const uint32_t idx = pair_of(v0 + vi);
-                    if (idx == 0xFFFFFFFFu) continue;
-                    const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
-                    const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
-                    const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
-                    ulonglong2 ow;
-                    uint64_t mw, lw;
-                    uint64_t t0 = 0;
-                    for (;;) {
-                        ow = tagged_load2_sys(local + rs.o + row * D + d);
-                        mw = tagged_load1_sys(local + rs.m + row);
-                        lw = tagged_load1_sys(local + rs.m + s_fan.n_rows + row);
-                        if (tags_are(ow, e) && uint32_t(mw >> 32) == e && uint32_t(lw >> 32) == e) break;
-                        const uint64_t now = global_timer_ns();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > s_fan.wait_ns || *reinterpret_cast<volatile uint32_t *>(&s_flag) == 4u) { s_flag = 4u; ow.x = ow.y = 0ull; mw = fanout_word(kMaskedScore, e); lw = 0ull; break; }
-                        else __nanosleep(40);
-                    }
-                    stg[r * nv + vi] = make_float4(tagged_value(ow.x), tagged_value(ow.y), tagged_value(mw), tagged_value(lw));
-                }
-                __syncthreads();
-                const bool late = s_flag == 4u;
-                for (uint32_t vi = threadIdx.x; vi < nv; vi += blockDim.x) {
-                    const uint32_t idx = pair_of(v0 + vi);
-                    if (idx == 0xFFFFFFFFu) continue;
-                    const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
-                    const uint64_t row = uint64_t(s) * p.n_q_heads + kvh * g + j;
-                    float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
-                    if (!late) {
-                        for (uint32_t r = 0; r < world; ++r) gmax = fmaxf(gmax, stg[r * nv + vi].z);
-                        for (uint32_t r = 0; r < world; ++r) {
-                            const float4 t = stg[r * nv + vi];
-                            const float kn = __expf(t.z - gmax);
-                            gsum = fmaf(t.w, kn, gsum);
-                            a0 = fmaf(t.x, kn, a0);
-                            a1 = fmaf(t.y, kn, a1);
+                const uint32_t P = pow2_at_least(world), ppw = 32u / P;
+                for (uint32_t b = warp * ppw; b < nv; b += uint32_t(kWarps) * ppw) {
+                    const uint32_t vi = b + lane / P, r = lane % P;
+                    const uint32_t idx = vi < nv ? pair_of(v0 + vi) : 0xFFFFFFFFu;
+                    const bool active = idx != 0xFFFFFFFFu && r < world;
+                    float o0 = 0.f, o1 = 0.f, m = kMaskedScore, l = 0.f;
+                    uint64_t row = 0;
+                    uint32_t d = 0;
+                    if (active) {
+                        d = 2 * (idx % HD2);
+                        row = uint64_t(s) * p.n_q_heads + kvh * g + idx / HD2;
+                        const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
+                        uint64_t t0 = 0;
+                        for (;;) {
+                            const ulonglong2 ow = tagged_load2_sys(local + rs.o + row * D + d);
+                            const uint64_t mw = tagged_load1_sys(local + rs.m + row);
+                            const uint64_t lw = tagged_load1_sys(local + rs.m + s_fan.n_rows + row);
+                            if (tags_are(ow, e) && uint32_t(mw >> 32) == e && uint32_t(lw >> 32) == e) {
+                                o0 = tagged_value(ow.x); o1 = tagged_value(ow.y); m = tagged_value(mw); l = tagged_value(lw);
+                                break;
+                            }
+                            const uint64_t now = global_timer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > s_fan.wait_ns || *reinterpret_cast<volatile uint32_t *>(&s_late) != 0u) { s_late = 1u; break; }
+                            else __nanosleep(40);
                         }
                     }
-                    const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;   // a rank that never answered: zeros, not garbage
-                    if (p.out) *reinterpret_cast<float2 *>(p.out + row * D + d) = make_float2(a0 * inv, a1 * inv);
+                    group_merge(P, o0, o1, m, l);
+                    // a rank that never answered: the row is written as zeros, not as a partial sum
+                    const bool late = *reinterpret_cast<volatile uint32_t *>(&s_late) != 0u;
+                    const float inv = (l > 0.f && !late) ? 1.0f / l : 0.f;
+                    if (active && r == 0u && p.out) *reinterpret_cast<float2 *>(p.out + row * D + d) = make_float2(o0 * inv, o1 * inv);
                 }
-                __syncthreads();
             }
         }
-        if (direct || s_flag == 3u) break;
+        if (direct || *reinterpret_cast<volatile uint32_t *>(&s_flag) == 3u) break;
     }
+    __syncthreads();
     if (threadIdx.x == 0) {
-        if (s_flag == 3u) atomicOr(p.status, 1u);     // a partial of this launch never arrived; those rows keep their old contents
-        if (s_flag == 4u) atomicOr(p.status, 8u);     // a rank's block did not arrive in time; those rows are zeros
+        if (s_flag == 3u) atomicOr(p.status, 1u);     // a partial of this launch never arrived; rows may be incomplete
+        if (s_late != 0u) atomicOr(p.status, 8u);     // a rank's block did not arrive in time; rows are zeros
     }
     VFKV_TRACE(9);
 }
@@ -1248,7 +1290,12 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     mp.tickets = ws ? ws->tickets : nullptr;
     mp.tag_part = ws ? ws->tag_part : nullptr;
     mp.merge_wait_ns = ctx->merge_wait_ns;
+    mp.launch_seq = (ws && n_splits > 1) ? ws->launch_seq++ : 0u;
     mp.trace = ctx->d_trace;
+    if (ctx->d_trace && ctx->trace_ring > 1) {      // successive launches write successive blocks of the buffer
+        const uint64_t ctas = uint64_t(n_splits) * a.kv.n_kv_heads * a.seq.n_seqs;
+        mp.trace = ctx->d_trace + (ctx->trace_seq++ % ctx->trace_ring) * ctas * 16;
+    }
     // Mode 2 prefetches K/V before it waits for the kernel in front of it.  When that kernel was
     // launched through this context and wrote rows of the very slab this call reads (the same layer
     // twice in a row, or a layer that reads its publisher's slab right after the publisher's

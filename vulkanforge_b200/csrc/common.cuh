@@ -28,6 +28,8 @@ struct vfkv_ctx {
     uint32_t cluster_merge = 0;        // 1: merge the splits inside a thread-block cluster where the device allows it
     uint64_t launches = 0;
     unsigned long long *d_trace = nullptr;   // caller-owned device buffer for kernel phase timestamps, or null
+    uint32_t trace_ring = 1;                 // blocks in d_trace; launch k of the decode kernel writes block k % trace_ring
+    uint64_t trace_seq = 0;
     void *encode_tiled = nullptr;      // cuTensorMapEncodeTiled, resolved at run time
     // per-kernel GPU timing, the analogue of the reference's ShaderProfiler
     // (src/backend/vulkan/profiler.rs:28-187); off unless vfkv_profile_enable(ctx, 1)
@@ -52,13 +54,15 @@ struct vfkv_workspace {
     float *part_m = nullptr;    // [seq][q_head][split]
     float *part_l = nullptr;    // [seq][q_head][split]
     uint32_t *d_u32 = nullptr;  // staging for scalar-call slot/len/start and host-step arrays
-    // Tensor-core kernel's split merge: one 64-bit ticket per (sequence, kv-head), {launch number << 8 |
-    // CTAs that have drawn}, never reset; and the split partials as 8-byte words {f32 value, u32 tag},
-    // tag = launch number + 1, so that a reader that finds the tag has the value.
+    // Tensor-core kernel's split merge: per (sequence, kv-head) 256 ticket words, one per split count,
+    // that only count up (ticket / n_splits = launch number, ticket % n_splits = place in the draw);
+    // and the split partials as 8-byte words {f32 value, u32 tag}, the tag made of the host's launch
+    // count and the device-side launch number, so that a reader that finds the tag has the value.
     unsigned long long *tickets = nullptr;
     uint64_t n_counters = 0;
     uint64_t *tag_part = nullptr;   // [seq * kv_head][split][ o[g][head_dim] | {m, l}[g] | decision pair ] words
     uint64_t tag_words = 0;
+    uint32_t launch_seq = 0;        // split launches issued on this workspace (the host's half of a tag)
     uint64_t bytes = 0;
     // staging for vfkv_decode_token_host, grown on first use
     float *stage_in = nullptr;
