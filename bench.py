@@ -15,8 +15,12 @@ roofline  the attention split kernel: algorithmic KV bytes per launch / its mean
 cpu_baseline  the CPU oracle (a C port of the reference's CPU attention and store code, the
           reference itself is Rust and cannot be built here) on a bounded sample
 
-Under torchrun every rank runs the same workload on its own sequence(s) and GPU (sharding by
-sequence, no collective on the data path); times are the max over ranks.
+Under torchrun every rank runs the headline workload on its own sequence(s) and GPU (sharding
+by sequence, no collective on the data path; times are the max over ranks), and the two sharded
+configurations are measured as well -- the long context cut by position over the ranks (partials
+exchanged by peer stores inside the attention kernel, output checked against one GPU) and the
+ragged batch of 64 dealt out by sequence -- each beside its one-GPU time from the same run.  They
+are the last key of the line ("sharded").
 """
 from __future__ import annotations
 
@@ -56,8 +60,17 @@ DT = {"F32": 0, "F16": 1, "F8": 2}
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
-# captures summarised under profiles/ (attn_split_mma_fp8_*.md)
+# captures summarised under profiles/ (one file per kernel and workload; a capture cannot run inside
+# a timed run, so these are read off the summaries; workloads without a capture report null)
 NCU_TRAFFIC_BYTES = {"qwen3_8b_fp8_ctx8192_b1": 16_843_000, "batch64_fp8_ctx8192": 1_081_500_000}
+
+
+def config_of(name, w):
+    """The workload as both arms print it (identical dictionaries, so the two lines can be matched)."""
+    return {"workload": name, "n_layers": w["n_layers"], "n_q_heads": w["hq"], "n_kv_heads": w["hkv"],
+            "head_dim": w["d"], "kv_dtype": w["dtype"], "batch_per_gpu": w["batch"], "context": w["ctx"],
+            "n_splits": w["n_splits"], "softcap": w["softcap"], "windows": w["windows"],
+            "ragged": list(w["ragged"]) if "ragged" in w else None}
 
 
 def algorithmic_bytes(w, lens, layer):
@@ -190,7 +203,7 @@ def run_reference(args, w, rank, world):
     line = {"metric": METRIC, "value": us, "unit": UNIT, "impl": "reference", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt_s * 1e3 / args.steps,
             "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": args.workload, **{k: v for k, v in w.items() if k != "windows"}},
+            "data": "synthetic", "config": config_of(args.workload, w),
             "cpu_baseline": {"value": us, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -239,17 +252,20 @@ def cpu_baseline_sample(w, budget_s=12.0):
 
 # ----------------------------------------------------------------------------------------------
 class Job:
-    """Cache + inputs of one rank, resident on its GPU."""
+    """Cache + inputs of one rank, resident on its GPU.  `lens` overrides the workload's sequence
+    lengths (a rank's share of a ragged batch)."""
 
-    def __init__(self, w, device, seed, ctx=None):
+    def __init__(self, w, device, seed, ctx=None, lens=None):
         import torch
         import vulkanforge_b200 as vf
         self.vf, self.torch, self.w = vf, torch, w
         torch.cuda.set_device(device)
+        self.own_ctx = ctx is None
         self.ctx = ctx if ctx is not None else vf.Context(device)
         rng = np.random.default_rng(seed)
-        self.lens = make_lens(w, rng)
-        B, L = w["batch"], w["ctx"]
+        self.lens = list(lens) if lens is not None else make_lens(w, rng)
+        B, L = len(self.lens), w["ctx"]
+        self.batch = B
         self.cache = vf.KvCache(self.ctx, vf.KvCacheConfig(w["n_layers"], w["hkv"], w["d"], L, n_slots=B),
                                 vf.KvDtype[w["dtype"]])
         sliding = [i for i, x in enumerate(w["windows"] or []) if x]
@@ -292,7 +308,15 @@ class Job:
 
     def step(self):
         """One token: every layer's append + attention, recorded by one library call."""
-        self.fwd.decode_token(self.q, self.k, self.v, self.out, None, self.pos, self.w["batch"], self.max_len)
+        self.fwd.decode_token(self.q, self.k, self.v, self.out, None, self.pos, self.batch, self.max_len)
+
+    def count_launches(self):
+        n0 = self.ctx.launch_count()
+        with self.torch.cuda.stream(self.stream):
+            self.step()
+        self.torch.cuda.synchronize()
+        self.launches_per_step = self.ctx.launch_count() - n0       # kernels of libvfkv.so per token
+        return self.launches_per_step
 
     def capture(self):
         """Records one step into a CUDA graph, the counterpart of the reference's pre-recorded
@@ -305,11 +329,12 @@ class Job:
 
     def close(self):
         self.torch.cuda.synchronize()
+        self.graph = None
         self.fwd.workspace.destroy()
         self.cache.destroy()
 
     def step_host(self):
-        self.fwd.decode_token_host(self.h_q, self.h_k, self.h_v, self.h_out, self.h_pos, self.w["batch"])
+        self.fwd.decode_token_host(self.h_q, self.h_k, self.h_v, self.h_out, self.h_pos, self.batch)
 
     def h2d_bytes(self):
         return self.h_q.numel() * 4 + self.h_k.numel() * 4 + self.h_v.numel() * 4 + self.h_pos.nbytes
@@ -336,33 +361,87 @@ class Job:
         return res
 
 
-def batch64_roofline(ctx, args, peak):
-    """The same kernel where it is bandwidth-bound: 64 sequences x 8192 tokens, FP8, one layer
-    (1 GiB of K/V per launch, far beyond L2).  Device events around `steps` launches."""
+def timed_blocks(fn, stream, steps, warmup, dist=None, min_total_ms=500.0, max_blocks=400):
+    """`warmup` untimed calls, then blocks of exactly `steps` calls each, every block bracketed by
+    a barrier + synchronize on both sides and timed with CUDA events on `stream`; blocks repeat until
+    the timed regions add up to `min_total_ms` (so that clocks can be sampled under load).  With
+    several ranks every block's time is the maximum over the ranks.  Returns (median block ms, number
+    of blocks, total timed ms)."""
     import torch
-    w = WORKLOADS["batch64_fp8_ctx8192"]
-    job = None
-    try:
-        job = Job(w, ctx.device, seed=77, ctx=ctx)
-        with torch.cuda.stream(job.stream):
-            for _ in range(3):
-                job.step()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def block():
+        with torch.cuda.stream(stream):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for _ in range(args.steps):
-                job.step()
+            for _ in range(steps):
+                fn()
             e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        return ms
+
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            fn()
+    barrier()
+    first = block()
+    n_blocks = int(min(max_blocks, max(1, np.ceil(min_total_ms / max(first, 1e-3)))))   # same on every rank
+    blocks = [first] + [block() for _ in range(n_blocks - 1)]
+    return float(np.median(blocks)), len(blocks), float(np.sum(blocks))
+
+
+def roofline_of(w, lens, us_per_launch, peak, peak_kind, traffic=None):
+    """Roofline object of the attention kernel for launches that take `us_per_launch` on average."""
+    per_launch = float(np.mean([algorithmic_bytes(w, lens, l) for l in range(w["n_layers"])]))
+    achieved = per_launch / (us_per_launch * 1e-6) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": traffic, "algorithmic_bytes_per_launch": per_launch, "mean_launch_us": us_per_launch,
+            "peak_source": f"{peak_kind} copy bandwidth", "frac_of_8000_nominal": achieved / 8000.0}
+
+
+def measure_workload(name, device, args, ctx=None, lens=None, seed=77, min_total_ms=200.0):
+    """One GPU, one workload: a CUDA graph of one token (every layer's fused kernel), device-timed.
+    Returns (us per token per layer, us per launch, job's sequence lengths, launches per step)."""
+    import torch
+    w = dict(WORKLOADS[name])
+    job = Job(w, device, seed=seed, ctx=ctx, lens=lens)
+    try:
+        job.ctx.set_dependent_launch(args.pdl)
+        with torch.cuda.stream(job.stream):
+            for _ in range(2):
+                job.step()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / args.steps
-        nbytes = algorithmic_bytes(w, job.lens, 0)
-        achieved = nbytes / (us * 1e-6) / 1e9
-        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES["batch64_fp8_ctx8192"], "algorithmic_bytes_per_launch": nbytes,
-                "mean_launch_us": us, "frac_of_8000_nominal": achieved / 8000.0,
-                "workload": "batch64_fp8_ctx8192: 64 sequences x 8192 tokens, 32 q / 8 kv / 128, FP8, 1 layer"}
+        launches = job.count_launches()
+        job.capture()
+        ms, _, _ = timed_blocks(job.graph.replay, job.stream, args.steps, 3, None, min_total_ms)
+        job.ctx.poll()
+        us_step = ms * 1e3 / args.steps
+        return us_step / (job.batch * w["n_layers"]), us_step / max(launches, 1), job.lens, launches
     finally:
-        if job is not None:
-            job.close()
+        job.close()
+
+
+def other_workloads(ctx, args, peak, peak_kind):
+    """The remaining configurations on one GPU, each with the roofline of its attention launches."""
+    out = {}
+    for name in ("llama3_8b_f16_ctx2048_b1", "batch64_fp8_ctx8192", "batch64_fp8_ragged_512_16384",
+                 "gemma_f16_ctx32768_b8", "long_fp8_ctx131072_b1"):
+        w = WORKLOADS[name]
+        us_tl, us_launch, lens, launches = measure_workload(name, ctx.device, args, ctx=ctx)
+        fused = launches == w["n_layers"]
+        out[name] = {"us_per_token_layer": us_tl, "launches_per_step": launches,
+                     "roofline": roofline_of(w, lens, us_launch, peak, peak_kind, NCU_TRAFFIC_BYTES.get(name))
+                     if fused else None}
+    return out
 
 
 def next_rows(ctx, args, peak, tensor_peak):
@@ -428,119 +507,274 @@ def next_rows(ctx, args, peak, tensor_peak):
 
 
 def run_probe(args):
-    """One kernel of the "next" rows on its own, for profiling: `--probe prefill` launches the
-    chunked-prefill attention `--steps` times (FP8, 32 q / 8 kv / 128, `--probe-m` queries ending
-    at position `--probe-ctx`); `--probe rope` the fused RoPE + append of a 512-token chunk."""
+    """One kernel on its own, for profiling (the commands of profiles/*.md).  `--probe prefill`: the
+    chunked-prefill attention (FP8, 32 q / 8 kv / 128, `--probe-m` queries ending at position
+    `--probe-ctx`); `rope`: RoPE fused with the append of a 512-token chunk; `append`: the plain
+    append of a 512-token chunk; `fp8_to_f16`: the cache read of `--probe-ctx` positions of one layer;
+    `generic`: the CUDA-core split kernel + merge kernel on an F32 cache of `--probe-ctx` positions;
+    `decode`: `--workload`'s fused decode kernel, one layer-step per launch over all its layers."""
     import torch
     import vulkanforge_b200 as vf
     ctx = vf.Context(0)
     hq, hkv, d, m, L = 32, 8, 128, args.probe_m, args.probe_ctx
-    q_start = L - m
-    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
-    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
-    g = torch.Generator(device="cuda").manual_seed(5)
-    for p in range(0, L, 4096):
-        n = min(4096, L - p)
-        kv = torch.randn(2, n, hkv * d, device="cuda", generator=g)
-        fwd.b_step_kv_write(0, kv[0], kv[1], n, p, 0)
-    q = torch.randn(m, hq, d, device="cuda", generator=g)
-    out = torch.zeros(m, hq, d, device="cuda")
-    kv = torch.randn(2, 512, hkv * d, device="cuda", generator=g)
-    if args.probe == "prefill":
-        fn = lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0)
-        work, unit = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2) / 1e12, "TFLOP/s"
+    if args.probe == "decode":
+        w = dict(WORKLOADS[args.workload])
+        if args.probe_batch:
+            w["batch"] = args.probe_batch
+        job = Job(w, 0, seed=77, ctx=ctx)
+        ctx.set_dependent_launch(args.pdl)
+        fn, work, unit = job.step, sum(algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"])) / 1e9, "GB/s"
+        stream = job.stream
     else:
-        fn = lambda: fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0)
-        work, unit = 2 * 512 * hkv * d * 5 / 1e9, "GB/s"
-    for _ in range(args.warmup):
-        fn()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        fn()
-    e1.record()
+        stream = torch.cuda.current_stream()
+        q_start = L - m
+        dtype = vf.KvDtype.F32 if args.probe == "generic" else vf.KvDtype.F8
+        cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), dtype)
+        fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=16 if args.probe == "generic" else 0)
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for p in range(0, L, 4096):
+            n = min(4096, L - p)
+            kv = torch.randn(2, n, hkv * d, device="cuda", generator=g)
+            fwd.b_step_kv_write(0, kv[0], kv[1], n, p, 0)
+        q = torch.randn(m, hq, d, device="cuda", generator=g)
+        out = torch.zeros(m, hq, d, device="cuda")
+        kv = torch.randn(2, 512, hkv * d, device="cuda", generator=g)
+        if args.probe == "prefill":
+            fn = lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0)
+            work, unit = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2) / 1e12, "TFLOP/s"
+        elif args.probe == "rope":
+            fn = lambda: fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0)
+            work, unit = 2 * 512 * hkv * d * 5 / 1e9, "GB/s"
+        elif args.probe == "append":
+            fn = lambda: fwd.b_step_kv_write(0, kv[0], kv[1], 512, q_start, 0)
+            work, unit = 2 * 512 * hkv * d * 5 / 1e9, "GB/s"
+        elif args.probe == "fp8_to_f16":
+            k16 = torch.empty(L, hkv, d, dtype=torch.float16, device="cuda")
+            v16 = torch.empty_like(k16)
+            fn = lambda: ctx.check(ctx._lib.vfkv_fp8_to_f16(cache.handle, 0, 0, L, k16.data_ptr(), v16.data_ptr(), None))
+            work, unit = 2 * L * hkv * d * 3 / 1e9, "GB/s"
+        else:                                      # generic: CUDA-core split kernel + merge kernel, F32 cache
+            fn = lambda: fwd.run_flash_attn_split_reduce(q[0], out[0], 0, L - 1, 16, 0, 0)
+            work, unit = 2 * L * hkv * d * 4 / 1e9, "GB/s"
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
     torch.cuda.synchronize()
     ctx.poll()
     us = e0.elapsed_time(e1) * 1e3 / args.steps
-    print(json.dumps({"probe": args.probe, "m": m, "context": L, "us_per_launch": us, "achieved": work / (us * 1e-6),
-                      "unit": unit, "steps": args.steps}), flush=True)
-    fwd.workspace.destroy()
-    cache.destroy()
-    ctx.destroy()
+    print(json.dumps({"probe": args.probe, "workload": args.workload if args.probe == "decode" else None, "m": m,
+                      "context": L, "us_per_call": us, "achieved": work / (us * 1e-6), "unit": unit,
+                      "steps": args.steps}), flush=True)
 
 
-def run_ours(args, w, rank, world, local_rank):
+# ----------------------------------------------------------------------------------------------
+def page_rows(page, hkv, d, seed=4000):
+    """K and V rows of one 256-position page of the long-context workload: the same on whichever
+    rank generates them (N(0,1), 1 % of the elements x20)."""
     import torch
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    job = Job(w, local_rank, seed=1000 + rank)
-    job.ctx.check(job.ctx._lib.vfkv_ctx_set_dependent_launch(job.ctx.handle, args.pdl))
-    job.ctx.set_cluster_merge(bool(args.cluster))
-    if args.tune:
-        wt, st = (int(x) for x in args.tune.split("x"))
-        job.ctx.check(job.ctx._lib.vfkv_ctx_set_attn_tuning(job.ctx.handle, wt, st))
+    g = torch.Generator(device="cuda").manual_seed(seed + page)
+    kv = torch.randn(2, 256, hkv * d, device="cuda", generator=g)
+    mask = torch.rand(2, 256, hkv * d, device="cuda", generator=g) < 0.01
+    return torch.where(mask, kv * 20.0, kv)
+
+
+def sharded_section(ctx, args, rank, world, local_rank, dist):
+    """The two sharded configurations at `world` GPUs, each with its one-GPU time from the same run.
+
+    long_fp8_ctx131072_b1: positions dealt round-robin in 256-row pages; per layer ONE launch per
+    rank (owner's append + attention + split merge + peer stores of the partial into every rank's
+    buffer + merge of all ranks' partials); the step is replayed from a CUDA graph.  Before timing,
+    rank 0 checks layer 0's output against a single-GPU decode step over the unsharded rows.
+    batch64_fp8_ragged_512_16384: sequences dealt out by `assign_sequences`; no exchange at all."""
+    import torch
+    import vulkanforge_b200 as vf
+    from vulkanforge_b200.shard import PositionShards, ShardedSequenceDecoder, assign_sequences
+    res = {}
+    peak, peak_kind = peaks()
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn):
-        """W warm-up steps, then K steps between two events on the job's stream."""
-        with torch.cuda.stream(job.stream):
-            for _ in range(args.warmup):
-                fn()
-            barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.steps):
-                fn()
-            e1.record()
-            barrier()
-        return e0.elapsed_time(e1)
+    # ---- long context, sharded by position -------------------------------------------------
+    name = "long_fp8_ctx131072_b1"
+    w = WORKLOADS[name]
+    L, hq, hkv, d, n_layers = w["ctx"], w["hq"], w["hkv"], w["d"], w["n_layers"]
+    one_gpu_us = None
+    if rank == 0:                                  # the same workload on one GPU, same run
+        one_gpu_us, _, _, _ = measure_workload(name, local_rank, args, ctx=ctx)
+    barrier()
+    sh = PositionShards(world, 256)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(n_layers, hkv, d, sh.local_capacity(L)), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=w["n_splits"])
+    exchange = vf.PeerExchange(ctx, world, rank, hq, d)
+    if dist is not None:
+        exchange.connect()
+    dec = ShardedSequenceDecoder(fwd, sh, rank, exchange=exchange)
+    ctx.set_dependent_launch(args.pdl)
+    n_pages = (L + 255) // 256
+    for page in range(rank, n_pages, world):       # this rank's pages of the earlier tokens
+        kv = page_rows(page, hkv, d)
+        m = min(256, L - 1 - page * 256)
+        if m <= 0:
+            continue
+        for layer in range(n_layers):
+            fwd.b_step_kv_write(layer, kv[0, :m], kv[1, :m], m, sh.local_pos(page * 256), 0)
+    g = torch.Generator(device="cuda").manual_seed(99)          # same inputs on every rank
+    q = torch.randn(n_layers, hq, d, device="cuda", generator=g)
+    kn = torch.randn(n_layers, 2, 1, hkv * d, device="cuda", generator=g)
+    out = torch.zeros(n_layers, hq, d, device="cuda")
+    stream = torch.cuda.Stream()
+    fwd.stream = stream.cuda_stream
+
+    def step():
+        for layer in range(n_layers):
+            dec.decode(layer, q[layer], kn[layer, 0], kn[layer, 1], out[layer], L - 1)
+
+    with torch.cuda.stream(stream):
+        step()
+    barrier()
+    n0 = ctx.launch_count()
+    with torch.cuda.stream(stream):
+        step()
+    barrier()
+    launches = ctx.launch_count() - n0
+    ctx.poll()
+    check = None
+    if rank == 0:                                  # layer 0 against one GPU holding every row
+        rc = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+        rf = vf.CudaForward(ctx, rc, n_heads=hq, n_splits=w["n_splits"])
+        for page in range(n_pages):
+            kv = page_rows(page, hkv, d)
+            m = min(256, L - 1 - page * 256)
+            if m > 0:
+                rf.b_step_kv_write(0, kv[0, :m], kv[1, :m], m, page * 256, 0)
+        ref = torch.zeros(hq, d, device="cuda")
+        pos = torch.tensor([L - 1], dtype=torch.int32, device="cuda")
+        rf.decode_step(0, q[0], kn[0, 0], kn[0, 1], ref, None, pos, 1, L)
+        torch.cuda.synchronize()
+        check = float((out[0] - ref).abs().max() / ref.abs().max())
+        rf.workspace.destroy()
+        rc.destroy()
+        if not check <= 1e-3:
+            raise RuntimeError(f"position-sharded output differs from one GPU: relative error {check}")
+    barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step()
+    ms, blocks, _ = timed_blocks(graph.replay, stream, args.steps, 3, dist, 200.0)
+    ctx.poll()
+    us = ms * 1e3 / args.steps / n_layers
+    res[name] = {"us_per_token_layer": us, "one_gpu_us_per_token_layer": one_gpu_us, "n_gpus": world,
+                 "launches_per_layer_per_rank": launches / n_layers,
+                 "check_rel_err_vs_one_gpu": check,
+                 "exchange": "peer stores from the attention kernel, merged in the same launch",
+                 "exchanged_bytes_per_rank_per_layer": (d + 2) * hq * 8 * world}
+    if one_gpu_us is not None:
+        res[name]["speedup"] = one_gpu_us / us
+        res[name]["efficiency"] = one_gpu_us / us / world
+        res[name]["roofline_frac_per_gpu"] = (algorithmic_bytes(w, [L], 0) / world) / (us * 1e-6) / 1e9 / peak
+    fwd.stream = None
+    barrier()
+    exchange.destroy()
+    fwd.workspace.destroy()
+    cache.destroy()
+
+    # ---- ragged batch of 64, sharded by sequence ----------------------------------------------
+    name = "batch64_fp8_ragged_512_16384"
+    w = WORKLOADS[name]
+    lens = make_lens(w, np.random.default_rng(1077))          # the same draw on every rank
+    one_gpu_us = None
+    if rank == 0:
+        one_gpu_us, _, _, _ = measure_workload(name, local_rank, args, ctx=ctx, lens=lens)
+    barrier()
+    mine = assign_sequences(lens, world)[rank]
+    job = Job(dict(w), local_rank, seed=2000 + rank, ctx=ctx, lens=[lens[i] for i in mine])
+    ctx.set_dependent_launch(args.pdl)
+    with torch.cuda.stream(job.stream):
+        job.step()
+    torch.cuda.synchronize()
+    job.capture()
+    ms, _, _ = timed_blocks(job.graph.replay, job.stream, args.steps, 3, dist, 200.0)
+    ctx.poll()
+    us = ms * 1e3 / args.steps / (len(lens) * w["n_layers"])
+    res[name] = {"us_per_token_layer": us, "one_gpu_us_per_token_layer": one_gpu_us, "n_gpus": world,
+                 "sequences_per_rank": [len(x) for x in assign_sequences(lens, world)],
+                 "positions_per_rank": [int(sum(lens[i] for i in x)) for x in assign_sequences(lens, world)],
+                 "exchange": "none"}
+    if one_gpu_us is not None:
+        res[name]["speedup"] = one_gpu_us / us
+        res[name]["efficiency"] = one_gpu_us / us / world
+    job.close()
+    barrier()
+    return res
+
+
+def run_ours(args, w, rank, world, local_rank):
+    import torch
+    dist = None
+    if world > 1:
+        import datetime
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=300))
+    job = Job(w, local_rank, seed=1000 + rank)
+    job.ctx.set_dependent_launch(args.pdl)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     with torch.cuda.stream(job.stream):
         for _ in range(args.warmup):
             job.step()
     barrier()
-    n0 = job.ctx.launch_count()
-    with torch.cuda.stream(job.stream):
-        job.step()
-    barrier()
-    job.launches_per_step = job.ctx.launch_count() - n0       # kernels of libvfkv.so per token
+    job.count_launches()
     if not args.no_graph:
         job.capture()
     barrier()
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
-    ms = timed(job.graph.replay if job.graph is not None else job.step)
-    launches = job.launches_per_step * args.steps
+    run = job.graph.replay if job.graph is not None else job.step
+    ms, blocks, total_ms = timed_blocks(run, job.stream, args.steps, args.warmup, dist)
     clocks = sampler.finish()
-    ms_stream = timed(job.step) if job.graph is not None else ms      # same steps, one launch call per kernel
+    launches = job.launches_per_step * args.steps * blocks
+    ms_stream = ms
+    if job.graph is not None:                                  # same steps, one launch call per kernel
+        ms_stream, _, _ = timed_blocks(job.step, job.stream, args.steps, 3, dist, 100.0)
     job.ctx.poll()
 
     # end-to-end leg: host buffers in, host buffers out, every step
     for _ in range(max(3, args.warmup)):
         job.step_host()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        job.step_host()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e_blocks = []
+    for _ in range(max(3, min(blocks, 50))):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            job.step_host()
+        barrier()
+        e2e_blocks.append((time.perf_counter() - t0) * 1e3)
+    e2e_ms = float(np.median(e2e_blocks))
 
     if dist is not None:
-        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        e2e_ms = float(t[0])
         tot = torch.tensor([launches], device="cuda", dtype=torch.int64)
         dist.all_reduce(tot)
         launches = int(tot[0])
 
+    line = None
     if rank == 0:
         tokens = w["batch"] * world                       # tokens decoded per step, all ranks
         denom = args.steps * tokens * w["n_layers"]
@@ -554,28 +788,24 @@ def run_ours(args, w, rank, world, local_rank):
             # are fused into it), so its mean launch duration inside the region is region time /
             # launches; consecutive launches overlap under dependent launch, which per-launch event
             # pairs (kept in "kernels", measured in a separate pass) cannot show.
-            per_launch = float(np.mean([algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"])]))
             fused = job.launches_per_step == w["n_layers"]
             mean_us = ms * 1e3 / (args.steps * w["n_layers"]) if fused else split["mean_us"]
-            achieved = per_launch / (mean_us * 1e-6) / 1e9
-            roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                        "kernel": "attn_split_mma_kernel (fa_split: append + attention + merge)" if fused else "fa_split",
-                        "algorithmic_bytes_per_launch": per_launch, "mean_launch_us": mean_us,
-                        "mean_launch_us_isolated_events": split["mean_us"],
-                        "peak_source": f"{peak_kind} copy bandwidth", "frac_of_8000_nominal": achieved / 8000.0}
+            roofline = roofline_of(w, job.lens, mean_us, peak, peak_kind, NCU_TRAFFIC_BYTES.get(args.workload))
+            roofline["kernel"] = "attn_split_mma_kernel (fa_split: append + attention + merge)" if fused else "fa_split"
+            roofline["mean_launch_us_isolated_events"] = split["mean_us"]
         step_bytes = sum(algorithmic_bytes(w, job.lens, l) for l in range(w["n_layers"]))
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32 (fp8/f16 storage)", "data": "synthetic",
-                "config": {"workload": args.workload, "n_layers": w["n_layers"], "n_q_heads": w["hq"],
-                           "n_kv_heads": w["hkv"], "head_dim": w["d"], "kv_dtype": w["dtype"], "batch_per_gpu": w["batch"],
-                           "context": w["ctx"], "n_splits": w["n_splits"], "softcap": w["softcap"],
-                           "l2": "each step streams the whole cache (larger than the 126 MB L2) before a layer repeats"
-                                 if step_bytes > 200e6 else "working set below L2: hot-L2 numbers",
-                           "launch": "one CUDA graph replay per token" if job.graph is not None else "stream launches",
-                           "dependent_launch_mode": args.pdl, "cluster_merge": args.cluster,
-                           "parallelism": f"sequence-sharded x{world}, no collective"},
+                "config": config_of(args.workload, w),
+                "run": {"l2": "each step streams the whole cache (larger than the 126 MB L2) before a layer repeats"
+                              if step_bytes > 200e6 else "working set below L2: hot-L2 numbers",
+                        "launch": "one CUDA graph replay per token" if job.graph is not None else "stream launches",
+                        "dependent_launch_mode": args.pdl,
+                        "parallelism": f"sequence-sharded x{world}, no collective",
+                        "timed_blocks": blocks, "timed_region_ms": total_ms,
+                        "value_is": "median over the blocks of (block time / steps); each block is exactly "
+                                    "--steps steps between barrier + synchronize, max over ranks"},
                 "value_stream_launches": ms_stream * 1e3 / denom,
                 "tokens_per_s": tokens * args.steps / (ms * 1e-3),
                 "achieved_gbs_whole_step": step_bytes * world * args.steps / (ms * 1e-3) / 1e9,
@@ -583,134 +813,25 @@ def run_ours(args, w, rank, world, local_rank):
                 "e2e": {"value": e2e_ms * 1e3 / denom, "unit": UNIT, "h2d_bytes_per_step": job.h2d_bytes(),
                         "d2h_bytes_per_step": job.d2h_bytes()}}
         if world == 1 and not args.no_extra and args.workload == DEFAULT_WORKLOAD:
-            line["roofline_batch64_ctx8192"] = batch64_roofline(job.ctx, args, peak)
+            others = other_workloads(job.ctx, args, peak, peak_kind)
+            line["roofline_batch64_ctx8192"] = dict(others["batch64_fp8_ctx8192"]["roofline"],
+                                                    workload="batch64_fp8_ctx8192: 64 sequences x 8192 tokens, "
+                                                             "32 q / 8 kv / 128, FP8, 1 layer")
+            line["other_workloads"] = others
             line["next_rows"] = next_rows(job.ctx, args, peak, tensor_peak())
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline_sample(w)
+    ctx = job.ctx
+    job.close()
+    if args.workload == DEFAULT_WORKLOAD and not args.no_extra:
+        sharded = sharded_section(ctx, args, rank, world, local_rank, dist)
+        if line is not None:
+            line["sharded"] = sharded                      # last key of the line
+    if line is not None:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
-
-
-def run_position_sharded(args, w, rank, world, local_rank):
-    """One long sequence cut into round-robin pages over the ranks (strong scaling): per step the
-    owner of the new position appends, every rank attends over its pages, the (m, l, o) partials are
-    all-gathered over NCCL and merged on every rank."""
-    import torch
-    import torch.distributed as dist
-    import vulkanforge_b200 as vf
-    from vulkanforge_b200.shard import PositionShards, ShardedSequenceDecoder
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    torch.cuda.set_device(local_rank)
-    import datetime
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
-                            timeout=datetime.timedelta(seconds=90))
-    ctx = vf.Context(local_rank)
-    sh = PositionShards(world, 256)
-    L, hq, hkv, d = w["ctx"], w["hq"], w["hkv"], w["d"]
-    cache = vf.KvCache(ctx, vf.KvCacheConfig(w["n_layers"], hkv, d, sh.local_capacity(L)), vf.KvDtype[w["dtype"]])
-    fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=w["n_splits"])
-    exchange = None
-    if args.exchange == "peer":                            # partials by peer stores from the attention kernel
-        exchange = vf.PeerExchange(ctx, world, rank, hq, d)
-        exchange.connect()
-    dec = ShardedSequenceDecoder(fwd, sh, rank, exchange=exchange)
-    g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    n_local = sh.local_len(L - 1, rank)
-    n_layers = w["n_layers"]
-    ctx.check(ctx._lib.vfkv_ctx_set_dependent_launch(ctx.handle, args.pdl))
-    for p in range(0, n_local, 4096):                      # this rank's pages of the 131071 earlier tokens
-        m = min(4096, n_local - p)
-        kv = torch.randn(2, m, hkv * d, device="cuda", generator=g)
-        mask = torch.rand(2, m, hkv * d, device="cuda", generator=g) < 0.01
-        kv = torch.where(mask, kv * 20.0, kv)
-        for layer in range(n_layers):
-            fwd.b_step_kv_write(layer, kv[0], kv[1], m, p, 0)
-    chunk = torch.randn(2, 512, hkv * d, device="cuda", generator=g)   # a 512-token chunked-prefill append
-    q = torch.randn(n_layers, hq, d, device="cuda", generator=g)
-    kn = torch.randn(n_layers, 2, 1, hkv * d, device="cuda", generator=g)
-    out = torch.zeros(n_layers, hq, d, device="cuda")
-
-    def step():
-        for layer in range(n_layers):
-            dec.decode(layer, q[layer], kn[layer, 0], kn[layer, 1], out[layer], L - 1)
-
-    def barrier():
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    stream = torch.cuda.Stream()
-    fwd.stream = stream.cuda_stream
-    with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
-            step()
-    barrier()
-    n0 = ctx.launch_count()
-    with torch.cuda.stream(stream):
-        step()
-    barrier()
-    launches = (ctx.launch_count() - n0) * args.steps
-    run, launch_kind = step, "stream launches"
-    if exchange is not None and not args.no_graph:         # only this library's kernels: always capturable
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step()
-        run, launch_kind = graph.replay, "one CUDA graph replay per token"
-    barrier()
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    sampler.start()
-    with torch.cuda.stream(stream):
-        for _ in range(args.warmup):
-            run()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            run()
-        e1.record()
-        barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.finish()
-    fwd.stream = None
-    # the chunked-prefill append of the same config, timed on its own
-    base = max(0, L - 1 - 512)
-    for _ in range(3):
-        dec.prefill(0, chunk[0].view(512, hkv, d), chunk[1].view(512, hkv, d), base, 512)
-    barrier()
-    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    p0.record()
-    for _ in range(args.steps):
-        dec.prefill(0, chunk[0].view(512, hkv, d), chunk[1].view(512, hkv, d), base, 512)
-    p1.record()
-    barrier()
-    prefill_ms = p0.elapsed_time(p1) / args.steps
-    t = torch.tensor([ms, prefill_ms], device="cuda", dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    tot = torch.tensor([launches], device="cuda", dtype=torch.int64)
-    dist.all_reduce(tot)
-    ctx.poll()
-    if rank == 0:
-        ms, prefill_ms = float(t[0]), float(t[1])
-        step_bytes = algorithmic_bytes(w, [L], 0) * w["n_layers"]
-        line = {"metric": METRIC, "value": ms * 1e3 / args.steps / w["n_layers"], "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False,
-                "scaling": "strong", "vs_baseline": None, "dtype": "f32 (fp8/f16 storage)", "data": "synthetic",
-                "config": {"workload": args.workload, "n_layers": w["n_layers"], "n_q_heads": hq, "n_kv_heads": hkv,
-                           "head_dim": d, "kv_dtype": w["dtype"], "context": L,
-                           "parallelism": f"positions sharded x{world} in 256-row pages, " + (
-                               "(m, l, o) stored into every GPU's buffer by the attention kernel, flag-waiting merge"
-                               if exchange is not None else "NCCL all-gather of (m, l, o)"),
-                           "exchange": args.exchange,
-                           "collective_bytes_per_rank": (d + 2) * hq * 4, "launch": launch_kind,
-                           "l2": "per-GPU share of the cache is %d MiB per step" % (step_bytes // world >> 20)},
-                "achieved_gbs_whole_step": step_bytes * args.steps / (ms * 1e-3) / 1e9,
-                "prefill_chunk_512_us": prefill_ms * 1e3, "clocks": clocks, "gpu_launches": int(tot[0])}
-        print(json.dumps(line), flush=True)
-    dist.barrier()
-    if exchange is not None:
-        exchange.destroy()
-    dist.destroy_process_group()
 
 
 def main():
@@ -721,26 +842,19 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline sample")
-    ap.add_argument("--no-extra", action="store_true", help="skip the batch-64 roofline measurement")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the other workloads, the next rows and the sharded configurations")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
-                    help="position-sharded mode: how the per-GPU partials travel (peer stores fused into the "
-                         "attention kernel, or an NCCL all-gather)")
-    ap.add_argument("--n-splits", type=int, default=None, help="override the workload's split count (0 = choose)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch mode of the attention kernel (vfkv_ctx_set_dependent_launch)")
-    ap.add_argument("--probe", default=None, choices=["prefill", "rope"],
-                    help="run one kernel of the next rows on its own (for profiling) and exit")
+    ap.add_argument("--probe", default=None, choices=["prefill", "rope", "append", "fp8_to_f16", "generic", "decode"],
+                    help="run one kernel on its own (for profiling) and exit")
     ap.add_argument("--probe-m", type=int, default=2048)
     ap.add_argument("--probe-ctx", type=int, default=16384)
-    ap.add_argument("--cluster", type=int, default=0, choices=[0, 1],
-                    help="merge the splits inside a thread-block cluster (vfkv_ctx_set_cluster_merge)")
-    ap.add_argument("--tune", default=None, help="tensor-core kernel shape WxS (warps x stages), e.g. 4x3")
+    ap.add_argument("--probe-batch", type=int, default=0, help="--probe decode: override the workload's batch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     w = dict(WORKLOADS[args.workload])
-    if args.n_splits is not None:
-        w["n_splits"] = args.n_splits
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -749,9 +863,6 @@ def main():
         return
     if args.impl == "reference":
         run_reference(args, w, rank, world)
-        return
-    if world > 1 and w.get("shard") == "positions":
-        run_position_sharded(args, w, rank, world, local_rank)
         return
     run_ours(args, w, rank, world, local_rank)
 

@@ -932,7 +932,14 @@ static int32_t attend_push_impl(vfkv_cache *cache, vfkv_workspace *ws, vfkv_exch
             if (did_fuse) *did_fuse = true;
         }
         DeviceGuard g(ctx->device);
-        return launch_attention(ctx, ws, a, as_stream(stream));
+        rc = launch_attention(ctx, ws, a, as_stream(stream));
+        if (rc == VFKV_ERR_UNSUPPORTED && a.fan_merge) {      // shape too large for the one-launch form: two launches
+            a.out = nullptr;
+            a.fan_merge = false;
+            if (did_fuse) *did_fuse = false;
+            rc = launch_attention(ctx, ws, a, as_stream(stream));
+        }
+        return rc;
     }
     if (has_new) {
         rc = vfkv_append(cache, layer, d_k_new, d_v_new, 1, slot, pos_end - 1, stream);

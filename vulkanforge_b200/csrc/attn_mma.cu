@@ -307,38 +307,13 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
     const uint32_t bars = ring + S::RING_BYTES;           // kWarps*kStages mbarriers, 8 bytes each
-    __shared__ uint32_t s_flag, s_epoch, s_tag, s_merger, s_safe, s_nlist, s_late, s_launch_no;
-    __shared__ uint8_t s_list[256];       // slices the last drawer takes over (n_splits <= 255)
+    __shared__ uint32_t s_flag, s_epoch, s_tag, s_merger, s_late;
     __shared__ PeerFanout s_fan;          // the group's fan-out table (position-sharded calls only)
 
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t gid = lane >> 2, tig = lane & 3;
     const uint32_t g = p.group;
-
-    // ---- split ticket, drawn before anything else ----------------------------------------------
-    // Every CTA of a (sequence, kv-head) draws a ticket from a 64-bit word that only ever counts up;
-    // there is one word per split count, so ticket / n_splits is the number of the launch among
-    // those that used this word and ticket % n_splits the CTA's place in the draw.  The last
-    // drawer is the one CTA that never has to wonder whether the others have started.  The launch
-    // number, together with the host's count of launches on this workspace, is the tag of this
-    // launch's partials.  Nothing waits on a ticket and nothing resets one, and a CTA draws before
-    // its first bounded wait, so the words are always consistent.  The result is published to the
-    // CTA before the barrier below; only after that barrier may a dependent launch start, so two
-    // launches never interleave their draws.
-    if (threadIdx.x == 32) {
-        uint32_t tag = 0u, merger = 0u, launch_no = 0u;
-        if (p.n_splits > 1u && mp.cluster == 0u) {
-            const unsigned long long old =
-                atomicAdd(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh) * 256u + p.n_splits, 1ull);
-            launch_no = uint32_t(old / p.n_splits);
-            merger = uint32_t(old % p.n_splits) == p.n_splits - 1u ? 1u : 0u;
-            // never 0, the value of a cleared workspace; launches that share a host count are replays
-            // of one graph node (same addresses), which the device-side number tells apart
-            tag = 0x80000000u | ((mp.launch_seq & 0x7FFFu) << 16) | (launch_no & 0xFFFFu);
-        }
-        s_tag = tag; s_merger = merger; s_launch_no = launch_no;
-    }
 
     // Q is fetched first: its address depends on the block index only, so these loads overlap the
     // (dependent) read of the sequence's position and the first TMA round trip.
@@ -411,7 +386,6 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_flag = 0;
         s_late = 0;
-        s_nlist = 0;
     }
 
     __syncthreads();
@@ -535,12 +509,24 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
     for (int nb = 0; nb < NDB; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f; }
     bool timed_out = false;
-    // Has every CTA of this (sequence, kv-head) started?  Asked now, used after the stream: the
-    // answer decides whether this CTA may wait for the others' partials (see the merge below).
-    unsigned long long ticket_now = 0ull;
-    if (threadIdx.x == 0 && p.n_splits > 1u && mp.cluster == 0u)
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(ticket_now)
-                     : "l"(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh) * 256u + p.n_splits) : "memory");
+    // ---- split ticket -----------------------------------------------------------------------------
+    // Every CTA of a (sequence, kv-head) draws one ticket from a 64-bit word that only ever counts
+    // up; there is one word per split count, so ticket / n_splits is the number of the launch among
+    // those that used the word and ticket % n_splits the CTA's place in the draw.  The CTA that
+    // draws last merges the splits; the launch number, together with the host's count of launches
+    // on this workspace, is the tag of this launch's partials.  The ticket is drawn by one thread
+    // as its warp starts on its last tile: late enough that the last drawer is one of the last
+    // CTAs to finish, early enough that the answer is there when the stream ends.  Nothing waits
+    // for a ticket, nothing resets one, and every CTA draws exactly one whatever happens to its
+    // tiles, so the words stay consistent.
+    unsigned long long ticket = 0ull;
+    bool drawn = false;
+    const bool draws = threadIdx.x == 32 && p.n_splits > 1u && mp.cluster == 0u;
+    auto draw_ticket = [&]() {
+        ticket = atomicAdd(mp.tickets + (uint64_t(s) * p.n_kv_heads + kvh) * 256u + p.n_splits, 1ull);
+        drawn = true;
+    };
+    if (draws && my_tiles <= 1u) draw_ticket();
     VFKV_TRACE(3);
 
     // Lane-constant parts of the swizzled shared-memory addresses (tile_addr with the tile base
@@ -569,6 +555,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const uint32_t st = n % kStages;
         const uint32_t t0 = begin + (warp + n * kWarps) * TP;
         const uint32_t kt = stage0 + st * S::STAGE_BYTES, vt = kt + S::TILE_BYTES;
+        if (draws && n != 0u && n + 1u == my_tiles) draw_ticket();
         if (!mbar_wait_bounded(bar0 + 8 * st, (n / kStages) & 1u)) { timed_out = true; break; }
         const uint32_t n_valid = min(uint32_t(TP), end - t0);
         if (n == 0) VFKV_TRACE(4);
@@ -715,8 +702,23 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     if (timed_out) {
         if (lane == 0) { atomicOr(p.status, 1u); s_flag = 1; }
     }
-    if (threadIdx.x == 0)     // had every CTA of this launch drawn when this CTA began to stream?
-        s_safe = ticket_now >= (uint64_t(s_launch_no) + 1u) * p.n_splits ? 1u : 0u;
+    if (threadIdx.x == 32) {
+        uint32_t tag = 0u, merger = 0u;
+        if (draws) {
+            if (!drawn) draw_ticket();            // a wait that ran out before the last tile
+            uint32_t place, launch_no;
+            if ((ticket >> 32) == 0ull) {         // the usual case, without a 64-bit division
+                place = uint32_t(ticket) % p.n_splits; launch_no = uint32_t(ticket) / p.n_splits;
+            } else {
+                place = uint32_t(ticket % p.n_splits); launch_no = uint32_t(ticket / p.n_splits);
+            }
+            merger = place == p.n_splits - 1u ? 1u : 0u;
+            // never 0, the value of a cleared workspace; launches that share a host count are replays
+            // of one graph node (same addresses), which the device-side number tells apart
+            tag = 0x80000000u | ((mp.launch_seq & 0x7FFFu) << 16) | (launch_no & 0xFFFFu);
+        }
+        s_tag = tag; s_merger = merger;
+    }
     __syncthreads();          // all tiles consumed (or abandoned): the ring is free for the merge
     VFKV_TRACE(6);
     const bool gave_up = s_flag != 0u;
@@ -892,238 +894,151 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         }
     };
 
-    // ---- several splits: publish the partial, then every CTA merges one slice of the rows ----------
+    // ---- several splits: publish the partial; the CTA that drew the last ticket merges -------------
     // The partial goes to the workspace as tagged words (one 16-byte store = two {value, tag}
-    // words); no fence and no flag follow, readers poll the words themselves until each carries
-    // this launch's tag.  The n_pairs output pairs are cut into n_splits slices and CTA i merges
-    // slice i over all splits (flash_attn_reduce.comp:51-80): one load round trip of a few KB per CTA
-    // instead of one CTA reading everything.  A CTA may only wait for CTAs that have started: it
-    // claims its slice if the ticket word showed, when it began to stream, that every CTA of the
-    // group had drawn (always true for the last drawer); otherwise it leaves the slice to the last
-    // drawer, which therefore never waits for a CTA that is not yet running.  Each CTA publishes
-    // that decision as one more tagged word.
-    // The work is spread over all threads, one (pair, split) item each, and combined with shuffles:
-    // this tail runs once per CTA with nothing to overlap it, so its cost is the length of its
-    // longest dependent chain (a thread that walks 16 splits by itself costs about 1 us more than
-    // 16 lanes that fetch one split each).
+    // words).  No fence and no flag follow: whoever merges polls the words themselves until each
+    // carries this launch's tag.  Every other CTA is done once its stores are issued and leaves
+    // its SM to the next launch.  The last drawer has drawn after every CTA of its group had begun
+    // its last tile, so it only ever waits for CTAs that are about to store.
     const uint32_t tag = s_tag;
-    const bool merger = s_merger != 0u;
     const uint64_t grp = uint64_t(s) * p.n_kv_heads + kvh;
-    const uint64_t pwords = uint64_t(g) * (D + 2) + 2;        // words of one CTA's partial: o[g][D], {m, l}[g], decision
+    const uint64_t pwords = uint64_t(g) * (D + 2);            // words of one CTA's partial: o[g][D], {m, l}[g]
     uint64_t *const gp = mp.tag_part + grp * p.n_splits * pwords;
-    const uint32_t per = (n_pairs + p.n_splits - 1) / p.n_splits;
     if (!direct) {
-        const bool claimed = merger || s_safe != 0u;
         uint64_t *mine = gp + uint64_t(split) * pwords;
         for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
             const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
             float O0, O1, Mn, L;
             cta_partial(j, d, O0, O1, Mn, L);
-            tagged_store2(mine + uint64_t(j) * D + d, O0, O1, tag);
+            tagged_store2(mine + 2 * idx, O0, O1, tag);        // = o[j][d], o[j][d + 1]
             if (d == 0) tagged_store2(mine + uint64_t(g) * D + 2 * j, Mn, L, tag);
         }
-        if (threadIdx.x == 0) tagged_store2(mine + uint64_t(g) * (D + 2), claimed ? 1.0f : 0.0f, 0.f, tag);
         VFKV_TRACE(7);
-        if (!claimed) return;
-        // The last drawer's last warp collects the other CTAs' decisions while the rest merge, and
-        // leaves the list of slices nobody claimed (usually empty) in shared memory.
-        if (merger && warp == uint32_t(kWarps) - 1u) {
-            uint32_t n = 0;
-            for (uint32_t c = 0; c < p.n_splits; c += 32) {
-                const uint32_t i = c + lane;
-                bool orphan = false;
-                if (i < p.n_splits) {
-                    const uint64_t *pd = gp + uint64_t(i) * pwords + uint64_t(g) * (D + 2);
-                    uint64_t t0 = 0;
-                    for (;;) {
-                        const ulonglong2 w = tagged_load2(pd);
-                        if (tags_are(w, tag)) { orphan = i != split && tagged_value(w.x) == 0.f; break; }
-                        const uint64_t now = global_timer_ns();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; break; }
-                        else __nanosleep(40);
-                    }
-                }
-                const uint32_t mask = __ballot_sync(0xffffffffu, orphan);
-                if (orphan) s_list[n + __popc(mask & ((1u << lane) - 1u))] = uint8_t(i);
-                n += __popc(mask);
-            }
-            if (lane == 0) s_nlist = n;
-        }
-    }
-    if (direct) {             // a single split: this CTA's partial is the local result
+        if (s_merger == 0u) return;
+    } else {                  // a single split: this CTA's partial is the local result
         for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
             float a0, a1, gmax, gsum;
             cta_partial(idx / HD2, 2 * (idx % HD2), a0, a1, gmax, gsum);
             emit(idx, a0, a1, gmax, gsum);
         }
         VFKV_TRACE(8);
-        if (!(fan && mp.fan_merge != 0u)) { VFKV_TRACE(9); return; }
     }
-    __syncthreads();          // the warps' partials are dead: the ring becomes the staging area
-
     const bool xrank = fan && mp.fan_merge != 0u;
-    float4 *stg = reinterpret_cast<float4 *>(ring_ptr);          // items {o0, o1, m, l}
-    constexpr uint32_t kStageItems = S::RING_BYTES / 16;
-    // Merge of up to 32 parts per output pair without shared memory: the parts of a pair sit in
-    // neighbouring lanes (groups of P lanes, P a power of two), which combine them with shuffles:
-    // the maximum first, then the weighted sums (flash_attn_reduce.comp:57-75).  Lane 0 of a group
-    // ends up with the pair's merged (o0, o1, m, l).  Lanes without a part pass m = -1e30, l = 0.
-    auto group_merge = [&](uint32_t P, float &o0, float &o1, float &m, float &l) {
-        float gm = m;
-        for (uint32_t off = P >> 1; off != 0; off >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, off));
-        const float kn = __expf(m - gm);
-        o0 *= kn; o1 *= kn; l *= kn;
-        for (uint32_t off = P >> 1; off != 0; off >>= 1) {
-            o0 += __shfl_xor_sync(0xffffffffu, o0, off);
-            o1 += __shfl_xor_sync(0xffffffffu, o1, off);
-            l += __shfl_xor_sync(0xffffffffu, l, off);
-        }
-        m = gm;
-    };
-    auto pow2_at_least = [](uint32_t n) { uint32_t q = 1; while (q < n) q <<= 1; return q; };
+    if (direct && !xrank) { VFKV_TRACE(9); return; }
 
-    // Pass 0: this CTA's slice (every pair when there is a single split).  Pass 1, last drawer only:
-    // the slices their owners left behind.
-    for (uint32_t pass = 0; pass < 2u; ++pass) {
-        uint32_t n_list = 1;
-        if (pass == 1u) {
-            if (direct || !merger) break;
-            n_list = s_nlist;                      // written before the barrier above
-            if (n_list == 0) break;
-        }
-        const uint32_t total_v = direct ? n_pairs : n_list * per;
-        const uint32_t parts_here = direct ? 1u : p.n_splits;
-        const uint32_t world_here = xrank ? s_fan.world : 1u;
-        const uint32_t chunk_v = max(1u, kStageItems / max(parts_here, world_here));
-        for (uint32_t v0 = 0; v0 < total_v; v0 += chunk_v) {
-            const uint32_t nv = min(chunk_v, total_v - v0);
-            // virtual index -> output pair (0xFFFFFFFF: beyond the last pair)
-            auto pair_of = [&](uint32_t v) -> uint32_t {
-                if (direct) return v;
-                const uint32_t sl = pass == 0u ? split : uint32_t(s_list[v / per]);
-                const uint32_t idx = sl * per + v % per;
-                return idx < n_pairs ? idx : 0xFFFFFFFFu;
-            };
-            // one (pair, split) item: poll its words until they carry this launch's tag
-            auto fetch_part = [&](uint32_t idx, uint32_t i, float &o0, float &o1, float &m, float &l) {
-                const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
-                const uint64_t *a_o = gp + uint64_t(i) * pwords + uint64_t(j) * D + d;
-                const uint64_t *a_m = gp + uint64_t(i) * pwords + uint64_t(g) * D + 2 * j;
-                uint64_t t0 = 0;
-                for (;;) {
-                    // two requests a quarter of a round trip apart: the CTAs of a group finish within
-                    // a few hundred ns of one another, so the second often finds what the first missed
-                    ulonglong2 ow = tagged_load2(a_o), mw = tagged_load2(a_m);
-                    __nanosleep(200);
-                    const ulonglong2 ow2 = tagged_load2(a_o), mw2 = tagged_load2(a_m);
-                    if (!(tags_are(ow, tag) && tags_are(mw, tag))) { ow = ow2; mw = mw2; }
-                    if (tags_are(ow, tag) && tags_are(mw, tag)) {
-                        o0 = tagged_value(ow.x); o1 = tagged_value(ow.y); m = tagged_value(mw.x); l = tagged_value(mw.y);
-                        return;
-                    }
-                    const uint64_t now = global_timer_ns();
-                    if (t0 == 0) t0 = now;
-                    else if (now - t0 > mp.merge_wait_ns) { s_flag = 3u; return; }
-                    else __nanosleep(40);
-                }
-            };
-            if (!direct && p.n_splits <= 32u) {
-                const uint32_t P = pow2_at_least(p.n_splits), ppw = 32u / P;       // pairs per warp and step
-                for (uint32_t b = warp * ppw; b < nv; b += uint32_t(kWarps) * ppw) {
-                    const uint32_t vi = b + lane / P, i = lane % P;
-                    const uint32_t idx = vi < nv ? pair_of(v0 + vi) : 0xFFFFFFFFu;
-                    const bool active = idx != 0xFFFFFFFFu && i < p.n_splits;
-                    float o0 = 0.f, o1 = 0.f, m = kMaskedScore, l = 0.f;
-                    if (active) fetch_part(idx, i, o0, o1, m, l);
-                    group_merge(P, o0, o1, m, l);
-                    if (active && i == 0u) emit(idx, o0, o1, m, l);
-                }
-            } else if (!direct) {
-                // more than 32 splits: the items of a chunk are staged in shared memory
-                for (uint32_t w = threadIdx.x; w < nv * p.n_splits; w += blockDim.x) {
-                    const uint32_t i = w / nv, vi = w % nv;
-                    const uint32_t idx = pair_of(v0 + vi);
-                    if (idx == 0xFFFFFFFFu) continue;
-                    float o0 = 0.f, o1 = 0.f, m = kMaskedScore, l = 0.f;
-                    fetch_part(idx, i, o0, o1, m, l);
-                    stg[i * nv + vi] = make_float4(o0, o1, m, l);
-                }
-                __syncthreads();
-                for (uint32_t vi = threadIdx.x; vi < nv; vi += blockDim.x) {
-                    const uint32_t idx = pair_of(v0 + vi);
-                    if (idx == 0xFFFFFFFFu) continue;
-                    float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
+    // ---- the last drawer merges the splits --------------------------------------------------------------
+    // Everything from here on runs once per launch on one CTA per (sequence, kv-head), straight after
+    // the hot loop: measured, such code costs what it takes to fetch its instructions, ten cycles
+    // and more apiece, so it is kept short and rolled.  All partials of the group (a few KB per
+    // split) are copied into the now idle ring with asynchronous 16-byte copies, one short loop
+    // that puts every request in flight at once; then each thread merges its output pairs out of
+    // shared memory (flash_attn_reduce.comp:51-80, maximum first) and checks the tags as it goes.
+    // A word that does not carry this launch's tag yet sends the whole step round again, up to
+    // the time limit.
+    __syncthreads();          // the warps' partials in the ring are dead (uniform: the whole CTA merges or none of it)
+    uint64_t *const stgw = reinterpret_cast<uint64_t *>(ring_ptr);
+    const uint32_t stg_base = ring;                               // shared-window address of stgw
+    if (!direct) {
+        const uint32_t n16 = uint32_t(p.n_splits * pwords / 2);   // 16-byte pieces
+        uint64_t t0 = 0;
+        for (;;) {
+            for (uint32_t k = threadIdx.x; k < n16; k += blockDim.x)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stg_base + 16u * k), "l"(gp + 2ull * k) : "memory");
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncthreads();
+            bool missing = false;
+            for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+                const uint32_t j = idx / HD2;
+                const uint64_t *po = stgw + 2 * idx, *pm = stgw + uint64_t(g) * D + 2 * j;
+                float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
 #pragma unroll 4
-                    for (uint32_t i = 0; i < p.n_splits; ++i) gmax = fmaxf(gmax, stg[i * nv + vi].z);
+                for (uint32_t i = 0; i < p.n_splits; ++i) {
+                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * pwords);
+                    missing = missing || !tags_are(mw, tag);
+                    gmax = fmaxf(gmax, tagged_value(mw.x));
+                }
 #pragma unroll 4
-                    for (uint32_t i = 0; i < p.n_splits; ++i) {
-                        const float4 t = stg[i * nv + vi];
-                        const float kn = __expf(t.z - gmax);
-                        gsum = fmaf(t.w, kn, gsum);
-                        a0 = fmaf(t.x, kn, a0);
-                        a1 = fmaf(t.y, kn, a1);
-                    }
-                    emit(idx, a0, a1, gmax, gsum);
+                for (uint32_t i = 0; i < p.n_splits; ++i) {
+                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(po + i * pwords);
+                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * pwords);
+                    missing = missing || !tags_are(ow, tag);
+                    const float kn = __expf(tagged_value(mw.x) - gmax);
+                    gsum = fmaf(tagged_value(mw.y), kn, gsum);
+                    a0 = fmaf(tagged_value(ow.x), kn, a0);
+                    a1 = fmaf(tagged_value(ow.y), kn, a1);
                 }
-                __syncthreads();                   // the staged items have been consumed
+                if (!missing) emit(idx, a0, a1, gmax, gsum);
             }
-            if (pass == 0u && v0 == 0 && !direct) VFKV_TRACE(8);
-            if (!xrank) continue;
-
-            // ---- position-sharded call: merge the blocks of all ranks for the same pairs ---------------
-            // Every rank's kernel stores its block of these rows into this GPU's buffer, this rank's
-            // own block included (emit above).  The words are polled, with the exchange's time limit,
-            // until they carry the exchange number; then the same merge runs over one part per rank
-            // (at most 8, so a group of lanes holds them).  Loads touch this GPU's memory only.
-            {
-                const uint64_t *local = s_fan.base[s_fan.rank];
-                const uint32_t e = fs.epoch, world = s_fan.world;
-                const uint32_t P = pow2_at_least(world), ppw = 32u / P;
-                for (uint32_t b = warp * ppw; b < nv; b += uint32_t(kWarps) * ppw) {
-                    const uint32_t vi = b + lane / P, r = lane % P;
-                    const uint32_t idx = vi < nv ? pair_of(v0 + vi) : 0xFFFFFFFFu;
-                    const bool active = idx != 0xFFFFFFFFu && r < world;
-                    float o0 = 0.f, o1 = 0.f, m = kMaskedScore, l = 0.f;
-                    uint64_t row = 0;
-                    uint32_t d = 0;
-                    if (active) {
-                        d = 2 * (idx % HD2);
-                        row = uint64_t(s) * p.n_q_heads + kvh * g + idx / HD2;
-                        const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
-                        uint64_t t0 = 0;
-                        for (;;) {
-                            const ulonglong2 ow = tagged_load2_sys(local + rs.o + row * D + d);
-                            const uint64_t mw = tagged_load1_sys(local + rs.m + row);
-                            const uint64_t lw = tagged_load1_sys(local + rs.m + s_fan.n_rows + row);
-                            if (tags_are(ow, e) && uint32_t(mw >> 32) == e && uint32_t(lw >> 32) == e) {
-                                o0 = tagged_value(ow.x); o1 = tagged_value(ow.y); m = tagged_value(mw); l = tagged_value(lw);
-                                break;
-                            }
-                            const uint64_t now = global_timer_ns();
-                            if (t0 == 0) t0 = now;
-                            else if (now - t0 > s_fan.wait_ns || *reinterpret_cast<volatile uint32_t *>(&s_late) != 0u) { s_late = 1u; break; }
-                            else __nanosleep(40);
-                        }
-                    }
-                    group_merge(P, o0, o1, m, l);
-                    // a rank that never answered: the row is written as zeros, not as a partial sum
-                    const bool late = *reinterpret_cast<volatile uint32_t *>(&s_late) != 0u;
-                    const float inv = (l > 0.f && !late) ? 1.0f / l : 0.f;
-                    if (active && r == 0u && p.out) *reinterpret_cast<float2 *>(p.out + row * D + d) = make_float2(o0 * inv, o1 * inv);
-                }
+            if (!__syncthreads_or(missing)) break;               // also: every thread is done with the staged words
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            if (__syncthreads_or(now - t0 > mp.merge_wait_ns)) { // a partial of this launch never arrived (decided together)
+                if (threadIdx.x == 0) atomicOr(p.status, 1u);
+                return;
             }
+            __nanosleep(200);
         }
-        if (direct || *reinterpret_cast<volatile uint32_t *>(&s_flag) == 3u) break;
+        VFKV_TRACE(8);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        if (s_flag == 3u) atomicOr(p.status, 1u);     // a partial of this launch never arrived; rows may be incomplete
-        if (s_late != 0u) atomicOr(p.status, 8u);     // a rank's block did not arrive in time; rows are zeros
+    if (!xrank) { VFKV_TRACE(9); return; }
+
+    // ---- position-sharded call: merge the blocks of all ranks ------------------------------------------
+    // Every rank's kernel stores its block of these rows into this GPU's buffer, this rank's own
+    // block included (emit above).  The same scheme as above, with the exchange's time limit: the o
+    // rows of this kv-head are contiguous in each rank's block and come in by asynchronous copies,
+    // the few m and l words by one polling load per thread.  Loads touch this GPU's memory only.
+    {
+        const uint64_t *local = s_fan.base[s_fan.rank];
+        const uint32_t e = fs.epoch, world = s_fan.world;
+        const uint64_t row0 = uint64_t(s) * p.n_q_heads + kvh * g;
+        const uint32_t o_words = g * D;                           // per rank
+        float *const s_ml = reinterpret_cast<float *>(stgw + uint64_t(world) * o_words);   // [world][2][g]
+        uint64_t t0 = 0;
+        bool late = false;
+        for (;;) {
+            for (uint32_t k = threadIdx.x; k < world * (o_words / 2); k += blockDim.x) {
+                const uint32_t r = k / (o_words / 2), q2 = k % (o_words / 2);
+                const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                             ::"r"(stg_base + 8u * (r * o_words + 2u * q2)), "l"(local + rs.o + row0 * D + 2ull * q2) : "memory");
+            }
+            bool missing = false;
+            for (uint32_t k = threadIdx.x; k < world * 2u * g; k += blockDim.x) {
+                const uint32_t r = k / (2u * g), which = (k / g) & 1u, j = k % g;
+                const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
+                const uint64_t w = tagged_load1_sys(local + rs.m + uint64_t(which) * s_fan.n_rows + row0 + j);
+                missing = missing || uint32_t(w >> 32) != e;
+                s_ml[k] = tagged_value(w);
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncthreads();
+            for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+                const uint32_t j = idx / HD2;
+                float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
+                for (uint32_t r = 0; r < world; ++r) gmax = fmaxf(gmax, s_ml[(r * 2u) * g + j]);
+                for (uint32_t r = 0; r < world; ++r) {
+                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(stgw + uint64_t(r) * o_words + 2 * idx);
+                    missing = missing || !tags_are(ow, e);
+                    const float kn = __expf(s_ml[(r * 2u) * g + j] - gmax);
+                    gsum = fmaf(s_ml[(r * 2u + 1u) * g + j], kn, gsum);
+                    a0 = fmaf(tagged_value(ow.x), kn, a0);
+                    a1 = fmaf(tagged_value(ow.y), kn, a1);
+                }
+                // a rank that never answered: the row is written as zeros, not as a partial sum
+                const float inv = (gsum > 0.f && !late) ? 1.0f / gsum : 0.f;
+                if ((!missing || late) && p.out)
+                    *reinterpret_cast<float2 *>(p.out + row0 * D + 2 * idx) = make_float2(a0 * inv, a1 * inv);
+            }
+            if (!__syncthreads_or(missing) || late) break;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            late = __syncthreads_or(now - t0 > s_fan.wait_ns);    // decided together; one more round writes the zeros
+            __nanosleep(200);
+        }
+        if (late && threadIdx.x == 0) atomicOr(p.status, 8u);
     }
     VFKV_TRACE(9);
 }
-
 
 // ---- host side -------------------------------------------------------------------------------------
 
@@ -1165,7 +1080,14 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
             if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tensor-core attention)");
             configured[ctx->device & 63].store(true, std::memory_order_release);
         }
-        dim3 grid(mp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
+        MmaParams lp = mp;
+        // The merging CTA stages the whole group's partials (and, in a one-launch exchange, every
+        // rank's block of the kv-head) in the ring: fewer splits where they would not fit.
+        const uint64_t pbytes = uint64_t(mp.a.group) * (D + 2) * 8;
+        if (uint64_t(lp.a.n_splits) * pbytes > uint64_t(S::RING_BYTES)) lp.a.n_splits = uint32_t(S::RING_BYTES / pbytes) > 0u ? uint32_t(S::RING_BYTES / pbytes) : 1u;
+        if (lp.fan_merge && 8ull * (uint64_t(mp.a.group) * D * 8 + 2ull * mp.a.group * 4) > uint64_t(S::RING_BYTES))
+            return set_error(ctx, VFKV_ERR_UNSUPPORTED, "one-launch exchange does not fit this kernel shape");
+        dim3 grid(lp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
         {
             ProfScope ps(ctx, VFKV_PROF_FA_SPLIT, st);
             cudaLaunchConfig_t cfg = {};
@@ -1185,21 +1107,20 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
             // Cluster form of the split merge: the splits of one (sequence, kv-head) as one cluster.
             // Used when the context asks for it, the merge scratch fits beside the ring, and the
             // device can keep every cluster of the grid resident at once (so none waits for another).
-            MmaParams lp = mp;
             constexpr int NH = (DT == VFKV_F8 || !ROWS2) ? 8 : 16;
             constexpr bool kFits = (W * NH * (D + 1) + 2 * W * NH + NH * D + 2 * NH) * 4 <= S::RING_BYTES;
-            if (kFits && ctx->cluster_merge && mp.fan_merge == 0u && mp.a.n_splits >= 2 && mp.a.n_splits <= 16) {
+            if (kFits && ctx->cluster_merge && mp.fan_merge == 0u && lp.a.n_splits >= 2 && lp.a.n_splits <= 16) {
                 static std::atomic<int> max_clusters[64][17];   // per device and cluster size; 0 = not asked yet, -1 = no
-                std::atomic<int> &slot_known = max_clusters[ctx->device & 63][mp.a.n_splits];
+                std::atomic<int> &slot_known = max_clusters[ctx->device & 63][lp.a.n_splits];
                 int known = slot_known.load(std::memory_order_acquire);
                 cudaLaunchAttribute &ca = attr[n_attr];
                 ca.id = cudaLaunchAttributeClusterDimension;
-                ca.val.clusterDim.x = mp.a.n_splits; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = 1;
+                ca.val.clusterDim.x = lp.a.n_splits; ca.val.clusterDim.y = 1; ca.val.clusterDim.z = 1;
                 cfg.numAttrs = n_attr + 1;
                 if (known == 0) {
                     known = -1;
                     bool ok = true;
-                    if (mp.a.n_splits > 8)
+                    if (lp.a.n_splits > 8)
                         ok = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
                     int n = 0;
                     if (ok && cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) known = n;
