@@ -203,7 +203,11 @@ int32_t vfkv_flash_attn_split_reduce(vfkv_ctx *ctx, vfkv_workspace *ws, const fl
  *     stream at the start of every call.  Two calls whose GPU work can overlap
  *     (different streams, or different threads) race on it: serialise them.
  *   - Errors: the return code, and vfkv_noalloc_last_error() for the text
- *     (per calling thread). */
+ *     (per calling thread).  Every argument is a scalar checked on the host, so
+ *     the device-side status word of the other entry points (out-of-range rows in
+ *     device arrays, waits that ran out) has nothing to report on this path and
+ *     there is nothing to poll: the word at the head of the array only exists
+ *     because the kernels' parameter block wants a valid address. */
 int32_t vfkv_flash_attn_split_reduce_noalloc(const float *d_q, const void *d_k, const void *d_v,
                                              float *d_out, uint32_t dtype, uint32_t n_heads,
                                              uint32_t n_kv_heads, uint32_t head_dim,

@@ -86,7 +86,9 @@ uint64_t vfkv_longest_common_prefix(const uint32_t *a, uint64_t n_a, const uint3
 /* The "KV prepare" of ServerSession::generate_reuse (state.rs:199-229): with reuse != 0,
  * k = min(lcp(cached, full), n_full - 1); k == 0 or reuse == 0 resets the slot's counter, else
  * the counter becomes k and rows [0, k) are kept; the caller prefills full[k..] at base_pos k.
- * *start_pos receives k. */
+ * *start_pos receives k.  As in the reference, the environment variable VF_KV_REUSE_OVERSHOOT=n
+ * (a test hook, state.rs:206-212) makes k overshoot the common prefix by n rows, bounded by
+ * n_cached and n_full - 1, so that a test can show that a wrong reuse changes the cache. */
 int32_t vfkv_kv_reuse_prepare(vfkv_cache *cache, uint32_t slot, const uint32_t *cached_tokens,
                               uint64_t n_cached, const uint32_t *full_tokens, uint64_t n_full,
                               int32_t reuse, uint32_t *start_pos);

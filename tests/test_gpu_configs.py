@@ -174,3 +174,102 @@ def test_config5_long_context_fp8_chunked_prefill_and_sharded_merge(ctx):
     finally:
         fwd.workspace.destroy()
         cache.destroy()
+
+
+def device_fill(fwd, gen, layer, slot, n, hkv, d, fp8, chunk=8192):
+    """Pre-fills positions [0, n) from a device-side generator (N(0,1), 1 % x20 outliers for FP8);
+    the oracle later reads the cache bytes back, so the values themselves need not reach the host."""
+    import torch
+    for p in range(0, n, chunk):
+        m = min(chunk, n - p)
+        kv = torch.randn(2, m, hkv * d, device="cuda", generator=gen)
+        if fp8:
+            kv = torch.where(torch.rand(2, m, hkv * d, device="cuda", generator=gen) < 0.01, kv * 20.0, kv)
+        fwd.b_step_kv_write(layer, kv[0], kv[1], m, p, slot)
+
+
+def test_config2_all_36_layers_in_one_decode_token_call(ctx):
+    """The whole workload as the benchmark runs it: 36 layers, FP8, context 8192, 16 splits, one
+    vfkv_decode_token call (36 fused launches), dependent-launch mode 2.  A sample of layers is
+    checked against the oracle reading that layer's cache bytes; the appended rows are bit-exact."""
+    import torch
+    hq, hkv, d, L, n_layers = 32, 8, 128, 8192, 36
+    rng = np.random.default_rng(22)
+    gen = torch.Generator(device="cuda").manual_seed(22)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(n_layers, hkv, d, L), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=16)
+    stream = torch.cuda.Stream()
+    try:
+        for layer in range(n_layers):
+            device_fill(fwd, gen, layer, 0, L - 1, hkv, d, True)
+        q = rng.standard_normal((n_layers, 1, hq, d), dtype=np.float32)
+        kn, vn = kv_values(rng, (n_layers, 1, hkv, d)), kv_values(rng, (n_layers, 1, hkv, d))
+        out = torch.zeros(n_layers, 1, hq, d, device="cuda")
+        dq, dk, dv, dpos = to_dev(q), to_dev(kn), to_dev(vn), to_dev(np.array([L - 1], np.uint32))
+        torch.cuda.synchronize()
+        fwd.stream = stream.cuda_stream
+        ctx.set_dependent_launch(2)
+        with torch.cuda.stream(stream):
+            fwd.decode_token(dq, dk, dv, out, None, dpos, 1, L)
+        stream.synchronize()
+        ctx.poll()
+        got = out.cpu().numpy()
+        for layer in (0, 1, 17, 34, 35):
+            kb, vb = slab_bytes(cache, layer, 0, L)
+            assert np.array_equal(kb[-1024:], oracle.kv_store_fp8(kn[layer, 0]))
+            assert np.array_equal(vb[-1024:], oracle.kv_store_fp8(vn[layer, 0]))
+            want = oracle.attention_ref(q[layer, 0], kb, vb, oracle.F8, hq, hkv, d, L)
+            err = rel_err(got[layer, 0], want)
+            assert err < 3e-2, (layer, err)
+            assert err < 1e-4, ("regression gate", layer, err)
+    finally:
+        ctx.set_dependent_launch(0)
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+def test_config4_batch8_over_the_six_layer_period_in_one_decode_token_call(ctx):
+    """The Gemma-style workload at its stated size: batch 8, context 32768, F16, head_dim 256, five
+    sliding layers (window 1024) and one global layer, soft-cap 50, through vfkv_decode_token with
+    its per-layer windows.  A sliding and the global layer are checked for the first and the last
+    sequence against the oracle."""
+    import torch
+    hq, hkv, d, L, B, n_layers = 16, 8, 256, 32768, 8, 6
+    rng = np.random.default_rng(44)
+    gen = torch.Generator(device="cuda").manual_seed(44)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(n_layers, hkv, d, L, n_slots=B), vf.KvDtype.F16)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, max_batch=B, sliding_window=1024, sliding_layers=[0, 1, 2, 3, 4],
+                         softcap=50.0)
+    stream = torch.cuda.Stream()
+    try:
+        for layer in range(n_layers):
+            for s in range(B):
+                device_fill(fwd, gen, layer, s, L - 1, hkv, d, False, chunk=16384)
+        q = rng.standard_normal((n_layers, B, hq, d), dtype=np.float32)
+        kn = rng.standard_normal((n_layers, B, hkv, d), dtype=np.float32)
+        vn = rng.standard_normal((n_layers, B, hkv, d), dtype=np.float32)
+        out = torch.zeros(n_layers, B, hq, d, device="cuda")
+        dq, dk, dv = to_dev(q), to_dev(kn), to_dev(vn)
+        dpos = to_dev(np.full(B, L - 1, np.uint32))
+        torch.cuda.synchronize()
+        fwd.stream = stream.cuda_stream
+        ctx.set_dependent_launch(2)
+        with torch.cuda.stream(stream):
+            fwd.decode_token(dq, dk, dv, out, None, dpos, B, L)
+        stream.synchronize()
+        ctx.poll()
+        got = out.cpu().numpy()
+        for layer in (3, 5):
+            start = L - 1024 if layer < 5 else 0
+            for s in (0, B - 1):
+                kb, vb = slab_bytes(cache, layer, s, L)
+                assert np.array_equal(kb.view(np.uint16)[-hkv * d:], oracle.kv_copy_fp16(kn[layer, s]))
+                want = oracle.attention_ref(q[layer, s], kb.view(np.uint16), vb.view(np.uint16), oracle.F16, hq, hkv, d,
+                                            L, start, None, 50.0)
+                err = float(np.max(np.abs(got[layer, s] - want)))
+                assert err < 2e-3, (layer, s, err)
+                assert err < 2e-5, ("regression gate", layer, s, err)
+    finally:
+        ctx.set_dependent_launch(0)
+        fwd.workspace.destroy()
+        cache.destroy()

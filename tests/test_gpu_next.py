@@ -306,3 +306,58 @@ def test_kv_reuse_prepare_and_invalidate(ctx):
         assert cache.seq_len(1) == 0
     finally:
         cache.destroy()
+
+
+def test_kv_reuse_is_byte_identical_and_an_overshoot_is_caught(ctx, monkeypatch):
+    """tests/kv_reuse_ident.rs:224-320 at cache level.  Reusing the longest common prefix and
+    prefilling the rest leaves exactly the bytes of a fresh prefill; with the reference's teeth hook
+    VF_KV_REUSE_OVERSHOOT the reuse keeps rows of the OLD prompt past the common prefix, and both
+    the cache bytes and the attention output differ from the fresh ones."""
+    import torch
+    hq, hkv, d, max_seq, vocab = 8, 2, 64, 128, 50
+    rng = np.random.default_rng(8)
+    table_k = kv_values(rng, (vocab, hkv, d))                 # a token's K and V rows depend on the token only
+    table_v = kv_values(rng, (vocab, hkv, d))
+    old = [int(x) for x in rng.integers(0, vocab, 60)]
+    new = old[:37] + [int(x) for x in (rng.integers(0, vocab, 30) + 1) % vocab]
+    new[37] = (old[37] + 1) % vocab                           # the prompts part ways at position 37
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+
+    def prefill(fwd, tokens, base):
+        if len(tokens) > base:
+            ids = np.array(tokens[base:])
+            fwd.b_step_kv_write(0, to_dev(table_k[ids]), to_dev(table_v[ids]), len(ids), base, 0)
+
+    def run(overshoot):
+        if overshoot:
+            monkeypatch.setenv("VF_KV_REUSE_OVERSHOOT", str(overshoot))
+        else:
+            monkeypatch.delenv("VF_KV_REUSE_OVERSHOOT", raising=False)
+        cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, max_seq), vf.KvDtype.F8)
+        fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+        try:
+            prefill(fwd, old, 0)
+            cache.set_seq_len(0, len(old))
+            k = cache.reuse_prepare(old, new)
+            prefill(fwd, new, k)
+            out = torch.zeros(hq, d, device="cuda")
+            fwd.step_attention(0, to_dev(q), out, len(new) - 1)
+            torch.cuda.synchronize()
+            nb = len(new) * cache.row_bytes(0)
+            return k, dev_view_bytes(cache.k_buffer, nb), out.cpu().numpy()
+        finally:
+            fwd.workspace.destroy()
+            cache.destroy()
+
+    fresh = oracle.kv_store_fp8(table_k[np.array(new)])
+    k, kb, out = run(0)
+    assert k == 37 and np.array_equal(kb, fresh)
+    want = oracle.attention_ref(q, fresh, oracle.kv_store_fp8(table_v[np.array(new)]), oracle.F8, hq, hkv, d, len(new))
+    assert rel_err(out, want) < 1e-4
+    k2, kb2, out2 = run(5)
+    assert k2 == 42
+    assert not np.array_equal(kb2, fresh)                     # rows 37..41 still hold the old prompt
+    assert np.array_equal(kb2[:37 * hkv * d], fresh[:37 * hkv * d]) and np.array_equal(kb2[42 * hkv * d:], fresh[42 * hkv * d:])
+    assert rel_err(out2, want) > 1e-3                         # and the output shows it
+    k3, _, _ = run(10 ** 6)                                   # bounded by the resident rows and the new prompt
+    assert k3 == min(len(old), len(new) - 1)

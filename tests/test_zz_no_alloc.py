@@ -82,3 +82,38 @@ def test_noalloc_entry_rejects_what_does_not_fit(ctx):
                                                    None) == E_INVAL
     assert L_.vfkv_flash_attn_split_reduce_noalloc(p, p, p, p, 7, 64, 8, 128, 8, 8, 1.0, 0, 0.0, 1, None) == E_INVAL
     torch.cuda.synchronize()
+
+
+def test_noalloc_entry_leaves_the_free_device_memory_unchanged(ctx):
+    """What the entry point is for: once a kernel shape has been used (the driver loads a kernel's
+    code when it is first launched), further calls take no device memory at all.  Free memory as
+    the driver reports it is read before and after a series of calls, head_dim 512 included (that
+    shape configures its kernel's dynamic shared memory on the way in)."""
+    import torch
+    L_ = ctx._lib
+    rng = np.random.default_rng(9)
+    cases = []
+    for dtype, hq, hkv, d, L, n_splits in ((oracle.F8, 32, 8, 128, 2000, 8), (oracle.F16, 16, 8, 256, 600, 4),
+                                            (oracle.F32, 8, 2, 512, 300, 3), (oracle.F32, 8, 2, 64, 100, 1)):
+        k = oracle.store(kv_values(rng, (L, hkv, d), outlier_frac=0.0), dtype)
+        q = rng.standard_normal((hq, d), dtype=np.float32)
+        out = torch.zeros(hq, d, device="cuda")
+        cases.append((to_dev(q), to_dev(k), out, dtype, hq, hkv, d, L, n_splits))
+
+    def call_all():
+        for dq, dk, out, dtype, hq, hkv, d, L, n_splits in cases:
+            rc = L_.vfkv_flash_attn_split_reduce_noalloc(dq.data_ptr(), dk.data_ptr(), dk.data_ptr(), out.data_ptr(),
+                                                         dtype, hq, hkv, d, L, L, float(1.0 / np.sqrt(d)), 0, 0.0,
+                                                         n_splits, None)
+            assert rc == 0, L_.vfkv_noalloc_last_error()
+
+    call_all()                                      # first use of every kernel shape
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call_all()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    for _, _, out, *_ in cases:
+        assert bool(torch.isfinite(out).all())

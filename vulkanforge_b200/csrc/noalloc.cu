@@ -124,6 +124,8 @@ int32_t vfkv_flash_attn_split_reduce_noalloc(const float *d_q, const void *d_k, 
 
     // The array keeps whatever the previous call left.  The partials are fully rewritten by
     // the split kernel before the merge reads them; only the status word must start at zero.
+    // (Nothing can raise it here -- the CUDA-core kernels only report out-of-range entries of
+    // device arrays, and this entry point passes host-checked scalars -- so no call reads it back.)
     cudaError_t e = cudaMemsetAsync(base, 0, sizeof(uint32_t), st);
     if (e != cudaSuccess) return fail(VFKV_ERR_CUDA, cudaGetErrorString(e));
 

@@ -3,6 +3,7 @@
 // the bookkeeping that moves the cache's length counter (src/server/state.rs:183-290,
 // src/server/auto_ctx.rs:107-141, src/backend/vulkan/forward/arch/gemma4.rs:27-49).
 // Everything here goes through the public C ABI of vfkv.h; no kernels.
+#include <cstdlib>
 #include "../../include/vfkv_next.h"
 
 namespace {
@@ -60,6 +61,18 @@ int32_t vfkv_kv_reuse_prepare(vfkv_cache *cache, uint32_t slot, const uint32_t *
         const uint64_t lcp = vfkv_longest_common_prefix(cached_tokens, n_cached, full_tokens, n_full);
         const uint64_t cap = n_full ? n_full - 1 : 0;      // at least one token is always prefilled
         k = lcp < cap ? lcp : cap;
+        // The reference's one fault-injection hook (state.rs:206-212, never set in production):
+        // reuse more rows than the prompts have in common, bounded by the resident rows and the
+        // new prompt, so that a test can show that a wrong reuse is caught.
+        if (const char *extra = std::getenv("VF_KV_REUSE_OVERSHOOT")) {
+            char *end = nullptr;
+            const unsigned long long n = std::strtoull(extra, &end, 10);
+            if (end != extra && *end == '\0') {
+                k += n;
+                if (k > n_cached) k = n_cached;
+                if (k > cap) k = cap;
+            }
+        }
     }
     if (k == 0) return vfkv_cache_reset(cache, slot);
     if (k > UINT32_MAX) return VFKV_ERR_OVERFLOW;
