@@ -350,6 +350,27 @@ int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, c
 int32_t vfkv_merge_partials_packed(vfkv_ctx *ctx, const float *d_packed, uint32_t n_parts,
                                    uint32_t n_rows, uint32_t head_dim, float *d_out, void *stream);
 
+/* ---- the sharding plan (host arithmetic only; no counterpart in the reference) ----------------
+ *
+ * By position: global position p of a sequence is held by rank (p / page) % world at local position
+ * ((p / page) / world) * page + p % page, so appends rotate over the GPUs and every rank's share of
+ * any context differs by at most one page.  local_len = how many of the positions [0, seq_len) a
+ * rank holds (they occupy its local rows [0, local_len)); local_capacity = rows a rank's slab needs
+ * for contexts up to max_seq_len.  world and page must be non-zero (0 is returned otherwise). */
+uint32_t vfkv_shard_owner(uint32_t world, uint32_t page, uint64_t pos);
+uint64_t vfkv_shard_local_pos(uint32_t world, uint32_t page, uint64_t pos);
+uint64_t vfkv_shard_local_len(uint32_t world, uint32_t page, uint64_t seq_len, uint32_t rank);
+uint64_t vfkv_shard_local_capacity(uint32_t world, uint32_t page, uint64_t max_seq_len);
+/* By sequence: longest-first greedy balancing of n sequences over `world` ranks by context length
+ * (ties: lower sequence index first, lower rank first); owner_out[i] = rank that owns sequence i. */
+int32_t vfkv_assign_sequences(const uint32_t *lengths, uint32_t n, uint32_t world, uint32_t *owner_out);
+/* By kv-head group: rank r of `world` owns kv-heads [first, first + count) and the q-heads
+ * [first * g, (first + count) * g) that read them (the kvh = h / g mapping of
+ * vk_shaders/flash_attn_split.comp:83-95); outputs are disjoint head slices, no exchange.  The
+ * heads are dealt as evenly as n_kv_heads allows. */
+int32_t vfkv_shard_kv_heads(uint32_t world, uint32_t rank, uint32_t n_kv_heads, uint32_t *first,
+                            uint32_t *count);
+
 /* ---- peer exchange of partials (position sharding without a library collective) -----------
  *
  * No counterpart in the reference.  Each GPU of the group owns one exchange buffer of 8-byte words

@@ -1,0 +1,245 @@
+//! `src/backend/cuda/mod.rs` -- the dispatch helpers of the KV-cache hot path on the CUDA backend.
+//!
+//! `Forward` keeps the method names it has in `src/backend/vulkan/forward/runs.rs` and
+//! `forward/executor/attention.rs`: `run_kv_store_fp8`, `run_kv_copy_fp16`, `run_scalar_attn`,
+//! `run_flash_attn_split_reduce`, `step_kv_write`, `step_attention`, `b_step_kv_write`.  What was
+//! (device, registry, command buffer) becomes (device, stream): work is enqueued on the stream in
+//! call order, which replaces the pipeline barriers the Vulkan code records between these
+//! dispatches.  Buffers are device pointers.  A decode step may also be issued as ONE call,
+//! `decode_step`, which appends the token and attends in a single kernel launch per layer.
+//!
+//! NOT COMPILED in the repository this file lives in (no Rust toolchain in its build image).
+pub mod kv_cache;
+
+use std::os::raw::c_void;
+use std::ptr;
+
+use kv_cache::{CudaDevice, KvCache};
+use vfkv_sys as sys;
+
+/// Per-layer routing the model configuration decides (forward/arch/gemma4.rs:27-73).
+pub struct AttnRouting {
+    pub sliding_window: u32,
+    pub sliding_layers: Vec<bool>,
+    /// publisher layer of each layer (itself unless it subscribes to another layer's K/V)
+    pub kv_read_layer: Vec<u32>,
+    pub attn_scale: f32,
+    pub softcap: f32,
+}
+
+pub struct Forward {
+    pub kv_cache: KvCache,
+    pub n_heads: u32,
+    pub routing: AttnRouting,
+    /// fa_scratch_out / _max / _sum of forward/setup.rs:203-230
+    workspace: *mut sys::vfkv_workspace,
+    /// q_buf / attn_out of the current slot (device pointers, f32)
+    pub q_buf: *const f32,
+    pub attn_out: *mut f32,
+}
+
+impl Forward {
+    pub fn new(
+        dev: &CudaDevice,
+        kv_cache: KvCache,
+        n_heads: u32,
+        routing: AttnRouting,
+    ) -> Result<Forward, String> {
+        let max_hd = (0..kv_cache.config.n_layers).map(|l| kv_cache.head_dim_for(l)).max().unwrap_or(0);
+        let mut workspace = ptr::null_mut();
+        dev.check(unsafe { sys::vfkv_workspace_create(dev.ctx, 1, n_heads, max_hd, 64, &mut workspace) })?;
+        Ok(Forward { kv_cache, n_heads, routing, workspace, q_buf: ptr::null(), attn_out: ptr::null_mut() })
+    }
+
+    // ---- runs.rs -----------------------------------------------------------------------------
+
+    /// runs.rs:2437-2478
+    pub fn run_kv_store_fp8(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        src: *const f32,
+        dst: *mut c_void,
+        n_elements: u32,
+        dst_byte_offset: u64,
+        _label: &'static str,
+    ) -> Result<(), String> {
+        dev.check(unsafe { sys::vfkv_kv_store_fp8(dev.ctx, src, dst, n_elements, dst_byte_offset, stream) })
+    }
+
+    /// runs.rs:2389-2430
+    pub fn run_kv_copy_fp16(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        src: *const f32,
+        dst: *mut c_void,
+        n_elements: u32,
+        dst_byte_offset: u64,
+        _label: &'static str,
+    ) -> Result<(), String> {
+        dev.check(unsafe { sys::vfkv_kv_copy_fp16(dev.ctx, src, dst, n_elements, dst_byte_offset, stream) })
+    }
+
+    fn kv_start(&self, layer: u32, position: u32) -> u32 {
+        if self.routing.sliding_layers.get(layer as usize).copied().unwrap_or(false) {
+            unsafe { sys::vfkv_sliding_kv_start(position, self.routing.sliding_window) }
+        } else {
+            0
+        }
+    }
+
+    /// runs.rs:722-821: kv_layer / kv_start routing, split path from two 64-position tiles on.
+    pub fn run_scalar_attn(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        position: u32,
+    ) -> Result<(), String> {
+        let kv_layer = self.routing.kv_read_layer.get(layer as usize).copied().unwrap_or(layer);
+        let kv_start = self.kv_start(layer, position);
+        dev.check(unsafe {
+            sys::vfkv_scalar_attn(
+                self.kv_cache.handle,
+                self.workspace,
+                layer,
+                kv_layer,
+                self.q_buf,
+                self.attn_out,
+                self.n_heads,
+                0,
+                position,
+                kv_start,
+                self.routing.attn_scale,
+                self.routing.softcap,
+                stream,
+            )
+        })
+    }
+
+    /// runs.rs:1463-1571; `n_tiles` is the split count here (0 = let the library choose).
+    #[allow(clippy::too_many_arguments)]
+    pub fn run_flash_attn_split_reduce(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        position: u32,
+        n_tiles: u32,
+        kv_layer: u32,
+        kv_start: u32,
+    ) -> Result<(), String> {
+        dev.check(unsafe {
+            sys::vfkv_attend(
+                self.kv_cache.handle,
+                self.workspace,
+                layer,
+                kv_layer,
+                self.q_buf,
+                self.attn_out,
+                self.n_heads,
+                0,
+                position + 1,
+                kv_start,
+                self.routing.attn_scale,
+                self.routing.softcap,
+                n_tiles,
+                stream,
+            )
+        })
+    }
+
+    // ---- executor/attention.rs ---------------------------------------------------------------
+
+    /// step_kv_write (attention.rs:546-596): one token's rotated K and its V into the cache.
+    pub fn step_kv_write(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        k_src: *const f32,
+        v_src: *const f32,
+        position: u32,
+    ) -> Result<(), String> {
+        dev.check(unsafe { sys::vfkv_append(self.kv_cache.handle, layer, k_src, v_src, 1, 0, position, stream) })
+    }
+
+    /// b_step_kv_write (attention.rs:2134-2190): `seq_len` consecutive tokens from `base_pos`.
+    #[allow(clippy::too_many_arguments)]
+    pub fn b_step_kv_write(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        k_src: *const f32,
+        v_src: *const f32,
+        seq_len: u32,
+        base_pos: u32,
+    ) -> Result<(), String> {
+        dev.check(unsafe { sys::vfkv_append(self.kv_cache.handle, layer, k_src, v_src, seq_len, 0, base_pos, stream) })
+    }
+
+    /// step_attention (attention.rs:599-626)
+    pub fn step_attention(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        position: u32,
+    ) -> Result<(), String> {
+        self.run_scalar_attn(dev, stream, layer, position)
+    }
+
+    /// KvWrite + Attention of one layer as one launch (layer_plan.rs:472-483 in one step).
+    /// `d_positions` is a device word holding `position`, so that a captured CUDA graph can be
+    /// replayed token after token.
+    #[allow(clippy::too_many_arguments)]
+    pub fn decode_step(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        k_src: *const f32,
+        v_src: *const f32,
+        d_positions: *const u32,
+        max_seq_len_hint: u32,
+    ) -> Result<(), String> {
+        let window = if self.routing.sliding_layers.get(layer as usize).copied().unwrap_or(false) {
+            self.routing.sliding_window
+        } else {
+            0
+        };
+        dev.check(unsafe {
+            sys::vfkv_decode_step(
+                self.kv_cache.handle,
+                self.workspace,
+                layer,
+                self.q_buf,
+                k_src,
+                v_src,
+                self.attn_out,
+                self.n_heads,
+                ptr::null(),
+                d_positions,
+                1,
+                max_seq_len_hint,
+                window,
+                self.routing.attn_scale,
+                self.routing.softcap,
+                0,
+                stream,
+            )
+        })
+    }
+
+    /// After the token's GPU work has been waited for (forward/decode.rs:812).
+    pub fn commit_position(&mut self, position: u32) {
+        self.kv_cache.set_current_seq_len(position + 1);
+    }
+
+    pub fn destroy(self) {
+        unsafe { sys::vfkv_workspace_destroy(self.workspace) };
+        self.kv_cache.destroy();
+    }
+}

@@ -274,6 +274,47 @@ def test_one_launch_exchange_wait_runs_out_and_context_survives(ctx):
         _destroy_group(ranks)
 
 
+@pytest.mark.parametrize("world,dtype", [(2, "F8"), (4, "F16"), (3, "F8")])
+def test_kv_head_group_sharding_needs_no_exchange(ctx, world, dtype):
+    """Sharding by kv-head group: rank r holds the rows of its kv-heads only (a cache with fewer
+    heads) and the q-heads that read them (kvh = h / g, flash_attn_split.comp:83-95).  Each rank's
+    decode step writes a disjoint slice of the output heads; put side by side the slices are the
+    full result.  Ranks are emulated one after the other: there is nothing to exchange."""
+    import ctypes as C
+    import torch
+    hq, hkv, d, L = 32, 8, 128, 3000
+    odt = {"F8": oracle.F8, "F16": oracle.F16}[dtype]
+    rng = np.random.default_rng(world)
+    k = kv_values(rng, (L, hkv, d), outlier_frac=0.01 if dtype == "F8" else 0.0)
+    v = kv_values(rng, (L, hkv, d), outlier_frac=0.01 if dtype == "F8" else 0.0)
+    q = rng.standard_normal((hq, d), dtype=np.float32)
+    g = hq // hkv
+    out = np.zeros((hq, d), np.float32)
+    first, count = C.c_uint32(), C.c_uint32()
+    for r in range(world):
+        ctx.check(ctx._lib.vfkv_shard_kv_heads(world, r, hkv, C.byref(first), C.byref(count)))
+        h0, n = first.value, count.value
+        cache = vf.KvCache(ctx, vf.KvCacheConfig(1, n, d, L), vf.KvDtype[dtype])
+        fwd = vf.CudaForward(ctx, cache, n_heads=n * g)
+        try:
+            fwd.b_step_kv_write(0, to_dev(k[:L - 1, h0:h0 + n]), to_dev(v[:L - 1, h0:h0 + n]), L - 1, 0)
+            o = torch.zeros(n * g, d, device="cuda")
+            pos = to_dev(np.array([L - 1], np.uint32))
+            fwd.decode_step(0, to_dev(q[h0 * g:(h0 + n) * g]), to_dev(k[L - 1:, h0:h0 + n]), to_dev(v[L - 1:, h0:h0 + n]),
+                            o, None, pos, 1)
+            torch.cuda.synchronize()
+            ctx.poll()
+            out[h0 * g:(h0 + n) * g] = o.cpu().numpy()
+        finally:
+            fwd.workspace.destroy()
+            cache.destroy()
+    want = oracle.attention_ref(q, encode_cache(k, odt), encode_cache(v, odt), odt, hq, hkv, d, L)
+    if dtype == "F8":
+        assert rel_err(out, want) < 1e-4
+    else:
+        assert np.max(np.abs(out - want)) < 2e-5
+
+
 def _nccl_rank(rank, world, port, seq_len, result_dir):
     import torch
     import torch.distributed as dist

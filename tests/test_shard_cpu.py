@@ -164,3 +164,44 @@ def test_sharded_decoder_owner_logic_with_peer_exchange(monkeypatch):
                 assert hi - 1 == sh.local_pos(position)        # the new row is the last local row of its owner
             total += hi
         assert owners == 1 and total == position + 1
+
+
+def test_c_abi_sharding_plan_equals_the_python_forms():
+    """A host without Python binds the plan through the C ABI (vfkv_shard_*, vfkv_assign_sequences):
+    the same numbers as the forms above, on every position of several contexts."""
+    import ctypes as C
+    import vulkanforge_b200 as vf
+    L = vf.load()
+    rng = np.random.default_rng(12)
+    for world, page in ((1, 256), (2, 256), (8, 256), (3, 64), (5, 7)):
+        sh = PositionShards(world, page)
+        for pos in list(range(0, 3 * world * page + 5)) + [131071, 2 ** 33 + 17]:
+            assert L.vfkv_shard_owner(world, page, pos) == sh.owner(pos)
+            assert L.vfkv_shard_local_pos(world, page, pos) == sh.local_pos(pos)
+        for seq_len in (0, 1, page, page + 1, 5 * page + 3, 131072, 2 ** 33 + 9):
+            for r in range(world):
+                assert L.vfkv_shard_local_len(world, page, seq_len, r) == sh.local_len(seq_len, r)
+            assert sum(L.vfkv_shard_local_len(world, page, seq_len, r) for r in range(world)) == seq_len
+            assert L.vfkv_shard_local_capacity(world, page, seq_len) == sh.local_capacity(seq_len)
+    assert L.vfkv_shard_owner(0, 256, 5) == 0 and L.vfkv_shard_local_len(4, 256, 1000, 4) == 0
+    for n, world in ((64, 1), (64, 2), (64, 8), (7, 3), (0, 4), (5, 8)):
+        lens = rng.integers(512, 16385, n).astype(np.uint32)
+        if n > 2:
+            lens[1] = lens[0]                                 # a tie
+        owner = np.full(max(n, 1), 99, np.uint32)
+        rc = L.vfkv_assign_sequences(lens.ctypes.data_as(C.POINTER(C.c_uint32)), n, world,
+                                     owner.ctypes.data_as(C.POINTER(C.c_uint32)))
+        assert rc == 0
+        want = assign_sequences(lens, world)
+        got = [[i for i in range(n) if owner[i] == r] for r in range(world)]
+        assert got == want
+    assert L.vfkv_assign_sequences(None, 3, 2, None) != 0 and L.vfkv_assign_sequences(None, 0, 0, None) != 0
+    first, count = C.c_uint32(), C.c_uint32()
+    for world, hkv in ((1, 8), (2, 8), (4, 8), (8, 8), (3, 8), (8, 2)):
+        covered = []
+        for r in range(world):
+            assert L.vfkv_shard_kv_heads(world, r, hkv, C.byref(first), C.byref(count)) == 0
+            covered += list(range(first.value, first.value + count.value))
+            assert abs(count.value - hkv / world) < 1
+        assert covered == list(range(hkv))
+    assert L.vfkv_shard_kv_heads(2, 2, 8, C.byref(first), C.byref(count)) != 0

@@ -86,6 +86,12 @@ SIGNATURES = {
     "vfkv_attend_partial": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp, vp, vp]),
     "vfkv_merge_partials": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, vp]),
     "vfkv_merge_partials_packed": (i32, [vp, vp, u32, u32, u32, vp, vp]),
+    "vfkv_shard_owner": (u32, [u32, u32, u64]),
+    "vfkv_shard_local_pos": (u64, [u32, u32, u64]),
+    "vfkv_shard_local_len": (u64, [u32, u32, u64, u32]),
+    "vfkv_shard_local_capacity": (u64, [u32, u32, u64]),
+    "vfkv_assign_sequences": (i32, [pu32, u32, u32, pu32]),
+    "vfkv_shard_kv_heads": (i32, [u32, u32, u32, pu32, pu32]),
     "vfkv_exchange_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
     "vfkv_exchange_destroy": (None, [vp]),
     "vfkv_exchange_bytes": (u64, [vp]),

@@ -3,7 +3,9 @@
 // the bookkeeping that moves the cache's length counter (src/server/state.rs:183-290,
 // src/server/auto_ctx.rs:107-141, src/backend/vulkan/forward/arch/gemma4.rs:27-49).
 // Everything here goes through the public C ABI of vfkv.h; no kernels.
+#include <algorithm>
 #include <cstdlib>
+#include <vector>
 #include "../../include/vfkv_next.h"
 
 namespace {
@@ -118,6 +120,63 @@ uint32_t vfkv_gemma4_kv_read_layer(const uint32_t *kv_source, uint32_t n_layers,
     for (uint32_t i = 0; i < n_layers; ++i)
         if (kv_source[i] == want) return i;
     return layer;
+}
+
+
+/* ---- the sharding plan ----------------------------------------------------------------------- */
+
+uint32_t vfkv_shard_owner(uint32_t world, uint32_t page, uint64_t pos)
+{
+    return world && page ? uint32_t((pos / page) % world) : 0u;
+}
+
+uint64_t vfkv_shard_local_pos(uint32_t world, uint32_t page, uint64_t pos)
+{
+    return world && page ? ((pos / page) / world) * page + pos % page : 0ull;
+}
+
+uint64_t vfkv_shard_local_len(uint32_t world, uint32_t page, uint64_t seq_len, uint32_t rank)
+{
+    if (!world || !page || rank >= world) return 0;
+    const uint64_t full_pages = seq_len / page, rest = seq_len % page;
+    uint64_t n = (full_pages / world) * page;
+    const uint64_t extra = full_pages % world;      // ranks below it hold one more full page, it holds the rest
+    if (rank < extra) n += page;
+    else if (rank == extra) n += rest;
+    return n;
+}
+
+uint64_t vfkv_shard_local_capacity(uint32_t world, uint32_t page, uint64_t max_seq_len)
+{
+    if (!world || !page) return 0;
+    const uint64_t pages = (max_seq_len + page - 1) / page;
+    return ((pages + world - 1) / world) * page;
+}
+
+int32_t vfkv_assign_sequences(const uint32_t *lengths, uint32_t n, uint32_t world, uint32_t *owner_out)
+{
+    if (!world || (n && (!lengths || !owner_out))) return VFKV_ERR_INVALID;
+    std::vector<uint32_t> order(n);
+    for (uint32_t i = 0; i < n; ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](uint32_t a, uint32_t b) { return lengths[a] > lengths[b]; });
+    std::vector<uint64_t> load(world, 0);
+    for (uint32_t i : order) {
+        uint32_t best = 0;
+        for (uint32_t r = 1; r < world; ++r)
+            if (load[r] < load[best]) best = r;
+        owner_out[i] = best;
+        load[best] += lengths[i];
+    }
+    return VFKV_OK;
+}
+
+int32_t vfkv_shard_kv_heads(uint32_t world, uint32_t rank, uint32_t n_kv_heads, uint32_t *first, uint32_t *count)
+{
+    if (!world || rank >= world || !first || !count) return VFKV_ERR_INVALID;
+    const uint32_t base = n_kv_heads / world, extra = n_kv_heads % world;   // the first `extra` ranks hold one more
+    *count = base + (rank < extra ? 1u : 0u);
+    *first = rank * base + (rank < extra ? rank : extra);
+    return VFKV_OK;
 }
 
 }  // extern "C"
