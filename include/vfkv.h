@@ -327,6 +327,25 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
                                const uint32_t *windows, float scale, float softcap,
                                uint32_t n_splits, void *stream);
 
+/* The same step without waiting, for two tokens in flight: the counterpart of pre_record /
+ * fill_embed_and_submit / wait_and_read_logits with their two command-buffer / fence pairs and
+ * per-slot scratch (src/backend/vulkan/forward/decode.rs:169-259, forward/setup.rs:203-230).
+ * submit enqueues the input copies (a stream of the workspace), the layers (one recorded CUDA
+ * graph per staging set, on `stream`, which must not be the default stream) and the output copy
+ * (another stream of the workspace), and returns a ticket at once; wait blocks until that
+ * token's h_out is complete.  Arguments as vfkv_decode_token_host.  At most two tickets are in
+ * flight (VFKV_ERR_INVALID for a third); the host buffers of a ticket must stay untouched until
+ * its wait returns, and should be pinned.  The layers of consecutive submits run in submit order
+ * on `stream`, so the cache sees the tokens in order; the copies of one token overlap the layers
+ * of the other. */
+int32_t vfkv_decode_token_host_submit(vfkv_cache *cache, vfkv_workspace *ws, const float *h_q,
+                                      const float *h_k, const float *h_v, float *h_out,
+                                      uint32_t n_q_heads, const uint32_t *h_slot_ids,
+                                      const uint32_t *h_positions, uint32_t n_seqs,
+                                      const uint32_t *windows, float scale, float softcap,
+                                      uint32_t n_splits, void *stream, uint64_t *ticket);
+int32_t vfkv_decode_token_host_wait(vfkv_workspace *ws, uint64_t ticket);
+
 /* ---------------------------------------------------------------------- */
 /* sequence-dimension sharding (no counterpart in the reference, which is    */
 /* single-GPU): local partials and the merge of flash_attn_reduce.comp:51-80 */

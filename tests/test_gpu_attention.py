@@ -387,6 +387,53 @@ def test_decode_token_host_replays_a_graph_over_several_tokens(ctx, n_layers):
         rig.close()
 
 
+def test_decode_token_host_submit_and_wait_with_two_tokens_in_flight(ctx):
+    """The asynchronous host-buffer step: two submits are interleaved before the first wait, a third
+    one is refused while both staging sets are busy, and every token's output -- positions advance,
+    so each token attends over the rows its predecessors appended -- matches the oracle."""
+    import torch
+    hq, hkv, d, max_seq, n_seqs, n_layers, base, steps = 32, 8, 128, 900, 2, 3, 700, 6
+    rng = np.random.default_rng(63)
+    rig = Rig(ctx, vf.KvDtype.F8, hq, hkv, d, max_seq, n_layers=n_layers, n_slots=n_seqs)
+    stream = torch.cuda.Stream()
+    try:
+        kc = encode_cache(kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d)), oracle.F8)
+        vc = encode_cache(kv_values(rng, (n_layers, n_seqs, max_seq, hkv, d)), oracle.F8)
+        for l in range(n_layers):
+            for s in range(n_seqs):
+                rig.put(l, s, kc[l, s], vc[l, s])
+        rig.fwd.stream = stream.cuda_stream
+        pin = lambda a: torch.from_numpy(a).pin_memory()
+        q = [pin(rng.standard_normal((n_layers, n_seqs, hq, d), dtype=np.float32)) for _ in range(steps)]
+        kn = [pin(kv_values(rng, (n_layers, n_seqs, hkv, d), outlier_frac=0.0)) for _ in range(steps)]
+        vn = [pin(kv_values(rng, (n_layers, n_seqs, hkv, d), outlier_frac=0.0)) for _ in range(steps)]
+        out = [torch.zeros(n_layers, n_seqs, hq, d).pin_memory() for _ in range(steps)]
+        pos = [np.array([base + t, base - 300 + t], np.uint32) for t in range(steps)]
+        want = []
+        for t in range(steps):                     # the oracle appends token t's rows, then attends
+            want.append([oracle.decode_step(q[t][l].numpy(), kn[t][l].numpy(), vn[t][l].numpy(), kc[l], vc[l], oracle.F8,
+                                            n_seqs, max_seq, hq, hkv, d, pos[t] + 1) for l in range(n_layers)])
+        tickets = {}
+        submit = lambda t: tickets.__setitem__(t, rig.fwd.decode_token_host_submit(q[t], kn[t], vn[t], out[t], pos[t], n_seqs))
+        submit(0)
+        submit(1)
+        with pytest.raises(vf.VfkvError):          # both staging sets are in flight
+            rig.fwd.decode_token_host_submit(q[2], kn[2], vn[2], out[2], pos[2], n_seqs)
+        for t in range(steps):
+            rig.fwd.decode_token_host_wait(tickets[t])
+            for l in range(n_layers):
+                check(out[t][l].numpy(), want[t][l], oracle.F8)
+            if t + 2 < steps:
+                submit(t + 2)
+        with pytest.raises(vf.VfkvError):
+            rig.fwd.decode_token_host_wait(tickets[0])     # no longer in flight
+        ctx.poll()
+    finally:
+        torch.cuda.synchronize()
+        rig.fwd.stream = None
+        rig.close()
+
+
 def test_attend_argument_errors(ctx):
     import torch
     rig = Rig(ctx, vf.KvDtype.F16, 32, 8, 128, 64)

@@ -83,6 +83,9 @@ SIGNATURES = {
     "vfkv_decode_step": (i32, [vp, vp, u32, vp, vp, vp, vp, u32, vp, vp, u32, u32, u32, f32, f32, u32, vp]),
     "vfkv_decode_token": (i32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, u32, vp, f32, f32, u32, vp]),
     "vfkv_decode_token_host": (i32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, vp, f32, f32, u32, vp]),
+    "vfkv_decode_token_host_submit": (i32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, vp, f32, f32, u32, vp,
+                                            C.POINTER(u64)]),
+    "vfkv_decode_token_host_wait": (i32, [vp, u64]),
     "vfkv_attend_partial": (i32, [vp, vp, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp, vp, vp]),
     "vfkv_merge_partials": (i32, [vp, vp, vp, vp, u32, u32, u32, vp, vp]),
     "vfkv_merge_partials_packed": (i32, [vp, vp, u32, u32, u32, vp, vp]),

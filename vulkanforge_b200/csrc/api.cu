@@ -506,6 +506,16 @@ int32_t vfkv_workspace_destroy(vfkv_workspace *ws)
     for (auto ev : ws->tok_events)
         if (ev) cudaEventDestroy(ev);
     if (ws->copy_stream) cudaStreamDestroy(ws->copy_stream);
+    for (auto &hs : ws->host_slot) {
+        cudaFree(hs.in); cudaFree(hs.out); cudaFree(hs.u32);
+        if (hs.graph) cudaGraphExecDestroy(hs.graph);
+        if (hs.ev_in) cudaEventDestroy(hs.ev_in);
+        if (hs.ev_done) cudaEventDestroy(hs.ev_done);
+        if (hs.ev_out) cudaEventDestroy(hs.ev_out);
+    }
+    if (ws->h2d_stream) cudaStreamDestroy(ws->h2d_stream);
+    if (ws->d2h_stream) cudaStreamDestroy(ws->d2h_stream);
+    cudaGetLastError();
     delete ws;
     return VFKV_OK;
 }
@@ -864,6 +874,144 @@ int32_t vfkv_decode_token_host(vfkv_cache *cache, vfkv_workspace *ws, const floa
     e = cudaMemcpyAsync(h_out, ws->stage_out, out_bytes, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     return check_cuda(ctx, e, "vfkv_decode_token_host: D2H");
+}
+
+/* ---- the same step without waiting: two tokens in flight ------------------------------------- */
+
+int32_t vfkv_decode_token_host_submit(vfkv_cache *cache, vfkv_workspace *ws, const float *h_q, const float *h_k,
+                                      const float *h_v, float *h_out, uint32_t n_q_heads, const uint32_t *h_slot_ids,
+                                      const uint32_t *h_positions, uint32_t n_seqs, const uint32_t *windows,
+                                      float scale, float softcap, uint32_t n_splits, void *stream, uint64_t *ticket)
+{
+    if (!cache || !ws) return VFKV_ERR_INVALID;
+    vfkv_ctx *ctx = cache->ctx;
+    KvCache &kv = cache->kv;
+    if (!h_q || !h_k || !h_v || !h_out || !h_positions || !ticket)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: null argument");
+    *ticket = 0;
+    if (!stream) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: needs a stream of its own, not the default stream");
+    if (kv.layer_byte_offsets) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_decode_token_host_submit: uniform-shape caches only");
+    if (n_seqs == 0 || n_seqs > ws->max_seqs) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: n_seqs outside the workspace");
+    if (ctx->profiling || ctx->d_trace)
+        return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_decode_token_host_submit: not while profiling or tracing");
+    uint32_t max_pos = 0;
+    for (uint32_t i = 0; i < n_seqs; ++i) {
+        if (h_positions[i] >= kv.config.max_seq_len) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: position exceeds max_seq_len");
+        if (h_slot_ids && h_slot_ids[i] >= kv.config.n_slots) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: slot out of range");
+        if (!h_slot_ids && i >= kv.config.n_slots) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: more sequences than slots");
+        max_pos = h_positions[i] > max_pos ? h_positions[i] : max_pos;
+    }
+    vfkv_workspace::HostSlot *hs = nullptr;
+    for (auto &cand : ws->host_slot)
+        if (cand.ticket == 0) { hs = &cand; break; }
+    if (!hs) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_submit: two tokens are in flight; wait for one first");
+    const uint32_t L = kv.config.n_layers, D = kv.config.head_dim, Hkv = kv.config.n_kv_heads;
+    const uint64_t q_elems = uint64_t(L) * n_seqs * n_q_heads * D, kv_elems = uint64_t(L) * n_seqs * Hkv * D;
+    const uint64_t in_bytes = (q_elems + 2 * kv_elems) * 4, out_bytes = q_elems * 4;
+    DeviceGuard g(ctx->device);
+    cudaStream_t st = as_stream(stream);
+    cudaError_t e = cudaSuccess;
+    if (!ws->h2d_stream) {
+        e = cudaStreamCreateWithFlags(&ws->h2d_stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->d2h_stream, cudaStreamNonBlocking);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host_submit: streams");
+    }
+    if (!hs->ev_in) {
+        e = cudaEventCreateWithFlags(&hs->ev_in, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs->ev_done, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hs->ev_out, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&hs->u32), uint64_t(ws->max_seqs) * 2 * 4);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host_submit: events");
+    }
+    // staging grows on first use (a free slot has nothing in flight, so this cannot pull memory from
+    // under a running step)
+    if (hs->in_bytes < in_bytes) {
+        cudaFree(hs->in); hs->in = nullptr; hs->in_bytes = 0;
+        e = cudaMalloc(reinterpret_cast<void **>(&hs->in), in_bytes);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host_submit: staging");
+        hs->in_bytes = in_bytes;
+    }
+    if (hs->out_bytes < out_bytes) {
+        cudaFree(hs->out); hs->out = nullptr; hs->out_bytes = 0;
+        e = cudaMalloc(reinterpret_cast<void **>(&hs->out), out_bytes);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host_submit: staging");
+        hs->out_bytes = out_bytes;
+    }
+    float *dq = hs->in, *dk = dq + q_elems, *dv = dk + kv_elems;
+    uint32_t *d_pos = hs->u32, *d_slots = hs->u32 + ws->max_seqs;
+    const uint64_t q_stride = uint64_t(n_seqs) * n_q_heads * D, kv_stride = uint64_t(n_seqs) * Hkv * D;
+    uint32_t hint = (max_pos + 1 + 1023u) / 1024u * 1024u;
+    if (hint > kv.config.max_seq_len) hint = kv.config.max_seq_len;
+    uint64_t wh = 1469598103934665603ull;
+    auto mix = [&](uint64_t x) { wh = (wh ^ x) * 1099511628211ull; };
+    for (uint32_t l = 0; windows && l < L; ++l) mix(windows[l]);
+    mix(reinterpret_cast<uint64_t>(kv.k_buffer)); mix(reinterpret_cast<uint64_t>(kv.v_buffer));
+    mix(L); mix(D); mix(Hkv); mix(uint64_t(kv.kv_dtype)); mix(kv.config.max_seq_len); mix(kv.config.n_slots);
+    mix(reinterpret_cast<uint64_t>(ws->tag_part));
+    uint32_t fs, fc;
+    memcpy(&fs, &scale, 4); memcpy(&fc, &softcap, 4);
+    const uint64_t key[8] = {reinterpret_cast<uint64_t>(cache), reinterpret_cast<uint64_t>(dq),
+                             reinterpret_cast<uint64_t>(hs->out), uint64_t(n_q_heads) << 32 | n_seqs,
+                             uint64_t(hint) << 32 | n_splits, uint64_t(fs) << 32 | fc, wh ^ (h_slot_ids ? 1u : 0u),
+                             uint64_t(ctx->pdl) | uint64_t(ctx->tune_warps) << 8 | uint64_t(ctx->tune_stages) << 16 |
+                                 uint64_t(ctx->attn_impl) << 24 | uint64_t(ctx->cluster_merge) << 32 |
+                                 uint64_t(reinterpret_cast<uintptr_t>(st) & 0xffffffu) << 40};
+    if (!hs->graph || memcmp(key, hs->key, sizeof(key)) != 0) {
+        if (hs->graph) { cudaGraphExecDestroy(hs->graph); hs->graph = nullptr; }
+        cudaGraph_t graph = nullptr;
+        e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+        if (e != cudaSuccess) return check_cuda(ctx, e, "vfkv_decode_token_host_submit: capture");
+        const uint64_t launches = ctx->launches;
+        int32_t rc = VFKV_OK;
+        for (uint32_t l = 0; l < L && rc == VFKV_OK; ++l)
+            rc = vfkv_decode_step(cache, ws, l, dq + l * q_stride, dk + l * kv_stride, dv + l * kv_stride,
+                                  hs->out + l * q_stride, n_q_heads, h_slot_ids ? d_slots : nullptr, d_pos, n_seqs, hint,
+                                  windows ? windows[l] : 0, scale, softcap, n_splits, stream);
+        hs->launches = uint32_t(ctx->launches - launches);
+        ctx->launches = launches;                               // recorded, not run
+        cudaError_t ce = cudaStreamEndCapture(st, &graph);
+        if (rc == VFKV_OK && ce == cudaSuccess && graph) ce = cudaGraphInstantiate(&hs->graph, graph, 0);
+        if (graph) cudaGraphDestroy(graph);
+        if (rc != VFKV_OK) return rc;
+        if (ce != cudaSuccess || !hs->graph) { hs->graph = nullptr; return check_cuda(ctx, ce != cudaSuccess ? ce : cudaErrorUnknown, "vfkv_decode_token_host_submit: graph"); }
+        memcpy(hs->key, key, sizeof(key));
+    }
+    // inputs on their own stream, the layers on the caller's, the outputs on a third: the copies of
+    // one token run beside the layers of the other
+    e = cudaMemcpyAsync(d_pos, h_positions, n_seqs * 4, cudaMemcpyHostToDevice, ws->h2d_stream);
+    if (e == cudaSuccess && h_slot_ids) e = cudaMemcpyAsync(d_slots, h_slot_ids, n_seqs * 4, cudaMemcpyHostToDevice, ws->h2d_stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dq, h_q, q_elems * 4, cudaMemcpyHostToDevice, ws->h2d_stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dk, h_k, kv_elems * 4, cudaMemcpyHostToDevice, ws->h2d_stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dv, h_v, kv_elems * 4, cudaMemcpyHostToDevice, ws->h2d_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(hs->ev_in, ws->h2d_stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st, hs->ev_in, 0);
+    if (e == cudaSuccess) e = cudaGraphLaunch(hs->graph, st);
+    if (e == cudaSuccess) e = cudaEventRecord(hs->ev_done, st);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ws->d2h_stream, hs->ev_done, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, hs->out, out_bytes, cudaMemcpyDeviceToHost, ws->d2h_stream);
+    if (e == cudaSuccess) e = cudaEventRecord(hs->ev_out, ws->d2h_stream);
+    if (e != cudaSuccess) {
+        // leave nothing of this call in flight
+        cudaStreamSynchronize(ws->h2d_stream); cudaStreamSynchronize(st); cudaStreamSynchronize(ws->d2h_stream);
+        return check_cuda(ctx, e, "vfkv_decode_token_host_submit");
+    }
+    ctx->launches += hs->launches;
+    hs->ticket = ws->next_ticket++;
+    *ticket = hs->ticket;
+    return VFKV_OK;
+}
+
+int32_t vfkv_decode_token_host_wait(vfkv_workspace *ws, uint64_t ticket)
+{
+    if (!ws || ticket == 0) return VFKV_ERR_INVALID;
+    for (auto &hs : ws->host_slot) {
+        if (hs.ticket != ticket) continue;
+        DeviceGuard g(ws->ctx->device);
+        cudaError_t e = cudaEventSynchronize(hs.ev_out);
+        hs.ticket = 0;
+        return check_cuda(ws->ctx, e, "vfkv_decode_token_host_wait");
+    }
+    return set_error(ws->ctx, VFKV_ERR_INVALID, "vfkv_decode_token_host_wait: no such ticket in flight");
 }
 
 /* ---- sequence-dimension sharding ------------------------------------------ */

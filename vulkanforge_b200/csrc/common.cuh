@@ -77,6 +77,22 @@ struct vfkv_workspace {
     uint64_t tok_key[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t tok_events[2 * kTokChunks] = {};         // inputs there / group done, per group
+    // vfkv_decode_token_host_submit / _wait: two tokens in flight, each with its own staging set and
+    // its own recorded graph (the analogue of the reference's two command-buffer / fence pairs and
+    // per-slot scratch, forward/decode.rs:169-259, forward/setup.rs:203-230).
+    struct HostSlot {
+        float *in = nullptr, *out = nullptr;
+        uint32_t *u32 = nullptr;                         // positions, then slot ids
+        uint64_t in_bytes = 0, out_bytes = 0;
+        cudaGraphExec_t graph = nullptr;
+        uint64_t key[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        cudaEvent_t ev_in = nullptr, ev_done = nullptr, ev_out = nullptr;
+        uint64_t ticket = 0;                             // ticket in flight on this slot, 0 = free
+        uint32_t launches = 0;
+    };
+    HostSlot host_slot[2];
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    uint64_t next_ticket = 1;
 };
 
 namespace vfkv {

@@ -212,6 +212,26 @@ class CudaForward:
             ptr(h_slot_ids), ptr(h_positions), n_seqs, C.cast(win, C.c_void_p) if win is not None else None,
             self.attn_scale, self.softcap, self.n_splits, self.stream))
 
+    def decode_token_host_submit(self, h_q, h_k, h_v, h_out, h_positions, n_seqs: int, h_slot_ids=None) -> int:
+        """decode_token_host without the wait (pre_record / fill_embed_and_submit,
+        forward/decode.rs:169-259): returns a ticket; at most two may be in flight."""
+        import ctypes as C
+        n_layers = self.kv_cache.config.n_layers
+        win = None
+        if self.sliding_layers and self.sliding_window:
+            win = (C.c_uint32 * n_layers)(*[self.sliding_window if l in self.sliding_layers else 0
+                                            for l in range(n_layers)])
+        ticket = C.c_uint64()
+        self.ctx.check(self._L.vfkv_decode_token_host_submit(
+            self.kv_cache.handle, self.workspace.handle, ptr(h_q), ptr(h_k), ptr(h_v), ptr(h_out), self.n_heads,
+            ptr(h_slot_ids), ptr(h_positions), n_seqs, C.cast(win, C.c_void_p) if win is not None else None,
+            self.attn_scale, self.softcap, self.n_splits, self.stream, C.byref(ticket)))
+        return int(ticket.value)
+
+    def decode_token_host_wait(self, ticket: int) -> None:
+        """wait_and_read_logits for this path: h_out of that ticket is complete on return."""
+        self.ctx.check(self._L.vfkv_decode_token_host_wait(self.workspace.handle, ticket))
+
     # ---- sequence-dimension sharding ---------------------------------------------
     def attend_partial(self, layer: int, q, pos_begin: int, pos_end: int, m, l, o, slot: int = 0,
                        kv_layer: Optional[int] = None):
