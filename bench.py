@@ -101,6 +101,26 @@ def tensor_peak():
     return 1590.0
 
 
+def copy_bandwidth_here(n_bytes=1 << 31, reps=10):
+    """The same measurement MEASURED_PEAKS.json's hbm_gbs comes from (a device-to-device copy of
+    bf16 elements, read + write bytes, best of `reps`, CUDA events), on the GPU this run got: boards of
+    one pool differ by several per cent, and the fractions printed here divide by the pool's figure."""
+    import torch
+    a = torch.empty(n_bytes // 2, dtype=torch.bfloat16, device="cuda").normal_()
+    b = torch.empty_like(a)
+    best = 0.0
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        b.copy_(a)
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, 2.0 * n_bytes / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    del a, b
+    torch.cuda.empty_cache()
+    return best
+
+
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML while the timed region runs (read only)."""
 
@@ -426,8 +446,11 @@ def roofline_of(w, lens, us_per_launch, peak, peak_kind, traffic=None):
 def measure_workload(name, device, args, ctx=None, lens=None, seed=77, min_total_ms=200.0):
     """One GPU, one workload: a CUDA graph of one token (every layer's fused kernel), device-timed.
     Returns (us per token per layer, us per launch, job's sequence lengths, launches per step)."""
+    import gc
     import torch
     w = dict(WORKLOADS[name])
+    gc.collect()
+    torch.cuda.empty_cache()      # hand the previous workload's blocks back before the cache is allocated
     job = Job(w, device, seed=seed, ctx=ctx, lens=lens)
     try:
         job.ctx.set_dependent_launch(args.pdl)
@@ -437,7 +460,10 @@ def measure_workload(name, device, args, ctx=None, lens=None, seed=77, min_total
         torch.cuda.synchronize()
         launches = job.count_launches()
         job.capture()
+        sampler = ClockSampler(physical_gpu_index(device))
+        sampler.start()
         ms, _, _ = timed_blocks(job.graph.replay, job.stream, args.steps, 3, None, min_total_ms)
+        measure_workload.last_clocks = sampler.finish()
         job.ctx.poll()
         us_step = ms * 1e3 / args.steps
         return us_step / (job.batch * w["n_layers"]), us_step / max(launches, 1), job.lens, launches
@@ -455,6 +481,7 @@ def other_workloads(ctx, args, peak, peak_kind):
         us_tl, us_launch, lens, launches = measure_workload(name, ctx.device, args, ctx=ctx)
         fused = launches == w["n_layers"]
         out[name] = {"us_per_token_layer": us_tl, "launches_per_step": launches,
+                     "clocks": measure_workload.last_clocks,
                      "roofline": roofline_of(w, lens, us_launch, peak, peak_kind, NCU_TRAFFIC_BYTES.get(name))
                      if fused else None}
     return out
@@ -843,6 +870,7 @@ def run_ours(args, w, rank, world, local_rank):
                         "value_one_token_at_a_time": e2e_sync_ms * 1e3 / denom,
                         "call_one_token_at_a_time": "vfkv_decode_token_host"}}
         if world == 1 and not args.no_extra and args.workload == DEFAULT_WORKLOAD:
+            line["copy_gbs_this_gpu"] = copy_bandwidth_here()
             others = other_workloads(job.ctx, args, peak, peak_kind)
             line["roofline_batch64_ctx8192"] = dict(others["batch64_fp8_ctx8192"]["roofline"],
                                                     workload="batch64_fp8_ctx8192: 64 sequences x 8192 tokens, "

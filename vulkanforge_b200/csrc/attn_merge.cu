@@ -125,6 +125,22 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     if (want < by_len && base >= slots) want = by_len;
     if (want > cap) want = cap;
     if (want < 1) want = 1;
+    // A stream-bound grid that spills a few CTAs into another wave pays for a whole wave: 64
+    // (sequence, kv-head) pairs x 5 splits = 320 CTAs on 296 slots took 571 us where 9 splits (576
+    // CTAs, two full waves) took 354 us and 4 splits (one wave, 86 % full) 379 us (F16, head_dim
+    // 256, 8 x 32768 positions).  So when the count above overshoots the slots, take the nearby
+    // count that fills its waves best, with a small price per split for the merge.
+    if (base * want > slots && base < slots) {
+        double best = -1.0;
+        uint64_t pick = want;
+        const uint64_t hi = cap < 4 * want ? cap : 4 * want;
+        for (uint64_t n = want > 1 ? want - 1 : 1; n <= hi; ++n) {
+            const uint64_t ctas = base * n, waves = (ctas + slots - 1) / slots;
+            const double score = double(ctas) / double(waves * slots) - 0.008 * double(n);
+            if (score > best) { best = score; pick = n; }
+        }
+        want = pick;
+    }
     return uint32_t(want);
 }
 
