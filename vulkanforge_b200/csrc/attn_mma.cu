@@ -156,6 +156,7 @@ struct MmaParams {
     uint64_t *tag_part;
     uint64_t merge_wait_ns;       // limit of the merging CTA's wait for the other splits' partials
     uint32_t launch_seq;          // host-side count of split launches on this workspace (part of the tag)
+    uint32_t n_mergers;           // CTAs per (sequence, kv-head) that share the merge of its splits
     const float *k_new, *v_new;   // [seq][kv_head][dim] f32 token to append at position len-1, or null
     unsigned long long *trace;    // null, or 16 timestamps (ns) per CTA written by thread 0 (this launch's block of the buffer)
     uint32_t pdl;                 // 0 plain launch, 1 dependent launch, 2 dependent launch with early K/V prefetch
@@ -712,7 +713,9 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             } else {
                 place = uint32_t(ticket % p.n_splits); launch_no = uint32_t(ticket / p.n_splits);
             }
-            merger = place == p.n_splits - 1u ? 1u : 0u;
+            // the last n_mergers drawers merge: merger = 1 + its rank among them, 0 for the others
+            const uint32_t n_mrg = min(mp.n_mergers, p.n_splits);
+            merger = place + n_mrg >= p.n_splits ? place + n_mrg - p.n_splits + 1u : 0u;
             // never 0, the value of a cleared workspace; launches that share a host count are replays
             // of one graph node (same addresses), which the device-side number tells apart
             tag = 0x80000000u | ((mp.launch_seq & 0x7FFFu) << 16) | (launch_no & 0xFFFFu);
@@ -926,41 +929,54 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const bool xrank = fan && mp.fan_merge != 0u;
     if (direct && !xrank) { VFKV_TRACE(9); return; }
 
-    // ---- the last drawer merges the splits --------------------------------------------------------------
-    // Everything from here on runs once per launch on one CTA per (sequence, kv-head), straight after
-    // the hot loop: measured, such code costs what it takes to fetch its instructions, ten cycles
-    // and more apiece, so it is kept short and rolled.  All partials of the group (a few KB per
-    // split) are copied into the now idle ring with asynchronous 16-byte copies, one short loop
-    // that puts every request in flight at once; then each thread merges its output pairs out of
-    // shared memory (flash_attn_reduce.comp:51-80, maximum first) and checks the tags as it goes.
-    // A word that does not carry this launch's tag yet sends the whole step round again, up to
-    // the time limit.
+    // ---- the last drawers merge the splits ---------------------------------------------------------------
+    // Everything from here on runs once per launch on a few CTAs per (sequence, kv-head), straight
+    // after the hot loop: measured, such code costs what it takes to fetch its instructions, ten
+    // cycles and more apiece, and one SM reads its L2 at some 64 bytes per clock, so the code is kept
+    // short and rolled and the work is shared: the last n_mergers drawers each take one slice of the
+    // output pairs.  (Only CTAs that have drawn wait, and at most n_mergers per group, far fewer
+    // than there are SMs, so a CTA that has yet to start always finds one.)  A merger copies its
+    // slice of every split's partial into the now idle ring with asynchronous 16-byte copies, one
+    // short loop that puts every request in flight at once; then each thread merges its output
+    // pairs out of shared memory (flash_attn_reduce.comp:51-80, maximum first) and checks the tags
+    // as it goes.  A word that does not carry this launch's tag yet sends the step round again, up
+    // to the time limit.
     __syncthreads();          // the warps' partials in the ring are dead (uniform: the whole CTA merges or none of it)
     uint64_t *const stgw = reinterpret_cast<uint64_t *>(ring_ptr);
     const uint32_t stg_base = ring;                               // shared-window address of stgw
+    // this CTA's slice of the pairs
+    const uint32_t n_mrg = direct ? 1u : min(mp.n_mergers, p.n_splits);
+    const uint32_t per = (n_pairs + n_mrg - 1) / n_mrg;
+    const uint32_t lo = direct ? 0u : min((s_merger - 1u) * per, n_pairs), hi = min(lo + per, n_pairs);
+    const uint32_t n_mine = hi - lo;
     if (!direct) {
-        const uint32_t n16 = uint32_t(p.n_splits * pwords / 2);   // 16-byte pieces
+        // staged per split: o words of pairs [lo, hi), then the {m, l} words of all g rows
+        const uint32_t span = 2u * per + 2u * g;                  // words
         uint64_t t0 = 0;
         for (;;) {
-            for (uint32_t k = threadIdx.x; k < n16; k += blockDim.x)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stg_base + 16u * k), "l"(gp + 2ull * k) : "memory");
+            for (uint32_t k = threadIdx.x; k < p.n_splits * (n_mine + g); k += blockDim.x) {
+                const uint32_t i = k / (n_mine + g), q2 = k % (n_mine + g);
+                const uint64_t *src = gp + uint64_t(i) * pwords + (q2 < n_mine ? 2ull * (lo + q2) : uint64_t(g) * D + 2ull * (q2 - n_mine));
+                const uint32_t dst = stg_base + 8u * (i * span + (q2 < n_mine ? 2u * q2 : 2u * per + 2u * (q2 - n_mine)));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
             asm volatile("cp.async.wait_all;" ::: "memory");
             __syncthreads();
             bool missing = false;
-            for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+            for (uint32_t idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
                 const uint32_t j = idx / HD2;
-                const uint64_t *po = stgw + 2 * idx, *pm = stgw + uint64_t(g) * D + 2 * j;
+                const uint64_t *po = stgw + 2 * (idx - lo), *pm = stgw + 2 * per + 2 * j;
                 float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
 #pragma unroll 4
                 for (uint32_t i = 0; i < p.n_splits; ++i) {
-                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * pwords);
+                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * span);
                     missing = missing || !tags_are(mw, tag);
                     gmax = fmaxf(gmax, tagged_value(mw.x));
                 }
 #pragma unroll 4
                 for (uint32_t i = 0; i < p.n_splits; ++i) {
-                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(po + i * pwords);
-                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * pwords);
+                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(po + i * span);
+                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * span);
                     missing = missing || !tags_are(ow, tag);
                     const float kn = __expf(tagged_value(mw.x) - gmax);
                     gsum = fmaf(tagged_value(mw.y), kn, gsum);
@@ -976,7 +992,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 if (threadIdx.x == 0) atomicOr(p.status, 1u);
                 return;
             }
-            __nanosleep(200);
+            __nanosleep(100);
         }
         VFKV_TRACE(8);
     }
@@ -984,23 +1000,24 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     // ---- position-sharded call: merge the blocks of all ranks ------------------------------------------
     // Every rank's kernel stores its block of these rows into this GPU's buffer, this rank's own
-    // block included (emit above).  The same scheme as above, with the exchange's time limit: the o
-    // rows of this kv-head are contiguous in each rank's block and come in by asynchronous copies,
-    // the few m and l words by one polling load per thread.  Loads touch this GPU's memory only.
+    // block included (emit above).  The same scheme as above for this CTA's pairs, with the
+    // exchange's time limit: the o words of a slice are contiguous in each rank's block and come in
+    // by asynchronous copies, the few m and l words by one polling load per thread.  Loads touch
+    // this GPU's memory only.
     {
         const uint64_t *local = s_fan.base[s_fan.rank];
         const uint32_t e = fs.epoch, world = s_fan.world;
         const uint64_t row0 = uint64_t(s) * p.n_q_heads + kvh * g;
-        const uint32_t o_words = g * D;                           // per rank
-        float *const s_ml = reinterpret_cast<float *>(stgw + uint64_t(world) * o_words);   // [world][2][g]
+        const uint32_t span = 2u * per;                           // words per rank
+        float *const s_ml = reinterpret_cast<float *>(stgw + uint64_t(world) * span);   // [world][2][g]
         uint64_t t0 = 0;
         bool late = false;
         for (;;) {
-            for (uint32_t k = threadIdx.x; k < world * (o_words / 2); k += blockDim.x) {
-                const uint32_t r = k / (o_words / 2), q2 = k % (o_words / 2);
+            for (uint32_t k = threadIdx.x; k < world * n_mine; k += blockDim.x) {
+                const uint32_t r = k / n_mine, q2 = k % n_mine;
                 const FanoutSlot rs = fanout_slot(s_fan, D, r, e);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
-                             ::"r"(stg_base + 8u * (r * o_words + 2u * q2)), "l"(local + rs.o + row0 * D + 2ull * q2) : "memory");
+                             ::"r"(stg_base + 8u * (r * span + 2u * q2)), "l"(local + rs.o + row0 * D + 2ull * (lo + q2)) : "memory");
             }
             bool missing = false;
             for (uint32_t k = threadIdx.x; k < world * 2u * g; k += blockDim.x) {
@@ -1012,12 +1029,12 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
             __syncthreads();
-            for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
+            for (uint32_t idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
                 const uint32_t j = idx / HD2;
                 float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
                 for (uint32_t r = 0; r < world; ++r) gmax = fmaxf(gmax, s_ml[(r * 2u) * g + j]);
                 for (uint32_t r = 0; r < world; ++r) {
-                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(stgw + uint64_t(r) * o_words + 2 * idx);
+                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(stgw + uint64_t(r) * span + 2 * (idx - lo));
                     missing = missing || !tags_are(ow, e);
                     const float kn = __expf(s_ml[(r * 2u) * g + j] - gmax);
                     gsum = fmaf(s_ml[(r * 2u + 1u) * g + j], kn, gsum);
@@ -1033,7 +1050,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
             late = __syncthreads_or(now - t0 > s_fan.wait_ns);    // decided together; one more round writes the zeros
-            __nanosleep(200);
+            __nanosleep(100);
         }
         if (late && threadIdx.x == 0) atomicOr(p.status, 8u);
     }
@@ -1212,6 +1229,13 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     mp.tag_part = ws ? ws->tag_part : nullptr;
     mp.merge_wait_ns = ctx->merge_wait_ns;
     mp.launch_seq = (ws && n_splits > 1) ? ws->launch_seq++ : 0u;
+    // Up to four CTAs per (sequence, kv-head) share the merge, as long as all the CTAs that may be
+    // waiting at one time stay a small part of the SMs (a waiting CTA holds its SM).
+    {
+        const uint64_t groups = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
+        const uint64_t room = uint64_t(ctx->sm_count) / 4 / (groups ? groups : 1);
+        mp.n_mergers = uint32_t(room < 1 ? 1 : room > 4 ? 4 : room);
+    }
     mp.trace = ctx->d_trace;
     if (ctx->d_trace && ctx->trace_ring > 1) {      // successive launches write successive blocks of the buffer
         const uint64_t ctas = uint64_t(n_splits) * a.kv.n_kv_heads * a.seq.n_seqs;
