@@ -555,7 +555,9 @@ def run_probe(args):
     `--probe-ctx`); `rope`: RoPE fused with the append of a 512-token chunk; `append`: the plain
     append of a 512-token chunk; `fp8_to_f16`: the cache read of `--probe-ctx` positions of one layer;
     `generic`: the CUDA-core split kernel + merge kernel on an F32 cache of `--probe-ctx` positions;
-    `decode`: `--workload`'s fused decode kernel, one layer-step per launch over all its layers."""
+    `decode`: `--workload`'s fused decode kernel, one layer-step per launch over all its layers;
+    `exchange`: the one-launch form of the position-sharded step (attention + fan-out + merge of the
+    ranks' blocks) in a group of one rank, 64 q / 8 kv / 128, FP8, `--probe-ctx` positions."""
     import torch
     import vulkanforge_b200 as vf
     ctx = vf.Context(0)
@@ -596,6 +598,14 @@ def run_probe(args):
             v16 = torch.empty_like(k16)
             fn = lambda: ctx.check(ctx._lib.vfkv_fp8_to_f16(cache.handle, 0, 0, L, k16.data_ptr(), v16.data_ptr(), None))
             work, unit = 2 * L * hkv * d * 3 / 1e9, "GB/s"
+        elif args.probe == "exchange":
+            fwd.workspace.destroy()
+            fwd = vf.CudaForward(ctx, cache, n_heads=64)
+            ex = vf.PeerExchange(ctx, 1, 0, 64, d)
+            q64 = torch.randn(64, d, device="cuda", generator=g)
+            out64 = torch.zeros(64, d, device="cuda")
+            fn = lambda: fwd.attend_exchange(ex, 0, q64, 0, L, out64)
+            work, unit = 2 * L * hkv * d / 1e9, "GB/s"
         else:                                      # generic: CUDA-core split kernel + merge kernel, F32 cache
             fn = lambda: fwd.run_flash_attn_split_reduce(q[0], out[0], 0, L - 1, 16, 0, 0)
             work, unit = 2 * L * hkv * d * 4 / 1e9, "GB/s"
@@ -905,7 +915,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph replay")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch mode of the attention kernel (vfkv_ctx_set_dependent_launch)")
-    ap.add_argument("--probe", default=None, choices=["prefill", "rope", "append", "fp8_to_f16", "generic", "decode"],
+    ap.add_argument("--probe", default=None, choices=["prefill", "rope", "append", "fp8_to_f16", "generic", "decode", "exchange"],
                     help="run one kernel on its own (for profiling) and exit")
     ap.add_argument("--probe-m", type=int, default=2048)
     ap.add_argument("--probe-ctx", type=int, default=16384)
