@@ -228,13 +228,17 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
 int32_t vfkv_workspace_destroy(vfkv_workspace *ws);
 uint64_t vfkv_workspace_bytes(const vfkv_workspace *ws);
 /* The tensor-core attention kernel merges its splits through the workspace without a second
- * launch: every CTA of a (sequence, kv-head) draws a ticket from a 64-bit word {launch number << 8
- * | CTAs drawn} when it starts, the last drawer is the one that will merge, and the partials are
- * 8-byte words {f32 value, u32 launch number + 1} that the merging CTA polls (at most the time set
- * with vfkv_ctx_set_merge_wait_ms; a wait that runs out raises bit 1 of the status word).  A
- * launch always leaves its ticket words complete, so an error needs no clean-up; after a kernel
- * was killed from outside (a debugger, a reset from another process) vfkv_workspace_reset puts
- * tickets and tags back to zero, in stream order. */
+ * launch.  Every CTA of a (sequence, kv-head) draws one ticket by adding 1 to a 64-bit word that
+ * only ever counts up; there is one such word per split count, so ticket / n_splits is the number
+ * of this launch on the word and ticket % n_splits the CTA's place in the draw.  Partials are
+ * 8-byte words {f32 value, u32 tag} written by one store each, the tag made of a launch counter
+ * kept by the host and the launch number on the word; the last drawers (up to four) each merge a
+ * slice of the output rows and accept only words that carry the tag of their own launch, waiting
+ * at most the time set with vfkv_ctx_set_merge_wait_ms (a wait that runs out raises bit 1 (value 1) of
+ * the status word).  Nothing is reset between launches, so a launch that gave up, a graph replay or
+ * a change of geometry leaves nothing that a later launch could mistake for its own;
+ * vfkv_workspace_reset puts tickets and tags back to zero, in stream order, for a host that
+ * wants a known state after a kernel was killed from outside. */
 int32_t vfkv_workspace_reset(vfkv_workspace *ws, void *stream);
 
 /* ---------------------------------------------------------------------- */

@@ -2,7 +2,9 @@
 //!
 //! `Forward` keeps the method names it has in `src/backend/vulkan/forward/runs.rs` and
 //! `forward/executor/attention.rs`: `run_kv_store_fp8`, `run_kv_copy_fp16`, `run_scalar_attn`,
-//! `run_flash_attn_split_reduce`, `step_kv_write`, `step_attention`, `b_step_kv_write`.  What was
+//! `run_flash_attn_split_reduce`, `run_flash_attn_batch`, `step_kv_write`, `step_attention`,
+//! `b_step_kv_write`, and at token level `record_decode_dispatches`, `forward_token`,
+//! `submit_token` / `wait_token`.  What was
 //! (device, registry, command buffer) becomes (device, stream): work is enqueued on the stream in
 //! call order, which replaces the pipeline barriers the Vulkan code records between these
 //! dispatches.  Buffers are device pointers.  A decode step may also be issued as ONE call,
@@ -231,6 +233,176 @@ impl Forward {
                 stream,
             )
         })
+    }
+
+    /// run_flash_attn_batch (runs.rs:933-1010) behind b_step_attention (attention.rs:2192-2393):
+    /// `m` queries at positions `q_start ..` attend causally over the cache rows `[kv_start, n_kv)`.
+    #[allow(clippy::too_many_arguments)]
+    pub fn run_flash_attn_batch(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        q_batch: *const f32,
+        out_batch: *mut f32,
+        m: u32,
+        q_start: u32,
+        n_kv: u32,
+    ) -> Result<(), String> {
+        let kv_layer = self.routing.kv_read_layer.get(layer as usize).copied().unwrap_or(layer);
+        let window = if self.routing.sliding_layers.get(layer as usize).copied().unwrap_or(false) {
+            self.routing.sliding_window
+        } else {
+            0
+        };
+        dev.check(unsafe {
+            sys::vfkv_attend_prefill(
+                self.kv_cache.handle,
+                layer,
+                kv_layer,
+                q_batch,
+                out_batch,
+                self.n_heads,
+                0,
+                m,
+                q_start,
+                n_kv,
+                0,
+                window,
+                self.routing.attn_scale,
+                self.routing.softcap,
+                stream,
+            )
+        })
+    }
+
+    /// Per-layer windows in the form the token-level calls take (0 = global layer).
+    fn windows(&self) -> Vec<u32> {
+        (0..self.kv_cache.config.n_layers as usize)
+            .map(|l| if self.routing.sliding_layers.get(l).copied().unwrap_or(false) { self.routing.sliding_window } else { 0 })
+            .collect()
+    }
+
+    /// record_decode_dispatches (forward/decode.rs:43-82) for this path: every layer's KvWrite +
+    /// Attention of one token, device inputs `[n_layers][..]`, nothing synchronises or allocates,
+    /// so the call can be captured in a CUDA graph once and replayed per token.
+    #[allow(clippy::too_many_arguments)]
+    pub fn record_decode_dispatches(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        d_q: *const f32,
+        d_k: *const f32,
+        d_v: *const f32,
+        d_out: *mut f32,
+        d_positions: *const u32,
+        max_seq_len_hint: u32,
+    ) -> Result<(), String> {
+        let windows = self.windows();
+        dev.check(unsafe {
+            sys::vfkv_decode_token(
+                self.kv_cache.handle,
+                self.workspace,
+                d_q,
+                d_k,
+                d_v,
+                d_out,
+                self.n_heads,
+                ptr::null(),
+                d_positions,
+                1,
+                max_seq_len_hint,
+                windows.as_ptr(),
+                self.routing.attn_scale,
+                self.routing.softcap,
+                0,
+                stream,
+            )
+        })
+    }
+
+    /// forward_token (forward/decode.rs:567-626) reduced to this path, with pinned HOST buffers:
+    /// copies in, all layers, copy out, wait.
+    #[allow(clippy::too_many_arguments)]
+    pub fn forward_token(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        h_q: *const f32,
+        h_k: *const f32,
+        h_v: *const f32,
+        h_out: *mut f32,
+        position: u32,
+    ) -> Result<(), String> {
+        let windows = self.windows();
+        dev.check(unsafe {
+            sys::vfkv_decode_token_host(
+                self.kv_cache.handle,
+                self.workspace,
+                h_q,
+                h_k,
+                h_v,
+                h_out,
+                self.n_heads,
+                ptr::null(),
+                &position,
+                1,
+                windows.as_ptr(),
+                self.routing.attn_scale,
+                self.routing.softcap,
+                0,
+                stream,
+            )
+        })?;
+        self.commit_position(position);
+        Ok(())
+    }
+
+    /// fill_embed_and_submit (forward/decode.rs:169-259): the same step without waiting; returns
+    /// the ticket that `wait_token` takes.  At most two tokens in flight; `stream` must not be
+    /// the default stream; the host buffers stay untouched until the ticket was waited for.
+    #[allow(clippy::too_many_arguments)]
+    pub fn submit_token(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        h_q: *const f32,
+        h_k: *const f32,
+        h_v: *const f32,
+        h_out: *mut f32,
+        position: u32,
+    ) -> Result<u64, String> {
+        let windows = self.windows();
+        let mut ticket: u64 = 0;
+        dev.check(unsafe {
+            sys::vfkv_decode_token_host_submit(
+                self.kv_cache.handle,
+                self.workspace,
+                h_q,
+                h_k,
+                h_v,
+                h_out,
+                self.n_heads,
+                ptr::null(),
+                &position,
+                1,
+                windows.as_ptr(),
+                self.routing.attn_scale,
+                self.routing.softcap,
+                0,
+                stream,
+                &mut ticket,
+            )
+        })?;
+        Ok(ticket)
+    }
+
+    /// wait_and_read_logits (forward/decode.rs:169-259) for this path: blocks until the token's
+    /// outputs are in its host buffer, then commits the position.
+    pub fn wait_token(&mut self, dev: &CudaDevice, ticket: u64, position: u32) -> Result<(), String> {
+        dev.check(unsafe { sys::vfkv_decode_token_host_wait(self.workspace, ticket) })?;
+        self.commit_position(position);
+        Ok(())
     }
 
     /// After the token's GPU work has been waited for (forward/decode.rs:812).
