@@ -23,8 +23,13 @@
 //   both : with up to 8 q-heads per kv-head the M tile has rows to spare, so Q and P are each
 //          split into a high and a low half-precision term (rows 0-7 / 8-15) and the result
 //          carries f32-grade operand precision.
-//   tail : warp partials merge in shared memory; the last CTA of a
-//          (sequence, kv-head) to finish merges the split partials with the
+//   few  : with at most 4 q-heads per kv-head the products are transposed (S^T = K Q^T,
+//          O^T = V^T P^T): positions and output dims on the M side, the heads' high and low
+//          terms on the 8 columns, P^T moved from accumulator to operand layout by movmatrix.
+//          Half the MMAs per tile (the legacy tensor path bounds the stream of a small grid)
+//          and two thirds of the registers.
+//   tail : warp partials merge in shared memory; the last CTAs of a
+//          (sequence, kv-head) to finish merge the split partials with the
 //          reduce shader's update (flash_attn_reduce.comp:51-80), so there is no
 //          second launch.
 //
@@ -284,11 +289,106 @@ __device__ __forceinline__ void pv_f16(const uint32_t (&vb)[4], const uint32_t (
     }
 }
 
+// ---- transposed products (at most 4 q-heads per kv-head) ------------------------------------------
+// With few q-heads the M = 16 rows of an MMA are mostly padding when the heads sit on M.  The
+// transposed products put the positions (S^T = K Q^T) and the output dims (O^T = V^T P^T) on M and
+// the heads on the N = 8 columns: column 2h carries the high half-precision term of head h, column
+// 2h + 1 the low term.  Half the MMAs per tile, and half the accumulator registers.
+
+// 8x8 transpose of 16-bit elements across the warp: row r of the result is column r of the source.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x)
+{
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+// p -> half2 {high term, low term}: the two columns of this thread's head
+__device__ __forceinline__ uint32_t hi_lo_f16x2(float x)
+{
+    const __half h = __float2half_rn(x);
+    const __half2 v = __halves2half2(h, __float2half_rn(x - __half2float(h)));
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+// S^T += K Q^T.  ksw[u] = K tile base + this lane's ldmatrix offset for unit pair u of a 128-byte
+// chunk (matrices in the order rows 0-7 / 8-15 of unit 2u, then of unit 2u + 1).
+// FP8: one ldmatrix covers 16 positions x 32 dims = two MMAs (qb[2J], qb[2J + 1]); the codes are
+// widened in registers, k slots {2tig, 2tig+1, 8+2tig, 9+2tig} <-> dims 4tig .. 4tig+3 of the unit.
+// F16: one ldmatrix is the A fragment of 16 positions x 16 dims.
+template <bool FP8, int TP, int D, int J = 0>
+__device__ __forceinline__ void qk_t(const uint32_t (&ksw)[4], const uint32_t (&qb)[D / 16][2], float (&sc)[TP / 16][4])
+{
+    constexpr int NJ = FP8 ? D / 32 : D / 16;
+    if constexpr (J < NJ) {
+        constexpr int C = (J / 4) * TP * 128;
+        uint32_t r0, r1, r2, r3;
+        if constexpr (FP8) {
+#pragma unroll
+            for (int mb = 0; mb < TP / 16; ++mb) {
+                if (mb == 0) ldmatrix_x4<C>(ksw[J % 4], r0, r1, r2, r3);
+                else ldmatrix_x4<C + 16 * 128>(ksw[J % 4], r0, r1, r2, r3);
+                uint32_t a[4];
+                e4m3x4_to_half2x2(r0, a[0], a[2]); e4m3x4_to_half2x2(r1, a[1], a[3]);
+                mma_f16(sc[mb], a, qb[2 * J][0], qb[2 * J][1]);
+                e4m3x4_to_half2x2(r2, a[0], a[2]); e4m3x4_to_half2x2(r3, a[1], a[3]);
+                mma_f16(sc[mb], a, qb[2 * J + 1][0], qb[2 * J + 1][1]);
+            }
+        } else {
+            ldmatrix_x4<C>(ksw[J % 4], r0, r1, r2, r3);
+            const uint32_t a[4] = {r0, r1, r2, r3};
+            mma_f16(sc[0], a, qb[J][0], qb[J][1]);
+        }
+        qk_t<FP8, TP, D, J + 1>(ksw, qb, sc);
+    }
+}
+// FP8 O^T += V^T P^T for dims 32Q .. 32Q+31: the same words, byte pairing and widening as pv_fp8; a
+// pair of positions of one dim is now an A register.  Row gid of block 2Q + pr is dim
+// 32Q + 4gid + 2pr, row gid + 8 is that dim + 1.  pb[h] = P^T fragment of positions 16h .. 16h+15.
+template <int TP, int D, int Q = 0>
+__device__ __forceinline__ void pv_t_fp8(const uint32_t (&vb)[8], const uint32_t (&pb)[2][2], float (&acc)[D / 16][4])
+{
+    if constexpr (Q < D / 32) {
+        constexpr int C = (Q / 4) * TP * 128, u = Q % 4;
+        const uint32_t be = vb[2 * u], bo = vb[2 * u + 1];
+        uint32_t w[8];
+        w[0] = lds32<C>(be);             w[1] = lds32<C>(bo);
+        w[2] = lds32<C + 8 * 128>(be);   w[3] = lds32<C + 8 * 128>(bo);
+        w[4] = lds32<C + 16 * 128>(be);  w[5] = lds32<C + 16 * 128>(bo);
+        w[6] = lds32<C + 24 * 128>(be);  w[7] = lds32<C + 24 * 128>(bo);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t b0[4], b1[4];       // per dim i: positions (2tig, 2tig+1) and (8+2tig, 9+2tig) of half h
+            e4m3x4_to_half2x2(prmt(w[4 * h], w[4 * h + 1], 0x5140), b0[0], b0[1]);
+            e4m3x4_to_half2x2(prmt(w[4 * h], w[4 * h + 1], 0x7362), b0[2], b0[3]);
+            e4m3x4_to_half2x2(prmt(w[4 * h + 2], w[4 * h + 3], 0x5140), b1[0], b1[1]);
+            e4m3x4_to_half2x2(prmt(w[4 * h + 2], w[4 * h + 3], 0x7362), b1[2], b1[3]);
+            const uint32_t a0[4] = {b0[0], b0[1], b1[0], b1[1]};
+            const uint32_t a1[4] = {b0[2], b0[3], b1[2], b1[3]};
+            mma_f16(acc[2 * Q], a0, pb[h][0], pb[h][1]);
+            mma_f16(acc[2 * Q + 1], a1, pb[h][0], pb[h][1]);
+        }
+        pv_t_fp8<TP, D, Q + 1>(vb, pb, acc);
+    }
+}
+// F16 O^T += V^T P^T for dims 16DB .. 16DB+15: ldmatrix.trans hands out the A fragment (matrices in
+// the order positions 0-7 of units 2u, 2u+1, then positions 8-15).
+template <int TP, int D, int DB = 0>
+__device__ __forceinline__ void pv_t_f16(const uint32_t (&vb)[4], const uint32_t (&pb)[2], float (&acc)[D / 16][4])
+{
+    if constexpr (DB < D / 16) {
+        uint32_t r0, r1, r2, r3;
+        ldmatrix_x4_trans<(DB / 4) * TP * 128>(vb[DB % 4], r0, r1, r2, r3);
+        const uint32_t a[4] = {r0, r1, r2, r3};
+        mma_f16(acc[DB], a, pb[0], pb[1]);
+        pv_t_f16<TP, D, DB + 1>(vb, pb, acc);
+    }
+}
+
 // W = warps per CTA, NS = TMA stages per warp.  Grids of several waves run 4 warps x 2 stages, which
 // lets three CTAs share an SM (12 warps hide the MMA / shuffle latencies of one another); grids that
 // leave SMs idle run 8 warps x 3 stages, spreading a CTA's short stream over more warps.
 // CAP compiles the score soft-cap in or out.
-template <int DT, int D, bool ROWS2, int W, int NS, bool CAP>
+// TR selects the transposed products (heads on the N side; the host picks it for groups of at most 4).
+template <int DT, int D, bool ROWS2, int W, int NS, bool CAP, bool TR>
 __global__ void __launch_bounds__(W * 32, (W == 4 && NS == 2 && Shape<DT, D, W, NS>::STAGE_BYTES <= 8192) ? 3 : 1)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                       const MmaParams mp)
@@ -298,7 +398,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     constexpr int kStages = NS;
     constexpr int TP = S::TP, NB = S::NB, NC = S::NC, KSTEPS = S::KSTEPS, NDB = S::NDB;
     constexpr bool FP8 = DT == VFKV_F8;
+    static_assert(!(TR && ROWS2), "the transposed products hold at most 4 heads");
     constexpr int RS = (!FP8 && ROWS2) ? 2 : 1;          // logical score rows per thread
+    constexpr int MB = TP / 16;                          // transposed form: 16-position M blocks per tile
+    constexpr int NQB = D / 16;                          // transposed form: 16-dim k steps of Q K^T / M blocks of O^T
     // With at most 8 q-heads per kv-head the M tile has room for a second term: rows 0-7 carry the
     // high part of Q (and of P), rows 8-15 the low part, and their products are summed in f32.
     constexpr bool SPLIT = FP8 || !ROWS2;
@@ -320,7 +423,12 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // (dependent) read of the sequence's position and the first TMA round trip.
     // element layout this thread needs: FP8  d = 32ks + 4tig + i  and  32ks + 16 + 4tig + i   (i < 4)
     //                                   F16  d = 16ks + 2tig + i  and  16ks + 8 + 2tig + i    (i < 2)
-    float qv[RS][KSTEPS][4], qv2[RS][KSTEPS][4];
+    // transposed form: this lane's column is head gid / 2 (high term in even, low term in odd
+    // columns) and it holds the dims its k slots carry:
+    //                                   FP8  d = 16u + 4tig + i                                (i < 4)
+    //                                   F16  d = 16u + 2tig + {0, 1}, 16u + 8 + 2tig + {0, 1}
+    float qv[TR ? 1 : RS][TR ? 1 : KSTEPS][4], qv2[TR ? 1 : RS][TR ? 1 : KSTEPS][4];
+    float qt[TR ? NQB : 1][4];
     // Programmatic dependent launch: this grid lets its successor in the stream begin once every CTA
     // has drawn its ticket (and, in mode 2, has seen its predecessor complete), and itself waits for
     // its predecessor before it touches anything the predecessor may have produced.  mp.pdl == 2 is
@@ -331,6 +439,22 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // Both instructions do nothing in a launch without the attribute.
     if (mp.pdl != 2u) asm volatile("griddepcontrol.wait;" ::: "memory");
     auto load_q = [&]() {
+    if constexpr (TR) {
+        const uint32_t hcol = gid >> 1;
+        const bool hv = hcol < g;
+        const float *qp = p.q + (uint64_t(s) * p.n_q_heads + kvh * g + (hv ? hcol : 0)) * D;
+#pragma unroll
+        for (int u = 0; u < NQB; ++u) {
+            if constexpr (FP8) {
+                const float4 a = hv ? *reinterpret_cast<const float4 *>(qp + 16 * u + 4 * tig) : make_float4(0, 0, 0, 0);
+                qt[u][0] = a.x; qt[u][1] = a.y; qt[u][2] = a.z; qt[u][3] = a.w;
+            } else {
+                const float2 a = hv ? *reinterpret_cast<const float2 *>(qp + 16 * u + 2 * tig) : make_float2(0, 0);
+                const float2 b = hv ? *reinterpret_cast<const float2 *>(qp + 16 * u + 8 + 2 * tig) : make_float2(0, 0);
+                qt[u][0] = a.x; qt[u][1] = a.y; qt[u][2] = b.x; qt[u][3] = b.y;
+            }
+        }
+    } else {
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
         const uint32_t hrow = gid + 8 * r;
@@ -350,6 +474,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 qv2[r][ks][0] = b.x; qv2[r][ks][1] = b.y; qv2[r][ks][2] = 0.f; qv2[r][ks][3] = 0.f;
             }
         }
+    }
     }
     };
     // Exchange number of a position-sharded call: read after the wait (the kernel that closed the
@@ -462,9 +587,34 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // FP8: rows 0-7 of the M tile hold the high E4M3 term of heads 0-7, rows 8-15 the low term.
     // F16: rows are heads 0-15.
     constexpr int QSTEPS = D / 16;       // one A fragment per 16 dims
-    uint32_t qa[QSTEPS][4];
+    uint32_t qa[TR ? 1 : QSTEPS][4];
+    uint32_t qb[TR ? NQB : 1][2];        // transposed form: B fragments of this lane's column
     float mult[RS];                      // score multiplier per logical row: scale / q_scale
-    {
+    if constexpr (TR) {
+        float amax = 0.f;
+#pragma unroll
+        for (int u = 0; u < NQB; ++u)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(qt[u][i]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        int e = int((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+        e = amax > 0.f ? max(-100, min(100, e)) : 7;
+        const float qs = __uint_as_float(uint32_t(7 - e + 127) << 23);
+        const float inv_qs = __uint_as_float(uint32_t(e - 7 + 127) << 23);
+        const bool low = (gid & 1u) != 0u;
+#pragma unroll
+        for (int u = 0; u < NQB; ++u) {
+            uint32_t h0, l0, h1, l1;
+            split_f16x2(qt[u][0] * qs, qt[u][1] * qs, h0, l0);
+            split_f16x2(qt[u][2] * qs, qt[u][3] * qs, h1, l1);
+            qb[u][0] = low ? l0 : h0;
+            qb[u][1] = low ? l1 : h1;
+        }
+        // the scores this lane will hold belong to head tig: fetch that head's multiplier from a
+        // lane whose column is one of its two
+        mult[0] = __shfl_sync(0xffffffffu, p.scale * inv_qs * (CAP ? 1.0f : kLog2e), (2u * tig) << 2);
+    } else {
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
             float amax = 0.f;
@@ -506,9 +656,10 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     float m[RS], l[RS];
 #pragma unroll
     for (int r = 0; r < RS; ++r) { m[r] = kMaskedScore; l[r] = 0.f; }
-    float acc[NDB][4];
+    constexpr int NACC = TR ? NQB : NDB;
+    float acc[NACC][4];
 #pragma unroll
-    for (int nb = 0; nb < NDB; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f; }
+    for (int nb = 0; nb < NACC; ++nb) { acc[nb][0] = acc[nb][1] = acc[nb][2] = acc[nb][3] = 0.f; }
     bool timed_out = false;
     // ---- split ticket -----------------------------------------------------------------------------
     // Every CTA of a (sequence, kv-head) draws one ticket from a 64-bit word that only ever counts
@@ -536,7 +687,9 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     const uint32_t lm = lane >> 3, lr = lane & 7;
     uint32_t qk_sw[4];        // K ldmatrix: row 8*(2jp + lm/2) + lr, unit 2u + (lm & 1)
 #pragma unroll
-    for (uint32_t u = 0; u < 4; ++u) qk_sw[u] = ((lm >> 1) * 8 + lr) * 128 + (((2 * u) ^ ((lm & 1) ^ lr)) << 4);
+    for (uint32_t u = 0; u < 4; ++u)
+        qk_sw[u] = TR ? ((lm & 1) * 8 + lr) * 128 + (((2 * u) ^ ((lm >> 1) ^ lr)) << 4)     // row half lm & 1, unit 2u + lm / 2
+                      : ((lm >> 1) * 8 + lr) * 128 + (((2 * u) ^ ((lm & 1) ^ lr)) << 4);
     // FP8 V words: row 2*tig + e (+8, +16, +24), unit 2u + gid/4, word gid%4
     // F16 V ldmatrix.trans: row 8*(lm & 1) + lr, unit 2u + lm/2
     uint32_t v_sw[FP8 ? 8 : 4];
@@ -549,7 +702,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     } else {
 #pragma unroll
         for (uint32_t u = 0; u < 4; ++u)
-            v_sw[u] = (8 * (lm & 1) + lr) * 128 + (((2 * u) ^ ((lm >> 1) ^ lr)) << 4);
+            v_sw[u] = TR ? (8 * (lm >> 1) + lr) * 128 + (((2 * u) ^ ((lm & 1) ^ lr)) << 4)  // row half lm / 2, unit 2u + (lm & 1)
+                         : (8 * (lm & 1) + lr) * 128 + (((2 * u) ^ ((lm >> 1) ^ lr)) << 4);
     }
 
     for (uint32_t n = 0; n < my_tiles; ++n) {
@@ -587,6 +741,62 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             __syncwarp();
         }
 
+        const bool full = n_valid == uint32_t(TP);
+        if constexpr (TR) {
+        // ---- S^T = K Q^T : M = 16 positions per block, N = the heads' high / low columns ----------
+        float sc[MB][4];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) { sc[mb][0] = sc[mb][1] = sc[mb][2] = sc[mb][3] = 0.f; }
+        {
+            const uint32_t kb[4] = {kt + qk_sw[0], kt + qk_sw[1], kt + qk_sw[2], kt + qk_sw[3]};
+            qk_t<FP8, TP, D>(kb, qb, sc);
+        }
+        // this thread's scores: head tig, positions t0 + 16mb + gid and + 8 (high + low column summed)
+        float x[MB][2];
+        float tmax = kMaskedScore;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float v = (sc[mb][2 * i] + sc[mb][2 * i + 1]) * mult[0];
+                if constexpr (CAP) v = p.softcap * tanhf(v / p.softcap) * kLog2e;
+                if (!full) v = uint32_t(16 * mb + 8 * i) + gid < n_valid ? v : kMaskedScore;
+                x[mb][i] = v;
+                tmax = fmaxf(tmax, v);
+            }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+        const float mn = fmaxf(m[0], tmax);
+        const float corr = fast_exp2(m[0] - mn);
+        const bool changed = mn != m[0];
+        m[0] = mn;
+        l[0] *= corr;
+        if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll
+            for (int nb = 0; nb < NACC; ++nb) { acc[nb][0] *= corr; acc[nb][1] *= corr; acc[nb][2] *= corr; acc[nb][3] *= corr; }
+        }
+        // p = 2^(x - m) as {high, low} half pairs = this thread's two columns of a position row;
+        // the 8x8 transpose turns them into the B fragment (k = positions, n = columns) of O^T += V^T P^T
+        uint32_t pb[MB][2];
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float pv = fast_exp2(x[mb][i] - mn);
+                l[0] += pv;
+                pb[mb][i] = movmatrix_trans(hi_lo_f16x2(pv));
+            }
+        if constexpr (FP8) {
+            uint32_t vb[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vb[i] = vt + v_sw[i];
+            pv_t_fp8<TP, D>(vb, pb, acc);
+        } else {
+            const uint32_t vb[4] = {vt + v_sw[0], vt + v_sw[1], vt + v_sw[2], vt + v_sw[3]};
+            pv_t_f16<TP, D>(vb, pb[0], acc);
+        }
+        } else {
         // ---- S = Q K^T : M = q rows, N = 8 positions per block, K = 32 bytes of the head slice ----
         float sc[NB][4];
 #pragma unroll
@@ -600,7 +810,6 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         // this thread's scores: logical row r, block j, element i  <->  position t0 + 8j + 2tig + i
         float x[RS][NB][2];
         float tmax[RS];
-        const bool full = n_valid == uint32_t(TP);
 #pragma unroll
         for (int r = 0; r < RS; ++r) {
             tmax[r] = kMaskedScore;
@@ -688,6 +897,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             const uint32_t vb[4] = {vt + v_sw[0], vt + v_sw[1], vt + v_sw[2], vt + v_sw[3]};
             pv_f16<TP, D>(vb, pa, acc);
         }
+        }
 
         // ---- refill this stage -----------------------------------------------------------------
         // The stage was only read (ldmatrix / ld.shared) since its barrier completed, except in a
@@ -733,6 +943,27 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     float *sm_o = reinterpret_cast<float *>(ring_ptr);        // [kWarps][NH][DP]
     float *sm_m = sm_o + kWarps * NH * DP;                    // [kWarps][NH]
     float *sm_l = sm_m + kWarps * NH;                         // [kWarps][NH]
+    if constexpr (TR) {
+        // this thread's head is tig; its l covers the positions of its own gid
+        l[0] += __shfl_xor_sync(0xffffffffu, l[0], 4);
+        l[0] += __shfl_xor_sync(0xffffffffu, l[0], 8);
+        l[0] += __shfl_xor_sync(0xffffffffu, l[0], 16);
+        if (tig < g) {
+            if (gid == 0) { sm_m[warp * NH + tig] = m[0]; sm_l[warp * NH + tig] = l[0]; }
+            float *o = sm_o + (warp * NH + tig) * DP;
+#pragma unroll
+            for (int db = 0; db < NACC; ++db) {
+                if constexpr (FP8) {
+                    const uint32_t d0 = 32 * (db / 2) + 4 * gid + 2 * (db % 2);
+                    o[d0] = acc[db][0] + acc[db][1];
+                    o[d0 + 1] = acc[db][2] + acc[db][3];
+                } else {
+                    o[16 * db + gid] = acc[db][0] + acc[db][1];
+                    o[16 * db + 8 + gid] = acc[db][2] + acc[db][3];
+                }
+            }
+        }
+    } else {
 #pragma unroll
     for (int r = 0; r < RS; ++r) {
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -760,6 +991,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 o[8 * DP + d0] = acc[nb][2]; o[8 * DP + d0 + 1] = acc[nb][3];
             }
         }
+    }
     }
     __syncthreads();
 
@@ -1078,7 +1310,7 @@ bool encode_map(vfkv_ctx *ctx, CUtensorMap *out, const void *base, uint64_t row_
     return r == CUDA_SUCCESS;
 }
 
-template <int DT, int D, bool ROWS2, int W, int NS, bool CAP>
+template <int DT, int D, bool ROWS2, int W, int NS, bool CAP, bool TR>
 int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
     using S = Shape<DT, D, W, NS>;
@@ -1088,7 +1320,7 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
     if constexpr (S::SMEM_BYTES > 227 * 1024 || !kMergeFits) {
         return set_error(ctx, VFKV_ERR_UNSUPPORTED, "tuning does not fit in shared memory for this shape");
     } else {
-        auto kern = attn_split_mma_kernel<DT, D, ROWS2, W, NS, CAP>;
+        auto kern = attn_split_mma_kernel<DT, D, ROWS2, W, NS, CAP, TR>;
         // per device, shared by every context and thread: setting the attribute twice is harmless,
         // the flag only saves the call
         static std::atomic<bool> configured[64];
@@ -1156,7 +1388,7 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
     }
 }
 
-template <int DT, int D, bool ROWS2, bool CAP>
+template <int DT, int D, bool ROWS2, bool CAP, bool TR>
 int32_t launch_c(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
     // Small grids (at most one CTA per SM): 8 warps x 3 stages where that fits in shared memory.
@@ -1175,19 +1407,25 @@ int32_t launch_c(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
     constexpr bool kOk2 = Shape<DT, D, 4, 2>::SMEM_BYTES <= kTwoPerSm && kMergeBytes <= Shape<DT, D, 4, 2>::RING_BYTES;
     constexpr bool kOk1 = Shape<DT, D, 4, 1>::SMEM_BYTES <= kTwoPerSm && kMergeBytes <= Shape<DT, D, 4, 1>::RING_BYTES;
     if (ns == 0) ns = (w == 8 || Shape<DT, D, 4, 3>::SMEM_BYTES <= kTwoPerSm) ? 3 : kOk2 ? 2 : kOk1 ? 1 : 3;
-    if (w == 8 && ns == 3) return launch_k<DT, D, ROWS2, 8, 3, CAP>(ctx, tk, tv, mp, st);
-    if (w == 4 && ns == 3) return launch_k<DT, D, ROWS2, 4, 3, CAP>(ctx, tk, tv, mp, st);
-    if (w == 4 && ns == 2) return launch_k<DT, D, ROWS2, 4, 2, CAP>(ctx, tk, tv, mp, st);
-    if (w == 4 && ns == 1) return launch_k<DT, D, ROWS2, 4, 1, CAP>(ctx, tk, tv, mp, st);
-    if (w == 8 && ns == 1) return launch_k<DT, D, ROWS2, 8, 1, CAP>(ctx, tk, tv, mp, st);
+    if (w == 8 && ns == 3) return launch_k<DT, D, ROWS2, 8, 3, CAP, TR>(ctx, tk, tv, mp, st);
+    if (w == 4 && ns == 3) return launch_k<DT, D, ROWS2, 4, 3, CAP, TR>(ctx, tk, tv, mp, st);
+    if (w == 4 && ns == 2) return launch_k<DT, D, ROWS2, 4, 2, CAP, TR>(ctx, tk, tv, mp, st);
+    if (w == 4 && ns == 1) return launch_k<DT, D, ROWS2, 4, 1, CAP, TR>(ctx, tk, tv, mp, st);
+    if (w == 8 && ns == 1) return launch_k<DT, D, ROWS2, 8, 1, CAP, TR>(ctx, tk, tv, mp, st);
     return set_error(ctx, VFKV_ERR_INVALID, "attention tuning must be 4x1, 4x2, 4x3, 8x1 or 8x3 (warps x stages)");
 }
 
 template <int DT, int D, bool ROWS2>
 int32_t launch_t(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, const MmaParams &mp, cudaStream_t st)
 {
-    return mp.a.softcap > 0.f ? launch_c<DT, D, ROWS2, true>(ctx, tk, tv, mp, st)
-                              : launch_c<DT, D, ROWS2, false>(ctx, tk, tv, mp, st);
+    // groups of at most 4 q-heads: the transposed products (heads on the N side of the MMAs)
+    if constexpr (!ROWS2) {
+        if (mp.a.group <= 4u)
+            return mp.a.softcap > 0.f ? launch_c<DT, D, ROWS2, true, true>(ctx, tk, tv, mp, st)
+                                      : launch_c<DT, D, ROWS2, false, true>(ctx, tk, tv, mp, st);
+    }
+    return mp.a.softcap > 0.f ? launch_c<DT, D, ROWS2, true, false>(ctx, tk, tv, mp, st)
+                              : launch_c<DT, D, ROWS2, false, false>(ctx, tk, tv, mp, st);
 }
 
 }  // namespace
