@@ -643,6 +643,8 @@ def sharded_section(ctx, args, rank, world, local_rank, dist):
     rank (owner's append + attention + split merge + peer stores of the partial into every rank's
     buffer + merge of all ranks' partials); the step is replayed from a CUDA graph.  Before timing,
     rank 0 checks layer 0's output against a single-GPU decode step over the unsharded rows.
+    long_fp8_ctx131072_b1_by_kv_head_group: the same sequence with every position on every rank but
+    only the rank's kv-heads (vfkv_shard_kv_heads) and their q-heads; nothing to exchange.
     batch64_fp8_ragged_512_16384: sequences dealt out by `assign_sequences`; no exchange at all."""
     import torch
     import vulkanforge_b200 as vf
@@ -700,6 +702,7 @@ def sharded_section(ctx, args, rank, world, local_rank, dist):
     launches = ctx.launch_count() - n0
     ctx.poll()
     check = None
+    ref = None
     if rank == 0:                                  # layer 0 against one GPU holding every row
         rc = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
         rf = vf.CudaForward(ctx, rc, n_heads=hq, n_splits=w["n_splits"])
@@ -738,6 +741,65 @@ def sharded_section(ctx, args, rank, world, local_rank, dist):
     exchange.destroy()
     fwd.workspace.destroy()
     cache.destroy()
+
+    # ---- the same long context, sharded by kv-head group ---------------------------------------
+    # Rank r holds kv-heads [first, first + count) of every position and the q-heads that read them:
+    # outputs are disjoint head ranges, there is nothing to exchange.  The split count is the
+    # library's own choice for a few kv-heads with the GPU to themselves.
+    import ctypes as C
+    first, count = C.c_uint32(), C.c_uint32()
+    ctx.check(ctx._lib.vfkv_shard_kv_heads(world, rank, hkv, C.byref(first), C.byref(count)))
+    h0, nh, grp = first.value, count.value, hq // hkv
+    if world <= hkv:                               # every rank has at least one kv-head
+        cache = vf.KvCache(ctx, vf.KvCacheConfig(n_layers, nh, d, L), vf.KvDtype.F8)
+        fwd = vf.CudaForward(ctx, cache, n_heads=nh * grp, n_splits=0, max_splits=255)
+        for page in range(n_pages):
+            kv = page_rows(page, hkv, d)
+            m = min(256, L - 1 - page * 256)
+            if m <= 0:
+                continue
+            kv = kv.view(2, 256, hkv, d)[:, :m, h0:h0 + nh].contiguous()
+            for layer in range(n_layers):
+                fwd.b_step_kv_write(layer, kv[0], kv[1], m, page * 256, 0)
+        qh = q.view(n_layers, hkv, grp, d)[:, h0:h0 + nh].reshape(n_layers, 1, nh * grp, d).contiguous()
+        kh = kn.view(n_layers, 2, hkv, d)[:, :, h0:h0 + nh].contiguous()
+        k_new = kh[:, 0].reshape(n_layers, 1, nh, d).contiguous()
+        v_new = kh[:, 1].reshape(n_layers, 1, nh, d).contiguous()
+        outh = torch.zeros(n_layers, 1, nh * grp, d, device="cuda")
+        pos = torch.tensor([L - 1], dtype=torch.int32, device="cuda")
+        fwd.stream = stream.cuda_stream
+
+        def step_heads():
+            fwd.decode_token(qh, k_new, v_new, outh, None, pos, 1, L)
+
+        with torch.cuda.stream(stream):
+            step_heads()
+        barrier()
+        ctx.poll()
+        check_heads = None
+        if rank == 0 and ref is not None:
+            mine = ref.view(hkv, grp, d)[h0:h0 + nh].reshape(nh * grp, d)
+            check_heads = float((outh[0, 0] - mine).abs().max() / ref.abs().max())
+            if not check_heads <= 1e-3:
+                raise RuntimeError(f"kv-head-sharded output differs from one GPU: relative error {check_heads}")
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step_heads()
+        ms, _, _ = timed_blocks(graph.replay, stream, args.steps, 3, dist, 200.0)
+        ctx.poll()
+        us = ms * 1e3 / args.steps / n_layers
+        key = name + "_by_kv_head_group"
+        res[key] = {"us_per_token_layer": us, "one_gpu_us_per_token_layer": one_gpu_us, "n_gpus": world,
+                    "kv_heads_per_rank": nh, "launches_per_layer_per_rank": 1.0,
+                    "check_rel_err_vs_one_gpu": check_heads, "exchange": "none (disjoint q-head ranges)"}
+        if one_gpu_us is not None:
+            res[key]["speedup"] = one_gpu_us / us
+            res[key]["efficiency"] = one_gpu_us / us / world
+            res[key]["roofline_frac_per_gpu"] = (algorithmic_bytes(w, [L], 0) / world) / (us * 1e-6) / 1e9 / peak
+        fwd.stream = None
+        barrier()
+        fwd.workspace.destroy()
+        cache.destroy()
 
     # ---- ragged batch of 64, sharded by sequence ----------------------------------------------
     name = "batch64_fp8_ragged_512_16384"

@@ -232,8 +232,9 @@ uint64_t vfkv_workspace_bytes(const vfkv_workspace *ws);
  * only ever counts up; there is one such word per split count, so ticket / n_splits is the number
  * of this launch on the word and ticket % n_splits the CTA's place in the draw.  Partials are
  * 8-byte words {f32 value, u32 tag} written by one store each, the tag made of a launch counter
- * kept by the host and the launch number on the word; the last drawers (up to four) each merge a
- * slice of the output rows and accept only words that carry the tag of their own launch, waiting
+ * kept by the host and the launch number on the word, and laid out by slice of the output rows so
+ * that each of the last drawers (four; up to sixteen when a few kv-heads are cut into many splits)
+ * finds its slice of every split in one block.  They accept only words that carry the tag of their own launch, waiting
  * at most the time set with vfkv_ctx_set_merge_wait_ms (a wait that runs out raises bit 1 (value 1) of
  * the status word).  Nothing is reset between launches, so a launch that gave up, a graph replay or
  * a change of geometry leaves nothing that a later launch could mistake for its own;
@@ -493,7 +494,8 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
 /* Latency analysis of the tensor-core attention kernel: while d_buffer is non-NULL, thread 0 of
  * every CTA stores 16 x uint64 nanosecond timestamps (globaltimer) at fixed phases -- 0 entry,
  * 1 range known, 2 barriers ready, 3 Q ready, 4 first tile landed, 5 stream done, 6 CTA joined,
- * 7 partial stored, 8 splits merged (merging CTA only), 9 rows written -- at CTA index * 16.  The buffer
+ * 7 partial stored, 8 splits merged, 9 rows written, 10 every split's partial seen, 11 first round of
+ * copies staged (8, 10 and 11: merging CTAs only) -- at CTA index * 16.  The buffer
  * must hold 16 x 8 bytes per CTA of the largest grid.  NULL switches it off.
  * The tcgen05 prefill kernel (vfkv_attend_prefill) uses the same buffer: thread 0 of each of its
  * two warpgroups stores, at its 4th K/V tile, 0 tile start, 1 loads issued and previous P V

@@ -476,7 +476,9 @@ int32_t vfkv_workspace_create(vfkv_ctx *ctx, uint32_t max_seqs, uint32_t n_q_hea
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->part_l), parts * 4);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->d_u32), u32_bytes);
     ws->n_counters = rows;
-    ws->tag_words = parts * (uint64_t(head_dim) + 4);     // o, {m, l} and one decision pair per CTA (kv-heads <= q-heads)
+    // per (q-head row, split): the o words, and room for the {m, l} words and padding of up to sixteen
+    // slices of the output (one per merging CTA; a launch takes fewer slices if that is not enough)
+    ws->tag_words = parts * (uint64_t(head_dim) + 68);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&ws->tickets), rows * 256 * 8);
     if (e == cudaSuccess) e = cudaMemset(ws->tickets, 0, rows * 256 * 8);
     // tag 0 is never used by a launch, so zeroed words read as "not there yet"

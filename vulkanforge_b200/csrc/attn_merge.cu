@@ -112,6 +112,23 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     // the extra CTAs save (one sequence of 16384 positions, 64 q-heads: 15.9 us with 16 splits,
     // 19.5 us with 37), unless the length rule below asks for more.
     if (want > 16) want = 16;
+    // Fewer than eight groups (one long sequence whose kv-heads are spread over several GPUs): the
+    // merge is then shared by up to sixteen CTAs of the group, each combining its outputs with a
+    // team of lanes, and one CTA per SM pays: 148 / groups splits.
+    const bool few_groups = base > 0 && base * 32 <= uint64_t(ctx->sm_count) && tile >= 128;
+    if (few_groups) {
+        want = uint64_t(ctx->sm_count) / base;
+        if (want > 255) want = 255;
+        cap = (uint64_t(max_len) + min_chunk - 1) / min_chunk;
+        if (cap < 1) cap = 1;
+        if (want > cap) want = cap;
+        // a CTA of 8 warps takes 256 positions per round of tiles: the fewest splits that need no
+        // more rounds than that count does (131 072 positions on one kv-head: 128 splits of 4
+        // rounds, 14.1 us, where 148 ragged ones took 15.6 us)
+        const uint64_t rounds = ((uint64_t(max_len) + want - 1) / want + 255) / 256;
+        const uint64_t fewest = (uint64_t(max_len) + rounds * 256 - 1) / (rounds * 256);
+        if (fewest >= 1 && fewest < want) want = fewest;
+    }
     // A CTA keeps at most its own ring of stages in flight, which bounds one CTA's stream to a few
     // tens of GB/s: in a ragged batch a sequence much longer than the rest would finish last on
     // its own.  No CTA gets more than 8192 positions, 4096 once contexts beyond 8192 are possible

@@ -48,6 +48,12 @@ namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+// P goes into the tensor cores as half-precision terms.  With tens of thousands of positions most
+// p = 2^(x - m) lie below the smallest normal half (6.1e-5), where the terms keep few or no bits
+// (measured: 6.5e-5 absolute error at 40 000 positions).  So P is fed as p * 2^14 (still at most
+// 16 384) and the accumulators are scaled back when the warp's partial is written; both scalings
+// are exact, and l is summed from the unscaled p.
+constexpr float kPScale = 16384.0f, kInvPScale = 1.0f / 16384.0f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -97,9 +103,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
-__device__ __forceinline__ void fence_proxy_async()
+__device__ __forceinline__ ulonglong2 lds_u64x2(uint32_t addr)
 {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    ulonglong2 w;
+    asm("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(w.x), "=l"(w.y) : "r"(addr) : "memory");
+    return w;
 }
 // The shared-memory loads take a register base plus a compile-time byte offset, so that the
 // per-lane swizzled part of an address is computed once per tile and the rest is an immediate.
@@ -168,6 +176,8 @@ struct MmaParams {
     uint32_t cluster;             // 1: the splits of a (sequence, kv-head) are one thread-block cluster
     uint32_t fan_merge;           // with a.fan: also wait for the other ranks' blocks and write the final rows
     uint32_t fail_split;          // test hook: this split of (sequence 0, kv-head 0) acts as if a TMA wait ran out
+    uint32_t per_recip;           // ceil(2^32 / output pairs per merging CTA): idx / per == umulhi(idx, per_recip) for idx < 65536
+    uint64_t tag_words;           // host side only: size of tag_part in words
 };
 
 // Phase timestamps for latency analysis; costs one predicated branch when tracing is off.
@@ -785,7 +795,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             for (int i = 0; i < 2; ++i) {
                 const float pv = fast_exp2(x[mb][i] - mn);
                 l[0] += pv;
-                pb[mb][i] = movmatrix_trans(hi_lo_f16x2(pv));
+                pb[mb][i] = movmatrix_trans(hi_lo_f16x2(pv * kPScale));
             }
         if constexpr (FP8) {
             uint32_t vb[8];
@@ -865,7 +875,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     const float pv = fast_exp2(x[r][j][i] - mo);
-                    x[r][j][i] = pv;
+                    x[r][j][i] = pv * kPScale;
                     l[r] += pv;
                 }
         }
@@ -955,11 +965,11 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             for (int db = 0; db < NACC; ++db) {
                 if constexpr (FP8) {
                     const uint32_t d0 = 32 * (db / 2) + 4 * gid + 2 * (db % 2);
-                    o[d0] = acc[db][0] + acc[db][1];
-                    o[d0 + 1] = acc[db][2] + acc[db][3];
+                    o[d0] = (acc[db][0] + acc[db][1]) * kInvPScale;
+                    o[d0 + 1] = (acc[db][2] + acc[db][3]) * kInvPScale;
                 } else {
-                    o[16 * db + gid] = acc[db][0] + acc[db][1];
-                    o[16 * db + 8 + gid] = acc[db][2] + acc[db][3];
+                    o[16 * db + gid] = (acc[db][0] + acc[db][1]) * kInvPScale;
+                    o[16 * db + 8 + gid] = (acc[db][2] + acc[db][3]) * kInvPScale;
                 }
             }
         }
@@ -979,16 +989,16 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             // column n of block nb is dim 32*(nb/4) + 4n + nb%4 (see the V transpose above)
             const uint32_t d0 = 32 * (nb / 4) + 4 * (2 * tig) + (nb % 4);
             float *o = sm_o + (warp * NH + gid) * DP;
-            o[d0] = acc[nb][0] + acc[nb][2];
-            o[d0 + 4] = acc[nb][1] + acc[nb][3];
+            o[d0] = (acc[nb][0] + acc[nb][2]) * kInvPScale;
+            o[d0 + 4] = (acc[nb][1] + acc[nb][3]) * kInvPScale;
         } else {
             const uint32_t d0 = 8 * nb + 2 * tig;
             float *o = sm_o + (warp * NH + gid) * DP;
             if constexpr (SPLIT) {
-                o[d0] = acc[nb][0] + acc[nb][2]; o[d0 + 1] = acc[nb][1] + acc[nb][3];
+                o[d0] = (acc[nb][0] + acc[nb][2]) * kInvPScale; o[d0 + 1] = (acc[nb][1] + acc[nb][3]) * kInvPScale;
             } else {
-                o[d0] = acc[nb][0]; o[d0 + 1] = acc[nb][1];
-                o[8 * DP + d0] = acc[nb][2]; o[8 * DP + d0 + 1] = acc[nb][3];
+                o[d0] = acc[nb][0] * kInvPScale; o[d0 + 1] = acc[nb][1] * kInvPScale;
+                o[8 * DP + d0] = acc[nb][2] * kInvPScale; o[8 * DP + d0 + 1] = acc[nb][3] * kInvPScale;
             }
         }
     }
@@ -1135,18 +1145,26 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // carries this launch's tag.  Every other CTA is done once its stores are issued and leaves
     // its SM to the next launch.  The last drawer has drawn after every CTA of its group had begun
     // its last tile, so it only ever waits for CTAs that are about to store.
+    // Layout of the group's partials: [slice of the output pairs = one per merging CTA][split][span],
+    // span = the o words of the slice's `per` pairs, then the {m, l} words of all g heads (every slice
+    // has its own copy of those), padded to an odd number of 16-byte units so that lanes reading the
+    // same unit of consecutive splits fall into different shared-memory banks.  All that one merging
+    // CTA needs is then one contiguous block.
     const uint32_t tag = s_tag;
     const uint64_t grp = uint64_t(s) * p.n_kv_heads + kvh;
-    const uint64_t pwords = uint64_t(g) * (D + 2);            // words of one CTA's partial: o[g][D], {m, l}[g]
-    uint64_t *const gp = mp.tag_part + grp * p.n_splits * pwords;
+    const uint32_t n_mrg = direct ? 1u : min(mp.n_mergers, p.n_splits);
+    const uint32_t per = (n_pairs + n_mrg - 1) / n_mrg;
+    const uint32_t span = 2u * (per + g) + (((per + g) & 1u) ? 0u : 2u);
+    uint64_t *const gp = mp.tag_part + grp * (uint64_t(p.n_splits) * n_mrg * span);
     if (!direct) {
-        uint64_t *mine = gp + uint64_t(split) * pwords;
         for (uint32_t idx = threadIdx.x; idx < n_pairs; idx += blockDim.x) {
             const uint32_t j = idx / HD2, d = 2 * (idx % HD2);
             float O0, O1, Mn, L;
             cta_partial(j, d, O0, O1, Mn, L);
-            tagged_store2(mine + 2 * idx, O0, O1, tag);        // = o[j][d], o[j][d + 1]
-            if (d == 0) tagged_store2(mine + uint64_t(g) * D + 2 * j, Mn, L, tag);
+            const uint32_t sl = per > 1u ? __umulhi(idx, mp.per_recip) : idx;       // = idx / per
+            tagged_store2(gp + (uint64_t(sl) * p.n_splits + split) * span + 2u * (idx - sl * per), O0, O1, tag);   // = o[j][d], o[j][d + 1]
+            const uint32_t c = idx % HD2;          // the first n_mrg threads of a head each write one copy of its {m, l}
+            if (c < n_mrg) tagged_store2(gp + (uint64_t(c) * p.n_splits + split) * span + 2u * per + 2u * j, Mn, L, tag);
         }
         VFKV_TRACE(7);
         if (s_merger == 0u) return;
@@ -1167,55 +1185,86 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // cycles and more apiece, and one SM reads its L2 at some 64 bytes per clock, so the code is kept
     // short and rolled and the work is shared: the last n_mergers drawers each take one slice of the
     // output pairs.  (Only CTAs that have drawn wait, and at most n_mergers per group, far fewer
-    // than there are SMs, so a CTA that has yet to start always finds one.)  A merger copies its
-    // slice of every split's partial into the now idle ring with asynchronous 16-byte copies, one
-    // short loop that puts every request in flight at once; then each thread merges its output
-    // pairs out of shared memory (flash_attn_reduce.comp:51-80, maximum first) and checks the tags
-    // as it goes.  A word that does not carry this launch's tag yet sends the step round again, up
-    // to the time limit.
+    // than there are SMs, so a CTA that has yet to start always finds one.)  A merger brings its
+    // slice of every split's partial into the now idle ring with asynchronous copies; then teams of lanes
+    // merge its output pairs out of shared memory (flash_attn_reduce.comp:51-80, maximum first)
+    // and check the tags as they go.  A word that does not carry this launch's tag yet sends the
+    // step round again, up to the time limit.
     __syncthreads();          // the warps' partials in the ring are dead (uniform: the whole CTA merges or none of it)
     uint64_t *const stgw = reinterpret_cast<uint64_t *>(ring_ptr);
     const uint32_t stg_base = ring;                               // shared-window address of stgw
     // this CTA's slice of the pairs
-    const uint32_t n_mrg = direct ? 1u : min(mp.n_mergers, p.n_splits);
-    const uint32_t per = (n_pairs + n_mrg - 1) / n_mrg;
     const uint32_t lo = direct ? 0u : min((s_merger - 1u) * per, n_pairs), hi = min(lo + per, n_pairs);
     const uint32_t n_mine = hi - lo;
     if (!direct) {
-        // staged per split: o words of pairs [lo, hi), then the {m, l} words of all g rows
-        const uint32_t span = 2u * per + 2u * g;                  // words
+        uint32_t team = 1u;                                       // power of two, at most a warp
+        while (team < 32u && 2u * team * n_mine <= blockDim.x && 2u * team <= p.n_splits) team *= 2u;
+        // Asynchronous 16-byte copies bring the slice's block ([split][span], contiguous) into the ring,
+        // all requests in flight at once; the tag checks of the merge below tell whether every word
+        // of this launch was there, and if not the step goes round again.  With a few splits the first
+        // copy is issued at once -- the merging CTAs are the last to finish, so the partials are
+        // usually there, and a look first would cost one more round trip.  With many splits, and in
+        // every later round, thread i first polls the word of split i that is stored last in this
+        // slice, so that a copy is not spent on a block that is still incomplete.
+        const uint64_t *const block = gp + uint64_t(s_merger - 1u) * p.n_splits * span;
         uint64_t t0 = 0;
-        for (;;) {
-            for (uint32_t k = threadIdx.x; k < p.n_splits * (n_mine + g); k += blockDim.x) {
-                const uint32_t i = k / (n_mine + g), q2 = k % (n_mine + g);
-                const uint64_t *src = gp + uint64_t(i) * pwords + (q2 < n_mine ? 2ull * (lo + q2) : uint64_t(g) * D + 2ull * (q2 - n_mine));
-                const uint32_t dst = stg_base + 8u * (i * span + (q2 < n_mine ? 2u * q2 : 2u * per + 2u * (q2 - n_mine)));
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        for (uint32_t round = 0;; ++round) {
+            if (round != 0u || p.n_splits > 32u) {
+                bool late = false;
+                const uint64_t t_in = global_timer_ns();
+                for (uint32_t i = threadIdx.x; i < p.n_splits; i += blockDim.x) {
+                    const uint64_t *w = block + uint64_t(i) * span + (n_mine != 0u ? 2u * (n_mine - 1u) : 2u * per);
+                    while (!tags_are(tagged_load2(w), tag)) {
+                        if (global_timer_ns() - t_in > mp.merge_wait_ns) { late = true; break; }
+                        __nanosleep(20);
+                    }
+                }
+                if (__syncthreads_or(late)) {                     // a partial of this launch never arrived
+                    if (threadIdx.x == 0) atomicOr(p.status, 1u);
+                    return;
+                }
             }
+            if (round == 0u) VFKV_TRACE(10);
+            for (uint32_t k = threadIdx.x; k < p.n_splits * span / 2u; k += blockDim.x)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stg_base + 16u * k), "l"(block + 2ull * k) : "memory");
             asm volatile("cp.async.wait_all;" ::: "memory");
             __syncthreads();
+            if (round == 0u) VFKV_TRACE(11);
+            // `team` neighbouring lanes share one output pair, each taking every team-th split (a
+            // slice has fewer pairs than the CTA has threads); they combine through shuffles
             bool missing = false;
-            for (uint32_t idx = lo + threadIdx.x; idx < hi; idx += blockDim.x) {
-                const uint32_t j = idx / HD2;
-                const uint64_t *po = stgw + 2 * (idx - lo), *pm = stgw + 2 * per + 2 * j;
+            const uint32_t sub = threadIdx.x % team, per_pass = blockDim.x / team;
+            for (uint32_t b = 0; b < n_mine; b += per_pass) {
+                const uint32_t q2 = b + threadIdx.x / team;
+                const bool live = q2 < n_mine;
+                const uint32_t idx = lo + (live ? q2 : 0u), j = idx / HD2;
+                const uint32_t po = stg_base + 8u * (sub * span + 2u * (idx - lo)), pm = stg_base + 8u * (sub * span + 2u * per + 2u * j);
+                const uint32_t step = 8u * team * span;
                 float gmax = kMaskedScore, gsum = 0.f, a0 = 0.f, a1 = 0.f;
 #pragma unroll 4
-                for (uint32_t i = 0; i < p.n_splits; ++i) {
-                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * span);
+                for (uint32_t i = sub, a = pm; i < p.n_splits; i += team, a += step) {
+                    const ulonglong2 mw = lds_u64x2(a);
                     missing = missing || !tags_are(mw, tag);
                     gmax = fmaxf(gmax, tagged_value(mw.x));
                 }
+                for (uint32_t o = 1; o < team; o <<= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
 #pragma unroll 4
-                for (uint32_t i = 0; i < p.n_splits; ++i) {
-                    const ulonglong2 ow = *reinterpret_cast<const ulonglong2 *>(po + i * span);
-                    const ulonglong2 mw = *reinterpret_cast<const ulonglong2 *>(pm + i * span);
+                for (uint32_t i = sub, a = po, am = pm; i < p.n_splits; i += team, a += step, am += step) {
+                    const ulonglong2 ow = lds_u64x2(a);
+                    const ulonglong2 mw = lds_u64x2(am);
                     missing = missing || !tags_are(ow, tag);
                     const float kn = __expf(tagged_value(mw.x) - gmax);
                     gsum = fmaf(tagged_value(mw.y), kn, gsum);
                     a0 = fmaf(tagged_value(ow.x), kn, a0);
                     a1 = fmaf(tagged_value(ow.y), kn, a1);
                 }
-                if (!missing) emit(idx, a0, a1, gmax, gsum);
+                for (uint32_t o = 1; o < team; o <<= 1) {
+                    gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
+                    a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+                }
+                const bool bad = __any_sync(0xffffffffu, missing);
+                if (live && sub == 0u && !bad) emit(idx, a0, a1, gmax, gsum);
             }
             if (!__syncthreads_or(missing)) break;               // also: every thread is done with the staged words
             const uint64_t now = global_timer_ns();
@@ -1224,7 +1273,6 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
                 if (threadIdx.x == 0) atomicOr(p.status, 1u);
                 return;
             }
-            __nanosleep(100);
         }
         VFKV_TRACE(8);
     }
@@ -1330,10 +1378,37 @@ int32_t launch_k(vfkv_ctx *ctx, const CUtensorMap &tk, const CUtensorMap &tv, co
             configured[ctx->device & 63].store(true, std::memory_order_release);
         }
         MmaParams lp = mp;
-        // The merging CTA stages the whole group's partials (and, in a one-launch exchange, every
-        // rank's block of the kv-head) in the ring: fewer splits where they would not fit.
-        const uint64_t pbytes = uint64_t(mp.a.group) * (D + 2) * 8;
-        if (uint64_t(lp.a.n_splits) * pbytes > uint64_t(S::RING_BYTES)) lp.a.n_splits = uint32_t(S::RING_BYTES / pbytes) > 0u ? uint32_t(S::RING_BYTES / pbytes) : 1u;
+        // A merging CTA stages its slice of every split's partial in the ring, and the group's partials
+        // ([slice][split][span] words, see the kernel) have to fit the workspace: fewer splits where the
+        // ring is too small, fewer merging CTAs where the workspace is.
+        const uint64_t n_pairs = uint64_t(mp.a.group) * (D / 2), groups = uint64_t(mp.a.n_kv_heads) * mp.a.n_seqs;
+        auto span_of = [&](uint32_t n_mrg) {
+            const uint64_t per = (n_pairs + n_mrg - 1) / n_mrg;
+            return 2 * (per + mp.a.group) + (((per + mp.a.group) & 1) ? 0 : 2);
+        };
+        if (lp.n_mergers == 0u) lp.n_mergers = 1u;
+        for (int pass = 0; pass < 3 && lp.a.n_splits > 1u; ++pass) {      // fewer splits can mean fewer mergers, hence larger slices
+            const uint32_t n_mrg = lp.n_mergers < lp.a.n_splits ? lp.n_mergers : lp.a.n_splits;
+            const uint64_t sbytes = span_of(n_mrg) * 8;
+            if (uint64_t(lp.a.n_splits) * sbytes <= uint64_t(S::RING_BYTES)) break;
+            lp.a.n_splits = uint32_t(S::RING_BYTES / sbytes) > 0u ? uint32_t(S::RING_BYTES / sbytes) : 1u;
+        }
+        while (lp.a.n_splits > 1u) {
+            const uint32_t n_mrg = lp.n_mergers < lp.a.n_splits ? lp.n_mergers : lp.a.n_splits;
+            if (groups * lp.a.n_splits * n_mrg * span_of(n_mrg) <= mp.tag_words) break;
+            if (lp.n_mergers == 1u) return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
+            lp.n_mergers = n_mrg - 1u;
+        }
+        if (lp.a.n_splits > 1u) {          // the last check of the ring, with the number of merging CTAs that was settled on
+            const uint32_t n_mrg = lp.n_mergers < lp.a.n_splits ? lp.n_mergers : lp.a.n_splits;
+            if (uint64_t(lp.a.n_splits) * span_of(n_mrg) * 8 > uint64_t(S::RING_BYTES))
+                lp.a.n_splits = uint32_t(S::RING_BYTES / (span_of(n_mrg) * 8)) > 0u ? uint32_t(S::RING_BYTES / (span_of(n_mrg) * 8)) : 1u;
+        }
+        {
+            const uint32_t n_mrg = lp.a.n_splits > 1u ? (lp.n_mergers < lp.a.n_splits ? lp.n_mergers : lp.a.n_splits) : 1u;
+            const uint64_t per = (n_pairs + n_mrg - 1) / n_mrg;
+            lp.per_recip = per > 1 ? uint32_t(((1ull << 32) + per - 1) / per) : 0xFFFFFFFFu;
+        }
         if (lp.fan_merge && 8ull * (uint64_t(mp.a.group) * D * 8 + 2ull * mp.a.group * 4) > uint64_t(S::RING_BYTES))
             return set_error(ctx, VFKV_ERR_UNSUPPORTED, "one-launch exchange does not fit this kernel shape");
         dim3 grid(lp.a.n_splits, mp.a.n_kv_heads, mp.a.n_seqs);
@@ -1465,14 +1540,18 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
     mp.a = make_params(ctx, ws, a, n_splits);
     mp.tickets = ws ? ws->tickets : nullptr;
     mp.tag_part = ws ? ws->tag_part : nullptr;
+    mp.tag_words = ws ? ws->tag_words : 0;
     mp.merge_wait_ns = ctx->merge_wait_ns;
     mp.launch_seq = (ws && n_splits > 1) ? ws->launch_seq++ : 0u;
-    // Up to four CTAs per (sequence, kv-head) share the merge, as long as all the CTAs that may be
-    // waiting at one time stay a small part of the SMs (a waiting CTA holds its SM).
+    // Several CTAs per (sequence, kv-head) share the merge -- four, or up to sixteen when a few
+    // groups have the GPU to themselves and are cut into many splits -- as long as all the CTAs that
+    // may be waiting at one time stay a small part of the SMs (a waiting CTA holds its SM).
     {
         const uint64_t groups = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
         const uint64_t room = uint64_t(ctx->sm_count) / 4 / (groups ? groups : 1);
-        mp.n_mergers = uint32_t(room < 1 ? 1 : room > 4 ? 4 : room);
+        const uint64_t most = n_splits > 16 ? (n_splits + 7) / 8 : 4;      // a merger for every eight splits
+        mp.n_mergers = uint32_t(room < 1 ? 1 : room > most ? most : room);
+        if (mp.n_mergers > 16u) mp.n_mergers = 16u;
     }
     mp.trace = ctx->d_trace;
     if (ctx->d_trace && ctx->trace_ring > 1) {      // successive launches write successive blocks of the buffer
@@ -1493,8 +1572,6 @@ int32_t launch_attn_mma(vfkv_ctx *ctx, vfkv_workspace *ws, const AttnArgs &a, ui
         return set_error(ctx, VFKV_ERR_INVALID, "new K/V rows must be 16-byte aligned");
     if (n_splits > 1 && (!mp.tickets || !mp.tag_part)) return set_error(ctx, VFKV_ERR_INVALID, "workspace has no split-merge storage");
     if (n_splits > 255) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "the tensor-core attention kernel merges at most 255 splits");
-    if (n_splits > 1 && uint64_t(a.seq.n_seqs) * n_splits * (a.n_q_heads * (uint64_t(D) + 2) + 2ull * a.kv.n_kv_heads) > ws->tag_words)
-        return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
     if (n_splits > 1 && uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads > ws->n_counters)
         return set_error(ctx, VFKV_ERR_INVALID, "workspace too small for this call");
     const uint32_t g = a.n_q_heads / a.kv.n_kv_heads;

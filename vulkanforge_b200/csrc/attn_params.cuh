@@ -138,13 +138,9 @@ __device__ __forceinline__ void tagged_store2(uint64_t *dst, float v0, float v1,
 }
 __device__ __forceinline__ ulonglong2 tagged_load2(const uint64_t *src)
 {
-#ifdef VFKV_EXPERIMENT_LDCG
-    return __ldcg(reinterpret_cast<const ulonglong2 *>(src));
-#else
     ulonglong2 w;
     asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w.x), "=l"(w.y) : "l"(src) : "memory");
     return w;
-#endif
 }
 __device__ __forceinline__ ulonglong2 tagged_load2_sys(const uint64_t *src)
 {

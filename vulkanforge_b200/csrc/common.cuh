@@ -60,7 +60,7 @@ struct vfkv_workspace {
     // count and the device-side launch number, so that a reader that finds the tag has the value.
     unsigned long long *tickets = nullptr;
     uint64_t n_counters = 0;
-    uint64_t *tag_part = nullptr;   // [seq * kv_head][split][ o[g][head_dim] | {m, l}[g] | decision pair ] words
+    uint64_t *tag_part = nullptr;   // per (seq, kv_head): [slice of the output pairs][split][ o words of the slice | {m, l}[g] | pad ]
     uint64_t tag_words = 0;
     uint32_t launch_seq = 0;        // split launches issued on this workspace (the host's half of a tag)
     uint64_t bytes = 0;
