@@ -63,7 +63,7 @@ DT = {"F32": 0, "F16": 1, "F8": 2}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu
 # captures summarised under profiles/ (one file per kernel and workload; a capture cannot run inside
 # a timed run, so these are read off the summaries; workloads without a capture report null)
-NCU_TRAFFIC_BYTES = {"qwen3_8b_fp8_ctx8192_b1": 16_843_000, "batch64_fp8_ctx8192": 1_081_500_000}
+NCU_TRAFFIC_BYTES = {"qwen3_8b_fp8_ctx8192_b1": 16_900_000, "batch64_fp8_ctx8192": 1_079_900_000}
 
 
 def config_of(name, w):
