@@ -18,20 +18,43 @@ merge_kernel(const float *__restrict__ pm, const float *__restrict__ pl, const f
 {
     const uint64_t row = blockIdx.x;
     constexpr int kMaxDims = 4;                      // 128 threads x 4 = head_dim 512
-    float acc[kMaxDims] = {0.f, 0.f, 0.f, 0.f};
+    __shared__ float s_red[4], s_sum[4];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // The shader walks the partials with a running (max, sum, acc); the same result, up to
     // rounding, comes from taking the maximum first and then one weighted sum, which leaves
-    // every load independent of the others.
+    // every load independent of the others.  The launch is a chain of L2 round trips and nothing
+    // else, so it is kept to two: the maxima and sums (one or two parts per thread), then the o rows.
     float gmax = kMaskedScore;
-#pragma unroll 8
-    for (uint32_t i = 0; i < n_parts; ++i) gmax = fmaxf(gmax, pm[uint64_t(i) * ml_part + row * ml_row]);
-    float gsum = 0.f;
-#pragma unroll 4
-    for (uint32_t i = 0; i < n_parts; ++i) {
+    float m_own[2] = {kMaskedScore, kMaskedScore}, l_own[2] = {0.f, 0.f};      // parts tid and tid + 128
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t i = threadIdx.x + 128 * k;
+        if (i < n_parts) {
+            const uint64_t pi = uint64_t(i) * ml_part + row * ml_row;
+            m_own[k] = pm[pi];
+            l_own[k] = pl[pi];
+        }
+    }
+    gmax = fmaxf(m_own[0], m_own[1]);
+    for (uint32_t i = threadIdx.x + 256; i < n_parts; i += 128) gmax = fmaxf(gmax, pm[uint64_t(i) * ml_part + row * ml_row]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gmax = fmaxf(gmax, __shfl_xor_sync(0xffffffffu, gmax, o));
+    if (lane == 0) s_red[warp] = gmax;
+    __syncthreads();
+    gmax = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    float gsum = fmaf(l_own[0], __expf(m_own[0] - gmax), l_own[1] * __expf(m_own[1] - gmax));
+    for (uint32_t i = threadIdx.x + 256; i < n_parts; i += 128) {
         const uint64_t pi = uint64_t(i) * ml_part + row * ml_row;
+        gsum = fmaf(pl[pi], __expf(pm[pi] - gmax), gsum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
+    if (lane == 0) s_sum[warp] = gsum;
+    float acc[kMaxDims] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 16
+    for (uint32_t i = 0; i < n_parts; ++i) {
         const uint64_t oi = uint64_t(i) * o_part + row * o_row;
-        const float kn = __expf(pm[pi] - gmax);
-        gsum = fmaf(pl[pi], kn, gsum);
+        const float kn = __expf(pm[uint64_t(i) * ml_part + row * ml_row] - gmax);
 #pragma unroll
         for (int j = 0; j < kMaxDims; ++j) {
             uint32_t d = threadIdx.x + j * 128;
@@ -39,6 +62,8 @@ merge_kernel(const float *__restrict__ pm, const float *__restrict__ pl, const f
             acc[j] = fmaf(t, kn, acc[j]);
         }
     }
+    __syncthreads();
+    gsum = (s_sum[0] + s_sum[1]) + (s_sum[2] + s_sum[3]);
     const float inv = gsum > 0.f ? 1.0f / gsum : 0.f;   // an empty range yields zeros, not NaN
 #pragma unroll
     for (int j = 0; j < kMaxDims; ++j) {
