@@ -116,7 +116,8 @@ int32_t launch_merge_partials_packed(vfkv_ctx *ctx, const float *packed, uint32_
 
 // Split count when the caller passes 0.  The reference always cuts at 64
 // positions (runs.rs:766-769); here the count only has to fill the GPU: aim
-// for about two CTAs per SM, never cut below 256 positions per split.
+// for about two CTAs per SM, never cut below 256 positions per split (128 on the tensor cores
+// with an F16 cache).
 uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
 {
     uint32_t max_len = a.seq.max_len_hint ? a.seq.max_len_hint : a.kv.max_seq;
@@ -128,7 +129,10 @@ uint32_t choose_splits(const vfkv_ctx *ctx, const AttnArgs &a, uint32_t tile)
     // never below 256 positions per split.
     const uint64_t base = uint64_t(a.seq.n_seqs) * a.kv.n_kv_heads;
     const uint64_t slots = uint64_t(ctx->sm_count) * 2;
-    const uint32_t min_chunk = tile < 256 ? 256 : tile;
+    // (an 8-warp CTA of the tensor-core kernel takes 8 tiles at a time: 256 positions of an FP8
+    // cache, 128 of an F16 cache, where 16 splits of 128 measured 6.2 us against 6.6 us with 8 of 256
+    // on 32 q / 8 kv / 128 at 2048 positions)
+    const uint32_t min_chunk = (tile >= 128 && a.kv.dtype == VFKV_F16) ? 128 : tile < 256 ? 256 : tile;
     uint64_t cap = (uint64_t(max_len) + min_chunk - 1) / min_chunk;
     if (cap < 1) cap = 1;
     if (cap > 64) cap = 64;
