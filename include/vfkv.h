@@ -253,6 +253,13 @@ int32_t vfkv_workspace_reset(vfkv_workspace *ws, void *stream);
  * src/server/state.rs:199-229). */
 int32_t vfkv_append(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v,
                     uint32_t n_tokens, uint32_t slot, uint32_t base_pos, void *stream);
+/* The same chunk on a cache sharded by position (the plan of vfkv_shard_owner below): base_pos is
+ * the global position of the first token; the rows whose page this rank owns are stored at their
+ * local positions, the others are skipped -- one launch per chunk whatever the page size.  The
+ * cache's max_seq_len is the rank's local capacity. */
+int32_t vfkv_append_sharded(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v,
+                            uint32_t n_tokens, uint32_t slot, uint32_t base_pos, uint32_t world,
+                            uint32_t page, uint32_t rank, void *stream);
 /* One token for each of n_seqs sequences: d_k/d_v are [n_seqs][kv_heads][head_dim],
  * d_slot_ids (NULL = 0..n_seqs-1) and d_positions are device arrays. */
 int32_t vfkv_append_batch(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v,

@@ -182,6 +182,28 @@ impl Forward {
         dev.check(unsafe { sys::vfkv_append(self.kv_cache.handle, layer, k_src, v_src, seq_len, 0, base_pos, stream) })
     }
 
+    /// b_step_kv_write on a cache sharded by position over `world` GPUs (pages of `page` positions
+    /// dealt round-robin): `base_pos` is global; this rank's rows of the chunk are stored at their
+    /// local positions by one launch.
+    #[allow(clippy::too_many_arguments)]
+    pub fn b_step_kv_write_sharded(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        layer: u32,
+        k_src: *const f32,
+        v_src: *const f32,
+        seq_len: u32,
+        base_pos: u32,
+        world: u32,
+        page: u32,
+        rank: u32,
+    ) -> Result<(), String> {
+        dev.check(unsafe {
+            sys::vfkv_append_sharded(self.kv_cache.handle, layer, k_src, v_src, seq_len, 0, base_pos, world, page, rank, stream)
+        })
+    }
+
     /// step_attention (attention.rs:599-626)
     pub fn step_attention(
         &mut self,

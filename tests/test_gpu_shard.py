@@ -26,6 +26,48 @@ def _inputs(seq_len, seed):
     return q, k, v
 
 
+@pytest.mark.parametrize("dtype", ["F8", "F16"])
+def test_sharded_chunk_append_stores_this_ranks_rows_in_one_launch(ctx, dtype):
+    """vfkv_append_sharded against one vfkv_append per page piece: the same cache bytes on every
+    rank, one launch per chunk; a chunk that would overrun the rank's rows is refused."""
+    import torch
+    from util import dev_view_bytes
+    world, page, seq_len = 3, 64, 1000
+    _, k, v = _inputs(seq_len, seed=77)
+    sh = PositionShards(world, page)
+    cap = sh.local_capacity(seq_len)
+    dk, dv = to_dev(k), to_dev(v)
+    for r in range(world):
+        caches = [vf.KvCache(ctx, vf.KvCacheConfig(1, HKV, D, cap), vf.KvDtype[dtype]) for _ in range(2)]
+        fwds = [vf.CudaForward(ctx, c, n_heads=HQ) for c in caches]
+        try:
+            for c in caches:
+                c.zero_fill()
+            for base, n in ((0, 37), (37, 500), (537, 463)):          # chunks that start and end inside pages
+                n0 = ctx.launch_count()
+                fwds[0].b_step_kv_write_sharded(0, dk[base:base + n], dv[base:base + n], n, base, world, page, r)
+                assert ctx.launch_count() - n0 == 1
+                p = base
+                while p < base + n:
+                    stop = min(base + n, (p // page + 1) * page)
+                    if sh.owner(p) == r:
+                        fwds[1].b_step_kv_write(0, dk[p:stop], dv[p:stop], stop - p, sh.local_pos(p))
+                    p = stop
+            torch.cuda.synchronize()
+            ctx.poll()
+            nbytes = caches[0].bytes_per_buffer()
+            for buf in ("k_buffer", "v_buffer"):
+                a = dev_view_bytes(getattr(caches[0], buf), nbytes)
+                b = dev_view_bytes(getattr(caches[1], buf), nbytes)
+                assert a.any() and np.array_equal(a, b)
+            with pytest.raises(vf.VfkvError):
+                fwds[0].b_step_kv_write_sharded(0, dk, dv, seq_len, world * cap, world, page, r)
+        finally:
+            for f, c in zip(fwds, caches):
+                f.workspace.destroy()
+                c.destroy()
+
+
 @pytest.mark.parametrize("world,page,seq_len", [(4, 256, 5000), (8, 256, 9000), (2, 64, 700), (3, 256, 100)])
 def test_emulated_ranks_chunked_prefill_append_and_merge(ctx, world, page, seq_len):
     import torch

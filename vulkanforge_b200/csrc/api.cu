@@ -577,6 +577,29 @@ int32_t vfkv_append(vfkv_cache *cache, uint32_t layer, const float *d_k, const f
     return launch_append(ctx, a, as_stream(stream));
 }
 
+int32_t vfkv_append_sharded(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v, uint32_t n_tokens,
+                            uint32_t slot, uint32_t base_pos, uint32_t world, uint32_t page, uint32_t rank, void *stream)
+{
+    int32_t rc = check_layer(cache, layer, "vfkv_append_sharded");
+    if (rc) return rc;
+    vfkv_ctx *ctx = cache->ctx;
+    if (!d_k || !d_v) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_append_sharded: null K or V");
+    if ((reinterpret_cast<uintptr_t>(d_k) | reinterpret_cast<uintptr_t>(d_v)) % 16 != 0)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_append_sharded: K and V inputs must be 16-byte aligned");
+    if (slot >= cache->kv.config.n_slots) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_append_sharded: slot out of range");
+    if (world == 0 || rank >= world || page == 0) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_append_sharded: bad sharding plan");
+    if (uint64_t(base_pos) + n_tokens > 0xFFFFFFFFull)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_append_sharded: base_pos + n_tokens overflows");
+    // the context-overflow check of src/backend/vulkan/decode.rs:523-533, on this rank's share
+    if (n_tokens && vfkv_shard_local_len(world, page, uint64_t(base_pos) + n_tokens, rank) > cache->kv.config.max_seq_len)
+        return set_error(ctx, VFKV_ERR_INVALID, "vfkv_append_sharded: this rank's rows exceed max_seq_len");
+    AppendArgs a = make_append(cache, layer, d_k, d_v);
+    a.n_rows = n_tokens; a.slot = slot; a.base_pos = base_pos;
+    a.shard_world = world; a.shard_rank = rank; a.shard_page = page;
+    DeviceGuard g(ctx->device);
+    return launch_append(ctx, a, as_stream(stream));
+}
+
 int32_t vfkv_append_batch(vfkv_cache *cache, uint32_t layer, const float *d_k, const float *d_v,
                           const uint32_t *d_slot_ids, const uint32_t *d_positions, uint32_t n_seqs, void *stream)
 {

@@ -131,6 +131,7 @@ struct AppendParams {
     const uint32_t *positions;
     uint64_t slot_stride_bytes, slot_stride_scales;
     uint32_t row_elems, head_dim, n_kv_heads, max_seq, n_slots, n_rows, slot, base_pos;
+    uint32_t shard_world, shard_rank, shard_page;   // world > 1: base_pos + row is a global position dealt out in pages
     uint32_t *status;
 };
 
@@ -143,6 +144,11 @@ __device__ __forceinline__ bool row_target(const AppendParams &p, uint32_t row, 
     } else {
         *slot = p.slot;
         *pos = p.base_pos + row;
+        if (p.shard_world > 1u) {        // pages of positions dealt round-robin: rows of other ranks are not stored here
+            const uint32_t page = *pos / p.shard_page;
+            if (page % p.shard_world != p.shard_rank) return false;
+            *pos = (page / p.shard_world) * p.shard_page + *pos % p.shard_page;
+        }
     }
     if (*slot >= p.n_slots || *pos >= p.max_seq) {
         atomicOr(p.status, 2u);   // out-of-range row: skipped, reported through vfkv_ctx_poll
@@ -226,6 +232,7 @@ int32_t launch_append(vfkv_ctx *ctx, const AppendArgs &a, cudaStream_t st)
     p.row_elems = a.row_elems; p.head_dim = a.head_dim; p.n_kv_heads = a.n_kv_heads;
     p.max_seq = a.max_seq; p.n_slots = a.n_slots; p.n_rows = a.n_rows; p.slot = a.slot;
     p.base_pos = a.base_pos; p.status = ctx->d_status;
+    p.shard_world = a.shard_world; p.shard_rank = a.shard_rank; p.shard_page = a.shard_page ? a.shard_page : 1u;
 
     if (a.k_scales) {
         if (a.head_dim % 4 != 0) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "scaled append needs head_dim % 4 == 0");

@@ -201,6 +201,8 @@ struct AppendArgs {
     uint32_t slot = 0, base_pos = 0;           // consecutive mode
     const uint32_t *slot_ids = nullptr;        // batch mode (positions != null)
     const uint32_t *positions = nullptr;
+    // consecutive mode on a position-sharded cache: base_pos is global, only this rank's rows are stored
+    uint32_t shard_world = 0, shard_rank = 0, shard_page = 0;
 };
 int32_t launch_append(vfkv_ctx *ctx, const AppendArgs &a, cudaStream_t st);
 

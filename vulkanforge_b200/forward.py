@@ -151,6 +151,13 @@ class CudaForward:
         self.ctx.check(self._L.vfkv_append(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src), seq_len, slot,
                                            base_pos, self.stream))
 
+    def b_step_kv_write_sharded(self, layer: int, k_src, v_src, seq_len: int, base_pos: int, world: int, page: int,
+                                rank: int, slot: int = 0):
+        """b_step_kv_write on a cache sharded by position: base_pos is global, this rank's rows of the
+        chunk are stored at their local positions, in one launch."""
+        self.ctx.check(self._L.vfkv_append_sharded(self.kv_cache.handle, layer, ptr(k_src), ptr(v_src), seq_len, slot,
+                                                   base_pos, world, page, rank, self.stream))
+
     def step_attention(self, layer: int, q, attn_out, position: int, slot: int = 0):
         """executor/attention.rs:599-626"""
         self.run_scalar_attn(q, attn_out, layer, position, slot)

@@ -118,18 +118,12 @@ class ShardedSequenceDecoder:
         return True
 
     def prefill(self, layer: int, k_src, v_src, base_pos: int, n_tokens: int) -> int:
-        """Chunked-prefill append: stores the rows of [base_pos, base_pos + n_tokens) this rank owns,
-        one call per page piece.  k_src / v_src are torch tensors [n_tokens][kv_heads][D]."""
-        done, p, end = 0, base_pos, base_pos + n_tokens
-        while p < end:
-            stop = min(end, (p // self.shards.page + 1) * self.shards.page)
-            if self.shards.owner(p) == self.rank:
-                i = p - base_pos
-                self.fwd.b_step_kv_write(layer, k_src[i:i + stop - p], v_src[i:i + stop - p], stop - p,
-                                         self.shards.local_pos(p), 0)
-                done += stop - p
-            p = stop
-        return done
+        """Chunked-prefill append: stores the rows of [base_pos, base_pos + n_tokens) this rank owns
+        (one launch for the chunk; the kernel skips the other ranks' pages) and returns how many
+        those are.  k_src / v_src are torch tensors [n_tokens][kv_heads][D]."""
+        self.fwd.b_step_kv_write_sharded(layer, k_src, v_src, n_tokens, base_pos, self.shards.world_size,
+                                         self.shards.page, self.rank)
+        return self.shards.local_len(base_pos + n_tokens, self.rank) - self.shards.local_len(base_pos, self.rank)
 
     def decode(self, layer: int, q, k_src, v_src, out, position: int):
         """One decode step of global ``position``: append (owner rank only) and attention over
