@@ -370,6 +370,18 @@ int32_t vfkv_attend_partial(vfkv_cache *cache, vfkv_workspace *ws, uint32_t laye
                             uint32_t slot, uint32_t pos_begin, uint32_t pos_end, float scale,
                             float softcap, uint32_t n_splits, float *d_m, float *d_l,
                             float *d_o, void *stream);
+/* The partial of this rank's positions, an all-gather of every rank's partial, and the merge, in
+ * one call, for a host that already holds an NCCL communicator over its GPUs: nccl_comm is its
+ * ncclComm_t; d_packed is scratch of world * n_q_heads * (head_dim + 2) floats (block r = rank r's
+ * m[rows], l[rows], o[rows][head_dim]); d_out [n_q_heads][head_dim] is complete on every rank.
+ * ncclAllGather is resolved at run time in the NCCL the process has loaded (VFKV_ERR_UNSUPPORTED if
+ * there is none); this library links no collective library itself.  Three launches and the
+ * collective's latency: the peer exchange further down (vfkv_attend_exchange) is the fast path. */
+int32_t vfkv_attend_allgather(vfkv_cache *cache, vfkv_workspace *ws, void *nccl_comm, uint32_t world,
+                              uint32_t rank, uint32_t layer, uint32_t kv_layer, const float *d_q,
+                              uint32_t n_q_heads, uint32_t slot, uint32_t pos_begin, uint32_t pos_end,
+                              float scale, float softcap, uint32_t n_splits, float *d_packed,
+                              float *d_out, void *stream);
 /* d_m, d_l: [n_parts][n_rows]; d_o: [n_parts][n_rows][head_dim];
  * d_out: [n_rows][head_dim]; n_rows = sequences x q-heads. */
 int32_t vfkv_merge_partials(vfkv_ctx *ctx, const float *d_m, const float *d_l, const float *d_o,

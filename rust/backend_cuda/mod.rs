@@ -204,6 +204,32 @@ impl Forward {
         })
     }
 
+    /// Attention of one query token over this rank's share [0, local_len) of a position-sharded
+    /// sequence, merged over the ranks through the host's NCCL communicator (`nccl_comm` is the
+    /// ncclComm_t): partial, all-gather and merge in one call.  `packed` is scratch of
+    /// world * n_heads * (head_dim + 2) floats.
+    #[allow(clippy::too_many_arguments)]
+    pub fn attend_allgather(
+        &mut self,
+        dev: &CudaDevice,
+        stream: *mut c_void,
+        nccl_comm: *mut c_void,
+        world: u32,
+        rank: u32,
+        layer: u32,
+        local_len: u32,
+        packed: *mut f32,
+    ) -> Result<(), String> {
+        let kv_layer = self.routing.kv_read_layer.get(layer as usize).copied().unwrap_or(layer);
+        dev.check(unsafe {
+            sys::vfkv_attend_allgather(
+                self.kv_cache.handle, self.workspace, nccl_comm, world, rank, layer, kv_layer, self.q_buf,
+                self.n_heads, 0, 0, local_len, self.routing.attn_scale, self.routing.softcap, 0, packed,
+                self.attn_out, stream,
+            )
+        })
+    }
+
     /// step_attention (attention.rs:599-626)
     pub fn step_attention(
         &mut self,

@@ -357,6 +357,36 @@ def test_kv_head_group_sharding_needs_no_exchange(ctx, world, dtype):
         assert np.max(np.abs(out - want)) < 2e-5
 
 
+def test_attend_allgather_on_a_communicator_of_one(ctx):
+    """vfkv_attend_allgather (partial, ncclAllGather on the caller's communicator, merge) with a
+    world of one: the collective is a copy, the result the plain attention."""
+    import torch
+    from util import NcclComm
+    seq_len = 3000
+    q, k, v = _inputs(seq_len, seed=12)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, HKV, D, seq_len), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=HQ)
+    comm = NcclComm(1, 0, lambda raw: raw)
+    try:
+        fwd.b_step_kv_write(0, to_dev(k[:seq_len]), to_dev(v[:seq_len]), seq_len, 0)
+        packed = torch.zeros(HQ * (D + 2), device="cuda")
+        out = torch.zeros(HQ, D, device="cuda")
+        fwd.attend_allgather(comm.handle, 1, 0, 0, to_dev(q), 0, seq_len, packed, out)
+        torch.cuda.synchronize()
+        ctx.poll()
+        kc, vc = encode_cache(k[:seq_len], oracle.F8), encode_cache(v[:seq_len], oracle.F8)
+        want = oracle.attention_ref(q, kc, vc, oracle.F8, HQ, HKV, D, seq_len)
+        assert rel_err(out.cpu().numpy(), want) < 1e-4
+        with pytest.raises(vf.VfkvError):
+            fwd.attend_allgather(0, 1, 0, 0, to_dev(q), 0, seq_len, packed, out)
+        with pytest.raises(vf.VfkvError):
+            fwd.attend_allgather(comm.handle, 1, 1, 0, to_dev(q), 0, seq_len, packed, out)
+    finally:
+        comm.destroy()
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
 def _nccl_rank(rank, world, port, seq_len, result_dir):
     import torch
     import torch.distributed as dist
@@ -382,6 +412,25 @@ def _nccl_rank(rank, world, port, seq_len, result_dir):
         kc, vc = encode_cache(k, oracle.F8), encode_cache(v, oracle.F8)
         want = oracle.attention_ref(q, kc, vc, oracle.F8, HQ, HKV, D, seq_len + 1)
         errs = [rel_err(out.cpu().numpy(), want)]
+        # the same through the C entry that carries the collective: a raw communicator (its unique
+        # id handed round over the process group), no PyTorch collective on the path
+        from util import NcclComm
+
+        def exchange_id(raw):
+            box = [raw]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+
+        comm = NcclComm(world, rank, exchange_id)
+        packed = torch.zeros(world * HQ * (D + 2), device="cuda")
+        for _ in range(2):
+            out.zero_()
+            fwd.attend_allgather(comm.handle, world, rank, 0, torch.from_numpy(q).cuda(), 0,
+                                 sh.local_len(seq_len + 1, rank), packed, out)
+            torch.cuda.synchronize()
+            ctx.poll()
+            errs.append(rel_err(out.cpu().numpy(), want))
+        comm.destroy()
         # the same attention with the partials exchanged by peer stores (IPC-mapped buffers),
         # first as plain launches, then replayed from a CUDA graph
         ex = vf.PeerExchange(ctx, world, rank, HQ, D)

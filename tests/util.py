@@ -70,6 +70,37 @@ def dev_write_bytes(addr: int, data: np.ndarray):
     ctx.check(L.vfkv_stream_synchronize(ctx.handle, None))
 
 
+class NcclComm:
+    """A raw NCCL communicator made with ctypes from the NCCL library the process has loaded (the
+    one PyTorch brings): what a host without PyTorch would hand to vfkv_attend_allgather.
+    ``exchange_id`` gets rank 0's 128-byte unique id and returns it on every rank."""
+
+    def __init__(self, world: int, rank: int, exchange_id):
+        import ctypes as C
+        import torch  # noqa: F401  (loads libnccl.so.2)
+
+        class UniqueId(C.Structure):
+            _fields_ = [("internal", C.c_char * 128)]
+
+        self._nccl = C.CDLL("libnccl.so.2")
+        uid = UniqueId()
+        if rank == 0:
+            rc = self._nccl.ncclGetUniqueId(C.byref(uid))
+            assert rc == 0, rc
+        raw = exchange_id(bytes(C.string_at(C.addressof(uid), 128)))
+        C.memmove(C.addressof(uid), raw, 128)
+        self._nccl.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+        comm = C.c_void_p()
+        rc = self._nccl.ncclCommInitRank(C.byref(comm), world, uid, rank)
+        assert rc == 0, rc
+        self.handle = comm.value
+
+    def destroy(self):
+        import ctypes as C
+        self._nccl.ncclCommDestroy.argtypes = [C.c_void_p]
+        self._nccl.ncclCommDestroy(self.handle)
+
+
 _CTX = None
 
 

@@ -96,6 +96,7 @@ SIGNATURES = {
     "vfkv_assign_sequences": (i32, [pu32, u32, u32, pu32]),
     "vfkv_shard_kv_heads": (i32, [u32, u32, u32, pu32, pu32]),
     "vfkv_append_sharded": (i32, [vp, u32, vp, vp, u32, u32, u32, u32, u32, u32, vp]),
+    "vfkv_attend_allgather": (i32, [vp, vp, vp, u32, u32, u32, u32, vp, u32, u32, u32, u32, f32, f32, u32, vp, vp, vp]),
     "vfkv_exchange_create": (i32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
     "vfkv_exchange_destroy": (None, [vp]),
     "vfkv_exchange_bytes": (u64, [vp]),

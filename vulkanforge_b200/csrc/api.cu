@@ -1,8 +1,12 @@
 // extern "C" surface of libvfkv.so (declared in include/vfkv.h): argument
 // validation, cache / workspace objects, and routing to the kernel launchers.
+#include <dlfcn.h>
+
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
+#include <string>
 
 #include "attn_params.cuh"
 
@@ -1059,6 +1063,55 @@ int32_t vfkv_attend_partial(vfkv_cache *cache, vfkv_workspace *ws, uint32_t laye
     a.softcap = softcap; a.n_splits = n_splits;
     DeviceGuard g(ctx->device);
     return launch_attention(ctx, ws, a, as_stream(stream));
+}
+
+// ---- the same exchange through a collective library -----------------------------------------------
+// ncclAllGather is looked up in the NCCL that the process has loaded (or can load) the first time
+// it is needed; the library itself links no collective library.
+namespace {
+typedef int (*NcclAllGatherFn)(const void *, void *, size_t, int, void *, cudaStream_t);
+NcclAllGatherFn find_nccl_all_gather()
+{
+    static std::mutex mu;
+    static bool looked = false;
+    static NcclAllGatherFn fn = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!looked) {
+        looked = true;
+        void *sym = dlsym(RTLD_DEFAULT, "ncclAllGather");
+        if (!sym) {
+            void *h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+            if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+            if (h) sym = dlsym(h, "ncclAllGather");
+        }
+        fn = reinterpret_cast<NcclAllGatherFn>(sym);
+    }
+    return fn;
+}
+}  // namespace
+
+int32_t vfkv_attend_allgather(vfkv_cache *cache, vfkv_workspace *ws, void *nccl_comm, uint32_t world, uint32_t rank,
+                              uint32_t layer, uint32_t kv_layer, const float *d_q, uint32_t n_q_heads, uint32_t slot,
+                              uint32_t pos_begin, uint32_t pos_end, float scale, float softcap, uint32_t n_splits,
+                              float *d_packed, float *d_out, void *stream)
+{
+    int32_t rc = attend_common(cache, layer, kv_layer, n_q_heads, "vfkv_attend_allgather");
+    if (rc) return rc;
+    vfkv_ctx *ctx = cache->ctx;
+    if (!nccl_comm || !d_packed || !d_out) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_allgather: null argument");
+    if (world == 0 || rank >= world) return set_error(ctx, VFKV_ERR_INVALID, "vfkv_attend_allgather: rank outside the world");
+    NcclAllGatherFn all_gather = find_nccl_all_gather();
+    if (!all_gather) return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_attend_allgather: no NCCL library in this process (ncclAllGather not found)");
+    const uint32_t D = cache->kv.head_dim_for(kv_layer);
+    const uint64_t block = uint64_t(n_q_heads) * (D + 2);        // m[rows], l[rows], o[rows][D] of one rank
+    float *mine = d_packed + uint64_t(rank) * block;
+    rc = vfkv_attend_partial(cache, ws, layer, kv_layer, d_q, n_q_heads, slot, pos_begin, pos_end, scale, softcap,
+                             n_splits, mine, mine + n_q_heads, mine + 2ull * n_q_heads, stream);
+    if (rc) return rc;
+    DeviceGuard g(ctx->device);
+    const int nrc = all_gather(mine, d_packed, size_t(block), /* ncclFloat32 */ 7, nccl_comm, as_stream(stream));
+    if (nrc != 0) return set_error(ctx, VFKV_ERR_CUDA, "vfkv_attend_allgather: ncclAllGather failed with code " + std::to_string(nrc));
+    return launch_merge_partials_packed(ctx, d_packed, world, n_q_heads, D, d_out, as_stream(stream));
 }
 
 // Shared by vfkv_attend_push (fused = false) and vfkv_attend_exchange (fused = true).

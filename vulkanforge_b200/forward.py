@@ -248,6 +248,17 @@ class CudaForward:
                                                    self.attn_scale, self.softcap, self.n_splits, ptr(m), ptr(l),
                                                    ptr(o), self.stream))
 
+    def attend_allgather(self, nccl_comm: int, world: int, rank: int, layer: int, q, pos_begin: int, pos_end: int,
+                         packed, out, slot: int = 0, kv_layer: Optional[int] = None):
+        """Partial over [pos_begin, pos_end), an NCCL all-gather of every rank's partial on the
+        caller's communicator (``nccl_comm`` = the ncclComm_t as an integer) and the merge, in one
+        library call.  ``packed`` is scratch of world * n_heads * (head_dim + 2) floats."""
+        kv_layer = self.gemma4_kv_read_layer(layer) if kv_layer is None else kv_layer
+        self.ctx.check(self._L.vfkv_attend_allgather(self.kv_cache.handle, self.workspace.handle, nccl_comm, world,
+                                                     rank, layer, kv_layer, ptr(q), self.n_heads, slot, pos_begin,
+                                                     pos_end, self.attn_scale, self.softcap, self.n_splits,
+                                                     ptr(packed), ptr(out), self.stream))
+
     def attend_push(self, exchange, layer: int, q, pos_begin: int, pos_end: int, slot: int = 0,
                     kv_layer: Optional[int] = None, k_new=None, v_new=None):
         """Local partial over [pos_begin, pos_end), stored by the kernel into every rank's exchange
