@@ -8,8 +8,9 @@ attend over the whole context.  The default workload is the FP8 Qwen3-8B-like ca
 (36 layers, 32 q / 8 kv / 128, batch 1, context 8192, 16 splits).  Prints ONE JSON line.
 
 value     device-timed, inputs resident in HBM, microseconds per token per layer
-e2e       the same through vfkv_decode_token_host with pinned HOST buffers (copies inside the
-          timed region)
+e2e       the same from pinned HOST buffers through vfkv_decode_token_host_submit / _wait with two
+          tokens in flight (every step's copies inside the timed region); the synchronous
+          vfkv_decode_token_host is reported beside it
 roofline  the attention split kernel: algorithmic KV bytes per launch / its mean launch time,
           against the measured HBM copy bandwidth
 cpu_baseline  the CPU oracle (a C port of the reference's CPU attention and store code, the
@@ -18,8 +19,9 @@ cpu_baseline  the CPU oracle (a C port of the reference's CPU attention and stor
 Under torchrun every rank runs the headline workload on its own sequence(s) and GPU (sharding
 by sequence, no collective on the data path; times are the max over ranks), and the two sharded
 configurations are measured as well -- the long context cut by position over the ranks (partials
-exchanged by peer stores inside the attention kernel, output checked against one GPU) and the
-ragged batch of 64 dealt out by sequence -- each beside its one-GPU time from the same run.  They
+exchanged by peer stores inside the attention kernel, output checked against one GPU), the same
+context cut by kv-head group (no exchange) and the ragged batch of 64 dealt out by sequence --
+each beside its one-GPU time from the same run.  They
 are the last key of the line ("sharded").
 """
 from __future__ import annotations
