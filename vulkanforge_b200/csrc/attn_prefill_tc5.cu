@@ -784,6 +784,347 @@ __global__ void __launch_bounds__(256, 1) prefill_tc5p_kernel(const Tc5Params p)
     }
 }
 
+
+// ---- specialised form ----------------------------------------------------------------------------------
+// tcgen05.mma holds the thread that issues it for as long as the tensor pipe is busy (measured in
+// the two forms above: 0.5-0.7 us per group of 8), and in those forms that thread also owns a row
+// of the softmax, so 127 threads wait for it at every barrier.  Here the roles are separate warps:
+//   warps 0-3 / 4-7   softmax of Q tile 0 / 1 (thread t = row t), in halves of 64 positions;
+//   warp 8            one thread issues every MMA;
+//   warps 9-11        fetch, widen and place the K/V tiles (two buffers each).
+// Twelve warps leave 168 registers a thread, which is why a row is handled 64 columns at a time;
+// per Q tile and K/V tile: S = Q K^T (N = 128, one piece: two N = 64 products measured twice the
+// time) -> softmax of columns 0-63 -> P half a (tensor memory) -> O += P V (K = 64) while the
+// softmax of columns 64-127 runs -> P half b -> O += P V, and right behind that the S of the next
+// K/V tile.  MMAs issued by the one thread execute in issue order, which is what lets the next S be
+// issued behind the P V that reads P from the same tensor-memory columns; with two Q tiles the
+// tensor pipe has the other tile's products to run while one is in its softmax.
+// mbarriers (count): S ready [tile] (1, commit)   P ready [tile][half] (128)   P V done
+// [tile][half] (1, commit)   K / V ready [buffer] (96)   K / V free [buffer] (1, commit).  Each
+// completes once per K/V tile (or once per two), so a wait on a phase parity is never more than
+// one phase away from the barrier's state.
+__host__ __device__ constexpr uint32_t idesc_f16_n(bool b_mn_major, uint32_t n)
+{
+    return (1u << 4) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+}
+
+// 64 columns of this thread's lane, loaded and waited for inside one statement: the compiler may
+// not touch the destination registers before the wait (it knows nothing of the load being
+// asynchronous).
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64])
+{
+    uint32_t r[64];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+                 : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int DT, bool CAP>
+__global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_bar[20];
+    __shared__ uint32_t s_tmem, s_abort;
+    const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - smem_addr(smem_raw));
+    const uint32_t q_sm = base, k_sm = base + 2 * TILE, v_sm = base + 4 * TILE;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t kvh = blockIdx.y, g = p.group;
+    const uint32_t n_rows = p.m * g;
+    const uint32_t row0 = (gridDim.x - 1u - blockIdx.x) * CTA_ROWS;
+    auto bar = [&](uint32_t i) { return smem_addr(&s_bar[i]); };
+    // 0-1 S ready (tile)   4-7 P ready (tile * 2 + half)   8-11 P V done (tile * 2 + half)   12-13 K ready
+    // 14-15 V ready   16-17 K free   18-19 V free
+    if (tid == 0) {
+        for (uint32_t i = 0; i < 4; ++i) mbar_init(bar(i), 1);
+        for (uint32_t i = 4; i < 8; ++i) mbar_init(bar(i), 128);
+        for (uint32_t i = 8; i < 12; ++i) mbar_init(bar(i), 1);
+        for (uint32_t i = 12; i < 16; ++i) mbar_init(bar(i), 96);
+        for (uint32_t i = 16; i < 20; ++i) mbar_init(bar(i), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0u;
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_addr(&s_tmem)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    uint32_t c_lo, c_hi;
+    {
+        const uint32_t qa = row0 / g;
+        uint32_t qb = (row0 + CTA_ROWS - 1) / g;
+        if (qb >= p.m) qb = p.m - 1;
+        uint32_t lo_a, hi_a, lo_b, hi_b;
+        query_range(p, qa, &lo_a, &hi_a);
+        query_range(p, qb, &lo_b, &hi_b);
+        c_lo = lo_a / BN * BN;
+        c_hi = hi_b;
+    }
+    const uint32_t n_tiles = c_hi > c_lo ? (c_hi - c_lo + BN - 1) / BN : 0u;
+
+    // Q tiles -> shared memory (half precision, scale folded in), all threads
+    const float qs = CAP ? p.scale : p.scale * kLog2e;
+    for (uint32_t i = tid; i < uint32_t(CTA_ROWS * 16); i += 384) {
+        const uint32_t row = i >> 4, c = i & 15u;
+        const uint32_t rr = row0 + row;
+        uint4 hv = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < n_rows) {
+            const float *qp = p.q + (uint64_t(rr / g) * p.n_q_heads + kvh * g + rr % g) * HD + 8 * c;
+            const float4 a = *reinterpret_cast<const float4 *>(qp), b = *reinterpret_cast<const float4 *>(qp + 4);
+            hv = make_uint4(pack_half2(a.x * qs, a.y * qs), pack_half2(a.z * qs, a.w * qs),
+                            pack_half2(b.x * qs, b.y * qs), pack_half2(b.z * qs, b.w * qs));
+        }
+        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) = hv;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    volatile uint32_t *abort_flag = &s_abort;
+#define TC5H_TRACE(slot)                                                                           \
+    do {                                                                                           \
+        if (p.trace != nullptr && it == 3u)                                                        \
+            p.trace[(blockIdx.y * gridDim.x + blockIdx.x) * 32 + (slot)] = timer_ns();             \
+    } while (0)
+
+    if (warp < 8) {
+        // ================= softmax warps: thread t of warpgroup wg owns row t of Q tile wg =============
+        const uint32_t wg = warp >> 2, t = tid & 127u;
+        const uint32_t r = row0 + wg * BM + t;
+        const bool r_ok = r < n_rows;
+        const uint32_t q_idx = r_ok ? r / g : 0u, hj = r_ok ? r % g : 0u;
+        uint32_t r_lo, r_hi;
+        query_range(p, q_idx, &r_lo, &r_hi);
+        if (!r_ok) { r_lo = 0u; r_hi = 0u; }
+        const uint32_t t_lane = ((warp & 3u) * 32u) << 16;
+        const uint32_t tm_s = tmem + wg * 128u, tm_o = tmem + 256u + wg * 128u;
+        float mref = kMaskedScore, lrow = 0.f;
+        bool ok = true;
+        for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+            if (tid == 0) TC5H_TRACE(16);
+            if (!mbar_wait(bar(wg), it & 1u)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+            for (uint32_t h = 0; h < 2u; ++h) {
+                const uint32_t t0 = c_lo + it * BN + h * 64u;
+                if (tid == 0) TC5H_TRACE(17 + 4 * h);
+                float s[64];
+                tmem_ld64(tm_s + t_lane + 64u * h, s);
+                const bool full = t0 >= r_lo && t0 + 64u <= r_hi;
+                const bool warp_full = __all_sync(0xffffffffu, full);
+                float mx = kMaskedScore;
+                if (warp_full && !CAP) {
+#pragma unroll
+                    for (int j = 0; j < 64; j += 2) mx = fmaxf(mx, fmaxf(s[j], s[j + 1]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) {
+                        float x = s[j];
+                        if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap) * kLog2e;
+                        if (!full) {
+                            const uint32_t pos = t0 + j;
+                            if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
+                        }
+                        s[j] = x;
+                        mx = fmaxf(mx, x);
+                    }
+                }
+                const bool grow = mx > mref + 8.0f;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float mnew = grow ? mx : mref;
+                    const float alpha = fast_exp2(mref - mnew);
+                    lrow *= alpha;
+                    mref = mnew;
+                    if (it > 0u || h > 0u) {
+                        // O is touched only between P V products: the latest one of this Q tile has to be
+                        // complete -- half b of the tile before, or half a of this tile
+                        if (!mbar_wait(bar(8u + wg * 2u + (h ^ 1u)), (h == 0u ? it - 1u : it) & 1u)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {
+                            float o[32];
+                            tmem_ld32(tm_o + t_lane + 32 * c, o);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) o[j] *= alpha;
+                            tmem_st32(tm_o + t_lane + 32 * c, o);
+                            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // the registers are reused by the next load
+                        }
+                    }
+                }
+                if (tid == 0) TC5H_TRACE(18 + 4 * h);
+                float sum = 0.f;
+                float pk[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float x0 = s[2 * j], x1 = s[2 * j + 1];
+                    float p0 = fast_exp2(x0 - mref), p1 = fast_exp2(x1 - mref);
+                    if (!warp_full) {
+                        p0 = x0 > 0.5f * kMaskedScore ? p0 : 0.f;
+                        p1 = x1 > 0.5f * kMaskedScore ? p1 : 0.f;
+                    }
+                    sum += p0 + p1;
+                    pk[j] = __uint_as_float(pack_half2(p0, p1));   // position 2j in the low half
+                }
+                lrow += sum;
+                tmem_st32(tm_s + t_lane + 64u * h, pk);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(bar(4u + wg * 2u + h));
+                if (tid == 0) TC5H_TRACE(19 + 4 * h);
+            }
+        }
+        if (!ok) *abort_flag = 1u;
+        // the last P V of this Q tile
+        bool ran = n_tiles > 0 && ok;
+        if (ran && !mbar_wait(bar(8u + wg * 2u + 1u), (n_tiles - 1u) & 1u)) { *abort_flag = 1u; ran = false; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const bool failed = *abort_flag != 0u;
+        {
+            const float inv = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
+            float *o = p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                float v[32];
+                if (ran && !failed) {
+                    tmem_ld32(tm_o + t_lane + 32 * c, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                }
+                if (r_ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4 *>(o + 32 * c + j) =
+                            make_float4(inv > 0.f ? v[j] * inv : 0.f, inv > 0.f ? v[j + 1] * inv : 0.f,
+                                        inv > 0.f ? v[j + 2] * inv : 0.f, inv > 0.f ? v[j + 3] * inv : 0.f);
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ================= the MMA thread ================================================================
+        if ((tid & 31u) == 0u && n_tiles > 0u) {
+            bool ok = true;
+            // S of one Q tile in one piece (N = 128): two N = 64 products take twice the time
+            auto issue_s = [&](uint32_t wg, uint32_t b) {
+#pragma unroll
+                for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                    umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
+                             smem_desc(k_sm + b * TILE + o, 16, 1024), idesc_f16(false), ks);
+                }
+                umma_commit(bar(wg));
+            };
+            if (!mbar_wait(bar(12u), 0u)) ok = false;
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                issue_s(0, 0); issue_s(1, 0);
+                umma_commit(bar(16u));
+            }
+            for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+                const uint32_t b = it & 1u;
+                const bool more = it + 1u < n_tiles;
+                // order: P V of half a for both Q tiles, then per Q tile P V of half b and, right behind
+                // it, S of the next K/V tile (the S region is free once both halves of P have been read)
+#pragma unroll 1
+                for (uint32_t c = 0; c < 4u && ok; ++c) {
+                    const uint32_t h = c >> 1, wg = c & 1u;
+                    TC5H_TRACE(3 * c);
+                    if (!mbar_wait(bar(4u + wg * 2u + h), it & 1u)) { ok = false; break; }
+                    TC5H_TRACE(3 * c + 1);
+                    if (c == 0u && !mbar_wait(bar(14u + b), (it >> 1) & 1u)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4u; ++kk)
+                        umma_f16_ts(tmem + 256u + wg * 128u, tmem + wg * 128u + 64u * h + kk * 8u,
+                                    smem_desc(v_sm + b * TILE + (4u * h + kk) * 2048u, SLAB, 1024), idesc_f16(true),
+                                    (it | h | kk) != 0u ? 1u : 0u);
+                    umma_commit(bar(8u + wg * 2u + h));
+                    TC5H_TRACE(3 * c + 2);
+                    if (c == 3u) umma_commit(bar(18u + b));
+                    if (more && h == 1u) {
+                        if (wg == 0u && !mbar_wait(bar(12u + (b ^ 1u)), ((it + 1u) >> 1) & 1u)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        issue_s(wg, b ^ 1u);
+                        if (wg == 1u) umma_commit(bar(16u + (b ^ 1u)));
+                    }
+                    if (c == 3u) TC5H_TRACE(12);
+                }
+            }
+            if (!ok) *abort_flag = 1u;
+        }
+    } else {
+        // ================= K/V tiles: fetch, widen, place (96 threads) =====================================
+        const uint32_t pt = tid - 288u;
+        constexpr uint32_t ES = DT == VFKV_F8 ? 1u : 2u;
+        constexpr uint32_t PIECES = DT == VFKV_F8 ? 1024u : 2048u;          // 16-byte pieces of one K (or V) tile
+        constexpr int NP = DT == VFKV_F8 ? 11 : 11;                          // pieces per thread and pass
+        constexpr int PASSES = DT == VFKV_F8 ? 1 : 2;
+        const uint8_t *kg = p.k + uint64_t(kvh) * HD * ES, *vg = p.v + uint64_t(kvh) * HD * ES;
+        bool ok = true;
+        auto move = [&](const uint8_t *src, uint32_t t0, uint32_t tile_sm, uint32_t free_bar, uint32_t it) {
+            uint8_t *dst = sm + (tile_sm - base);
+#pragma unroll 1
+            for (int pass = 0; pass < PASSES; ++pass) {
+                uint4 raw[NP];
+#pragma unroll
+                for (int i = 0; i < NP; ++i) {
+                    const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
+                    const uint32_t pos = DT == VFKV_F8 ? idx >> 3 : idx >> 4, c = DT == VFKV_F8 ? idx & 7u : idx & 15u;
+                    const bool in = idx < PIECES && t0 + pos < p.n_kv;
+                    const uint64_t off = uint64_t(in ? t0 + pos : 0u) * p.row_bytes + c * 16;
+                    raw[i] = in ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
+                }
+                // the buffer is free once the products of the tile that used it two tiles ago are complete
+                if (pass == 0 && it >= 2u && !mbar_wait(free_bar, ((it >> 1) & 1u) ^ 1u)) ok = false;
+#pragma unroll
+                for (int i = 0; i < NP; ++i) {
+                    const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
+                    if (idx >= PIECES) continue;
+                    if constexpr (DT == VFKV_F8) {
+                        const uint32_t pos = idx >> 3, c16 = idx & 7u;
+                        const uint4 x = raw[i];
+                        __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
+                        __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
+                        __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
+                        __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
+                        *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
+                            make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                       *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                        *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
+                            make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
+                                       *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+                    } else {
+                        *reinterpret_cast<uint4 *>(dst + tile_off(idx >> 4, idx & 15u)) = raw[i];
+                    }
+                }
+            }
+        };
+        for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+            const uint32_t b = it & 1u, t0 = c_lo + it * BN;
+            if (pt == 0) TC5H_TRACE(24);
+            move(kg, t0, k_sm + b * TILE, bar(16u + b), it);
+            if (pt == 0) TC5H_TRACE(25);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(12u + b));
+            move(vg, t0, v_sm + b * TILE, bar(18u + b), it);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(14u + b));
+            if (pt == 0) TC5H_TRACE(26);
+        }
+        if (!ok) *abort_flag = 1u;
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort != 0u && tid == 0) atomicOr(p.status, 1u);
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "n"(TMEM_COLS) : "memory");
+    }
+}
+
 }  // namespace
 
 bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales)
@@ -816,6 +1157,33 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
     }
     const dim3 grid((m * p.group + CTA_ROWS - 1) / CTA_ROWS, n_kv_heads);
     const bool cap = softcap > 0.f;
+    // The specialised form (roles on separate warps) for FP8 caches; vfkv_ctx_set_attn_tuning(ctx, 4, 2)
+    // keeps the pipelined form, (4, 1) the simple one.  F16 caches stay on the pipelined form: their
+    // tiles are twice the bytes, and three warps of plain loads do not bring them in fast enough
+    // (441 against 563 TFLOP/s).
+    if ((ctx->tune_stages == 0 && dtype == VFKV_F8) || ctx->tune_stages == 3) {
+        static bool configured_h[64] = {};
+        if (!configured_h[ctx->device & 63]) {
+            const void *kernels[4] = {reinterpret_cast<const void *>(prefill_tc5h_kernel<VFKV_F8, false>),
+                                      reinterpret_cast<const void *>(prefill_tc5h_kernel<VFKV_F8, true>),
+                                      reinterpret_cast<const void *>(prefill_tc5h_kernel<VFKV_F16, false>),
+                                      reinterpret_cast<const void *>(prefill_tc5h_kernel<VFKV_F16, true>)};
+            for (const void *kn : kernels) {
+                cudaError_t e = cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+                if (e != cudaSuccess) return check_cuda(ctx, e, "cudaFuncSetAttribute(tcgen05 prefill attention)");
+            }
+            configured_h[ctx->device & 63] = true;
+        }
+        if (dtype == VFKV_F8) {
+            if (cap) prefill_tc5h_kernel<VFKV_F8, true><<<grid, 384, kSmemBytes, st>>>(p);
+            else prefill_tc5h_kernel<VFKV_F8, false><<<grid, 384, kSmemBytes, st>>>(p);
+        } else {
+            if (cap) prefill_tc5h_kernel<VFKV_F16, true><<<grid, 384, kSmemBytes, st>>>(p);
+            else prefill_tc5h_kernel<VFKV_F16, false><<<grid, 384, kSmemBytes, st>>>(p);
+        }
+        ctx->launches++;
+        return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
+    }
     if (ctx->tune_stages != 1) {          // the pipelined form; vfkv_ctx_set_attn_tuning(ctx, 4, 1) keeps the simple one
         static bool configured_p[64] = {};
         if (!configured_p[ctx->device & 63]) {
