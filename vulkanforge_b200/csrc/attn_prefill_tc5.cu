@@ -832,9 +832,11 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
     uint8_t *sm = smem_raw + (base - smem_addr(smem_raw));
     const uint32_t q_sm = base, k_sm = base + 2 * TILE, v_sm = base + 4 * TILE;
     const uint32_t tid = threadIdx.x, warp = tid >> 5;
-    const uint32_t kvh = blockIdx.y, g = p.group;
+    // grid = (kv-heads, row blocks): the heaviest row blocks (latest queries) of every kv-head start
+    // first, so the last wave is made of the lightest CTAs
+    const uint32_t kvh = blockIdx.x, g = p.group;
     const uint32_t n_rows = p.m * g;
-    const uint32_t row0 = (gridDim.x - 1u - blockIdx.x) * CTA_ROWS;
+    const uint32_t row0 = (gridDim.y - 1u - blockIdx.y) * CTA_ROWS;
     auto bar = [&](uint32_t i) { return smem_addr(&s_bar[i]); };
     // 0-1 S ready (tile)   4-7 P ready (tile * 2 + half)   8-11 P V done (tile * 2 + half)   12-13 K ready
     // 14-15 V ready   16-17 K free   18-19 V free
@@ -888,7 +890,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
 #define TC5H_TRACE(slot)                                                                           \
     do {                                                                                           \
         if (p.trace != nullptr && it == 3u)                                                        \
-            p.trace[(blockIdx.y * gridDim.x + blockIdx.x) * 32 + (slot)] = timer_ns();             \
+            p.trace[(blockIdx.x * gridDim.y + blockIdx.y) * 32 + (slot)] = timer_ns();             \
     } while (0)
 
     if (warp < 8) {
@@ -1027,10 +1029,24 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
             for (uint32_t it = 0; it < n_tiles && ok; ++it) {
                 const uint32_t b = it & 1u;
                 const bool more = it + 1u < n_tiles;
-                // order: P V of half a for both Q tiles, then per Q tile P V of half b and, right behind
-                // it, S of the next K/V tile (the S region is free once both halves of P have been read)
+                // Order: P V of half a for both Q tiles, P V of half b of tile 0, then -- in one interleaved
+                // stream -- S of the next K/V tile for Q tile 0 and P V of half b of Q tile 1, then S for
+                // Q tile 1.  Consecutive MMAs into the same accumulator follow one another about every
+                // 60 ns, MMAs into different accumulators about every 40 ns (measured), so the two
+                // independent products are issued alternately.  The S region of a Q tile is free once
+                // both halves of its P have been read, i.e. behind its P V of half b in issue order.
+                auto pv_step = [&](uint32_t wg, uint32_t h, uint32_t kk) {
+                    umma_f16_ts(tmem + 256u + wg * 128u, tmem + wg * 128u + 64u * h + kk * 8u,
+                                smem_desc(v_sm + b * TILE + (4u * h + kk) * 2048u, SLAB, 1024), idesc_f16(true),
+                                (it | h | kk) != 0u ? 1u : 0u);
+                };
+                auto s_step = [&](uint32_t wg, uint32_t bb, uint32_t ks) {
+                    const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                    umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
+                             smem_desc(k_sm + bb * TILE + o, 16, 1024), idesc_f16(false), ks);
+                };
 #pragma unroll 1
-                for (uint32_t c = 0; c < 4u && ok; ++c) {
+                for (uint32_t c = 0; c < 3u && ok; ++c) {              // (tile 0, a), (tile 1, a), (tile 0, b)
                     const uint32_t h = c >> 1, wg = c & 1u;
                     TC5H_TRACE(3 * c);
                     if (!mbar_wait(bar(4u + wg * 2u + h), it & 1u)) { ok = false; break; }
@@ -1038,21 +1054,37 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                     if (c == 0u && !mbar_wait(bar(14u + b), (it >> 1) & 1u)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                    for (uint32_t kk = 0; kk < 4u; ++kk)
-                        umma_f16_ts(tmem + 256u + wg * 128u, tmem + wg * 128u + 64u * h + kk * 8u,
-                                    smem_desc(v_sm + b * TILE + (4u * h + kk) * 2048u, SLAB, 1024), idesc_f16(true),
-                                    (it | h | kk) != 0u ? 1u : 0u);
+                    for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(wg, h, kk);
                     umma_commit(bar(8u + wg * 2u + h));
                     TC5H_TRACE(3 * c + 2);
-                    if (c == 3u) umma_commit(bar(18u + b));
-                    if (more && h == 1u) {
-                        if (wg == 0u && !mbar_wait(bar(12u + (b ^ 1u)), ((it + 1u) >> 1) & 1u)) { ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        issue_s(wg, b ^ 1u);
-                        if (wg == 1u) umma_commit(bar(16u + (b ^ 1u)));
-                    }
-                    if (c == 3u) TC5H_TRACE(12);
                 }
+                if (!ok) break;
+                TC5H_TRACE(9);
+                if (!mbar_wait(bar(4u + 2u + 1u), it & 1u)) { ok = false; break; }          // P of (tile 1, b)
+                TC5H_TRACE(10);
+                if (more && !mbar_wait(bar(12u + (b ^ 1u)), ((it + 1u) >> 1) & 1u)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (more) {
+#pragma unroll
+                    for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                        s_step(0, b ^ 1u, ks);
+                        if (ks < 4u) pv_step(1, 1, ks);
+                    }
+                    umma_commit(bar(8u + 2u + 1u));
+                    umma_commit(bar(18u + b));
+                    umma_commit(bar(0u));
+                    TC5H_TRACE(11);
+#pragma unroll
+                    for (uint32_t ks = 0; ks < HD / 16; ++ks) s_step(1, b ^ 1u, ks);
+                    umma_commit(bar(1u));
+                    umma_commit(bar(16u + (b ^ 1u)));
+                } else {
+#pragma unroll
+                    for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(1, 1, kk);
+                    umma_commit(bar(8u + 2u + 1u));
+                    umma_commit(bar(18u + b));
+                }
+                TC5H_TRACE(12);
             }
             if (!ok) *abort_flag = 1u;
         }
@@ -1125,6 +1157,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
     }
 }
 
+
 }  // namespace
 
 bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales)
@@ -1174,12 +1207,13 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             }
             configured_h[ctx->device & 63] = true;
         }
+        const dim3 grid_h(grid.y, grid.x);
         if (dtype == VFKV_F8) {
-            if (cap) prefill_tc5h_kernel<VFKV_F8, true><<<grid, 384, kSmemBytes, st>>>(p);
-            else prefill_tc5h_kernel<VFKV_F8, false><<<grid, 384, kSmemBytes, st>>>(p);
+            if (cap) prefill_tc5h_kernel<VFKV_F8, true><<<grid_h, 384, kSmemBytes, st>>>(p);
+            else prefill_tc5h_kernel<VFKV_F8, false><<<grid_h, 384, kSmemBytes, st>>>(p);
         } else {
-            if (cap) prefill_tc5h_kernel<VFKV_F16, true><<<grid, 384, kSmemBytes, st>>>(p);
-            else prefill_tc5h_kernel<VFKV_F16, false><<<grid, 384, kSmemBytes, st>>>(p);
+            if (cap) prefill_tc5h_kernel<VFKV_F16, true><<<grid_h, 384, kSmemBytes, st>>>(p);
+            else prefill_tc5h_kernel<VFKV_F16, false><<<grid_h, 384, kSmemBytes, st>>>(p);
         }
         ctx->launches++;
         return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
