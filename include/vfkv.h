@@ -489,8 +489,11 @@ int32_t vfkv_stream_synchronize(vfkv_ctx *ctx, void *stream);
  * vfkv_attend_prefill takes its mma.sync kernel where it would take the tcgen05 one. */
 int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
 /* Shape of the tensor-core attention kernel for subsequent calls: warps per CTA x TMA stages per
- * warp; 4x2, 4x3 or 8x3, 0x0 = choose per call (4x2, or 8x3 when the grid has at most one CTA per
- * SM).  The reference has fixed workgroup shapes; this is a measurement knob. */
+ * warp; 4x1, 4x2, 4x3, 8x1 or 8x3, 0x0 = choose per call (4 warps, or 8x3 when the grid has at most
+ * one CTA per SM).  The reference has fixed workgroup shapes; this is a measurement knob.  The
+ * stage count also picks the form of the tcgen05 prefill kernel of vfkv_attend_prefill: 1 the
+ * simple one, 2 the pipelined one, 3 the one with the roles on separate warps, 0 = the last for
+ * FP8 caches and the pipelined one for F16 caches. */
 int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages);
 /* Programmatic dependent launch of the tensor-core attention kernel, the CUDA counterpart of
  * relaxing the full pipeline barrier the reference records between dispatches
