@@ -148,7 +148,19 @@ def test_prefill_attention_shapes(ctx, dtype, hq, hkv, d, m, q_start, kv_start, 
             fwd.run_flash_attn_batch(1, to_dev(q), out2, m, q_start, n_kv, 1, kv_start, slot=1, window=window)
             torch.cuda.synchronize()
             _check(out2.cpu().numpy(), want, dtype)
+        # the three forms of the tcgen05 kernel (1 simple, 2 pipelined, 3 roles on separate warps),
+        # whichever of them the automatic choice takes for this cache type
+        if tc5:
+            ctx.set_attn_impl(2)
+            for stages in (1, 2, 3):
+                ctx.set_attn_tuning(4, stages)
+                out3 = torch.zeros(m, hq, d, device="cuda")
+                fwd.run_flash_attn_batch(1, to_dev(q), out3, m, q_start, n_kv, 1, kv_start, slot=1, window=window)
+                torch.cuda.synchronize()
+                ctx.poll()
+                _check(out3.cpu().numpy(), want, dtype)
     finally:
+        ctx.set_attn_tuning(0, 0)
         ctx.set_attn_impl(0)
         fwd.workspace.destroy()
         cache.destroy()
