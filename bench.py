@@ -519,7 +519,8 @@ def next_rows(ctx, args, peak, tensor_peak):
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) * 1e3 / reps
 
-        us_attn = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 10)
+        time.sleep(1.0)       # let the board's power average settle after the decode workloads
+        us_attn = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 30)
         us_rope = timed(lambda: fwd.rope_kv_write(0, kv[0], kv[1], 512, q_start, freq_base=500000.0), 20)
         # the same launches replayed from a CUDA graph: device time without the host's call overhead
         side = torch.cuda.Stream()
@@ -540,7 +541,7 @@ def next_rows(ctx, args, peak, tensor_peak):
         return {"prefill_attention": {"workload": "2048 queries at positions 14336..16383, FP8 cache, 32/8/128",
                                       "us": us_attn, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
                                       "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None,
-                                      "note": "tcgen05.mma kernel, S and O in tensor memory"},
+                                      "note": "tcgen05.mma kernel (roles on separate warps), S, P and O in tensor memory"},
                 "rope_append": {"workload": "512 tokens x 8 kv-heads x 128, FP8 cache, K rotated", "us": us_rope,
                                 "us_in_graph": us_rope_graph,
                                 "bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak,
