@@ -151,6 +151,7 @@ int32_t vfkv_ctx_destroy(vfkv_ctx *ctx)
     if (!ctx) return VFKV_OK;
     DeviceGuard g(ctx->device);
     cudaFree(ctx->d_status);
+    cudaFree(ctx->d_prefill_scratch);
     prof_clear(ctx);
     delete ctx;
     return VFKV_OK;

@@ -23,6 +23,8 @@
 #include "common.cuh"
 #include "fp8_codec.cuh"
 
+#include <algorithm>
+
 namespace vfkv {
 namespace {
 
@@ -31,6 +33,7 @@ constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int SLAB = 128 * 128;                 // bytes of one [128 rows][64 halves] slab
 constexpr int TILE = 2 * SLAB;                  // a [128][128] half-precision tile
 constexpr int CTA_ROWS = 2 * BM;                // two Q tiles per CTA, one per warpgroup
+constexpr uint32_t kMaxRowBlocks = 512;         // row blocks of 256 rows a launch can spread evenly over the CTAs
 constexpr uint32_t TMEM_COLS = 512;             // S of tile 0 and 1: columns 0..255; O of tile 0 and 1: 256..511
 
 struct Tc5Params {
@@ -42,6 +45,16 @@ struct Tc5Params {
     float scale, softcap;
     uint32_t *status;
     unsigned long long *trace;         // null, or 16 timestamps per warpgroup (phase analysis)
+    // specialised form, work spread evenly over the CTAs (n_cta != 0): the K/V tiles of all
+    // (row block, kv-head) items in launch order form one line of total_tiles tiles, CTA c takes
+    // tiles [c * total / n_cta, (c + 1) * total / n_cta); pieces of items cut by that go to scratch
+    uint32_t n_rb, total_tiles, n_cta;
+    float *scratch;                    // [n_cta][2] pieces of {O [256][128], reference maximum [256], sum [256]}
+    // inline_merge: the CTA that holds the head of a cut item puts it together itself (at most
+    // three more pieces, each the first segment of one of the next CTAs, announced by
+    // flags[cta] = epoch); the launch is cooperative, so the CTAs it waits for are resident
+    uint32_t inline_merge, epoch;
+    uint32_t *flags;
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -160,7 +173,7 @@ __device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t c)
     return (c >> 3) * SLAB + r * 128 + (((c & 7u) ^ (r & 7u)) << 4);
 }
 
-__device__ __forceinline__ void query_range(const Tc5Params &p, uint32_t i, uint32_t *lo, uint32_t *hi)
+__host__ __device__ __forceinline__ void query_range(const Tc5Params &p, uint32_t i, uint32_t *lo, uint32_t *hi)
 {
     uint32_t c = p.q_start + i + 1u;
     if (c > p.n_kv) c = p.n_kv;
@@ -168,6 +181,23 @@ __device__ __forceinline__ void query_range(const Tc5Params &p, uint32_t i, uint
     if (p.window != 0u && c > p.window && c - p.window > l) l = c - p.window;
     if (l > c) l = c;
     *lo = l; *hi = c;
+}
+
+// Row block rb (0 = the latest queries, the most K/V tiles) of any kv-head: its first row, the
+// first position of its first K/V tile and the number of tiles.
+__host__ __device__ __forceinline__ void item_extent(const Tc5Params &p, uint32_t rb, uint32_t *row0, uint32_t *c_lo, uint32_t *n_tiles)
+{
+    const uint32_t r0 = (p.n_rb - 1u - rb) * uint32_t(CTA_ROWS);
+    const uint32_t qa = r0 / p.group;
+    uint32_t qb = (r0 + uint32_t(CTA_ROWS) - 1u) / p.group;
+    if (qb >= p.m) qb = p.m - 1u;
+    uint32_t lo_a, hi_a, lo_b, hi_b;
+    query_range(p, qa, &lo_a, &hi_a);
+    query_range(p, qb, &lo_b, &hi_b);
+    const uint32_t lo = lo_a / uint32_t(BN) * uint32_t(BN);
+    *row0 = r0;
+    *c_lo = lo;
+    *n_tiles = hi_b > lo ? (hi_b - lo + uint32_t(BN) - 1u) / uint32_t(BN) : 0u;
 }
 
 template <int DT, bool CAP>
@@ -822,21 +852,44 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64])
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Bounded wait for a flag that another CTA of this (cooperative) launch sets; false after a second.
+__device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t want)
+{
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v == want) return true;
+        if ((it & 63u) == 63u) {
+            if (t0 == 0) t0 = timer_ns();
+            else if (timer_ns() - t0 > 1000000000ull) return false;
+        }
+    }
+}
+
 template <int DT, bool CAP>
 __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_bar[20];
-    __shared__ uint32_t s_tmem, s_abort;
+    __shared__ uint32_t s_tmem, s_abort, s_seg[7];
+    __shared__ uint32_t s_tj[kMaxRowBlocks], s_cl[kMaxRowBlocks];      // tiles and first position of every row block
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;
     uint8_t *sm = smem_raw + (base - smem_addr(smem_raw));
     const uint32_t q_sm = base, k_sm = base + 2 * TILE, v_sm = base + 4 * TILE;
     const uint32_t tid = threadIdx.x, warp = tid >> 5;
-    // grid = (kv-heads, row blocks): the heaviest row blocks (latest queries) of every kv-head start
-    // first, so the last wave is made of the lightest CTAs
-    const uint32_t kvh = blockIdx.x, g = p.group;
+    // One CTA per item (n_cta == 0): grid = (kv-heads, row blocks), the heaviest row blocks (latest
+    // queries) of every kv-head start first.  Work spread evenly (n_cta != 0): grid = n_cta, this CTA
+    // takes its share of the line of all items' tiles as a sequence of segments, each a run of
+    // K/V tiles of one item; a segment that is a whole item writes the output rows, the first and
+    // the last segment may be pieces of items and go to scratch for prefill_tc5_merge_kernel.
+    const uint32_t g = p.group;
     const uint32_t n_rows = p.m * g;
-    const uint32_t row0 = (gridDim.y - 1u - blockIdx.y) * CTA_ROWS;
+#define TC5H_STAMP(slot)                                                                           \
+    do {                                                                                           \
+        if (p.trace != nullptr && seg_i == 0u)                                                     \
+            p.trace[(blockIdx.x * gridDim.y + blockIdx.y) * 32 + (slot)] = timer_ns();             \
+    } while (0)
     auto bar = [&](uint32_t i) { return smem_addr(&s_bar[i]); };
     // 0-1 S ready (tile)   4-7 P ready (tile * 2 + half)   8-11 P V done (tile * 2 + half)   12-13 K ready
     // 14-15 V ready   16-17 K free   18-19 V free
@@ -854,42 +907,104 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_addr(&s_tmem)), "n"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    uint32_t c_lo, c_hi;
-    {
-        const uint32_t qa = row0 / g;
-        uint32_t qb = (row0 + CTA_ROWS - 1) / g;
-        if (qb >= p.m) qb = p.m - 1;
-        uint32_t lo_a, hi_a, lo_b, hi_b;
-        query_range(p, qa, &lo_a, &hi_a);
-        query_range(p, qb, &lo_b, &hi_b);
-        c_lo = lo_a / BN * BN;
-        c_hi = hi_b;
-    }
-    const uint32_t n_tiles = c_hi > c_lo ? (c_hi - c_lo + BN - 1) / BN : 0u;
-
-    // Q tiles -> shared memory (half precision, scale folded in), all threads
     const float qs = CAP ? p.scale : p.scale * kLog2e;
-    for (uint32_t i = tid; i < uint32_t(CTA_ROWS * 16); i += 384) {
-        const uint32_t row = i >> 4, c = i & 15u;
-        const uint32_t rr = row0 + row;
-        uint4 hv = make_uint4(0u, 0u, 0u, 0u);
-        if (rr < n_rows) {
-            const float *qp = p.q + (uint64_t(rr / g) * p.n_q_heads + kvh * g + rr % g) * HD + 8 * c;
-            const float4 a = *reinterpret_cast<const float4 *>(qp), b = *reinterpret_cast<const float4 *>(qp + 4);
-            hv = make_uint4(pack_half2(a.x * qs, a.y * qs), pack_half2(a.z * qs, a.w * qs),
-                            pack_half2(b.x * qs, b.y * qs), pack_half2(b.z * qs, b.w * qs));
-        }
-        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) = hv;
+    volatile uint32_t *abort_flag = &s_abort;
+    uint32_t cur = 0u, t_end = 0u;                       // this CTA's tiles on the line of all tiles
+    if (p.n_cta != 0u) {
+        cur = uint32_t(uint64_t(blockIdx.x) * p.total_tiles / p.n_cta);
+        t_end = uint32_t(uint64_t(blockIdx.x + 1u) * p.total_tiles / p.n_cta);
     }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    const uint32_t t_begin = cur;
+    if (p.n_cta != 0u) {
+        // one thread walking the row blocks with item_extent (divisions, clamps) costs 0.8 us a row
+        // block; all threads fill a table once, the walk then only adds
+        for (uint32_t rb = tid; rb < p.n_rb; rb += 384u) {
+            uint32_t r0, cl, tj;
+            item_extent(p, rb, &r0, &cl, &tj);
+            s_tj[rb] = tj;
+            s_cl[rb] = cl;
+        }
+        __syncthreads();
+    }
+    // K/V tiles this CTA has been through: every barrier completes once per tile (K/V ready and
+    // free: once per two), so all phase parities follow from this count, across segments
+    uint32_t gt = 0u;
+    uint32_t tmem = 0u;
+    for (uint32_t seg_i = 0u;; ++seg_i) {
+    if (tid == 0) {
+        TC5H_STAMP(13);
+        uint32_t live = 0u, kvh_ = 0u, row0_ = 0u, c_lo_ = 0u, nt_ = 0u, mode_ = 0u, more_ = 0u;
+        if (p.n_cta == 0u) {
+            if (seg_i == 0u) { live = 1u; kvh_ = blockIdx.x; item_extent(p, blockIdx.y, &row0_, &c_lo_, &nt_); }
+        } else if (cur < t_end) {
+            uint32_t acc = 0u;
+            for (uint32_t rb = 0u; rb < p.n_rb; ++rb) {
+                const uint32_t tj = s_tj[rb];
+                const uint32_t blk = tj * p.n_kv_heads;
+                if (cur < acc + blk) {
+                    const uint32_t rel = cur - acc;
+                    kvh_ = rel / tj;
+                    const uint32_t tin = rel - kvh_ * tj;
+                    nt_ = min(tj - tin, t_end - cur);
+                    row0_ = (p.n_rb - 1u - rb) * uint32_t(CTA_ROWS);
+                    c_lo_ = s_cl[rb] + tin * BN;
+                    // 0: a whole item; 1 / 2: a piece of one for the merge kernel, as this CTA's first / a
+                    // later segment; 3: a piece that is not the item's head, for the CTA that holds the
+                    // head; 4: the head, which waits for the more_ pieces of the next CTAs
+                    if (tin == 0u && nt_ == tj) mode_ = 0u;
+                    else if (p.inline_merge == 0u) mode_ = cur == t_begin ? 1u : 2u;
+                    else if (tin != 0u) mode_ = 3u;
+                    else {
+                        mode_ = 4u;
+                        const uint64_t e = uint64_t(acc) + uint64_t(kvh_ + 1u) * tj;
+                        more_ = uint32_t((e * p.n_cta - 1u) / p.total_tiles) - blockIdx.x;
+                    }
+                    live = 1u;
+                    break;
+                }
+                acc += blk;
+            }
+        }
+        s_seg[0] = live; s_seg[1] = kvh_; s_seg[2] = row0_; s_seg[3] = c_lo_; s_seg[4] = nt_; s_seg[5] = mode_; s_seg[6] = more_;
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = s_tmem;
-    volatile uint32_t *abort_flag = &s_abort;
+    tmem = s_tmem;
+    if (s_seg[0] == 0u) break;
+    const uint32_t kvh = s_seg[1], row0 = s_seg[2], c_lo = s_seg[3], n_tiles = s_seg[4], mode = s_seg[5], n_more = s_seg[6];
+
+    // Q tiles -> shared memory (half precision, scale folded in), all threads
+    // by the nine warps that are not fetching K/V (those start on their first tiles meanwhile); five
+    // pieces a thread in flight at a time
+    if (warp < 9u) {
+        constexpr uint32_t QT = 288u, QB = 5u;
+        for (uint32_t i0 = tid; i0 < uint32_t(CTA_ROWS * 16); i0 += QT * QB) {
+            float4 qa[QB], qb[QB];
+#pragma unroll
+            for (uint32_t u = 0; u < QB; ++u) {
+                const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u, rr = row0 + row;
+                const bool in = i < uint32_t(CTA_ROWS * 16) && rr < n_rows;
+                const float *qp = p.q + (uint64_t(in ? rr / g : 0u) * p.n_q_heads + kvh * g + (in ? rr % g : 0u)) * HD + 8 * c;
+                qa[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                qb[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < QB; ++u) {
+                const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u;
+                if (i < uint32_t(CTA_ROWS * 16))
+                    *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) =
+                        make_uint4(pack_half2(qa[u].x * qs, qa[u].y * qs), pack_half2(qa[u].z * qs, qa[u].w * qs),
+                                   pack_half2(qb[u].x * qs, qb[u].y * qs), pack_half2(qb[u].z * qs, qb[u].w * qs));
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("bar.sync 1, 288;" ::: "memory");
+    }
+    if (tid == 0) TC5H_STAMP(14);
 #define TC5H_TRACE(slot)                                                                           \
     do {                                                                                           \
-        if (p.trace != nullptr && it == 3u)                                                        \
+        if (p.trace != nullptr && it == 3u && seg_i == 0u)                                         \
             p.trace[(blockIdx.x * gridDim.y + blockIdx.y) * 32 + (slot)] = timer_ns();             \
     } while (0)
 
@@ -908,7 +1023,9 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
         bool ok = true;
         for (uint32_t it = 0; it < n_tiles && ok; ++it) {
             if (tid == 0) TC5H_TRACE(16);
-            if (!mbar_wait(bar(wg), it & 1u)) { ok = false; break; }
+            const uint32_t gi = gt + it;
+            if (!mbar_wait(bar(wg), gi & 1u)) { ok = false; break; }
+            if (tid == 0 && it == 0u) TC5H_STAMP(15);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (uint32_t h = 0; h < 2u; ++h) {
@@ -944,7 +1061,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                     if (it > 0u || h > 0u) {
                         // O is touched only between P V products: the latest one of this Q tile has to be
                         // complete -- half b of the tile before, or half a of this tile
-                        if (!mbar_wait(bar(8u + wg * 2u + (h ^ 1u)), (h == 0u ? it - 1u : it) & 1u)) { ok = false; break; }
+                        if (!mbar_wait(bar(8u + wg * 2u + (h ^ 1u)), (h == 0u ? gi - 1u : gi) & 1u)) { ok = false; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
                         for (int c = 0; c < 4; ++c) {
@@ -980,16 +1097,68 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
             }
         }
         if (!ok) *abort_flag = 1u;
+        if (tid == 0) TC5H_STAMP(27);
         // the last P V of this Q tile
         bool ran = n_tiles > 0 && ok;
-        if (ran && !mbar_wait(bar(8u + wg * 2u + 1u), (n_tiles - 1u) & 1u)) { *abort_flag = 1u; ran = false; }
+        if (ran && !mbar_wait(bar(8u + wg * 2u + 1u), (gt + n_tiles - 1u) & 1u)) { *abort_flag = 1u; ran = false; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool failed = *abort_flag != 0u;
+        if (tid == 0) TC5H_STAMP(28);
+        // The rows leave through shared memory so that a warp's store covers one row's 512 bytes (a
+        // thread storing its own row writes 32 separate sectors an instruction: 5 us a CTA).  Each
+        // softmax warp stages its 32 rows in its own 16 KB of the Q and K tiles, which no product
+        // reads any more: every S product was issued before, and so completed before, the P V this
+        // thread has just waited for.  16-byte pieces are placed at (piece ^ row) so that neither
+        // the row-wise writes nor the piece-wise reads meet in a bank.
+        float row_scale;
+        float *row_dst;
+        float piece_scale[3] = {0.f, 0.f, 0.f};
+        constexpr uint64_t PIECE = uint64_t(CTA_ROWS) * (HD + 2);
+        if (mode == 4u) {
+            // the head of a cut item: the other pieces were the first work of the next CTAs
+            const uint32_t rl = wg * BM + t;
+            bool got = true;
+            for (uint32_t i = 1u; i <= n_more; ++i) got = flag_wait(p.flags + blockIdx.x + i, p.epoch) && got;
+            if (!got) *abort_flag = 1u;
+            const bool mine_ok = ran && !failed;
+            float mx = mine_ok ? mref : kMaskedScore, pm[3], pl[3];
+#pragma unroll
+            for (uint32_t i = 0; i < 3u; ++i) {
+                const bool on = i < n_more && got;
+                const float *pc = p.scratch + uint64_t(blockIdx.x + 1u + (on ? i : 0u)) * 2u * PIECE;
+                pm[i] = on ? __ldcg(pc + CTA_ROWS * HD + rl) : kMaskedScore;
+                pl[i] = on ? __ldcg(pc + CTA_ROWS * HD + CTA_ROWS + rl) : 0.f;
+                mx = fmaxf(mx, pm[i]);
+            }
+            const float w_own = mine_ok ? fast_exp2(mref - mx) : 0.f;
+            float lsum = w_own * lrow;
+#pragma unroll
+            for (uint32_t i = 0; i < 3u; ++i) {
+                piece_scale[i] = fast_exp2(pm[i] - mx);
+                lsum += piece_scale[i] * pl[i];
+            }
+            const float inv = (lsum > 0.f && got && !failed) ? 1.0f / lsum : 0.f;
+            row_scale = w_own * inv;
+#pragma unroll
+            for (uint32_t i = 0; i < 3u; ++i) piece_scale[i] *= inv;
+            row_dst = r_ok ? p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD : nullptr;
+        } else if (mode != 0u) {
+            // a piece of an item: O as it stands, with the reference maximum (log2 units) and the sum
+            float *sc = p.scratch + (uint64_t(blockIdx.x) * 2u + (mode == 2u ? 1u : 0u)) * PIECE;
+            const uint32_t rl = wg * BM + t;
+            sc[CTA_ROWS * HD + rl] = (ran && !failed) ? mref : kMaskedScore;
+            sc[CTA_ROWS * HD + CTA_ROWS + rl] = (ran && !failed) ? lrow : 0.f;
+            row_scale = 1.0f;
+            row_dst = sc + rl * HD;
+        } else {
+            row_scale = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
+            row_dst = r_ok ? p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD : nullptr;
+        }
         {
-            const float inv = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
-            float *o = p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD;
+            uint8_t *stage = sm + (q_sm - base) + warp * 16384u;
+            const uint32_t lane = tid & 31u;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (uint32_t c = 0; c < 4u; ++c) {
                 float v[32];
                 if (ran && !failed) {
                     tmem_ld32(tm_o + t_lane + 32 * c, v);
@@ -997,14 +1166,31 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0.f;
                 }
-                if (r_ok) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4 *>(o + 32 * c + j) =
-                            make_float4(inv > 0.f ? v[j] * inv : 0.f, inv > 0.f ? v[j + 1] * inv : 0.f,
-                                        inv > 0.f ? v[j + 2] * inv : 0.f, inv > 0.f ? v[j + 3] * inv : 0.f);
-                }
+                for (uint32_t j = 0; j < 8u; ++j)
+                    *reinterpret_cast<float4 *>(stage + lane * 512u + ((((8u * c + j) ^ lane) & 31u) << 4)) =
+                        make_float4(v[4 * j] * row_scale, v[4 * j + 1] * row_scale, v[4 * j + 2] * row_scale, v[4 * j + 3] * row_scale);
             }
+            __syncwarp();
+            const unsigned long long mine = reinterpret_cast<unsigned long long>(row_dst);
+#pragma unroll 4
+            for (uint32_t r = 0; r < 32u; ++r) {
+                const unsigned long long dst = __shfl_sync(0xffffffffu, mine, int(r));
+                float4 x = *reinterpret_cast<const float4 *>(stage + r * 512u + (((lane ^ r) & 31u) << 4));
+                if (mode == 4u) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 3u; ++i) {
+                        const float ps = __shfl_sync(0xffffffffu, piece_scale[i], int(r));
+                        if (i < n_more && dst != 0ull) {
+                            const float4 y = __ldcg(reinterpret_cast<const float4 *>(
+                                p.scratch + uint64_t(blockIdx.x + 1u + i) * 2u * PIECE + (wg * BM + (warp & 3u) * 32u + r) * HD + 4u * lane));
+                            x.x += ps * y.x; x.y += ps * y.y; x.z += ps * y.z; x.w += ps * y.w;
+                        }
+                    }
+                }
+                if (dst != 0ull) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(dst) + 4u * lane) = x;
+            }
+            __syncwarp();
         }
     } else if (warp == 8) {
         // ================= the MMA thread ================================================================
@@ -1020,14 +1206,14 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                 }
                 umma_commit(bar(wg));
             };
-            if (!mbar_wait(bar(12u), 0u)) ok = false;
+            if (!mbar_wait(bar(12u + (gt & 1u)), (gt >> 1) & 1u)) ok = false;
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_s(0, 0); issue_s(1, 0);
-                umma_commit(bar(16u));
+                issue_s(0, gt & 1u); issue_s(1, gt & 1u);
+                umma_commit(bar(16u + (gt & 1u)));
             }
             for (uint32_t it = 0; it < n_tiles && ok; ++it) {
-                const uint32_t b = it & 1u;
+                const uint32_t gi = gt + it, b = gi & 1u;
                 const bool more = it + 1u < n_tiles;
                 // Order: P V of half a for both Q tiles, P V of half b of tile 0, then -- in one interleaved
                 // stream -- S of the next K/V tile for Q tile 0 and P V of half b of Q tile 1, then S for
@@ -1049,9 +1235,9 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                 for (uint32_t c = 0; c < 3u && ok; ++c) {              // (tile 0, a), (tile 1, a), (tile 0, b)
                     const uint32_t h = c >> 1, wg = c & 1u;
                     TC5H_TRACE(3 * c);
-                    if (!mbar_wait(bar(4u + wg * 2u + h), it & 1u)) { ok = false; break; }
+                    if (!mbar_wait(bar(4u + wg * 2u + h), gi & 1u)) { ok = false; break; }
                     TC5H_TRACE(3 * c + 1);
-                    if (c == 0u && !mbar_wait(bar(14u + b), (it >> 1) & 1u)) { ok = false; break; }
+                    if (c == 0u && !mbar_wait(bar(14u + b), (gi >> 1) & 1u)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(wg, h, kk);
@@ -1060,9 +1246,9 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                 }
                 if (!ok) break;
                 TC5H_TRACE(9);
-                if (!mbar_wait(bar(4u + 2u + 1u), it & 1u)) { ok = false; break; }          // P of (tile 1, b)
+                if (!mbar_wait(bar(4u + 2u + 1u), gi & 1u)) { ok = false; break; }          // P of (tile 1, b)
                 TC5H_TRACE(10);
-                if (more && !mbar_wait(bar(12u + (b ^ 1u)), ((it + 1u) >> 1) & 1u)) { ok = false; break; }
+                if (more && !mbar_wait(bar(12u + (b ^ 1u)), ((gi + 1u) >> 1) & 1u)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (more) {
 #pragma unroll
@@ -1097,7 +1283,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
         constexpr int PASSES = DT == VFKV_F8 ? 1 : 2;
         const uint8_t *kg = p.k + uint64_t(kvh) * HD * ES, *vg = p.v + uint64_t(kvh) * HD * ES;
         bool ok = true;
-        auto move = [&](const uint8_t *src, uint32_t t0, uint32_t tile_sm, uint32_t free_bar, uint32_t it) {
+        auto move = [&](const uint8_t *src, uint32_t t0, uint32_t tile_sm, uint32_t free_bar, uint32_t gi) {
             uint8_t *dst = sm + (tile_sm - base);
 #pragma unroll 1
             for (int pass = 0; pass < PASSES; ++pass) {
@@ -1111,7 +1297,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                     raw[i] = in ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
                 }
                 // the buffer is free once the products of the tile that used it two tiles ago are complete
-                if (pass == 0 && it >= 2u && !mbar_wait(free_bar, ((it >> 1) & 1u) ^ 1u)) ok = false;
+                if (pass == 0 && gi >= 2u && !mbar_wait(free_bar, ((gi >> 1) & 1u) ^ 1u)) ok = false;
 #pragma unroll
                 for (int i = 0; i < NP; ++i) {
                     const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
@@ -1136,18 +1322,33 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
             }
         };
         for (uint32_t it = 0; it < n_tiles && ok; ++it) {
-            const uint32_t b = it & 1u, t0 = c_lo + it * BN;
+            const uint32_t gi = gt + it, b = gi & 1u, t0 = c_lo + it * BN;
             if (pt == 0) TC5H_TRACE(24);
-            move(kg, t0, k_sm + b * TILE, bar(16u + b), it);
+            move(kg, t0, k_sm + b * TILE, bar(16u + b), gi);
             if (pt == 0) TC5H_TRACE(25);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(bar(12u + b));
-            move(vg, t0, v_sm + b * TILE, bar(18u + b), it);
+            move(vg, t0, v_sm + b * TILE, bar(18u + b), gi);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(bar(14u + b));
             if (pt == 0) TC5H_TRACE(26);
         }
         if (!ok) *abort_flag = 1u;
+    }
+    // end of the segment: every product of it is complete (the softmax threads waited for the last
+    // P V before they read O), so Q, the tensor memory and the barriers' phases can be taken over
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (tid == 0) TC5H_STAMP(29);
+    if (mode == 3u && tid == 0) {
+        // the piece is in scratch (every thread's stores are ordered before the barrier above)
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p.flags + blockIdx.x), "r"(s_abort != 0u ? 0u : p.epoch) : "memory");
+    }
+    if (s_abort != 0u || p.n_cta == 0u) break;
+    gt += n_tiles;
+    cur += n_tiles;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -1157,6 +1358,62 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
     }
 }
 
+
+
+// Items that the even spread cut into pieces: combine the pieces' O, reference maxima and sums
+// (the split-merge of flash_attn_reduce.comp, per row).  grid = (n_cta - 1 share boundaries, 16
+// sixteenths of the 256 rows): the block of the first boundary inside an item merges it; a warp
+// per row, a lane per four output dims.
+__global__ void __launch_bounds__(256) prefill_tc5_merge_kernel(const Tc5Params p)
+{
+    __shared__ uint32_t s_tj[kMaxRowBlocks];
+    for (uint32_t rb = threadIdx.x; rb < p.n_rb; rb += 256u) {
+        uint32_t r0, cl, tj;
+        item_extent(p, rb, &r0, &cl, &tj);
+        s_tj[rb] = tj;
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.wait;" ::: "memory");     // launched ahead of the end of the attention kernel
+    const uint64_t T = p.total_tiles, n = p.n_cta;
+    const uint32_t cut = uint32_t(uint64_t(blockIdx.x + 1u) * T / n);      // first tile of CTA blockIdx.x + 1
+    uint32_t acc = 0u, rb = 0u, tj = 0u;
+    for (; rb < p.n_rb; ++rb) {
+        tj = s_tj[rb];
+        if (cut < acc + tj * p.n_kv_heads) break;
+        acc += tj * p.n_kv_heads;
+    }
+    if (rb == p.n_rb) return;
+    const uint32_t kvh = (cut - acc) / tj;
+    const uint32_t s = acc + kvh * tj, e = s + tj;
+    if (cut == s) return;                                                   // the share ends where the item does
+    const uint32_t c_first = uint32_t((uint64_t(s + 1u) * n - 1u) / T), c_last = uint32_t((uint64_t(e) * n - 1u) / T);
+    if (c_first != blockIdx.x) return;                                      // an earlier boundary lies inside this item too
+    const uint32_t g = p.group, n_rows = p.m * g, row0 = (p.n_rb - 1u - rb) * uint32_t(CTA_ROWS);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    constexpr uint64_t PIECE = uint64_t(CTA_ROWS) * (HD + 2);
+    for (uint32_t rl = blockIdx.y * 16u + warp; rl < blockIdx.y * 16u + 16u; rl += 8u) {
+        const uint32_t r = row0 + rl;
+        if (r >= n_rows) break;
+        float mx = kMaskedScore;
+        for (uint32_t c = c_first; c <= c_last; ++c) {
+            const uint32_t slot = uint32_t(uint64_t(c) * T / n) >= s ? 0u : 1u;
+            mx = fmaxf(mx, p.scratch[(uint64_t(c) * 2u + slot) * PIECE + CTA_ROWS * HD + rl]);
+        }
+        float l = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t c = c_first; c <= c_last; ++c) {
+            const uint32_t slot = uint32_t(uint64_t(c) * T / n) >= s ? 0u : 1u;
+            const float *pc = p.scratch + (uint64_t(c) * 2u + slot) * PIECE;
+            const float w = fast_exp2(pc[CTA_ROWS * HD + rl] - mx);
+            l += w * pc[CTA_ROWS * HD + CTA_ROWS + rl];
+            const float4 x = *reinterpret_cast<const float4 *>(pc + rl * HD + 4u * lane);
+            o.x += w * x.x; o.y += w * x.y; o.z += w * x.z; o.w += w * x.w;
+        }
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        float *out = p.out + (uint64_t(r / g) * p.n_q_heads + kvh * g + r % g) * HD + 4u * lane;
+        *reinterpret_cast<float4 *>(out) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+    }
+}
 
 }  // namespace
 
@@ -1207,15 +1464,107 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             }
             configured_h[ctx->device & 63] = true;
         }
-        const dim3 grid_h(grid.y, grid.x);
-        if (dtype == VFKV_F8) {
-            if (cap) prefill_tc5h_kernel<VFKV_F8, true><<<grid_h, 384, kSmemBytes, st>>>(p);
-            else prefill_tc5h_kernel<VFKV_F8, false><<<grid_h, 384, kSmemBytes, st>>>(p);
-        } else {
-            if (cap) prefill_tc5h_kernel<VFKV_F16, true><<<grid_h, 384, kSmemBytes, st>>>(p);
-            else prefill_tc5h_kernel<VFKV_F16, false><<<grid_h, 384, kSmemBytes, st>>>(p);
+        dim3 grid_h(grid.y, grid.x);
+        p.n_rb = grid.x;
+        // One CTA per (kv-head, row block) item leaves the last wave part empty (256 items on 148 SMs:
+        // the time of two items for 1.73 items' worth of SM time).  When that loses more than a
+        // twentieth and the items are long, one CTA per SM takes an even share of all K/V tiles
+        // instead; items cut by the shares are put together by prefill_tc5_merge_kernel.  Needs
+        // every query to see at least one position, 39 MB of scratch that the context allocates at
+        // the first such call (not inside a stream capture), and tuning 0x0 or 8x3; 4x3 keeps one
+        // CTA per item.
+        bool spread = false;
+        if (ctx->tune_warps != 4 && p.n_rb <= kMaxRowBlocks && kv_start < std::min(q_start + 1u, n_kv)) {
+            const uint32_t n_sm = uint32_t(ctx->sm_count);
+            uint64_t total = 0;
+            for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
+                uint32_t r0, cl, tj;
+                item_extent(p, rb, &r0, &cl, &tj);
+                total += uint64_t(tj) * n_kv_heads;
+            }
+            uint32_t tj_max = 0;
+            for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
+                uint32_t r0, cl, tj;
+                item_extent(p, rb, &r0, &cl, &tj);
+                tj_max = std::max(tj_max, tj);
+            }
+            const uint64_t items = uint64_t(p.n_rb) * n_kv_heads, waves = (items + n_sm - 1) / n_sm;
+            // (measured: 2048 queries at 14 336, 256 items of ~120 tiles: 717 -> 672 us; 4096 queries at
+            // 4096, 512 items of ~48: 584 -> 599 us, the shares' segments and the merge cost more
+            // than the last wave loses)
+            const bool worth = ctx->tune_warps == 8 || (items * 20 < waves * n_sm * 19 && total >= items * 96);
+            if (worth && n_sm >= 2 && total >= uint64_t(n_sm) * 8 && total < (1ull << 31)) {
+                if (ctx->d_prefill_scratch == nullptr) {
+                    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+                    cudaStreamIsCapturing(st, &cs);
+                    if (cs == cudaStreamCaptureStatusNone) {
+                        const size_t bytes = size_t(n_sm) * 2 * CTA_ROWS * (HD + 2) * sizeof(float);
+                        void *d = nullptr;
+                        // the pieces, then one flag per CTA
+                        if (cudaMalloc(&d, bytes + n_sm * sizeof(uint32_t)) == cudaSuccess &&
+                            cudaMemset(static_cast<uint8_t *>(d) + bytes, 0, n_sm * sizeof(uint32_t)) == cudaSuccess) {
+                            ctx->d_prefill_scratch = static_cast<float *>(d);
+                            ctx->prefill_scratch_ctas = n_sm;
+                        } else {
+                            (void)cudaGetLastError();      // no room: one CTA per item
+                        }
+                    }
+                }
+                if (ctx->d_prefill_scratch != nullptr && ctx->prefill_scratch_ctas >= n_sm) {
+                    spread = true;
+                    p.total_tiles = uint32_t(total);
+                    p.n_cta = n_sm;
+                    p.scratch = ctx->d_prefill_scratch;
+                    p.flags = reinterpret_cast<uint32_t *>(p.scratch + size_t(n_sm) * 2 * CTA_ROWS * (HD + 2));
+                    // an item is cut into at most ceil(longest item / smallest share) + 1 pieces
+                    const uint64_t share = total / n_sm;
+                    p.inline_merge = (tj_max + share - 1) / share <= 3 ? 1u : 0u;
+                    grid_h = dim3(n_sm, 1, 1);
+                }
+            }
         }
+        void (*kern)(const Tc5Params) = dtype == VFKV_F8 ? (cap ? prefill_tc5h_kernel<VFKV_F8, true> : prefill_tc5h_kernel<VFKV_F8, false>)
+                                                         : (cap ? prefill_tc5h_kernel<VFKV_F16, true> : prefill_tc5h_kernel<VFKV_F16, false>);
+        if (spread && p.inline_merge != 0u) {
+            // CTAs of this launch wait for one another's pieces: a cooperative launch, which the
+            // driver accepts only if the whole grid is resident at once
+            if (++ctx->prefill_epoch == 0u) ++ctx->prefill_epoch;
+            p.epoch = ctx->prefill_epoch;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = grid_h;
+            cfg.blockDim = dim3(384);
+            cfg.dynamicSmemBytes = kSmemBytes;
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeCooperative;
+            attr[0].val.cooperative = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess) {
+                ctx->launches++;
+                return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
+            }
+            (void)cudaGetLastError();          // not all resident: the pieces go to the merge kernel instead
+            p.inline_merge = 0u;
+        }
+        kern<<<grid_h, 384, kSmemBytes, st>>>(p);
         ctx->launches++;
+        if (spread) {
+            // launched as a programmatic dependent: it is resident, its table built, when the last CTA
+            // of the attention kernel ends
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(p.n_cta - 1, 16);
+            cfg.blockDim = dim3(256);
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t e = cudaLaunchKernelEx(&cfg, prefill_tc5_merge_kernel, p);
+            if (e != cudaSuccess) return check_cuda(ctx, e, "tcgen05 prefill merge launch");
+            ctx->launches++;
+        }
         return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
     }
     if (ctx->tune_stages != 1) {          // the pipelined form; vfkv_ctx_set_attn_tuning(ctx, 4, 1) keeps the simple one

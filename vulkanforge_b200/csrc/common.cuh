@@ -19,6 +19,9 @@ struct vfkv_ctx {
     uint32_t *d_status = nullptr;      // device word written by bounded waits that give up
     uint32_t attn_impl = 0;            // 0 auto, 1 CUDA-core only, 2 tensor-core only, 3 as 0 but mma.sync instead of tcgen05 (prefill)
     uint32_t tune_warps = 0, tune_stages = 0;   // tensor-core kernel shape, 0 = choose
+    float *d_prefill_scratch = nullptr;         // pieces of prefill items cut between CTAs; allocated at first use
+    uint32_t prefill_scratch_ctas = 0;
+    uint32_t prefill_epoch = 0;                 // value the flags of the current spread prefill launch take
     uint32_t pdl = 0;                  // programmatic dependent launch mode of the attention kernel (0 / 1 / 2)
     // Layer slab (K base address) that the last launch on this context wrote cache rows into, or
     // null: a mode-2 launch that reads the same slab next waits before its K/V prefetch (mode 1).
