@@ -197,6 +197,107 @@ def test_prefill_large_chunk_takes_tcgen05_and_matches_mma(ctx):
         cache.destroy()
 
 
+@pytest.mark.parametrize("dtype,m,q_start,kv_start,window,softcap,tune", [
+    ("F8", 640, 3000, 0, 0, 0.0, (8, 3)),        # 80 items of ~27 tiles in 148 shares: heads merge in the kernel
+    ("F8", 1000, 3000, 100, 0, 0.0, (8, 3)),     # kv_start, ragged last row block
+    ("F8", 1024, 5000, 0, 2048, 0.0, (8, 3)),    # per-query window: items start late
+    ("F8", 640, 3000, 0, 0, 30.0, (8, 3)),       # soft-cap
+    ("F8", 64, 20000, 0, 0, 0.0, (0, 0)),        # 8 items of 157 tiles: taken automatically, ~20 pieces an item -> merge kernel
+    ("F16", 64, 20000, 0, 0, 0.0, (0, 0)),       # so few items that F16 rows take the specialised form too
+    ("F16", 640, 3000, 0, 0, 0.0, (8, 3)),
+])
+def test_prefill_even_shares_of_tiles(ctx, dtype, m, q_start, kv_start, window, softcap, tune):
+    """The specialised tcgen05 form with one CTA per SM and an even share of all K/V tiles each:
+    items cut between CTAs are put together by the CTA holding the head, or by the merge kernel.
+    Compared everywhere with the one-CTA-per-item form and the mma.sync kernel, and with the
+    oracle on sampled queries; launches counted to see which path ran."""
+    import torch
+    hq, hkv, d = 32, 8, 128
+    L = q_start + m
+    rng = np.random.default_rng(m + q_start + window)
+    frac = 0.01 if dtype == "F8" else 0.0
+    k, v = kv_values(rng, (L, hkv, d), frac), kv_values(rng, (L, hkv, d), frac)
+    q = rng.standard_normal((m, hq, d), dtype=np.float32)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype[dtype])
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, softcap=softcap)
+    try:
+        _fill(fwd, k, v)
+        outs, launches = {}, {}
+        for name, impl, tn in (("shares", 2, tune), ("per_item", 2, (4, 3)), ("mma", 3, (0, 0))):
+            ctx.set_attn_impl(impl)
+            ctx.set_attn_tuning(*tn)
+            out = torch.full((m, hq, d), float("nan"), device="cuda")
+            before = ctx.launch_count()
+            for _ in range(2):          # twice: the second launch finds the flags of the first
+                fwd.run_flash_attn_batch(0, to_dev(q), out, m, q_start, L, 0, kv_start, window=window)
+            torch.cuda.synchronize()
+            ctx.poll()
+            launches[name] = (ctx.launch_count() - before) // 2
+            outs[name] = out.cpu().numpy()
+            assert np.isfinite(outs[name]).all()
+        assert launches["per_item"] == 1
+        many_pieces = m == 64
+        assert launches["shares"] == (2 if many_pieces else 1)      # the attention kernel (+ the merge kernel)
+        # row by row against the one-CTA-per-item form: both round P to half precision, against
+        # different reference maxima, so they differ by ~2^-11 of a row's largest value
+        diff = np.max(np.abs(outs["shares"] - outs["per_item"]), axis=-1)
+        assert float(np.max(diff / np.maximum(np.max(np.abs(outs["per_item"]), axis=-1), 1e-3))) < 4e-3
+        assert rel_err(outs["shares"], outs["mma"]) < 5e-3
+        kc, vc = encode_cache(k, ODT[dtype]), encode_cache(v, ODT[dtype])
+        for i in (0, 1, 63, m // 2, m - 1):
+            causal = q_start + i + 1
+            lo = max(kv_start, causal - window) if window and causal > window else kv_start
+            want = oracle.attention_ref(q[i], kc, vc, ODT[dtype], hq, hkv, d, causal, kv_start=lo, softcap=softcap)
+            if dtype == "F8":
+                assert rel_err(outs["shares"][i], want) < 3e-2
+            else:
+                assert float(np.max(np.abs(outs["shares"][i] - want))) < 2e-3
+    finally:
+        ctx.set_attn_tuning(0, 0)
+        ctx.set_attn_impl(0)
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+def test_prefill_even_shares_captured_in_a_graph(ctx):
+    """Inside a stream capture the cut items go through the merge kernel (a replay would find the
+    flag values of the replay before); the graph replays to the same result as a direct call."""
+    import torch
+    hq, hkv, d, m, q_start = 32, 8, 128, 640, 3000
+    L = q_start + m
+    rng = np.random.default_rng(5)
+    k, v = kv_values(rng, (L, hkv, d), 0.01), kv_values(rng, (L, hkv, d), 0.01)
+    q = to_dev(rng.standard_normal((m, hq, d), dtype=np.float32))
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    stream = torch.cuda.Stream()
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq, stream=stream.cuda_stream)
+    try:
+        ctx.set_attn_impl(2)
+        ctx.set_attn_tuning(8, 3)
+        with torch.cuda.stream(stream):
+            _fill(fwd, k, v)
+            direct = torch.zeros(m, hq, d, device="cuda")
+            fwd.run_flash_attn_batch(0, q, direct, m, q_start, L, 0, 0)     # allocates the scratch
+            stream.synchronize()
+            out = torch.zeros(m, hq, d, device="cuda")
+            graph = torch.cuda.CUDAGraph()
+            before = ctx.launch_count()
+            with torch.cuda.graph(graph, stream=stream):
+                fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0)
+            assert ctx.launch_count() - before == 2
+            for _ in range(3):
+                out.fill_(float("nan"))
+                graph.replay()
+                stream.synchronize()
+                assert float(((out - direct).abs().amax(-1) / direct.abs().amax(-1).clamp_min(1e-3)).max()) < 4e-3
+        ctx.poll()
+    finally:
+        ctx.set_attn_tuning(0, 0)
+        ctx.set_attn_impl(0)
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
 def test_prefill_then_decode_agree(ctx):
     """The last query of a prefill chunk and a decode step at the same position see the same
     cache: their outputs agree (the force_per_token_prefill bisect of executor/attention.rs:2207-2213)."""

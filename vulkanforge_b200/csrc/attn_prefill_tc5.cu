@@ -1447,11 +1447,69 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
     }
     const dim3 grid((m * p.group + CTA_ROWS - 1) / CTA_ROWS, n_kv_heads);
     const bool cap = softcap > 0.f;
+    // One CTA per (kv-head, row block) item leaves the last wave part empty (256 items on 148 SMs:
+    // the time of two items for 1.73 items' worth of SM time) and, with few items, most SMs (a chunk
+    // of 64 queries x 8 kv-heads is 8 items, however long the context).  When that loses more than
+    // a twentieth and the items are long, the specialised form runs one CTA per SM, each taking an
+    // even share of all K/V tiles; the pieces of items cut by the shares are put together by the
+    // CTA that holds the item's head (up to four pieces an item) or by prefill_tc5_merge_kernel.
+    // Needs every query to see at least one position, 39 MB of scratch that the context allocates
+    // at the first such call (not inside a stream capture), and tuning 0x0 or 8x3; 4x3 keeps one
+    // CTA per item.  Measured: 2048 queries at 14 336 (256 items of ~120 tiles) 706 -> 658 us;
+    // 256 queries at 60 000 (8 items) 1356 -> 342 us; 4096 queries at 4096 (512 items of ~48
+    // tiles) 579 -> 584 us, hence the floor of 96 tiles an item.
+    p.n_rb = grid.x;
+    const uint32_t n_sm = uint32_t(ctx->sm_count);
+    const uint64_t items = uint64_t(p.n_rb) * n_kv_heads;
+    bool spread = false;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if ((ctx->tune_stages == 0 || ctx->tune_stages == 3) && ctx->tune_warps != 4 && p.n_rb <= kMaxRowBlocks &&
+        kv_start < std::min(q_start + 1u, n_kv)) {
+        uint64_t total = 0;
+        uint32_t tj_max = 0;
+        for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
+            uint32_t r0, cl, tj;
+            item_extent(p, rb, &r0, &cl, &tj);
+            total += uint64_t(tj) * n_kv_heads;
+            tj_max = std::max(tj_max, tj);
+        }
+        const uint64_t waves = (items + n_sm - 1) / n_sm;
+        const bool worth = ctx->tune_warps == 8 || (items * 20 < waves * n_sm * 19 && total >= items * 96);
+        if (worth && n_sm >= 2 && total >= uint64_t(n_sm) * 8 && total < (1ull << 31)) {
+            cudaStreamIsCapturing(st, &capturing);
+            if (ctx->d_prefill_scratch == nullptr && capturing == cudaStreamCaptureStatusNone) {
+                const size_t bytes = size_t(n_sm) * 2 * CTA_ROWS * (HD + 2) * sizeof(float);
+                void *d = nullptr;
+                // the pieces, then one flag per CTA
+                if (cudaMalloc(&d, bytes + n_sm * sizeof(uint32_t)) == cudaSuccess &&
+                    cudaMemset(static_cast<uint8_t *>(d) + bytes, 0, n_sm * sizeof(uint32_t)) == cudaSuccess) {
+                    ctx->d_prefill_scratch = static_cast<float *>(d);
+                    ctx->prefill_scratch_ctas = n_sm;
+                } else {
+                    (void)cudaGetLastError();      // no room: one CTA per item
+                }
+            }
+            if (ctx->d_prefill_scratch != nullptr && ctx->prefill_scratch_ctas >= n_sm) {
+                spread = true;
+                p.total_tiles = uint32_t(total);
+                p.n_cta = n_sm;
+                p.scratch = ctx->d_prefill_scratch;
+                p.flags = reinterpret_cast<uint32_t *>(p.scratch + size_t(n_sm) * 2 * CTA_ROWS * (HD + 2));
+                // An item is cut into at most ceil(longest item / smallest share) + 1 pieces.  A
+                // captured launch would replay with the flag value of the capture, which the flags
+                // still hold from the replay before: those go through the merge kernel.
+                const uint64_t share = total / n_sm;
+                p.inline_merge = ((tj_max + share - 1) / share <= 3 && capturing == cudaStreamCaptureStatusNone) ? 1u : 0u;
+            }
+        }
+    }
     // The specialised form (roles on separate warps) for FP8 caches; vfkv_ctx_set_attn_tuning(ctx, 4, 2)
     // keeps the pipelined form, (4, 1) the simple one.  F16 caches stay on the pipelined form: their
     // tiles are twice the bytes, and three warps of plain loads do not bring them in fast enough
-    // (441 against 563 TFLOP/s).
-    if ((ctx->tune_stages == 0 && dtype == VFKV_F8) || ctx->tune_stages == 3) {
+    // (441 against 563 TFLOP/s) -- unless the items are so few that the pipelined form, one CTA an
+    // item, would leave half the SMs idle.
+    const bool f16_few = dtype == VFKV_F16 && spread && items * 2 <= n_sm;
+    if ((ctx->tune_stages == 0 && (dtype == VFKV_F8 || f16_few)) || ctx->tune_stages == 3) {
         static bool configured_h[64] = {};
         if (!configured_h[ctx->device & 63]) {
             const void *kernels[4] = {reinterpret_cast<const void *>(prefill_tc5h_kernel<VFKV_F8, false>),
@@ -1464,65 +1522,7 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             }
             configured_h[ctx->device & 63] = true;
         }
-        dim3 grid_h(grid.y, grid.x);
-        p.n_rb = grid.x;
-        // One CTA per (kv-head, row block) item leaves the last wave part empty (256 items on 148 SMs:
-        // the time of two items for 1.73 items' worth of SM time).  When that loses more than a
-        // twentieth and the items are long, one CTA per SM takes an even share of all K/V tiles
-        // instead; items cut by the shares are put together by prefill_tc5_merge_kernel.  Needs
-        // every query to see at least one position, 39 MB of scratch that the context allocates at
-        // the first such call (not inside a stream capture), and tuning 0x0 or 8x3; 4x3 keeps one
-        // CTA per item.
-        bool spread = false;
-        if (ctx->tune_warps != 4 && p.n_rb <= kMaxRowBlocks && kv_start < std::min(q_start + 1u, n_kv)) {
-            const uint32_t n_sm = uint32_t(ctx->sm_count);
-            uint64_t total = 0;
-            for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
-                uint32_t r0, cl, tj;
-                item_extent(p, rb, &r0, &cl, &tj);
-                total += uint64_t(tj) * n_kv_heads;
-            }
-            uint32_t tj_max = 0;
-            for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
-                uint32_t r0, cl, tj;
-                item_extent(p, rb, &r0, &cl, &tj);
-                tj_max = std::max(tj_max, tj);
-            }
-            const uint64_t items = uint64_t(p.n_rb) * n_kv_heads, waves = (items + n_sm - 1) / n_sm;
-            // (measured: 2048 queries at 14 336, 256 items of ~120 tiles: 717 -> 672 us; 4096 queries at
-            // 4096, 512 items of ~48: 584 -> 599 us, the shares' segments and the merge cost more
-            // than the last wave loses)
-            const bool worth = ctx->tune_warps == 8 || (items * 20 < waves * n_sm * 19 && total >= items * 96);
-            if (worth && n_sm >= 2 && total >= uint64_t(n_sm) * 8 && total < (1ull << 31)) {
-                if (ctx->d_prefill_scratch == nullptr) {
-                    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-                    cudaStreamIsCapturing(st, &cs);
-                    if (cs == cudaStreamCaptureStatusNone) {
-                        const size_t bytes = size_t(n_sm) * 2 * CTA_ROWS * (HD + 2) * sizeof(float);
-                        void *d = nullptr;
-                        // the pieces, then one flag per CTA
-                        if (cudaMalloc(&d, bytes + n_sm * sizeof(uint32_t)) == cudaSuccess &&
-                            cudaMemset(static_cast<uint8_t *>(d) + bytes, 0, n_sm * sizeof(uint32_t)) == cudaSuccess) {
-                            ctx->d_prefill_scratch = static_cast<float *>(d);
-                            ctx->prefill_scratch_ctas = n_sm;
-                        } else {
-                            (void)cudaGetLastError();      // no room: one CTA per item
-                        }
-                    }
-                }
-                if (ctx->d_prefill_scratch != nullptr && ctx->prefill_scratch_ctas >= n_sm) {
-                    spread = true;
-                    p.total_tiles = uint32_t(total);
-                    p.n_cta = n_sm;
-                    p.scratch = ctx->d_prefill_scratch;
-                    p.flags = reinterpret_cast<uint32_t *>(p.scratch + size_t(n_sm) * 2 * CTA_ROWS * (HD + 2));
-                    // an item is cut into at most ceil(longest item / smallest share) + 1 pieces
-                    const uint64_t share = total / n_sm;
-                    p.inline_merge = (tj_max + share - 1) / share <= 3 ? 1u : 0u;
-                    grid_h = dim3(n_sm, 1, 1);
-                }
-            }
-        }
+        const dim3 grid_h = spread ? dim3(n_sm, 1, 1) : dim3(grid.y, grid.x);
         void (*kern)(const Tc5Params) = dtype == VFKV_F8 ? (cap ? prefill_tc5h_kernel<VFKV_F8, true> : prefill_tc5h_kernel<VFKV_F8, false>)
                                                          : (cap ? prefill_tc5h_kernel<VFKV_F16, true> : prefill_tc5h_kernel<VFKV_F16, false>);
         if (spread && p.inline_merge != 0u) {
