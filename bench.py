@@ -535,18 +535,51 @@ def next_rows(ctx, args, peak, tensor_peak):
         fwd.stream = None
         us_rope_graph = timed(graph.replay, 5) / 20
         flops = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2)              # causal: query i sees q_start + i + 1 rows
+        few = prefill_few_items(ctx, tensor_peak, timed)
         rope_bytes = 2 * 512 * hkv * d * (4 + 1)                             # f32 in, one byte out, K and V
         tf = flops / (us_attn * 1e-6) / 1e12
         gbs = rope_bytes / (us_rope_graph * 1e-6) / 1e9                      # device time: the graph replay
         return {"prefill_attention": {"workload": "2048 queries at positions 14336..16383, FP8 cache, 32/8/128",
                                       "us": us_attn, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
                                       "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None,
-                                      "note": "tcgen05.mma kernel (roles on separate warps), S, P and O in tensor memory"},
+                                      "note": "tcgen05.mma kernel (roles on separate warps, one CTA per SM with an even "
+                                              "share of all K/V tiles), S, P and O in tensor memory"},
+                "prefill_attention_few_items": few,
                 "rope_append": {"workload": "512 tokens x 8 kv-heads x 128, FP8 cache, K rotated", "us": us_rope,
                                 "us_in_graph": us_rope_graph,
                                 "bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak,
                                 "note": "5 MiB per launch: launch latency, not bandwidth, sets the time; "
                                         "us = one library call per launch from Python, us_in_graph = graph replay"}}
+    finally:
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
+def prefill_few_items(ctx, tensor_peak, timed):
+    """A short chunk late in a long context: 256 queries at position 60 000 are 8 (kv-head, row
+    block) items, which one CTA per item would run on 8 SMs; the even shares use all of them."""
+    import torch
+    import vulkanforge_b200 as vf
+    hq, hkv, d, m, q_start = 32, 8, 128, 256, 60000
+    L = q_start + m
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        g = torch.Generator(device="cuda").manual_seed(6)
+        for p in range(0, L, 4096):
+            n = min(4096, L - p)
+            kv = torch.randn(2, n, hkv * d, device="cuda", generator=g)
+            fwd.b_step_kv_write(0, kv[0], kv[1], n, p, 0)
+        q = torch.randn(m, hq, d, device="cuda", generator=g)
+        out = torch.zeros(m, hq, d, device="cuda")
+        us = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 20)
+        ctx.set_attn_tuning(4, 3)                       # shares off: the automatic choice is then the 64-row mma.sync kernel
+        us_per_item = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 5)
+        ctx.set_attn_tuning(0, 0)
+        tf = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2) / (us * 1e-6) / 1e12
+        return {"workload": "256 queries at positions 60000..60255, FP8 cache, 32/8/128", "us": us,
+                "us_without_even_shares": us_per_item, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
+                "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None}
     finally:
         fwd.workspace.destroy()
         cache.destroy()

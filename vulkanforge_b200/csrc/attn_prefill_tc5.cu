@@ -1309,6 +1309,9 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                         __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
                         __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
                         __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
+                        // (storing even pieces from four threads of a row and odd pieces from the other four,
+                        // which takes the two-way bank conflict out of these stores, measured 5 % slower
+                        // at contexts of 30 000 and more, and the same below)
                         *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
                             make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
                                        *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
@@ -1415,11 +1418,47 @@ __global__ void __launch_bounds__(256) prefill_tc5_merge_kernel(const Tc5Params 
     }
 }
 
+// Whether the even shares are allowed for this call and expected to pay; the sum of all items'
+// tiles and the longest item on the way.  p.n_rb is set.
+bool spread_pays(const vfkv_ctx *ctx, const Tc5Params &p, uint64_t *total_out, uint32_t *tj_max_out)
+{
+    if (!(ctx->tune_stages == 0 || ctx->tune_stages == 3) || ctx->tune_warps == 4 || p.n_rb > kMaxRowBlocks ||
+        p.kv_start >= std::min(p.q_start + 1u, p.n_kv))
+        return false;
+    const uint32_t n_sm = uint32_t(ctx->sm_count);
+    const uint64_t items = uint64_t(p.n_rb) * p.n_kv_heads;
+    uint64_t total = 0;
+    uint32_t tj_max = 0;
+    for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
+        uint32_t r0, cl, tj;
+        item_extent(p, rb, &r0, &cl, &tj);
+        total += uint64_t(tj) * p.n_kv_heads;
+        tj_max = std::max(tj_max, tj);
+    }
+    *total_out = total;
+    *tj_max_out = tj_max;
+    const uint64_t waves = (items + n_sm - 1) / n_sm;
+    const bool worth = ctx->tune_warps == 8 || (items * 20 < waves * n_sm * 19 && total >= items * 96);
+    return worth && n_sm >= 2 && total >= uint64_t(n_sm) * 8 && total < (1ull << 31);
+}
+
 }  // namespace
 
 bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales)
 {
     return (dtype == VFKV_F8 || dtype == VFKV_F16) && head_dim == 128 && !has_scales && group != 0 && BM % group == 0;
+}
+
+bool prefill_tc5_spreads(const vfkv_ctx *ctx, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
+                         uint32_t n_kv, uint32_t kv_start, uint32_t window)
+{
+    Tc5Params p{};
+    p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
+    p.m = m; p.q_start = q_start; p.n_kv = n_kv; p.kv_start = kv_start; p.window = window;
+    p.n_rb = (m * p.group + CTA_ROWS - 1) / CTA_ROWS;
+    uint64_t total = 0;
+    uint32_t tj_max = 0;
+    return spread_pays(ctx, p, &total, &tj_max);
 }
 
 int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, const uint8_t *v, const float *q, float *out,
@@ -1463,19 +1502,10 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
     const uint64_t items = uint64_t(p.n_rb) * n_kv_heads;
     bool spread = false;
     cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-    if ((ctx->tune_stages == 0 || ctx->tune_stages == 3) && ctx->tune_warps != 4 && p.n_rb <= kMaxRowBlocks &&
-        kv_start < std::min(q_start + 1u, n_kv)) {
+    {
         uint64_t total = 0;
         uint32_t tj_max = 0;
-        for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
-            uint32_t r0, cl, tj;
-            item_extent(p, rb, &r0, &cl, &tj);
-            total += uint64_t(tj) * n_kv_heads;
-            tj_max = std::max(tj_max, tj);
-        }
-        const uint64_t waves = (items + n_sm - 1) / n_sm;
-        const bool worth = ctx->tune_warps == 8 || (items * 20 < waves * n_sm * 19 && total >= items * 96);
-        if (worth && n_sm >= 2 && total >= uint64_t(n_sm) * 8 && total < (1ull << 31)) {
+        if (spread_pays(ctx, p, &total, &tj_max)) {
             cudaStreamIsCapturing(st, &capturing);
             if (ctx->d_prefill_scratch == nullptr && capturing == cudaStreamCaptureStatusNone) {
                 const size_t bytes = size_t(n_sm) * 2 * CTA_ROWS * (HD + 2) * sizeof(float);
