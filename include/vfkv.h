@@ -493,7 +493,17 @@ int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
  * one CTA per SM).  The reference has fixed workgroup shapes; this is a measurement knob.  The
  * stage count also picks the form of the tcgen05 prefill kernel of vfkv_attend_prefill: 1 the
  * simple one, 2 the pipelined one, 3 the one with the roles on separate warps, 0 = the last for
- * FP8 caches and the pipelined one for F16 caches. */
+ * FP8 caches and the pipelined one for F16 caches.  The specialised form runs either one CTA per
+ * (kv-head, block of 256 rows) item -- always with 4x3 -- or one CTA per SM, each taking an even
+ * share of all items' K/V tiles -- with 8x3 whenever the call allows it (every query sees at
+ * least one position, at most 512 row blocks, at least 8 tiles a share), with 0x0 when in
+ * addition one CTA per item would leave a twentieth of the SM time unused and an item averages 96
+ * tiles or more (F16 caches: when the items are at most half the SMs).  Items cut between CTAs
+ * are put together by the CTA holding the item's head (a cooperative launch, at most four
+ * pieces an item, not inside a stream capture) or by a small second kernel.  The shares need
+ * 39 MB of device scratch, which the context allocates at the first such call outside a stream
+ * capture and frees in vfkv_ctx_destroy; calls that would use it must not run concurrently on
+ * two streams of one context. */
 int32_t vfkv_ctx_set_attn_tuning(vfkv_ctx *ctx, uint32_t warps, uint32_t stages);
 /* Programmatic dependent launch of the tensor-core attention kernel, the CUDA counterpart of
  * relaxing the full pipeline barrier the reference records between dispatches
@@ -526,7 +536,9 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * specialised form (FP8 caches) stores 32 slots per CTA at its 4th tile: 0-11 the MMA thread (per
  * product group: loop top, P there, P V issued), 12 its end of tile; 16-23 thread 0 of the softmax
  * warps (tile top; per half: S there, maximum known, P handed over); 24-26 the first K/V thread
- * (tile top, K placed, V placed). */
+ * (tile top, K placed, V placed); and once per CTA, for its first item or share segment, by thread
+ * 0: 13 start, 14 Q placed, 15 first S there, 27 last tile's softmax done, 28 last P V complete,
+ * 29 rows written. */
 /* Split merge inside a thread-block cluster (tensor-core kernel, 2..16 splits): the CTAs of one
  * (sequence, kv-head) exchange their partials through distributed shared memory instead of
  * global scratch and a ticket.  Taken only when every cluster of the grid can be resident at

@@ -42,7 +42,11 @@ uint32_t vfkv_scalar_attn_uses_split(uint32_t position);
  * uses the last query's window).  window != 0 (extension) applies the exact per-query bound
  * max(kv_start, q_start + i + 1 - window) instead.  d_out [m][n_q_heads][head_dim] f32.
  * The cache rows [0, n_kv) of `slot` must already hold the chunk (append precedes attention,
- * executor/attention.rs:2134-2190). */
+ * executor/attention.rs:2134-2190).
+ * One or two kernel launches.  For head_dim 128, FP8 or F16 rows and long items the tcgen05
+ * kernel may spread the work as even shares of K/V tiles over all SMs (vfkv_ctx_set_attn_tuning
+ * in vfkv.h); the first such call on a context outside a stream capture allocates 39 MB of
+ * device scratch (a synchronising cudaMalloc), owned and freed by the context. */
 int32_t vfkv_attend_prefill(vfkv_cache *cache, uint32_t layer, uint32_t kv_layer, const float *d_q,
                             float *d_out, uint32_t n_q_heads, uint32_t slot, uint32_t m,
                             uint32_t q_start, uint32_t n_kv, uint32_t kv_start, uint32_t window,
