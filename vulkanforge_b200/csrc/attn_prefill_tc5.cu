@@ -931,427 +931,427 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
     uint32_t gt = 0u;
     uint32_t tmem = 0u;
     for (uint32_t seg_i = 0u;; ++seg_i) {
-    if (tid == 0) {
-        TC5H_STAMP(13);
-        uint32_t live = 0u, kvh_ = 0u, row0_ = 0u, c_lo_ = 0u, nt_ = 0u, mode_ = 0u, more_ = 0u;
-        if (p.n_cta == 0u) {
-            if (seg_i == 0u) { live = 1u; kvh_ = blockIdx.x; item_extent(p, blockIdx.y, &row0_, &c_lo_, &nt_); }
-        } else if (cur < t_end) {
-            uint32_t acc = 0u;
-            for (uint32_t rb = 0u; rb < p.n_rb; ++rb) {
-                const uint32_t tj = s_tj[rb];
-                const uint32_t blk = tj * p.n_kv_heads;
-                if (cur < acc + blk) {
-                    const uint32_t rel = cur - acc;
-                    kvh_ = rel / tj;
-                    const uint32_t tin = rel - kvh_ * tj;
-                    nt_ = min(tj - tin, t_end - cur);
-                    row0_ = (p.n_rb - 1u - rb) * uint32_t(CTA_ROWS);
-                    c_lo_ = s_cl[rb] + tin * BN;
-                    // 0: a whole item; 1 / 2: a piece of one for the merge kernel, as this CTA's first / a
-                    // later segment; 3: a piece that is not the item's head, for the CTA that holds the
-                    // head; 4: the head, which waits for the more_ pieces of the next CTAs
-                    if (tin == 0u && nt_ == tj) mode_ = 0u;
-                    else if (p.inline_merge == 0u) mode_ = cur == t_begin ? 1u : 2u;
-                    else if (tin != 0u) mode_ = 3u;
-                    else {
-                        mode_ = 4u;
-                        const uint64_t e = uint64_t(acc) + uint64_t(kvh_ + 1u) * tj;
-                        more_ = uint32_t((e * p.n_cta - 1u) / p.total_tiles) - blockIdx.x;
+        if (tid == 0) {
+            TC5H_STAMP(13);
+            uint32_t live = 0u, kvh_ = 0u, row0_ = 0u, c_lo_ = 0u, nt_ = 0u, mode_ = 0u, more_ = 0u;
+            if (p.n_cta == 0u) {
+                if (seg_i == 0u) { live = 1u; kvh_ = blockIdx.x; item_extent(p, blockIdx.y, &row0_, &c_lo_, &nt_); }
+            } else if (cur < t_end) {
+                uint32_t acc = 0u;
+                for (uint32_t rb = 0u; rb < p.n_rb; ++rb) {
+                    const uint32_t tj = s_tj[rb];
+                    const uint32_t blk = tj * p.n_kv_heads;
+                    if (cur < acc + blk) {
+                        const uint32_t rel = cur - acc;
+                        kvh_ = rel / tj;
+                        const uint32_t tin = rel - kvh_ * tj;
+                        nt_ = min(tj - tin, t_end - cur);
+                        row0_ = (p.n_rb - 1u - rb) * uint32_t(CTA_ROWS);
+                        c_lo_ = s_cl[rb] + tin * BN;
+                        // 0: a whole item; 1 / 2: a piece of one for the merge kernel, as this CTA's first / a
+                        // later segment; 3: a piece that is not the item's head, for the CTA that holds the
+                        // head; 4: the head, which waits for the more_ pieces of the next CTAs
+                        if (tin == 0u && nt_ == tj) mode_ = 0u;
+                        else if (p.inline_merge == 0u) mode_ = cur == t_begin ? 1u : 2u;
+                        else if (tin != 0u) mode_ = 3u;
+                        else {
+                            mode_ = 4u;
+                            const uint64_t e = uint64_t(acc) + uint64_t(kvh_ + 1u) * tj;
+                            more_ = uint32_t((e * p.n_cta - 1u) / p.total_tiles) - blockIdx.x;
+                        }
+                        live = 1u;
+                        break;
                     }
-                    live = 1u;
-                    break;
+                    acc += blk;
                 }
-                acc += blk;
             }
+            s_seg[0] = live; s_seg[1] = kvh_; s_seg[2] = row0_; s_seg[3] = c_lo_; s_seg[4] = nt_; s_seg[5] = mode_; s_seg[6] = more_;
         }
-        s_seg[0] = live; s_seg[1] = kvh_; s_seg[2] = row0_; s_seg[3] = c_lo_; s_seg[4] = nt_; s_seg[5] = mode_; s_seg[6] = more_;
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    tmem = s_tmem;
-    if (s_seg[0] == 0u) break;
-    const uint32_t kvh = s_seg[1], row0 = s_seg[2], c_lo = s_seg[3], n_tiles = s_seg[4], mode = s_seg[5], n_more = s_seg[6];
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem = s_tmem;
+        if (s_seg[0] == 0u) break;
+        const uint32_t kvh = s_seg[1], row0 = s_seg[2], c_lo = s_seg[3], n_tiles = s_seg[4], mode = s_seg[5], n_more = s_seg[6];
 
-    // Q tiles -> shared memory (half precision, scale folded in), all threads
-    // by the nine warps that are not fetching K/V (those start on their first tiles meanwhile); five
-    // pieces a thread in flight at a time
-    if (warp < 9u) {
-        constexpr uint32_t QT = 288u, QB = 5u;
-        for (uint32_t i0 = tid; i0 < uint32_t(CTA_ROWS * 16); i0 += QT * QB) {
-            float4 qa[QB], qb[QB];
+        // Q tiles -> shared memory (half precision, scale folded in), all threads
+        // by the nine warps that are not fetching K/V (those start on their first tiles meanwhile); five
+        // pieces a thread in flight at a time
+        if (warp < 9u) {
+            constexpr uint32_t QT = 288u, QB = 5u;
+            for (uint32_t i0 = tid; i0 < uint32_t(CTA_ROWS * 16); i0 += QT * QB) {
+                float4 qa[QB], qb[QB];
 #pragma unroll
-            for (uint32_t u = 0; u < QB; ++u) {
-                const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u, rr = row0 + row;
-                const bool in = i < uint32_t(CTA_ROWS * 16) && rr < n_rows;
-                const float *qp = p.q + (uint64_t(in ? rr / g : 0u) * p.n_q_heads + kvh * g + (in ? rr % g : 0u)) * HD + 8 * c;
-                qa[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                qb[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+                for (uint32_t u = 0; u < QB; ++u) {
+                    const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u, rr = row0 + row;
+                    const bool in = i < uint32_t(CTA_ROWS * 16) && rr < n_rows;
+                    const float *qp = p.q + (uint64_t(in ? rr / g : 0u) * p.n_q_heads + kvh * g + (in ? rr % g : 0u)) * HD + 8 * c;
+                    qa[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    qb[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
 #pragma unroll
-            for (uint32_t u = 0; u < QB; ++u) {
-                const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u;
-                if (i < uint32_t(CTA_ROWS * 16))
-                    *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) =
-                        make_uint4(pack_half2(qa[u].x * qs, qa[u].y * qs), pack_half2(qa[u].z * qs, qa[u].w * qs),
-                                   pack_half2(qb[u].x * qs, qb[u].y * qs), pack_half2(qb[u].z * qs, qb[u].w * qs));
+                for (uint32_t u = 0; u < QB; ++u) {
+                    const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u;
+                    if (i < uint32_t(CTA_ROWS * 16))
+                        *reinterpret_cast<uint4 *>(sm + (q_sm - base) + (row >> 7) * TILE + tile_off(row & 127u, c)) =
+                            make_uint4(pack_half2(qa[u].x * qs, qa[u].y * qs), pack_half2(qa[u].z * qs, qa[u].w * qs),
+                                       pack_half2(qb[u].x * qs, qb[u].y * qs), pack_half2(qb[u].z * qs, qb[u].w * qs));
+                }
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, 288;" ::: "memory");
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("bar.sync 1, 288;" ::: "memory");
-    }
-    if (tid == 0) TC5H_STAMP(14);
+        if (tid == 0) TC5H_STAMP(14);
 #define TC5H_TRACE(slot)                                                                           \
     do {                                                                                           \
         if (p.trace != nullptr && it == 3u && seg_i == 0u)                                         \
             p.trace[(blockIdx.x * gridDim.y + blockIdx.y) * 32 + (slot)] = timer_ns();             \
     } while (0)
 
-    if (warp < 8) {
-        // ================= softmax warps: thread t of warpgroup wg owns row t of Q tile wg =============
-        const uint32_t wg = warp >> 2, t = tid & 127u;
-        const uint32_t r = row0 + wg * BM + t;
-        const bool r_ok = r < n_rows;
-        const uint32_t q_idx = r_ok ? r / g : 0u, hj = r_ok ? r % g : 0u;
-        uint32_t r_lo, r_hi;
-        query_range(p, q_idx, &r_lo, &r_hi);
-        if (!r_ok) { r_lo = 0u; r_hi = 0u; }
-        const uint32_t t_lane = ((warp & 3u) * 32u) << 16;
-        const uint32_t tm_s = tmem + wg * 128u, tm_o = tmem + 256u + wg * 128u;
-        float mref = kMaskedScore, lrow = 0.f;
-        bool ok = true;
-        for (uint32_t it = 0; it < n_tiles && ok; ++it) {
-            if (tid == 0) TC5H_TRACE(16);
-            const uint32_t gi = gt + it;
-            if (!mbar_wait(bar(wg), gi & 1u)) { ok = false; break; }
-            if (tid == 0 && it == 0u) TC5H_STAMP(15);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (uint32_t h = 0; h < 2u; ++h) {
-                const uint32_t t0 = c_lo + it * BN + h * 64u;
-                if (tid == 0) TC5H_TRACE(17 + 4 * h);
-                float s[64];
-                tmem_ld64(tm_s + t_lane + 64u * h, s);
-                const bool full = t0 >= r_lo && t0 + 64u <= r_hi;
-                const bool warp_full = __all_sync(0xffffffffu, full);
-                float mx = kMaskedScore;
-                if (warp_full && !CAP) {
-#pragma unroll
-                    for (int j = 0; j < 64; j += 2) mx = fmaxf(mx, fmaxf(s[j], s[j + 1]));
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 64; ++j) {
-                        float x = s[j];
-                        if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap) * kLog2e;
-                        if (!full) {
-                            const uint32_t pos = t0 + j;
-                            if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
-                        }
-                        s[j] = x;
-                        mx = fmaxf(mx, x);
-                    }
-                }
-                const bool grow = mx > mref + 8.0f;
-                if (__any_sync(0xffffffffu, grow)) {
-                    const float mnew = grow ? mx : mref;
-                    const float alpha = fast_exp2(mref - mnew);
-                    lrow *= alpha;
-                    mref = mnew;
-                    if (it > 0u || h > 0u) {
-                        // O is touched only between P V products: the latest one of this Q tile has to be
-                        // complete -- half b of the tile before, or half a of this tile
-                        if (!mbar_wait(bar(8u + wg * 2u + (h ^ 1u)), (h == 0u ? gi - 1u : gi) & 1u)) { ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-                        for (int c = 0; c < 4; ++c) {
-                            float o[32];
-                            tmem_ld32(tm_o + t_lane + 32 * c, o);
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) o[j] *= alpha;
-                            tmem_st32(tm_o + t_lane + 32 * c, o);
-                            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // the registers are reused by the next load
-                        }
-                    }
-                }
-                if (tid == 0) TC5H_TRACE(18 + 4 * h);
-                float sum = 0.f;
-                float pk[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const float x0 = s[2 * j], x1 = s[2 * j + 1];
-                    float p0 = fast_exp2(x0 - mref), p1 = fast_exp2(x1 - mref);
-                    if (!warp_full) {
-                        p0 = x0 > 0.5f * kMaskedScore ? p0 : 0.f;
-                        p1 = x1 > 0.5f * kMaskedScore ? p1 : 0.f;
-                    }
-                    sum += p0 + p1;
-                    pk[j] = __uint_as_float(pack_half2(p0, p1));   // position 2j in the low half
-                }
-                lrow += sum;
-                tmem_st32(tm_s + t_lane + 64u * h, pk);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                mbar_arrive(bar(4u + wg * 2u + h));
-                if (tid == 0) TC5H_TRACE(19 + 4 * h);
-            }
-        }
-        if (!ok) *abort_flag = 1u;
-        if (tid == 0) TC5H_STAMP(27);
-        // the last P V of this Q tile
-        bool ran = n_tiles > 0 && ok;
-        if (ran && !mbar_wait(bar(8u + wg * 2u + 1u), (gt + n_tiles - 1u) & 1u)) { *abort_flag = 1u; ran = false; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const bool failed = *abort_flag != 0u;
-        if (tid == 0) TC5H_STAMP(28);
-        // The rows leave through shared memory so that a warp's store covers one row's 512 bytes (a
-        // thread storing its own row writes 32 separate sectors an instruction: 5 us a CTA).  Each
-        // softmax warp stages its 32 rows in its own 16 KB of the Q and K tiles, which no product
-        // reads any more: every S product was issued before, and so completed before, the P V this
-        // thread has just waited for.  16-byte pieces are placed at (piece ^ row) so that neither
-        // the row-wise writes nor the piece-wise reads meet in a bank.
-        float row_scale;
-        float *row_dst;
-        float piece_scale[3] = {0.f, 0.f, 0.f};
-        constexpr uint64_t PIECE = uint64_t(CTA_ROWS) * (HD + 2);
-        if (mode == 4u) {
-            // the head of a cut item: the other pieces were the first work of the next CTAs
-            const uint32_t rl = wg * BM + t;
-            bool got = true;
-            for (uint32_t i = 1u; i <= n_more; ++i) got = flag_wait(p.flags + blockIdx.x + i, p.epoch) && got;
-            if (!got) *abort_flag = 1u;
-            const bool mine_ok = ran && !failed;
-            float mx = mine_ok ? mref : kMaskedScore, pm[3], pl[3];
-#pragma unroll
-            for (uint32_t i = 0; i < 3u; ++i) {
-                const bool on = i < n_more && got;
-                const float *pc = p.scratch + uint64_t(blockIdx.x + 1u + (on ? i : 0u)) * 2u * PIECE;
-                pm[i] = on ? __ldcg(pc + CTA_ROWS * HD + rl) : kMaskedScore;
-                pl[i] = on ? __ldcg(pc + CTA_ROWS * HD + CTA_ROWS + rl) : 0.f;
-                mx = fmaxf(mx, pm[i]);
-            }
-            const float w_own = mine_ok ? fast_exp2(mref - mx) : 0.f;
-            float lsum = w_own * lrow;
-#pragma unroll
-            for (uint32_t i = 0; i < 3u; ++i) {
-                piece_scale[i] = fast_exp2(pm[i] - mx);
-                lsum += piece_scale[i] * pl[i];
-            }
-            const float inv = (lsum > 0.f && got && !failed) ? 1.0f / lsum : 0.f;
-            row_scale = w_own * inv;
-#pragma unroll
-            for (uint32_t i = 0; i < 3u; ++i) piece_scale[i] *= inv;
-            row_dst = r_ok ? p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD : nullptr;
-        } else if (mode != 0u) {
-            // a piece of an item: O as it stands, with the reference maximum (log2 units) and the sum
-            float *sc = p.scratch + (uint64_t(blockIdx.x) * 2u + (mode == 2u ? 1u : 0u)) * PIECE;
-            const uint32_t rl = wg * BM + t;
-            sc[CTA_ROWS * HD + rl] = (ran && !failed) ? mref : kMaskedScore;
-            sc[CTA_ROWS * HD + CTA_ROWS + rl] = (ran && !failed) ? lrow : 0.f;
-            row_scale = 1.0f;
-            row_dst = sc + rl * HD;
-        } else {
-            row_scale = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
-            row_dst = r_ok ? p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD : nullptr;
-        }
-        {
-            uint8_t *stage = sm + (q_sm - base) + warp * 16384u;
-            const uint32_t lane = tid & 31u;
-#pragma unroll 1
-            for (uint32_t c = 0; c < 4u; ++c) {
-                float v[32];
-                if (ran && !failed) {
-                    tmem_ld32(tm_o + t_lane + 32 * c, v);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = 0.f;
-                }
-#pragma unroll
-                for (uint32_t j = 0; j < 8u; ++j)
-                    *reinterpret_cast<float4 *>(stage + lane * 512u + ((((8u * c + j) ^ lane) & 31u) << 4)) =
-                        make_float4(v[4 * j] * row_scale, v[4 * j + 1] * row_scale, v[4 * j + 2] * row_scale, v[4 * j + 3] * row_scale);
-            }
-            __syncwarp();
-            const unsigned long long mine = reinterpret_cast<unsigned long long>(row_dst);
-#pragma unroll 4
-            for (uint32_t r = 0; r < 32u; ++r) {
-                const unsigned long long dst = __shfl_sync(0xffffffffu, mine, int(r));
-                float4 x = *reinterpret_cast<const float4 *>(stage + r * 512u + (((lane ^ r) & 31u) << 4));
-                if (mode == 4u) {
-#pragma unroll
-                    for (uint32_t i = 0; i < 3u; ++i) {
-                        const float ps = __shfl_sync(0xffffffffu, piece_scale[i], int(r));
-                        if (i < n_more && dst != 0ull) {
-                            const float4 y = __ldcg(reinterpret_cast<const float4 *>(
-                                p.scratch + uint64_t(blockIdx.x + 1u + i) * 2u * PIECE + (wg * BM + (warp & 3u) * 32u + r) * HD + 4u * lane));
-                            x.x += ps * y.x; x.y += ps * y.y; x.z += ps * y.z; x.w += ps * y.w;
-                        }
-                    }
-                }
-                if (dst != 0ull) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(dst) + 4u * lane) = x;
-            }
-            __syncwarp();
-        }
-    } else if (warp == 8) {
-        // ================= the MMA thread ================================================================
-        if ((tid & 31u) == 0u && n_tiles > 0u) {
+        if (warp < 8) {
+            // ================= softmax warps: thread t of warpgroup wg owns row t of Q tile wg =============
+            const uint32_t wg = warp >> 2, t = tid & 127u;
+            const uint32_t r = row0 + wg * BM + t;
+            const bool r_ok = r < n_rows;
+            const uint32_t q_idx = r_ok ? r / g : 0u, hj = r_ok ? r % g : 0u;
+            uint32_t r_lo, r_hi;
+            query_range(p, q_idx, &r_lo, &r_hi);
+            if (!r_ok) { r_lo = 0u; r_hi = 0u; }
+            const uint32_t t_lane = ((warp & 3u) * 32u) << 16;
+            const uint32_t tm_s = tmem + wg * 128u, tm_o = tmem + 256u + wg * 128u;
+            float mref = kMaskedScore, lrow = 0.f;
             bool ok = true;
-            // S of one Q tile in one piece (N = 128): two N = 64 products take twice the time
-            auto issue_s = [&](uint32_t wg, uint32_t b) {
-#pragma unroll
-                for (uint32_t ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
-                    umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
-                             smem_desc(k_sm + b * TILE + o, 16, 1024), idesc_f16(false), ks);
-                }
-                umma_commit(bar(wg));
-            };
-            if (!mbar_wait(bar(12u + (gt & 1u)), (gt >> 1) & 1u)) ok = false;
-            if (ok) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                issue_s(0, gt & 1u); issue_s(1, gt & 1u);
-                umma_commit(bar(16u + (gt & 1u)));
-            }
             for (uint32_t it = 0; it < n_tiles && ok; ++it) {
-                const uint32_t gi = gt + it, b = gi & 1u;
-                const bool more = it + 1u < n_tiles;
-                // Order: P V of half a for both Q tiles, P V of half b of tile 0, then -- in one interleaved
-                // stream -- S of the next K/V tile for Q tile 0 and P V of half b of Q tile 1, then S for
-                // Q tile 1.  Consecutive MMAs into the same accumulator follow one another about every
-                // 60 ns, MMAs into different accumulators about every 40 ns (measured), so the two
-                // independent products are issued alternately.  The S region of a Q tile is free once
-                // both halves of its P have been read, i.e. behind its P V of half b in issue order.
-                auto pv_step = [&](uint32_t wg, uint32_t h, uint32_t kk) {
-                    umma_f16_ts(tmem + 256u + wg * 128u, tmem + wg * 128u + 64u * h + kk * 8u,
-                                smem_desc(v_sm + b * TILE + (4u * h + kk) * 2048u, SLAB, 1024), idesc_f16(true),
-                                (it | h | kk) != 0u ? 1u : 0u);
-                };
-                auto s_step = [&](uint32_t wg, uint32_t bb, uint32_t ks) {
-                    const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
-                    umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
-                             smem_desc(k_sm + bb * TILE + o, 16, 1024), idesc_f16(false), ks);
-                };
-#pragma unroll 1
-                for (uint32_t c = 0; c < 3u && ok; ++c) {              // (tile 0, a), (tile 1, a), (tile 0, b)
-                    const uint32_t h = c >> 1, wg = c & 1u;
-                    TC5H_TRACE(3 * c);
-                    if (!mbar_wait(bar(4u + wg * 2u + h), gi & 1u)) { ok = false; break; }
-                    TC5H_TRACE(3 * c + 1);
-                    if (c == 0u && !mbar_wait(bar(14u + b), (gi >> 1) & 1u)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(wg, h, kk);
-                    umma_commit(bar(8u + wg * 2u + h));
-                    TC5H_TRACE(3 * c + 2);
-                }
-                if (!ok) break;
-                TC5H_TRACE(9);
-                if (!mbar_wait(bar(4u + 2u + 1u), gi & 1u)) { ok = false; break; }          // P of (tile 1, b)
-                TC5H_TRACE(10);
-                if (more && !mbar_wait(bar(12u + (b ^ 1u)), ((gi + 1u) >> 1) & 1u)) { ok = false; break; }
+                if (tid == 0) TC5H_TRACE(16);
+                const uint32_t gi = gt + it;
+                if (!mbar_wait(bar(wg), gi & 1u)) { ok = false; break; }
+                if (tid == 0 && it == 0u) TC5H_STAMP(15);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (more) {
+#pragma unroll 1
+                for (uint32_t h = 0; h < 2u; ++h) {
+                    const uint32_t t0 = c_lo + it * BN + h * 64u;
+                    if (tid == 0) TC5H_TRACE(17 + 4 * h);
+                    float s[64];
+                    tmem_ld64(tm_s + t_lane + 64u * h, s);
+                    const bool full = t0 >= r_lo && t0 + 64u <= r_hi;
+                    const bool warp_full = __all_sync(0xffffffffu, full);
+                    float mx = kMaskedScore;
+                    if (warp_full && !CAP) {
+#pragma unroll
+                        for (int j = 0; j < 64; j += 2) mx = fmaxf(mx, fmaxf(s[j], s[j + 1]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j) {
+                            float x = s[j];
+                            if constexpr (CAP) x = p.softcap * tanhf(x / p.softcap) * kLog2e;
+                            if (!full) {
+                                const uint32_t pos = t0 + j;
+                                if (pos < r_lo || pos >= r_hi) x = kMaskedScore;
+                            }
+                            s[j] = x;
+                            mx = fmaxf(mx, x);
+                        }
+                    }
+                    const bool grow = mx > mref + 8.0f;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        const float mnew = grow ? mx : mref;
+                        const float alpha = fast_exp2(mref - mnew);
+                        lrow *= alpha;
+                        mref = mnew;
+                        if (it > 0u || h > 0u) {
+                            // O is touched only between P V products: the latest one of this Q tile has to be
+                            // complete -- half b of the tile before, or half a of this tile
+                            if (!mbar_wait(bar(8u + wg * 2u + (h ^ 1u)), (h == 0u ? gi - 1u : gi) & 1u)) { ok = false; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                            for (int c = 0; c < 4; ++c) {
+                                float o[32];
+                                tmem_ld32(tm_o + t_lane + 32 * c, o);
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) o[j] *= alpha;
+                                tmem_st32(tm_o + t_lane + 32 * c, o);
+                                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // the registers are reused by the next load
+                            }
+                        }
+                    }
+                    if (tid == 0) TC5H_TRACE(18 + 4 * h);
+                    float sum = 0.f;
+                    float pk[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float x0 = s[2 * j], x1 = s[2 * j + 1];
+                        float p0 = fast_exp2(x0 - mref), p1 = fast_exp2(x1 - mref);
+                        if (!warp_full) {
+                            p0 = x0 > 0.5f * kMaskedScore ? p0 : 0.f;
+                            p1 = x1 > 0.5f * kMaskedScore ? p1 : 0.f;
+                        }
+                        sum += p0 + p1;
+                        pk[j] = __uint_as_float(pack_half2(p0, p1));   // position 2j in the low half
+                    }
+                    lrow += sum;
+                    tmem_st32(tm_s + t_lane + 64u * h, pk);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(bar(4u + wg * 2u + h));
+                    if (tid == 0) TC5H_TRACE(19 + 4 * h);
+                }
+            }
+            if (!ok) *abort_flag = 1u;
+            if (tid == 0) TC5H_STAMP(27);
+            // the last P V of this Q tile
+            bool ran = n_tiles > 0 && ok;
+            if (ran && !mbar_wait(bar(8u + wg * 2u + 1u), (gt + n_tiles - 1u) & 1u)) { *abort_flag = 1u; ran = false; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool failed = *abort_flag != 0u;
+            if (tid == 0) TC5H_STAMP(28);
+            // The rows leave through shared memory so that a warp's store covers one row's 512 bytes (a
+            // thread storing its own row writes 32 separate sectors an instruction: 5 us a CTA).  Each
+            // softmax warp stages its 32 rows in its own 16 KB of the Q and K tiles, which no product
+            // reads any more: every S product was issued before, and so completed before, the P V this
+            // thread has just waited for.  16-byte pieces are placed at (piece ^ row) so that neither
+            // the row-wise writes nor the piece-wise reads meet in a bank.
+            float row_scale;
+            float *row_dst;
+            float piece_scale[3] = {0.f, 0.f, 0.f};
+            constexpr uint64_t PIECE = uint64_t(CTA_ROWS) * (HD + 2);
+            if (mode == 4u) {
+                // the head of a cut item: the other pieces were the first work of the next CTAs
+                const uint32_t rl = wg * BM + t;
+                bool got = true;
+                for (uint32_t i = 1u; i <= n_more; ++i) got = flag_wait(p.flags + blockIdx.x + i, p.epoch) && got;
+                if (!got) *abort_flag = 1u;
+                const bool mine_ok = ran && !failed;
+                float mx = mine_ok ? mref : kMaskedScore, pm[3], pl[3];
+#pragma unroll
+                for (uint32_t i = 0; i < 3u; ++i) {
+                    const bool on = i < n_more && got;
+                    const float *pc = p.scratch + uint64_t(blockIdx.x + 1u + (on ? i : 0u)) * 2u * PIECE;
+                    pm[i] = on ? __ldcg(pc + CTA_ROWS * HD + rl) : kMaskedScore;
+                    pl[i] = on ? __ldcg(pc + CTA_ROWS * HD + CTA_ROWS + rl) : 0.f;
+                    mx = fmaxf(mx, pm[i]);
+                }
+                const float w_own = mine_ok ? fast_exp2(mref - mx) : 0.f;
+                float lsum = w_own * lrow;
+#pragma unroll
+                for (uint32_t i = 0; i < 3u; ++i) {
+                    piece_scale[i] = fast_exp2(pm[i] - mx);
+                    lsum += piece_scale[i] * pl[i];
+                }
+                const float inv = (lsum > 0.f && got && !failed) ? 1.0f / lsum : 0.f;
+                row_scale = w_own * inv;
+#pragma unroll
+                for (uint32_t i = 0; i < 3u; ++i) piece_scale[i] *= inv;
+                row_dst = r_ok ? p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD : nullptr;
+            } else if (mode != 0u) {
+                // a piece of an item: O as it stands, with the reference maximum (log2 units) and the sum
+                float *sc = p.scratch + (uint64_t(blockIdx.x) * 2u + (mode == 2u ? 1u : 0u)) * PIECE;
+                const uint32_t rl = wg * BM + t;
+                sc[CTA_ROWS * HD + rl] = (ran && !failed) ? mref : kMaskedScore;
+                sc[CTA_ROWS * HD + CTA_ROWS + rl] = (ran && !failed) ? lrow : 0.f;
+                row_scale = 1.0f;
+                row_dst = sc + rl * HD;
+            } else {
+                row_scale = (lrow > 0.f && !failed) ? 1.0f / lrow : 0.f;
+                row_dst = r_ok ? p.out + (uint64_t(q_idx) * p.n_q_heads + kvh * g + hj) * HD : nullptr;
+            }
+            {
+                uint8_t *stage = sm + (q_sm - base) + warp * 16384u;
+                const uint32_t lane = tid & 31u;
+#pragma unroll 1
+                for (uint32_t c = 0; c < 4u; ++c) {
+                    float v[32];
+                    if (ran && !failed) {
+                        tmem_ld32(tm_o + t_lane + 32 * c, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+                    }
+#pragma unroll
+                    for (uint32_t j = 0; j < 8u; ++j)
+                        *reinterpret_cast<float4 *>(stage + lane * 512u + ((((8u * c + j) ^ lane) & 31u) << 4)) =
+                            make_float4(v[4 * j] * row_scale, v[4 * j + 1] * row_scale, v[4 * j + 2] * row_scale, v[4 * j + 3] * row_scale);
+                }
+                __syncwarp();
+                const unsigned long long mine = reinterpret_cast<unsigned long long>(row_dst);
+#pragma unroll 4
+                for (uint32_t r = 0; r < 32u; ++r) {
+                    const unsigned long long dst = __shfl_sync(0xffffffffu, mine, int(r));
+                    float4 x = *reinterpret_cast<const float4 *>(stage + r * 512u + (((lane ^ r) & 31u) << 4));
+                    if (mode == 4u) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 3u; ++i) {
+                            const float ps = __shfl_sync(0xffffffffu, piece_scale[i], int(r));
+                            if (i < n_more && dst != 0ull) {
+                                const float4 y = __ldcg(reinterpret_cast<const float4 *>(
+                                    p.scratch + uint64_t(blockIdx.x + 1u + i) * 2u * PIECE + (wg * BM + (warp & 3u) * 32u + r) * HD + 4u * lane));
+                                x.x += ps * y.x; x.y += ps * y.y; x.z += ps * y.z; x.w += ps * y.w;
+                            }
+                        }
+                    }
+                    if (dst != 0ull) *reinterpret_cast<float4 *>(reinterpret_cast<float *>(dst) + 4u * lane) = x;
+                }
+                __syncwarp();
+            }
+        } else if (warp == 8) {
+            // ================= the MMA thread ================================================================
+            if ((tid & 31u) == 0u && n_tiles > 0u) {
+                bool ok = true;
+                // S of one Q tile in one piece (N = 128): two N = 64 products take twice the time
+                auto issue_s = [&](uint32_t wg, uint32_t b) {
 #pragma unroll
                     for (uint32_t ks = 0; ks < HD / 16; ++ks) {
-                        s_step(0, b ^ 1u, ks);
-                        if (ks < 4u) pv_step(1, 1, ks);
+                        const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                        umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
+                                 smem_desc(k_sm + b * TILE + o, 16, 1024), idesc_f16(false), ks);
                     }
-                    umma_commit(bar(8u + 2u + 1u));
-                    umma_commit(bar(18u + b));
-                    umma_commit(bar(0u));
-                    TC5H_TRACE(11);
-#pragma unroll
-                    for (uint32_t ks = 0; ks < HD / 16; ++ks) s_step(1, b ^ 1u, ks);
-                    umma_commit(bar(1u));
-                    umma_commit(bar(16u + (b ^ 1u)));
-                } else {
-#pragma unroll
-                    for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(1, 1, kk);
-                    umma_commit(bar(8u + 2u + 1u));
-                    umma_commit(bar(18u + b));
+                    umma_commit(bar(wg));
+                };
+                if (!mbar_wait(bar(12u + (gt & 1u)), (gt >> 1) & 1u)) ok = false;
+                if (ok) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    issue_s(0, gt & 1u); issue_s(1, gt & 1u);
+                    umma_commit(bar(16u + (gt & 1u)));
                 }
-                TC5H_TRACE(12);
+                for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+                    const uint32_t gi = gt + it, b = gi & 1u;
+                    const bool more = it + 1u < n_tiles;
+                    // Order: P V of half a for both Q tiles, P V of half b of tile 0, then -- in one interleaved
+                    // stream -- S of the next K/V tile for Q tile 0 and P V of half b of Q tile 1, then S for
+                    // Q tile 1.  Consecutive MMAs into the same accumulator follow one another about every
+                    // 60 ns, MMAs into different accumulators about every 40 ns (measured), so the two
+                    // independent products are issued alternately.  The S region of a Q tile is free once
+                    // both halves of its P have been read, i.e. behind its P V of half b in issue order.
+                    auto pv_step = [&](uint32_t wg, uint32_t h, uint32_t kk) {
+                        umma_f16_ts(tmem + 256u + wg * 128u, tmem + wg * 128u + 64u * h + kk * 8u,
+                                    smem_desc(v_sm + b * TILE + (4u * h + kk) * 2048u, SLAB, 1024), idesc_f16(true),
+                                    (it | h | kk) != 0u ? 1u : 0u);
+                    };
+                    auto s_step = [&](uint32_t wg, uint32_t bb, uint32_t ks) {
+                        const uint32_t o = (ks >> 2) * SLAB + (ks & 3u) * 32;
+                        umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
+                                 smem_desc(k_sm + bb * TILE + o, 16, 1024), idesc_f16(false), ks);
+                    };
+#pragma unroll 1
+                    for (uint32_t c = 0; c < 3u && ok; ++c) {              // (tile 0, a), (tile 1, a), (tile 0, b)
+                        const uint32_t h = c >> 1, wg = c & 1u;
+                        TC5H_TRACE(3 * c);
+                        if (!mbar_wait(bar(4u + wg * 2u + h), gi & 1u)) { ok = false; break; }
+                        TC5H_TRACE(3 * c + 1);
+                        if (c == 0u && !mbar_wait(bar(14u + b), (gi >> 1) & 1u)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(wg, h, kk);
+                        umma_commit(bar(8u + wg * 2u + h));
+                        TC5H_TRACE(3 * c + 2);
+                    }
+                    if (!ok) break;
+                    TC5H_TRACE(9);
+                    if (!mbar_wait(bar(4u + 2u + 1u), gi & 1u)) { ok = false; break; }          // P of (tile 1, b)
+                    TC5H_TRACE(10);
+                    if (more && !mbar_wait(bar(12u + (b ^ 1u)), ((gi + 1u) >> 1) & 1u)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (more) {
+#pragma unroll
+                        for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                            s_step(0, b ^ 1u, ks);
+                            if (ks < 4u) pv_step(1, 1, ks);
+                        }
+                        umma_commit(bar(8u + 2u + 1u));
+                        umma_commit(bar(18u + b));
+                        umma_commit(bar(0u));
+                        TC5H_TRACE(11);
+#pragma unroll
+                        for (uint32_t ks = 0; ks < HD / 16; ++ks) s_step(1, b ^ 1u, ks);
+                        umma_commit(bar(1u));
+                        umma_commit(bar(16u + (b ^ 1u)));
+                    } else {
+#pragma unroll
+                        for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(1, 1, kk);
+                        umma_commit(bar(8u + 2u + 1u));
+                        umma_commit(bar(18u + b));
+                    }
+                    TC5H_TRACE(12);
+                }
+                if (!ok) *abort_flag = 1u;
+            }
+        } else {
+            // ================= K/V tiles: fetch, widen, place (96 threads) =====================================
+            const uint32_t pt = tid - 288u;
+            constexpr uint32_t ES = DT == VFKV_F8 ? 1u : 2u;
+            constexpr uint32_t PIECES = DT == VFKV_F8 ? 1024u : 2048u;          // 16-byte pieces of one K (or V) tile
+            constexpr int NP = DT == VFKV_F8 ? 11 : 11;                          // pieces per thread and pass
+            constexpr int PASSES = DT == VFKV_F8 ? 1 : 2;
+            const uint8_t *kg = p.k + uint64_t(kvh) * HD * ES, *vg = p.v + uint64_t(kvh) * HD * ES;
+            bool ok = true;
+            auto move = [&](const uint8_t *src, uint32_t t0, uint32_t tile_sm, uint32_t free_bar, uint32_t gi) {
+                uint8_t *dst = sm + (tile_sm - base);
+#pragma unroll 1
+                for (int pass = 0; pass < PASSES; ++pass) {
+                    uint4 raw[NP];
+#pragma unroll
+                    for (int i = 0; i < NP; ++i) {
+                        const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
+                        const uint32_t pos = DT == VFKV_F8 ? idx >> 3 : idx >> 4, c = DT == VFKV_F8 ? idx & 7u : idx & 15u;
+                        const bool in = idx < PIECES && t0 + pos < p.n_kv;
+                        const uint64_t off = uint64_t(in ? t0 + pos : 0u) * p.row_bytes + c * 16;
+                        raw[i] = in ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    // the buffer is free once the products of the tile that used it two tiles ago are complete
+                    if (pass == 0 && gi >= 2u && !mbar_wait(free_bar, ((gi >> 1) & 1u) ^ 1u)) ok = false;
+#pragma unroll
+                    for (int i = 0; i < NP; ++i) {
+                        const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
+                        if (idx >= PIECES) continue;
+                        if constexpr (DT == VFKV_F8) {
+                            const uint32_t pos = idx >> 3, c16 = idx & 7u;
+                            const uint4 x = raw[i];
+                            __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
+                            __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
+                            __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
+                            __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
+                            // (storing even pieces from four threads of a row and odd pieces from the other four,
+                            // which takes the two-way bank conflict out of these stores, measured 5 % slower
+                            // at contexts of 30 000 and more, and the same below)
+                            *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
+                                make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
+                                           *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
+                            *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
+                                make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
+                                           *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
+                        } else {
+                            *reinterpret_cast<uint4 *>(dst + tile_off(idx >> 4, idx & 15u)) = raw[i];
+                        }
+                    }
+                }
+            };
+            for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+                const uint32_t gi = gt + it, b = gi & 1u, t0 = c_lo + it * BN;
+                if (pt == 0) TC5H_TRACE(24);
+                move(kg, t0, k_sm + b * TILE, bar(16u + b), gi);
+                if (pt == 0) TC5H_TRACE(25);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(bar(12u + b));
+                move(vg, t0, v_sm + b * TILE, bar(18u + b), gi);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(bar(14u + b));
+                if (pt == 0) TC5H_TRACE(26);
             }
             if (!ok) *abort_flag = 1u;
         }
-    } else {
-        // ================= K/V tiles: fetch, widen, place (96 threads) =====================================
-        const uint32_t pt = tid - 288u;
-        constexpr uint32_t ES = DT == VFKV_F8 ? 1u : 2u;
-        constexpr uint32_t PIECES = DT == VFKV_F8 ? 1024u : 2048u;          // 16-byte pieces of one K (or V) tile
-        constexpr int NP = DT == VFKV_F8 ? 11 : 11;                          // pieces per thread and pass
-        constexpr int PASSES = DT == VFKV_F8 ? 1 : 2;
-        const uint8_t *kg = p.k + uint64_t(kvh) * HD * ES, *vg = p.v + uint64_t(kvh) * HD * ES;
-        bool ok = true;
-        auto move = [&](const uint8_t *src, uint32_t t0, uint32_t tile_sm, uint32_t free_bar, uint32_t gi) {
-            uint8_t *dst = sm + (tile_sm - base);
-#pragma unroll 1
-            for (int pass = 0; pass < PASSES; ++pass) {
-                uint4 raw[NP];
-#pragma unroll
-                for (int i = 0; i < NP; ++i) {
-                    const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
-                    const uint32_t pos = DT == VFKV_F8 ? idx >> 3 : idx >> 4, c = DT == VFKV_F8 ? idx & 7u : idx & 15u;
-                    const bool in = idx < PIECES && t0 + pos < p.n_kv;
-                    const uint64_t off = uint64_t(in ? t0 + pos : 0u) * p.row_bytes + c * 16;
-                    raw[i] = in ? __ldg(reinterpret_cast<const uint4 *>(src + off)) : make_uint4(0u, 0u, 0u, 0u);
-                }
-                // the buffer is free once the products of the tile that used it two tiles ago are complete
-                if (pass == 0 && gi >= 2u && !mbar_wait(free_bar, ((gi >> 1) & 1u) ^ 1u)) ok = false;
-#pragma unroll
-                for (int i = 0; i < NP; ++i) {
-                    const uint32_t idx = pt + 96u * uint32_t(i) + uint32_t(pass) * (96u * NP);
-                    if (idx >= PIECES) continue;
-                    if constexpr (DT == VFKV_F8) {
-                        const uint32_t pos = idx >> 3, c16 = idx & 7u;
-                        const uint4 x = raw[i];
-                        __half2 h0 = e4m3x2_to_half2(x.x & 0xffffu), h1 = e4m3x2_to_half2(x.x >> 16);
-                        __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
-                        __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
-                        __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
-                        // (storing even pieces from four threads of a row and odd pieces from the other four,
-                        // which takes the two-way bank conflict out of these stores, measured 5 % slower
-                        // at contexts of 30 000 and more, and the same below)
-                        *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
-                            make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
-                                       *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
-                        *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16 + 1)) =
-                            make_uint4(*reinterpret_cast<uint32_t *>(&h4), *reinterpret_cast<uint32_t *>(&h5),
-                                       *reinterpret_cast<uint32_t *>(&h6), *reinterpret_cast<uint32_t *>(&h7));
-                    } else {
-                        *reinterpret_cast<uint4 *>(dst + tile_off(idx >> 4, idx & 15u)) = raw[i];
-                    }
-                }
-            }
-        };
-        for (uint32_t it = 0; it < n_tiles && ok; ++it) {
-            const uint32_t gi = gt + it, b = gi & 1u, t0 = c_lo + it * BN;
-            if (pt == 0) TC5H_TRACE(24);
-            move(kg, t0, k_sm + b * TILE, bar(16u + b), gi);
-            if (pt == 0) TC5H_TRACE(25);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar(12u + b));
-            move(vg, t0, v_sm + b * TILE, bar(18u + b), gi);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar(14u + b));
-            if (pt == 0) TC5H_TRACE(26);
+        // end of the segment: every product of it is complete (the softmax threads waited for the last
+        // P V before they read O), so Q, the tensor memory and the barriers' phases can be taken over
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (tid == 0) TC5H_STAMP(29);
+        if (mode == 3u && tid == 0) {
+            // the piece is in scratch (every thread's stores are ordered before the barrier above)
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p.flags + blockIdx.x), "r"(s_abort != 0u ? 0u : p.epoch) : "memory");
         }
-        if (!ok) *abort_flag = 1u;
-    }
-    // end of the segment: every product of it is complete (the softmax threads waited for the last
-    // P V before they read O), so Q, the tensor memory and the barriers' phases can be taken over
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0) TC5H_STAMP(29);
-    if (mode == 3u && tid == 0) {
-        // the piece is in scratch (every thread's stores are ordered before the barrier above)
-        __threadfence();
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p.flags + blockIdx.x), "r"(s_abort != 0u ? 0u : p.epoch) : "memory");
-    }
-    if (s_abort != 0u || p.n_cta == 0u) break;
-    gt += n_tiles;
-    cur += n_tiles;
+        if (s_abort != 0u || p.n_cta == 0u) break;
+        gt += n_tiles;
+        cur += n_tiles;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
