@@ -533,8 +533,8 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * two warpgroups stores, at its 4th K/V tile, 0 tile start, 1 loads issued and previous P V
  * complete, 2 K/V converted, 3 CTA barrier passed, 4 S issued, 5 S complete, 6 row maximum,
  * 7 rescale decided, 8 P written, 9 P V issued -- at (CTA index * 2 + warpgroup) * 16.  Its
- * specialised form (FP8 caches) stores 32 slots per CTA at its 4th tile: 0-11 the MMA thread (per
- * product group: loop top, P there, P V issued), 12 its end of tile; 16-23 thread 0 of the softmax
+ * specialised form (FP8 caches) stores 32 slots per CTA at its 4th tile: 0 and 12 the MMA thread
+ * (tile top, all of the tile's products issued); 16-23 thread 0 of the softmax
  * warps (tile top; per half: S there, maximum known, P handed over); 24-26 the first K/V thread
  * (tile top, K placed, V placed); and once per CTA, for its first item or share segment, by thread
  * 0: 13 start, 14 Q placed, 15 first S there, 27 last tile's softmax done, 28 last P V complete,

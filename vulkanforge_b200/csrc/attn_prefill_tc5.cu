@@ -64,20 +64,33 @@ __device__ __forceinline__ uint64_t timer_ns()
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
+// One look at the phase with the given parity.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0u;
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
 }
-// Bounded wait for the phase with the given parity; false after one second.
+// Bounded wait for the phase with the given parity; false after one second.  The hint lets the
+// hardware park the thread for up to that long instead of returning for another look (a waiting
+// warp that spins takes issue slots from the warps of its scheduler that work).
+constexpr uint32_t kSuspendNs = 20000u;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         uint32_t done;
         asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                      "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                     : "=r"(done) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
         if (done) return true;
         // the timer is slow to read: look at it only now and then
         if ((it & 255u) == 255u) {
@@ -1075,6 +1088,8 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                         }
                     }
                     if (tid == 0) TC5H_TRACE(18 + 4 * h);
+                    // (the offsets and the row sum as packed add.f32x2, two columns an instruction:
+                    // 653 -> 696 us on 2048 queries at 14 336, not kept)
                     float sum = 0.f;
                     float pk[32];
 #pragma unroll
@@ -1212,15 +1227,19 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                     issue_s(0, gt & 1u); issue_s(1, gt & 1u);
                     umma_commit(bar(16u + (gt & 1u)));
                 }
+                // Per K/V tile six groups of products: P V of (Q tile, half) x 4 and S of the next tile x 2.
+                // They are issued as their inputs arrive -- a look at the four P barriers in turn -- and
+                // not in a fixed order: in a fixed order (P V a0, a1, b0, then S0 alternating with P V
+                // b1, then S1) Q tile 0 waited for Q tile 1's softmax before its next S was issued
+                // (653 -> 643 us on 2048 queries at 14 336, 1258 -> 1234 at 30 000).  The S of the next
+                // tile for a Q tile goes right behind that Q tile's P V of half b (its S columns hold
+                // P until then; MMAs of one thread execute in order), alternating with a P V of the
+                // other Q tile when one is ready at that moment: consecutive MMAs into the same
+                // accumulator follow one another about every 60 ns, MMAs into different accumulators
+                // about every 40 ns (measured).
                 for (uint32_t it = 0; it < n_tiles && ok; ++it) {
                     const uint32_t gi = gt + it, b = gi & 1u;
                     const bool more = it + 1u < n_tiles;
-                    // Order: P V of half a for both Q tiles, P V of half b of tile 0, then -- in one interleaved
-                    // stream -- S of the next K/V tile for Q tile 0 and P V of half b of Q tile 1, then S for
-                    // Q tile 1.  Consecutive MMAs into the same accumulator follow one another about every
-                    // 60 ns, MMAs into different accumulators about every 40 ns (measured), so the two
-                    // independent products are issued alternately.  The S region of a Q tile is free once
-                    // both halves of its P have been read, i.e. behind its P V of half b in issue order.
                     auto pv_step = [&](uint32_t wg, uint32_t h, uint32_t kk) {
                         umma_f16_ts(tmem + 256u + wg * 128u, tmem + wg * 128u + 64u * h + kk * 8u,
                                     smem_desc(v_sm + b * TILE + (4u * h + kk) * 2048u, SLAB, 1024), idesc_f16(true),
@@ -1231,45 +1250,64 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                         umma_f16(tmem + wg * 128u, smem_desc(q_sm + wg * TILE + o, 16, 1024),
                                  smem_desc(k_sm + bb * TILE + o, 16, 1024), idesc_f16(false), ks);
                     };
+                    TC5H_TRACE(0);
+                    if (!mbar_wait(bar(14u + b), (gi >> 1) & 1u)) { ok = false; break; }
+                    bool k_next = !more;
+                    uint32_t todo = 0xFu;                  // bit h * 2 + wg: P V of (Q tile wg, half h) not issued yet
+                    uint64_t t_idle = 0;
+                    uint32_t idle = 0;
+                    while (todo != 0u && ok) {
+                        bool did = false;
 #pragma unroll 1
-                    for (uint32_t c = 0; c < 3u && ok; ++c) {              // (tile 0, a), (tile 1, a), (tile 0, b)
-                        const uint32_t h = c >> 1, wg = c & 1u;
-                        TC5H_TRACE(3 * c);
-                        if (!mbar_wait(bar(4u + wg * 2u + h), gi & 1u)) { ok = false; break; }
-                        TC5H_TRACE(3 * c + 1);
-                        if (c == 0u && !mbar_wait(bar(14u + b), (gi >> 1) & 1u)) { ok = false; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        for (uint32_t wg = 0; wg < 2u && ok; ++wg) {
+                            const uint32_t h = ((todo >> wg) & 1u) ? 0u : 1u;            // half a before half b
+                            if (((todo >> (h * 2u + wg)) & 1u) == 0u) continue;
+                            if (!mbar_test(bar(4u + wg * 2u + h), gi & 1u)) continue;
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                            did = true;
 #pragma unroll
-                        for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(wg, h, kk);
-                        umma_commit(bar(8u + wg * 2u + h));
-                        TC5H_TRACE(3 * c + 2);
+                            for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(wg, h, kk);
+                            umma_commit(bar(8u + wg * 2u + h));
+                            todo &= ~(1u << (h * 2u + wg));
+                            if (h == 0u || !more) continue;
+                            // S of the next K/V tile for this Q tile: its S columns are free behind the P V
+                            // just issued.  Alternating with a P V of the other Q tile if one is ready now.
+                            if (!k_next) {
+                                if (!mbar_wait(bar(12u + (b ^ 1u)), ((gi + 1u) >> 1) & 1u)) { ok = false; break; }
+                                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                                k_next = true;
+                            }
+                            const uint32_t other = wg ^ 1u, ho = ((todo >> other) & 1u) ? 0u : 1u;
+                            const bool pair = ((todo >> (ho * 2u + other)) & 1u) != 0u && mbar_test(bar(4u + other * 2u + ho), gi & 1u);
+                            if (pair) asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                            for (uint32_t ks = 0; ks < HD / 16; ++ks) {
+                                s_step(wg, b ^ 1u, ks);
+                                if (pair && ks < 4u) pv_step(other, ho, ks);
+                            }
+                            if (pair) {
+                                umma_commit(bar(8u + other * 2u + ho));
+                                todo &= ~(1u << (ho * 2u + other));
+                            }
+                            umma_commit(bar(wg));
+                            if (pair && ho == 1u) {
+#pragma unroll
+                                for (uint32_t ks = 0; ks < HD / 16; ++ks) s_step(other, b ^ 1u, ks);
+                                umma_commit(bar(other));
+                            }
+                        }
+                        if (!did) {
+                            if ((++idle & 1023u) == 0u) {
+                                if (t_idle == 0) t_idle = timer_ns();
+                                else if (timer_ns() - t_idle > 1000000000ull) ok = false;
+                            }
+                        } else {
+                            idle = 0; t_idle = 0;
+                        }
                     }
                     if (!ok) break;
-                    TC5H_TRACE(9);
-                    if (!mbar_wait(bar(4u + 2u + 1u), gi & 1u)) { ok = false; break; }          // P of (tile 1, b)
-                    TC5H_TRACE(10);
-                    if (more && !mbar_wait(bar(12u + (b ^ 1u)), ((gi + 1u) >> 1) & 1u)) { ok = false; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    if (more) {
-#pragma unroll
-                        for (uint32_t ks = 0; ks < HD / 16; ++ks) {
-                            s_step(0, b ^ 1u, ks);
-                            if (ks < 4u) pv_step(1, 1, ks);
-                        }
-                        umma_commit(bar(8u + 2u + 1u));
-                        umma_commit(bar(18u + b));
-                        umma_commit(bar(0u));
-                        TC5H_TRACE(11);
-#pragma unroll
-                        for (uint32_t ks = 0; ks < HD / 16; ++ks) s_step(1, b ^ 1u, ks);
-                        umma_commit(bar(1u));
-                        umma_commit(bar(16u + (b ^ 1u)));
-                    } else {
-#pragma unroll
-                        for (uint32_t kk = 0; kk < 4u; ++kk) pv_step(1, 1, kk);
-                        umma_commit(bar(8u + 2u + 1u));
-                        umma_commit(bar(18u + b));
-                    }
+                    umma_commit(bar(18u + b));
+                    if (more) umma_commit(bar(16u + (b ^ 1u)));
                     TC5H_TRACE(12);
                 }
                 if (!ok) *abort_flag = 1u;
