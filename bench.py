@@ -535,7 +535,11 @@ def next_rows(ctx, args, peak, tensor_peak):
         fwd.stream = None
         us_rope_graph = timed(graph.replay, 5) / 20
         flops = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2)              # causal: query i sees q_start + i + 1 rows
-        few = prefill_few_items(ctx, tensor_peak, timed)
+        # a short chunk late in a long context: 8 (kv-head, row block) items, which one CTA per item
+        # would run on 8 SMs (with the shares switched off the automatic choice is the mma.sync kernel)
+        few = prefill_extra(ctx, tensor_peak, timed, "F8", 256, 60000, (4, 3, "us_without_even_shares"))
+        # F16 rows: K/V tiles by TMA in the specialised form, against the pipelined form
+        f16 = prefill_extra(ctx, tensor_peak, timed, "F16", 2048, 14336, (4, 2, "us_pipelined_form"))
         rope_bytes = 2 * 512 * hkv * d * (4 + 1)                             # f32 in, one byte out, K and V
         tf = flops / (us_attn * 1e-6) / 1e12
         gbs = rope_bytes / (us_rope_graph * 1e-6) / 1e9                      # device time: the graph replay
@@ -545,6 +549,7 @@ def next_rows(ctx, args, peak, tensor_peak):
                                       "note": "tcgen05.mma kernel (roles on separate warps, one CTA per SM with an even "
                                               "share of all K/V tiles), S, P and O in tensor memory"},
                 "prefill_attention_few_items": few,
+                "prefill_attention_f16": f16,
                 "rope_append": {"workload": "512 tokens x 8 kv-heads x 128, FP8 cache, K rotated", "us": us_rope,
                                 "us_in_graph": us_rope_graph,
                                 "bound": "hbm", "achieved": gbs, "unit": "GB/s", "peak": peak, "frac": gbs / peak,
@@ -555,14 +560,14 @@ def next_rows(ctx, args, peak, tensor_peak):
         cache.destroy()
 
 
-def prefill_few_items(ctx, tensor_peak, timed):
-    """A short chunk late in a long context: 256 queries at position 60 000 are 8 (kv-head, row
-    block) items, which one CTA per item would run on 8 SMs; the even shares use all of them."""
+def prefill_extra(ctx, tensor_peak, timed, dtype, m, q_start, compare):
+    """One more prefill-attention case, 32 q / 8 kv / 128: `compare` = (warps, stages, key) times the
+    same call with that tuning beside the automatic choice."""
     import torch
     import vulkanforge_b200 as vf
-    hq, hkv, d, m, q_start = 32, 8, 128, 256, 60000
+    hq, hkv, d = 32, 8, 128
     L = q_start + m
-    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype[dtype])
     fwd = vf.CudaForward(ctx, cache, n_heads=hq)
     try:
         g = torch.Generator(device="cuda").manual_seed(6)
@@ -573,12 +578,12 @@ def prefill_few_items(ctx, tensor_peak, timed):
         q = torch.randn(m, hq, d, device="cuda", generator=g)
         out = torch.zeros(m, hq, d, device="cuda")
         us = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 20)
-        ctx.set_attn_tuning(4, 3)                       # shares off: the automatic choice is then the 64-row mma.sync kernel
-        us_per_item = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 5)
+        ctx.set_attn_tuning(compare[0], compare[1])
+        us_other = timed(lambda: fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0), 5)
         ctx.set_attn_tuning(0, 0)
         tf = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2) / (us * 1e-6) / 1e12
-        return {"workload": "256 queries at positions 60000..60255, FP8 cache, 32/8/128", "us": us,
-                "us_without_even_shares": us_per_item, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
+        return {"workload": f"{m} queries at positions {q_start}..{L - 1}, {dtype} cache, 32/8/128", "us": us,
+                compare[2]: us_other, "bound": "tensor", "achieved": tf, "unit": "TFLOP/s",
                 "peak": tensor_peak, "frac": tf / tensor_peak if tensor_peak else None}
     finally:
         fwd.workspace.destroy()

@@ -24,6 +24,7 @@
 #include "fp8_codec.cuh"
 
 #include <algorithm>
+#include <cstring>
 
 namespace vfkv {
 namespace {
@@ -55,6 +56,7 @@ struct Tc5Params {
     // flags[cta] = epoch); the launch is cooperative, so the CTAs it waits for are resident
     uint32_t inline_merge, epoch;
     uint32_t *flags;
+    uint32_t use_tma;                  // F16 rows, specialised form: K/V tiles by TMA through the two tensor maps
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -63,6 +65,16 @@ __device__ __forceinline__ uint64_t timer_ns()
     uint64_t t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+// One box of a byte-typed 2-D tensor map (x bytes into the row, row y) into 128-byte-swizzled shared memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 :: "r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 // One look at the phase with the given parity.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity)
@@ -881,7 +893,8 @@ __device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t want)
 }
 
 template <int DT, bool CAP>
-__global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
+__global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p, const __grid_constant__ CUtensorMap tm_k,
+                                                              const __grid_constant__ CUtensorMap tm_v)
 {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_bar[20];
@@ -910,7 +923,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
         for (uint32_t i = 0; i < 4; ++i) mbar_init(bar(i), 1);
         for (uint32_t i = 4; i < 8; ++i) mbar_init(bar(i), 128);
         for (uint32_t i = 8; i < 12; ++i) mbar_init(bar(i), 1);
-        for (uint32_t i = 12; i < 16; ++i) mbar_init(bar(i), 96);
+        for (uint32_t i = 12; i < 16; ++i) mbar_init(bar(i), p.use_tma != 0u ? 1u : 96u);
         for (uint32_t i = 16; i < 20; ++i) mbar_init(bar(i), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0u;
@@ -1362,6 +1375,28 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p)
                     }
                 }
             };
+            if (DT == VFKV_F16 && p.use_tma != 0u) {
+                // F16 rows need no widening: one thread has the TMA unit copy each tile's two slabs of
+                // K and of V (box = 128 bytes x 128 positions, the swizzle the descriptors expect;
+                // positions from n_kv on, outside the map, arrive as zeros)
+                if (pt == 0u) {
+                    for (uint32_t it = 0; it < n_tiles && ok; ++it) {
+                        const uint32_t gi = gt + it, b = gi & 1u;
+                        const int32_t t0 = int32_t(c_lo + it * BN), x = int32_t(kvh * HD * 2u);
+                        TC5H_TRACE(24);
+                        if (gi >= 2u && !mbar_wait(bar(16u + b), ((gi >> 1) & 1u) ^ 1u)) { ok = false; break; }
+                        mbar_expect_tx(bar(12u + b), TILE);
+                        tma_load_2d(k_sm + b * TILE, &tm_k, x, t0, bar(12u + b));
+                        tma_load_2d(k_sm + b * TILE + SLAB, &tm_k, x + 128, t0, bar(12u + b));
+                        TC5H_TRACE(25);
+                        if (gi >= 2u && !mbar_wait(bar(18u + b), ((gi >> 1) & 1u) ^ 1u)) { ok = false; break; }
+                        mbar_expect_tx(bar(14u + b), TILE);
+                        tma_load_2d(v_sm + b * TILE, &tm_v, x, t0, bar(14u + b));
+                        tma_load_2d(v_sm + b * TILE + SLAB, &tm_v, x + 128, t0, bar(14u + b));
+                        TC5H_TRACE(26);
+                    }
+                }
+            } else
             for (uint32_t it = 0; it < n_tiles && ok; ++it) {
                 const uint32_t gi = gt + it, b = gi & 1u, t0 = c_lo + it * BN;
                 if (pt == 0) TC5H_TRACE(24);
@@ -1571,13 +1606,14 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             }
         }
     }
-    // The specialised form (roles on separate warps) for FP8 caches; vfkv_ctx_set_attn_tuning(ctx, 4, 2)
-    // keeps the pipelined form, (4, 1) the simple one.  F16 caches stay on the pipelined form: their
-    // tiles are twice the bytes, and three warps of plain loads do not bring them in fast enough
-    // (441 against 563 TFLOP/s) -- unless the items are so few that the pipelined form, one CTA an
-    // item, would leave half the SMs idle.
-    const bool f16_few = dtype == VFKV_F16 && spread && items * 2 <= n_sm;
-    if ((ctx->tune_stages == 0 && (dtype == VFKV_F8 || f16_few)) || ctx->tune_stages == 3) {
+    // The specialised form (roles on separate warps) is the default; vfkv_ctx_set_attn_tuning(ctx, 4, 2)
+    // keeps the pipelined form, (4, 1) the simple one.  F16 rows are twice the bytes of FP8 codes and
+    // three warps of plain loads do not bring them in fast enough (441-516 against 532-558 TFLOP/s
+    // for the pipelined form), so for F16 caches the tiles come by TMA (776-836); without the
+    // driver entry point for tensor maps they stay on the pipelined form -- unless the items are so
+    // few that one CTA an item would leave half the SMs idle.
+    const bool f16_h = dtype == VFKV_F16 && (ctx->encode_tiled != nullptr || (spread && items * 2 <= n_sm));
+    if ((ctx->tune_stages == 0 && (dtype == VFKV_F8 || f16_h)) || ctx->tune_stages == 3) {
         static bool configured_h[64] = {};
         if (!configured_h[ctx->device & 63]) {
             const void *kernels[4] = {reinterpret_cast<const void *>(prefill_tc5h_kernel<VFKV_F8, false>),
@@ -1591,7 +1627,29 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             configured_h[ctx->device & 63] = true;
         }
         const dim3 grid_h = spread ? dim3(n_sm, 1, 1) : dim3(grid.y, grid.x);
-        void (*kern)(const Tc5Params) = dtype == VFKV_F8 ? (cap ? prefill_tc5h_kernel<VFKV_F8, true> : prefill_tc5h_kernel<VFKV_F8, false>)
+        // F16 rows by TMA: byte-typed maps of the slot's rows [0, n_kv), one row = one position
+        CUtensorMap tm_k, tm_v;
+        memset(&tm_k, 0, sizeof tm_k);
+        memset(&tm_v, 0, sizeof tm_v);
+        if (dtype == VFKV_F16 && ctx->encode_tiled != nullptr && n_kv != 0u) {
+            typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+            cuuint64_t dims[2] = {row_bytes, n_kv};
+            cuuint64_t strides[1] = {row_bytes};
+            cuuint32_t box[2] = {128, 128};
+            cuuint32_t estr[2] = {1, 1};
+            auto enc = reinterpret_cast<EncodeTiledFn>(ctx->encode_tiled);
+            const bool made =
+                enc(&tm_k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(k), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS &&
+                enc(&tm_v, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(v), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            p.use_tma = made ? 1u : 0u;
+        }
+        void (*kern)(const Tc5Params, const CUtensorMap, const CUtensorMap) = dtype == VFKV_F8 ? (cap ? prefill_tc5h_kernel<VFKV_F8, true> : prefill_tc5h_kernel<VFKV_F8, false>)
                                                          : (cap ? prefill_tc5h_kernel<VFKV_F16, true> : prefill_tc5h_kernel<VFKV_F16, false>);
         if (spread && p.inline_merge != 0u) {
             // CTAs of this launch wait for one another's pieces: a cooperative launch, which the
@@ -1608,14 +1666,14 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             attr[0].val.cooperative = 1;
             cfg.attrs = attr;
             cfg.numAttrs = 1;
-            if (cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess) {
+            if (cudaLaunchKernelEx(&cfg, kern, p, tm_k, tm_v) == cudaSuccess) {
                 ctx->launches++;
                 return check_cuda(ctx, cudaGetLastError(), "tcgen05 prefill attention launch");
             }
             (void)cudaGetLastError();          // not all resident: the pieces go to the merge kernel instead
             p.inline_merge = 0u;
         }
-        kern<<<grid_h, 384, kSmemBytes, st>>>(p);
+        kern<<<grid_h, 384, kSmemBytes, st>>>(p, tm_k, tm_v);
         ctx->launches++;
         if (spread) {
             // launched as a programmatic dependent: it is resident, its table built, when the last CTA
