@@ -492,13 +492,14 @@ int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
  * warp; 4x1, 4x2, 4x3, 8x1 or 8x3, 0x0 = choose per call (4 warps, or 8x3 when the grid has at most
  * one CTA per SM).  The reference has fixed workgroup shapes; this is a measurement knob.  The
  * stage count also picks the form of the tcgen05 prefill kernel of vfkv_attend_prefill: 1 the
- * simple one, 2 the pipelined one, 3 the one with the roles on separate warps, 0 = the last for
- * FP8 caches and the pipelined one for F16 caches.  The specialised form runs either one CTA per
+ * simple one, 2 the pipelined one, 3 the one with the roles on separate warps (F16 rows by TMA
+ * when the driver offers tensor maps), 0 = the last (the pipelined one for F16 caches without
+ * tensor maps).  The specialised form runs either one CTA per
  * (kv-head, block of 256 rows) item -- always with 4x3 -- or one CTA per SM, each taking an even
  * share of all items' K/V tiles -- with 8x3 whenever the call allows it (every query sees at
  * least one position, at most 512 row blocks, at least 8 tiles a share), with 0x0 when in
  * addition one CTA per item would leave a twentieth of the SM time unused and an item averages 96
- * tiles or more (F16 caches: when the items are at most half the SMs).  Items cut between CTAs
+ * tiles or more.  Items cut between CTAs
  * are put together by the CTA holding the item's head (a cooperative launch, at most four
  * pieces an item, not inside a stream capture) or by a small second kernel.  The shares need
  * 39 MB of device scratch, which the context allocates at the first such call outside a stream
@@ -533,7 +534,7 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * two warpgroups stores, at its 4th K/V tile, 0 tile start, 1 loads issued and previous P V
  * complete, 2 K/V converted, 3 CTA barrier passed, 4 S issued, 5 S complete, 6 row maximum,
  * 7 rescale decided, 8 P written, 9 P V issued -- at (CTA index * 2 + warpgroup) * 16.  Its
- * specialised form (FP8 caches) stores 32 slots per CTA at its 4th tile: 0 and 12 the MMA thread
+ * specialised form stores 32 slots per CTA at its 4th tile: 0 and 12 the MMA thread
  * (tile top, all of the tile's products issued); 16-23 thread 0 of the softmax
  * warps (tile top; per half: S there, maximum known, P handed over); 24-26 the first K/V thread
  * (tile top, K placed, V placed); and once per CTA, for its first item or share segment, by thread

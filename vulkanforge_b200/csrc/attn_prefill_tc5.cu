@@ -846,7 +846,8 @@ __global__ void __launch_bounds__(256, 1) prefill_tc5p_kernel(const Tc5Params p)
 // of the softmax, so 127 threads wait for it at every barrier.  Here the roles are separate warps:
 //   warps 0-3 / 4-7   softmax of Q tile 0 / 1 (thread t = row t), in halves of 64 positions;
 //   warp 8            one thread issues every MMA;
-//   warps 9-11        fetch, widen and place the K/V tiles (two buffers each).
+//   warps 9-11        fetch, widen and place the K/V tiles (two buffers each); F16 rows: one thread
+//                     of them issues TMA copies instead.
 // Twelve warps leave 168 registers a thread, which is why a row is handled 64 columns at a time;
 // per Q tile and K/V tile: S = Q K^T (N = 128, one piece: two N = 64 products measured twice the
 // time) -> softmax of columns 0-63 -> P half a (tensor memory) -> O += P V (K = 64) while the
