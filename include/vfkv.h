@@ -545,12 +545,16 @@ int32_t vfkv_ctx_set_dependent_launch(vfkv_ctx *ctx, uint32_t mode);
  * global scratch and a ticket.  Taken only when every cluster of the grid can be resident at
  * once; otherwise the call falls back to the scratch + ticket form.  0 = off (default), 1 = on. */
 int32_t vfkv_ctx_set_cluster_merge(vfkv_ctx *ctx, uint32_t on);
-/* Time limit of the merging CTA's wait for the other splits' partials (1..10000 ms, default 1000). */
+/* Time limit of the merging CTA's wait for the other splits' partials, and of the prefill kernel's
+ * wait for the other pieces of an item cut between CTAs (1..10000 ms, default 1000). */
 int32_t vfkv_ctx_set_merge_wait_ms(vfkv_ctx *ctx, uint32_t ms);
 /* Host-side failure injection for tests of the bounded waits: in later launches of the tensor-core
  * attention kernel the CTA of (sequence 0, kv-head 0, split `split`) behaves as if its wait for a
  * TMA tile had run out -- it raises bit 1 of the status word and publishes no partial -- so the
- * merging CTA's own wait runs out as well.  Nothing faults or hangs.  0xFFFFFFFF = off (default). */
+ * merging CTA's own wait runs out as well.  In the prefill kernel's even-shares form the CTA with
+ * index `split` does not announce its piece of a cut item, so the wait of the CTA that holds the
+ * item's head runs out (status bit 1, that item's rows are zeros).  Nothing faults or hangs.
+ * 0xFFFFFFFF = off (default). */
 int32_t vfkv_ctx_debug_fail_split(vfkv_ctx *ctx, uint32_t split);
 int32_t vfkv_ctx_set_trace_buffer(vfkv_ctx *ctx, void *d_buffer);
 /* With n_blocks > 1 the k-th launch of the decode attention kernel after this call (or after the

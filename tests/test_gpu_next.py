@@ -259,6 +259,48 @@ def test_prefill_even_shares_of_tiles(ctx, dtype, m, q_start, kv_start, window, 
         cache.destroy()
 
 
+def test_prefill_piece_that_never_arrives_runs_into_the_time_limit(ctx):
+    """Host-side failure injection: CTA 1 does not announce its piece of the item it shares with
+    CTA 0, whose bounded wait runs out: status word set, the context stays usable, and the next
+    call (injection off) is right again.  Nothing faults or hangs."""
+    import torch
+    hq, hkv, d, m, q_start = 32, 8, 128, 640, 3000
+    L = q_start + m
+    rng = np.random.default_rng(9)
+    k, v = kv_values(rng, (L, hkv, d), 0.01), kv_values(rng, (L, hkv, d), 0.01)
+    q = to_dev(rng.standard_normal((m, hq, d), dtype=np.float32))
+    cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), vf.KvDtype.F8)
+    fwd = vf.CudaForward(ctx, cache, n_heads=hq)
+    try:
+        _fill(fwd, k, v)
+        ctx.set_attn_impl(2)
+        ctx.set_attn_tuning(8, 3)
+        good = torch.zeros(m, hq, d, device="cuda")
+        fwd.run_flash_attn_batch(0, q, good, m, q_start, L, 0, 0)
+        torch.cuda.synchronize()
+        ctx.poll()
+        ctx.set_merge_wait_ms(50)
+        ctx.debug_fail_split(1)
+        out = torch.zeros(m, hq, d, device="cuda")
+        fwd.run_flash_attn_batch(0, q, out, m, q_start, L, 0, 0)
+        torch.cuda.synchronize()
+        with pytest.raises(vf.VfkvError):
+            ctx.poll()
+        ctx.debug_fail_split(None)
+        out2 = torch.zeros(m, hq, d, device="cuda")
+        fwd.run_flash_attn_batch(0, q, out2, m, q_start, L, 0, 0)
+        torch.cuda.synchronize()
+        ctx.poll()
+        assert float(((out2 - good).abs().amax(-1) / good.abs().amax(-1).clamp_min(1e-3)).max()) < 4e-3
+    finally:
+        ctx.debug_fail_split(None)
+        ctx.set_merge_wait_ms(1000)
+        ctx.set_attn_tuning(0, 0)
+        ctx.set_attn_impl(0)
+        fwd.workspace.destroy()
+        cache.destroy()
+
+
 def test_prefill_even_shares_captured_in_a_graph(ctx):
     """Inside a stream capture the cut items go through the merge kernel (a replay would find the
     flag values of the replay before); the graph replays to the same result as a direct call."""

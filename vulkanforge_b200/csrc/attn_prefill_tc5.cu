@@ -57,6 +57,8 @@ struct Tc5Params {
     uint32_t inline_merge, epoch;
     uint32_t *flags;
     uint32_t use_tma;                  // F16 rows, specialised form: K/V tiles by TMA through the two tensor maps
+    uint64_t wait_ns;                  // time limit of the head CTA's wait for the other pieces
+    uint32_t fail_cta;                 // failure injection (tests): this CTA never announces its piece
 };
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
@@ -878,8 +880,8 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, float (&v)[64])
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Bounded wait for a flag that another CTA of this (cooperative) launch sets; false after a second.
-__device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t want)
+// Bounded wait for a flag that another CTA of this (cooperative) launch sets; false after limit_ns.
+__device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t want, uint64_t limit_ns)
 {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
@@ -888,7 +890,7 @@ __device__ __forceinline__ bool flag_wait(const uint32_t *flag, uint32_t want)
         if (v == want) return true;
         if ((it & 63u) == 63u) {
             if (t0 == 0) t0 = timer_ns();
-            else if (timer_ns() - t0 > 1000000000ull) return false;
+            else if (timer_ns() - t0 > limit_ns) return false;
         }
     }
 }
@@ -1147,7 +1149,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p,
                 // the head of a cut item: the other pieces were the first work of the next CTAs
                 const uint32_t rl = wg * BM + t;
                 bool got = true;
-                for (uint32_t i = 1u; i <= n_more; ++i) got = flag_wait(p.flags + blockIdx.x + i, p.epoch) && got;
+                for (uint32_t i = 1u; i <= n_more; ++i) got = flag_wait(p.flags + blockIdx.x + i, p.epoch, p.wait_ns) && got;
                 if (!got) *abort_flag = 1u;
                 const bool mine_ok = ran && !failed;
                 float mx = mine_ok ? mref : kMaskedScore, pm[3], pl[3];
@@ -1418,7 +1420,7 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p,
         __syncthreads();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (tid == 0) TC5H_STAMP(29);
-        if (mode == 3u && tid == 0) {
+        if (mode == 3u && tid == 0 && blockIdx.x != p.fail_cta) {
             // the piece is in scratch (every thread's stores are ordered before the barrier above)
             __threadfence();
             asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p.flags + blockIdx.x), "r"(s_abort != 0u ? 0u : p.epoch) : "memory");
@@ -1657,6 +1659,8 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
             // driver accepts only if the whole grid is resident at once
             if (++ctx->prefill_epoch == 0u) ++ctx->prefill_epoch;
             p.epoch = ctx->prefill_epoch;
+            p.wait_ns = ctx->merge_wait_ns;
+            p.fail_cta = ctx->debug_fail_split;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = grid_h;
             cfg.blockDim = dim3(384);
