@@ -1120,6 +1120,8 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p,
                         pk[j] = __uint_as_float(pack_half2(p0, p1));   // position 2j in the low half
                     }
                     lrow += sum;
+                    // (P of half a stored and S of half b loaded in one statement, both in flight together:
+                    // 632 -> 702 us on 2048 queries at 14 336, not kept)
                     tmem_st32(tm_s + t_lane + 64u * h, pk);
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
