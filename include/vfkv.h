@@ -499,7 +499,8 @@ int32_t vfkv_ctx_set_attn_impl(vfkv_ctx *ctx, uint32_t impl);
  * share of all items' K/V tiles -- with 8x3 whenever the call allows it (every query sees at
  * least one position, at most 512 row blocks, at least 8 tiles a share), with 0x0 when in
  * addition one CTA per item would leave a twentieth of the SM time unused and an item averages 96
- * tiles or more.  Items cut between CTAs
+ * tiles or more, or the items are at most half the SMs and the shares are ten tiles shorter than
+ * the longest item.  Items cut between CTAs
  * are put together by the CTA holding the item's head (a cooperative launch, at most four
  * pieces an item, not inside a stream capture) or by a small second kernel.  The shares need
  * 39 MB of device scratch, which the context allocates at the first such call outside a stream

@@ -533,18 +533,17 @@ extern "C" int32_t vfkv_attend_prefill(vfkv_cache *cache, uint32_t layer, uint32
     if (ctx->attn_impl == 2 && !mma_ok)
         return set_error(ctx, VFKV_ERR_UNSUPPORTED, "vfkv_attend_prefill: shape outside the tensor-core kernel");
     // The tcgen05 kernel works on 256-row blocks, one CTA per SM: it pays once those fill most of
-    // the GPU; smaller chunks keep the 64-row mma.sync kernel (four times the CTAs) -- unless the
-    // context is so long that the tcgen05 kernel cuts the items into even shares for all SMs (256
-    // queries at position 60 000: 1955 us on the mma.sync kernel, 342 us).  attn_impl 2 forces it.
-    const uint64_t blocks256 = (uint64_t(m) * p.group + 255) / 256 * hkv;
+    // the GPU, or the context is long enough for it to cut the blocks' K/V tiles into even shares
+    // for all SMs (256 queries at position 60 000: 1955 us on the mma.sync kernel, 332 us), or
+    // for its faster tiles to outweigh its fixed cost; short chunks at short contexts keep the
+    // 64-row mma.sync kernel (four times the CTAs).  attn_impl 2 forces it.
     // F16 caches carry the error budget of the reference's f32 shader (2e-3 absolute): the tcgen05
     // kernel feeds Q as one half-precision value, which holds it (1e-4 .. 5e-4 measured) with the usual
     // 1/sqrt(head_dim) scale but not with scale 1.0 (1e-2: the Gemma-4 rule); those keep the
     // mma.sync kernel and its hi + lo split of Q.
     const bool tc5_accurate = dt == VFKV_F8 || scale * sqrtf(float(D)) <= 1.5f;
     if (mma_ok && ctx->attn_impl != 3 && prefill_tc5_supported(dt, D, p.group, kv.k_scales != nullptr) && tc5_accurate &&
-        (blocks256 * 4 >= uint64_t(ctx->sm_count) * 3 || ctx->attn_impl == 2 ||
-         prefill_tc5_spreads(ctx, n_q_heads, hkv, m, q_start, n_kv, kv_start, window)))
+        (ctx->attn_impl == 2 || prefill_tc5_pays(ctx, n_q_heads, hkv, m, q_start, n_kv, kv_start, window)))
         return launch_prefill_tc5(ctx, dt, p.k, p.v, d_q, d_out, p.row_bytes, n_q_heads, hkv, m, q_start, n_kv, kv_start,
                                   window, scale, softcap, st);
     if (mma_ok) {

@@ -1516,8 +1516,13 @@ bool spread_pays(const vfkv_ctx *ctx, const Tc5Params &p, uint64_t *total_out, u
     *total_out = total;
     *tj_max_out = tj_max;
     const uint64_t waves = (items + n_sm - 1) / n_sm;
-    const bool worth = ctx->tune_warps == 8 || (items * 20 < waves * n_sm * 19 && total >= items * 96);
-    return worth && n_sm >= 2 && total >= uint64_t(n_sm) * 8 && total < (1ull << 31);
+    // Items for at most half the SMs: shares of two tiles or more, if they shorten the longest CTA
+    // by ten tiles (29 us) -- the shares' segments, the pieces and the merge kernel cost about half of
+    // that (512 queries at 1024, 64 items of 12 tiles: 46 us one CTA an item, 56 us in shares of 5;
+    // 256 queries at 2048, 32 items of 18: 63 against 54; 256 at 8192, 8 of 66: 193 against 85).
+    const bool few = items * 2 <= n_sm && uint64_t(tj_max) >= total / n_sm + 10;
+    const bool worth = ctx->tune_warps == 8 || few || (items * 20 < waves * n_sm * 19 && total >= items * 96);
+    return worth && n_sm >= 2 && total >= uint64_t(n_sm) * (few ? 2 : 8) && total < (1ull << 31);
 }
 
 }  // namespace
@@ -1527,16 +1532,30 @@ bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bo
     return (dtype == VFKV_F8 || dtype == VFKV_F16) && head_dim == 128 && !has_scales && group != 0 && BM % group == 0;
 }
 
-bool prefill_tc5_spreads(const vfkv_ctx *ctx, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
-                         uint32_t n_kv, uint32_t kv_start, uint32_t window)
+bool prefill_tc5_pays(const vfkv_ctx *ctx, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
+                      uint32_t n_kv, uint32_t kv_start, uint32_t window)
 {
     Tc5Params p{};
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.group = n_q_heads / n_kv_heads;
     p.m = m; p.q_start = q_start; p.n_kv = n_kv; p.kv_start = kv_start; p.window = window;
     p.n_rb = (m * p.group + CTA_ROWS - 1) / CTA_ROWS;
+    // 256-row blocks that fill most of the GPU
+    if (uint64_t(p.n_rb) * n_kv_heads * 4 >= uint64_t(ctx->sm_count) * 3) return true;
     uint64_t total = 0;
     uint32_t tj_max = 0;
-    return spread_pays(ctx, p, &total, &tj_max);
+    if (p.n_rb > kMaxRowBlocks) return false;
+    if (spread_pays(ctx, p, &total, &tj_max)) return true;
+    // Fewer blocks, one CTA each: a CTA pays about 12 us once and 2.9 us per 128 positions, the
+    // 64-row mma.sync kernel (four times the CTAs) 2.15 us per 64 positions -- measured on 64
+    // queries at 4096: 103 against 140 us, on 128 at 2048: 60 against 76 -- so from ten K/V tiles on
+    // the tcgen05 kernel is ahead even on a few SMs.
+    tj_max = 0;
+    for (uint32_t rb = 0; rb < p.n_rb; ++rb) {
+        uint32_t r0, cl, tj;
+        item_extent(p, rb, &r0, &cl, &tj);
+        tj_max = std::max(tj_max, tj);
+    }
+    return tj_max >= 10;
 }
 
 int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, const uint8_t *v, const float *q, float *out,

@@ -219,9 +219,10 @@ int32_t launch_merge_partials_packed(vfkv_ctx *ctx, const float *packed, uint32_
 
 // prefill attention on tcgen05 (attn_prefill_tc5.cu); k / v point at the slot's rows of the layer
 bool prefill_tc5_supported(uint32_t dtype, uint32_t head_dim, uint32_t group, bool has_scales);
-// true when the tcgen05 kernel would run this chunk as even shares of all K/V tiles, one CTA per SM
-bool prefill_tc5_spreads(const vfkv_ctx *ctx, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
-                         uint32_t n_kv, uint32_t kv_start, uint32_t window);
+// true when the tcgen05 kernel is expected to beat the 64-row mma.sync kernel on this chunk: enough
+// 256-row blocks, or even shares of all K/V tiles over the SMs, or at least ten K/V tiles an item
+bool prefill_tc5_pays(const vfkv_ctx *ctx, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
+                      uint32_t n_kv, uint32_t kv_start, uint32_t window);
 int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, const uint8_t *v, const float *q, float *out,
                            uint64_t row_bytes, uint32_t n_q_heads, uint32_t n_kv_heads, uint32_t m, uint32_t q_start,
                            uint32_t n_kv, uint32_t kv_start, uint32_t window, float scale, float softcap,
