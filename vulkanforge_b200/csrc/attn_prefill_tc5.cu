@@ -1004,17 +1004,18 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p,
         const uint32_t kvh = s_seg[1], row0 = s_seg[2], c_lo = s_seg[3], n_tiles = s_seg[4], mode = s_seg[5], n_more = s_seg[6];
 
         // Q tiles -> shared memory (half precision, scale folded in), all threads
-        // by the nine warps that are not fetching K/V (those start on their first tiles meanwhile); five
-        // pieces a thread in flight at a time
+        // by the nine warps that are not fetching K/V (those start on their first tiles meanwhile);
+        // eight pieces a thread in flight at a time, two rounds.  g divides 128, so it is a power of two.
         if (warp < 9u) {
-            constexpr uint32_t QT = 288u, QB = 5u;
+            constexpr uint32_t QT = 288u, QB = 8u;
+            const uint32_t g_shift = uint32_t(__ffs(int(g))) - 1u;
             for (uint32_t i0 = tid; i0 < uint32_t(CTA_ROWS * 16); i0 += QT * QB) {
                 float4 qa[QB], qb[QB];
 #pragma unroll
                 for (uint32_t u = 0; u < QB; ++u) {
                     const uint32_t i = i0 + QT * u, row = i >> 4, c = i & 15u, rr = row0 + row;
                     const bool in = i < uint32_t(CTA_ROWS * 16) && rr < n_rows;
-                    const float *qp = p.q + (uint64_t(in ? rr / g : 0u) * p.n_q_heads + kvh * g + (in ? rr % g : 0u)) * HD + 8 * c;
+                    const float *qp = p.q + (uint64_t(in ? rr >> g_shift : 0u) * p.n_q_heads + kvh * g + (in ? rr & (g - 1u) : 0u)) * HD + 8 * c;
                     qa[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp)) : make_float4(0.f, 0.f, 0.f, 0.f);
                     qb[u] = in ? __ldg(reinterpret_cast<const float4 *>(qp + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
