@@ -1366,9 +1366,10 @@ __global__ void __launch_bounds__(384, 1) prefill_tc5h_kernel(const Tc5Params p,
                             __half2 h2 = e4m3x2_to_half2(x.y & 0xffffu), h3 = e4m3x2_to_half2(x.y >> 16);
                             __half2 h4 = e4m3x2_to_half2(x.z & 0xffffu), h5 = e4m3x2_to_half2(x.z >> 16);
                             __half2 h6 = e4m3x2_to_half2(x.w & 0xffffu), h7 = e4m3x2_to_half2(x.w >> 16);
-                            // (storing even pieces from four threads of a row and odd pieces from the other four,
-                            // which takes the two-way bank conflict out of these stores, measured 5 % slower
-                            // at contexts of 30 000 and more, and the same below)
+                            // (two ways of taking the two-way bank conflict out of these stores -- even pieces
+                            // from four threads of a row and odd pieces from the other four; two adjacent rows
+                            // x four pieces per group of eight threads -- both measured 4-5 % slower at contexts
+                            // of 30 000 and more, and the same below)
                             *reinterpret_cast<uint4 *>(dst + tile_off(pos, 2 * c16)) =
                                 make_uint4(*reinterpret_cast<uint32_t *>(&h0), *reinterpret_cast<uint32_t *>(&h1),
                                            *reinterpret_cast<uint32_t *>(&h2), *reinterpret_cast<uint32_t *>(&h3));
