@@ -535,8 +535,8 @@ def next_rows(ctx, args, peak, tensor_peak):
         fwd.stream = None
         us_rope_graph = timed(graph.replay, 5) / 20
         flops = 4.0 * hq * d * (m * q_start + m * (m + 1) // 2)              # causal: query i sees q_start + i + 1 rows
-        # a short chunk late in a long context: 8 (kv-head, row block) items, which one CTA per item
-        # would run on 8 SMs (with the shares switched off the automatic choice is the mma.sync kernel)
+        # a short chunk late in a long context: 32 (kv-head, row block) items, which one CTA per item
+        # would run on 32 SMs (with the shares switched off the tcgen05 kernel runs one CTA per item)
         few = prefill_extra(ctx, tensor_peak, timed, "F8", 256, 60000, (4, 3, "us_without_even_shares"))
         # F16 rows: K/V tiles by TMA in the specialised form, against the pipelined form
         f16 = prefill_extra(ctx, tensor_peak, timed, "F16", 2048, 14336, (4, 2, "us_pipelined_form"))

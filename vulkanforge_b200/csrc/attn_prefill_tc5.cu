@@ -1521,7 +1521,7 @@ bool spread_pays(const vfkv_ctx *ctx, const Tc5Params &p, uint64_t *total_out, u
     // Items for at most half the SMs: shares of two tiles or more, if they shorten the longest CTA
     // by ten tiles (29 us) -- the shares' segments, the pieces and the merge kernel cost about half of
     // that (512 queries at 1024, 64 items of 12 tiles: 46 us one CTA an item, 56 us in shares of 5;
-    // 256 queries at 2048, 32 items of 18: 63 against 54; 256 at 8192, 8 of 66: 193 against 85).
+    // 256 queries at 2048, 32 items of 18: 63 against 54; 256 at 8192, 32 of 66: 193 against 85).
     const bool few = items * 2 <= n_sm && uint64_t(tj_max) >= total / n_sm + 10;
     const bool worth = ctx->tune_warps == 8 || few || (items * 20 < waves * n_sm * 19 && total >= items * 96);
     return worth && n_sm >= 2 && total >= uint64_t(n_sm) * (few ? 2 : 8) && total < (1ull << 31);
@@ -1594,7 +1594,7 @@ int32_t launch_prefill_tc5(vfkv_ctx *ctx, uint32_t dtype, const uint8_t *k, cons
     // Needs every query to see at least one position, 39 MB of scratch that the context allocates
     // at the first such call (not inside a stream capture), and tuning 0x0 or 8x3; 4x3 keeps one
     // CTA per item.  Measured: 2048 queries at 14 336 (256 items of ~120 tiles) 706 -> 658 us;
-    // 256 queries at 60 000 (8 items) 1356 -> 342 us; 4096 queries at 4096 (512 items of ~48
+    // 256 queries at 60 000 (32 items) 1356 -> 332 us; 4096 queries at 4096 (512 items of ~48
     // tiles) 579 -> 584 us, hence the floor of 96 tiles an item.
     p.n_rb = grid.x;
     const uint32_t n_sm = uint32_t(ctx->sm_count);
