@@ -1477,21 +1477,37 @@ __global__ void __launch_bounds__(256) prefill_tc5_merge_kernel(const Tc5Params 
     for (uint32_t rl = blockIdx.y * 16u + warp; rl < blockIdx.y * 16u + 16u; rl += 8u) {
         const uint32_t r = row0 + rl;
         if (r >= n_rows) break;
-        float mx = kMaskedScore;
-        for (uint32_t c = c_first; c <= c_last; ++c) {
+        // the pieces' reference maxima and sums a lane each (an item cut into many pieces would
+        // otherwise pay one round trip a piece, twice), 32 pieces a pass
+        const uint32_t np = c_last - c_first + 1u;
+        auto piece_of = [&](uint32_t i) {
+            const uint32_t c = c_first + i;
             const uint32_t slot = uint32_t(uint64_t(c) * T / n) >= s ? 0u : 1u;
-            mx = fmaxf(mx, p.scratch[(uint64_t(c) * 2u + slot) * PIECE + CTA_ROWS * HD + rl]);
-        }
+            return p.scratch + (uint64_t(c) * 2u + slot) * PIECE;
+        };
+        float mx = kMaskedScore;
+        for (uint32_t i = lane; i < np; i += 32u) mx = fmaxf(mx, piece_of(i)[CTA_ROWS * HD + rl]);
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
         float l = 0.f;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t c = c_first; c <= c_last; ++c) {
-            const uint32_t slot = uint32_t(uint64_t(c) * T / n) >= s ? 0u : 1u;
-            const float *pc = p.scratch + (uint64_t(c) * 2u + slot) * PIECE;
-            const float w = fast_exp2(pc[CTA_ROWS * HD + rl] - mx);
-            l += w * pc[CTA_ROWS * HD + CTA_ROWS + rl];
-            const float4 x = *reinterpret_cast<const float4 *>(pc + rl * HD + 4u * lane);
-            o.x += w * x.x; o.y += w * x.y; o.z += w * x.z; o.w += w * x.w;
+        for (uint32_t i0 = 0u; i0 < np; i0 += 32u) {
+            float w_mine = 0.f;
+            if (i0 + lane < np) {
+                const float *pc = piece_of(i0 + lane);
+                w_mine = fast_exp2(pc[CTA_ROWS * HD + rl] - mx);
+                l += w_mine * pc[CTA_ROWS * HD + CTA_ROWS + rl];
+            }
+            const uint32_t cnt = min(32u, np - i0);
+#pragma unroll 4
+            for (uint32_t i = 0u; i < cnt; ++i) {
+                const float w = __shfl_sync(0xffffffffu, w_mine, int(i));
+                const float4 x = *reinterpret_cast<const float4 *>(piece_of(i0 + i) + rl * HD + 4u * lane);
+                o.x += w * x.x; o.y += w * x.y; o.z += w * x.z; o.w += w * x.w;
+            }
         }
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) l += __shfl_xor_sync(0xffffffffu, l, d);
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         float *out = p.out + (uint64_t(r / g) * p.n_q_heads + kvh * g + r % g) * HD + 4u * lane;
         *reinterpret_cast<float4 *>(out) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
