@@ -592,8 +592,8 @@ def prefill_extra(ctx, tensor_peak, timed, dtype, m, q_start, compare):
 
 def run_probe(args):
     """One kernel on its own, for profiling (the commands of profiles/*.md).  `--probe prefill`: the
-    chunked-prefill attention (FP8, 32 q / 8 kv / 128, `--probe-m` queries ending at position
-    `--probe-ctx`); `rope`: RoPE fused with the append of a 512-token chunk; `append`: the plain
+    chunked-prefill attention (`--probe-dtype` cache, 32 q / 8 kv / 128, `--probe-m` queries ending
+    at position `--probe-ctx`); `rope`: RoPE fused with the append of a 512-token chunk; `append`: the plain
     append of a 512-token chunk; `fp8_to_f16`: the cache read of `--probe-ctx` positions of one layer;
     `generic`: the CUDA-core split kernel + merge kernel on an F32 cache of `--probe-ctx` positions;
     `decode`: `--workload`'s fused decode kernel, one layer-step per launch over all its layers;
@@ -614,7 +614,7 @@ def run_probe(args):
     else:
         stream = torch.cuda.current_stream()
         q_start = L - m
-        dtype = vf.KvDtype.F32 if args.probe == "generic" else vf.KvDtype.F8
+        dtype = vf.KvDtype.F32 if args.probe == "generic" else vf.KvDtype[args.probe_dtype]
         cache = vf.KvCache(ctx, vf.KvCacheConfig(1, hkv, d, L), dtype)
         fwd = vf.CudaForward(ctx, cache, n_heads=hq, n_splits=16 if args.probe == "generic" else 0)
         g = torch.Generator(device="cuda").manual_seed(5)
@@ -1022,6 +1022,7 @@ def main():
                     help="run one kernel on its own (for profiling) and exit")
     ap.add_argument("--probe-m", type=int, default=2048)
     ap.add_argument("--probe-ctx", type=int, default=16384)
+    ap.add_argument("--probe-dtype", default="F8", choices=["F8", "F16"], help="--probe prefill: cache element type")
     ap.add_argument("--probe-batch", type=int, default=0, help="--probe decode: override the workload's batch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
