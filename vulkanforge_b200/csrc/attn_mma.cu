@@ -89,10 +89,14 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    // the timer is slow to read: it is looked at only after a few hundred misses
+    uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 255u && global_timer_ns() - t0 > 1000000000ull) return false;
+        if ((it & 255u) == 255u) {
+            if (t0 == 0) t0 = global_timer_ns();
+            else if (global_timer_ns() - t0 > 1000000000ull) return false;
+        }
     }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int32_t x, int32_t y,
